@@ -1,0 +1,314 @@
+// Native CPU backend: OpenMP loops around the math that the sm_100a kernels use (rgs_math.h).
+//
+// It serves three purposes: (1) the rasteriser of CPU/gloo ranks, so that every multi-rank code
+// path can run on a machine without a GPU; (2) the validation vehicle for the shared math
+// against a PyTorch-autograd restatement; (3) the timed CPU baseline.
+// The reference has no CPU path at all (its rasteriser is CUDA-only:
+// rasterization_kernels/diff-gaussian-rasterization-half-gaussian/cuda_rasterizer_hgs/).
+#include <algorithm>
+#include <cstring>
+#include <numeric>
+#include <vector>
+#include "rgs_api.h"
+#include "rgs_loss_math.h"
+
+extern "C" {
+
+int rgs_cpu_project_emit(const RgsCamera* cam, const RgsSegment* seg, int64_t id_base, RgsSplat* splats,
+                         int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint64_t* keys, uint32_t* vals,
+                         int64_t cap_inst, int32_t* counters, void*) {
+    int64_t n_vis = counters[RGS_CNT_VIS], n_inst = counters[RGS_CNT_INST];
+    for (int64_t i = 0; i < seg->count; ++i) {
+        RgsSplat sp; RgsRect rc; int radius; unsigned clamped;
+        if (!rgs_project(*cam, seg->xyz + 3 * i, seg->scale + 3 * i, seg->rot + 4 * i, seg->opacity[i],
+                         seg->sh + 48 * i, sp, rc, radius, clamped))
+            continue;
+        if (n_vis >= cap_vis) { counters[RGS_CNT_OVERFLOW] = 1; continue; }
+        int64_t cnt = (int64_t)(rc.x1 - rc.x0) * (rc.y1 - rc.y0);
+        int64_t base = n_inst;
+        n_inst += cnt;
+        if (n_inst > cap_inst) { counters[RGS_CNT_OVERFLOW] = 1; continue; }
+        int64_t slot = n_vis++;
+        splats[slot] = sp;
+        vis_ids[slot] = (int32_t)(id_base + i);
+        aux[slot] = ((uint32_t)radius << 3) | clamped;
+        uint32_t dbits; std::memcpy(&dbits, &sp.depth, 4);
+        for (int y = rc.y0; y < rc.y1; ++y)
+            for (int x = rc.x0; x < rc.x1; ++x) {
+                uint64_t key = (uint64_t)(y * cam->tiles_x + x);
+                keys[base] = (key << 32) | dbits;
+                vals[base] = (uint32_t)slot;
+                ++base;
+            }
+    }
+    counters[RGS_CNT_VIS] = (int32_t)n_vis;
+    counters[RGS_CNT_INST] = (int32_t)std::min<int64_t>(n_inst, 0x7fffffff);
+    return 0;
+}
+
+int64_t rgs_cpu_sort_scratch_words(int64_t) { return 1; }
+
+// Sorts the instances by (tile, depth) and writes [start,end) per tile. The sorted lists end up in
+// keys/vals (the *_tmp buffers are scratch, as for the GPU sort).
+int rgs_cpu_sort_ranges(uint64_t* keys, uint32_t* vals, uint64_t* keys_tmp, uint32_t* vals_tmp, int64_t cap_inst,
+                        const int32_t* counters, int64_t num_tiles, int32_t* ranges, void*, void*) {
+    int64_t n = std::min<int64_t>(counters[RGS_CNT_INST], cap_inst);
+    if (counters[RGS_CNT_OVERFLOW]) n = 0;
+    std::vector<int64_t> idx(n);
+    std::iota(idx.begin(), idx.end(), 0);
+    std::stable_sort(idx.begin(), idx.end(), [&](int64_t a, int64_t b) { return keys[a] < keys[b]; });
+    for (int64_t i = 0; i < n; ++i) { keys_tmp[i] = keys[idx[i]]; vals_tmp[i] = vals[idx[i]]; }
+    std::memcpy(keys, keys_tmp, n * 8);
+    std::memcpy(vals, vals_tmp, n * 4);
+    std::memset(ranges, 0, num_tiles * 8);
+    for (int64_t i = 0; i < n; ++i) {
+        int64_t t = (int64_t)(keys[i] >> 32);
+        if (i == 0 || (int64_t)(keys[i - 1] >> 32) != t) ranges[2 * t] = (int32_t)i;
+        if (i == n - 1 || (int64_t)(keys[i + 1] >> 32) != t) ranges[2 * t + 1] = (int32_t)(i + 1);
+    }
+    return 0;
+}
+
+// out: (H,W,4) premultiplied RGB + transmittance; depth: optional (H,W); n_contrib: (H,W)
+int rgs_cpu_blend_fwd(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
+                      float* out, float* depth, int32_t* n_contrib, int32_t* counters, void*) {
+    (void)counters;
+    const int W = cam->W, H = cam->H;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int tile = 0; tile < cam->tiles_x * cam->tiles_y; ++tile) {
+        int tx = tile % cam->tiles_x, ty = tile / cam->tiles_x;
+        int r0 = ranges[2 * tile], r1 = ranges[2 * tile + 1];
+        for (int ly = 0; ly < RGS_TILE; ++ly)
+            for (int lx = 0; lx < RGS_TILE; ++lx) {
+                int x = tx * RGS_TILE + lx, y = ty * RGS_TILE + ly;
+                if (x >= W || y >= H) continue;
+                RgsPixelRay ray; rgs_pixel_ray(*cam, (float)x, (float)y, ray);
+                RgsPixelState st; rgs_pixel_init(st);
+                for (int i = r0; i < r1 && !st.done; ++i)
+                    rgs_blend_fwd_step(*cam, ray, (float)x, (float)y, splats[vals[i]], st);
+                int64_t pid = (int64_t)y * W + x;
+                out[4 * pid + 0] = st.C[0]; out[4 * pid + 1] = st.C[1]; out[4 * pid + 2] = st.C[2];
+                out[4 * pid + 3] = st.T;
+                if (depth) depth[pid] = st.D;
+                n_contrib[pid] = st.last;
+            }
+    }
+    return 0;
+}
+
+// grad_out: (H,W,4) = dL/dC (rgb), dL/dT. splat_grads[n_vis] must be zeroed by the caller.
+int rgs_cpu_blend_bwd(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
+                      const float* out, const int32_t* n_contrib, const float* grad_out, RgsSplatGrad* splat_grads,
+                      int32_t* counters, void*) {
+    (void)counters;
+    const int W = cam->W, H = cam->H;
+    // serial over tiles: the accumulation order is then fixed, which makes this path the
+    // deterministic reference for the atomically accumulating GPU kernel.
+    for (int tile = 0; tile < cam->tiles_x * cam->tiles_y; ++tile) {
+        int tx = tile % cam->tiles_x, ty = tile / cam->tiles_x;
+        int r0 = ranges[2 * tile];
+        for (int ly = 0; ly < RGS_TILE; ++ly)
+            for (int lx = 0; lx < RGS_TILE; ++lx) {
+                int x = tx * RGS_TILE + lx, y = ty * RGS_TILE + ly;
+                if (x >= W || y >= H) continue;
+                int64_t pid = (int64_t)y * W + x;
+                RgsPixelRay ray; rgs_pixel_ray(*cam, (float)x, (float)y, ray);
+                RgsPixelBwd st;
+                rgs_pixel_bwd_init(st, out[4 * pid + 3], grad_out + 4 * pid, grad_out[4 * pid + 3]);
+                for (int i = r0 + n_contrib[pid] - 1; i >= r0; --i) {
+                    RgsSplatGrad g;
+                    uint32_t slot = vals[i];
+                    if (!rgs_blend_bwd_step(*cam, ray, (float)x, (float)y, splats[slot], st, g)) continue;
+                    float* dst = reinterpret_cast<float*>(&splat_grads[slot]);
+                    const float* src = reinterpret_cast<const float*>(&g);
+                    for (int k = 0; k < 10; ++k) dst[k] += src[k];
+                }
+            }
+    }
+    return 0;
+}
+
+static inline const RgsSegment* find_segment(const RgsSegment* segs, int nseg, int64_t id, int64_t& local) {
+    for (int s = 0; s < nseg; ++s) {
+        if (id < segs[s].count) { local = id; return &segs[s]; }
+        id -= segs[s].count;
+    }
+    local = 0;
+    return nullptr;
+}
+
+int rgs_cpu_geom_bwd(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg, const int32_t* counters,
+                     const RgsSplat* splats, const int32_t* vis_ids, const uint32_t* aux,
+                     const RgsSplatGrad* splat_grads, int64_t cap_vis, void*) {
+    (void)splats; (void)cap_vis;
+    int64_t n_vis = counters[RGS_CNT_VIS];
+    for (int64_t slot = 0; slot < n_vis; ++slot) {
+        int64_t i;
+        const RgsSegment* sg = find_segment(segs, (int)nseg, vis_ids[slot], i);
+        if (!sg) continue;
+        float gx[3] = {0, 0, 0}, gsh[48], gs[3] = {0, 0, 0}, gq[4] = {0, 0, 0, 0}, go[1] = {0};
+        for (int k = 0; k < 48; ++k) gsh[k] = 0.f;
+        unsigned clamped = aux[slot] & 7u;
+        float radius = (float)(aux[slot] >> 3);
+        float nrm = rgs_project_bwd(*cam, sg->xyz + 3 * i, sg->scale + 3 * i, sg->rot + 4 * i, sg->opacity[i],
+                                    sg->sh + 48 * i, clamped, splat_grads[slot], gx, gsh, gs, gq, go);
+        if (sg->g_xyz) for (int k = 0; k < 3; ++k) sg->g_xyz[3 * i + k] += gx[k];
+        if (sg->g_sh) for (int k = 0; k < 48; ++k) sg->g_sh[48 * i + k] += gsh[k];
+        if (sg->g_scale) for (int k = 0; k < 3; ++k) sg->g_scale[3 * i + k] += gs[k];
+        if (sg->g_rot) for (int k = 0; k < 4; ++k) sg->g_rot[4 * i + k] += gq[k];
+        if (sg->g_opacity) sg->g_opacity[i] += go[0];
+        if (sg->g_mean2d) {
+            sg->g_mean2d[2 * i] = splat_grads[slot].dpx * 0.5f * cam->W;
+            sg->g_mean2d[2 * i + 1] = splat_grads[slot].dpy * 0.5f * cam->H;
+        }
+        if (sg->stat_grad) sg->stat_grad[i] += nrm;
+        if (sg->stat_denom) sg->stat_denom[i] += 1.0f;
+        if (sg->stat_maxrad) sg->stat_maxrad[i] = std::max(sg->stat_maxrad[i], radius);
+    }
+    return 0;
+}
+
+// radii (P) of one segment, for API parity with the reference's `radii` output.
+int rgs_cpu_scatter_radii(const int32_t* counters, const int32_t* vis_ids, const uint32_t* aux, int64_t id_base,
+                          int64_t count, int32_t* radii, void*) {
+    int64_t n_vis = counters[RGS_CNT_VIS];
+    for (int64_t s = 0; s < n_vis; ++s) {
+        int64_t i = (int64_t)vis_ids[s] - id_base;
+        if (i >= 0 && i < count) radii[i] = (int32_t)(aux[s] >> 3);
+    }
+    return 0;
+}
+
+// Fused Adam over the grouped parameter block. The block holds five groups of `cap` rows each:
+// xyz(3) sh(48) scale(3) rot(4) opacity(1); only the first `count` rows of each group are live.
+// `skip` (optional int32) != 0 turns the whole update into a no-op (overflow-guarded commit).
+int rgs_cpu_adam(float* p, const float* g, float* m, float* v, int64_t count, int64_t cap, const double* lrs,
+                 double beta1, double beta2, double eps, int64_t step, const int32_t* skip, void*) {
+    if (skip && skip[RGS_CNT_OVERFLOW]) return 0;
+    const int widths[5] = {3, 48, 3, 4, 1};
+    float bc1 = (float)(1.0 - std::pow(beta1, (double)step));
+    float bc2s = (float)std::sqrt(1.0 - std::pow(beta2, (double)step));
+    int64_t off = 0;
+    for (int grp = 0; grp < 5; ++grp) {
+        int w = widths[grp];
+#pragma omp parallel for
+        for (int64_t e = 0; e < count * w; ++e) {
+            int col = (int)(e % w);
+            float lr;
+            switch (grp) {
+                case 0: lr = (float)lrs[RGS_LR_XYZ]; break;
+                case 1: lr = (float)(col < 3 ? lrs[RGS_LR_FDC] : lrs[RGS_LR_FREST]); break;
+                case 2: lr = (float)lrs[RGS_LR_SCALE]; break;
+                case 3: lr = (float)lrs[RGS_LR_ROT]; break;
+                default: lr = (float)lrs[RGS_LR_OPACITY]; break;
+            }
+            int64_t k = off + e;
+            rgs_adam_elem(p[k], g[k], m[k], v[k], lr, (float)beta1, (float)beta2, (float)eps, bc1, bc2s);
+        }
+        off += cap * w;
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Compositing of K partial images (front to back) and the fused L1 + D-SSIM loss.
+// ---------------------------------------------------------------------------------------------
+
+// partials: K pointers to (H,W,4) buffers in front-to-back order. image: (3,H,W) planar,
+// trans: (H,W) total transmittance. Rows [row0,row1) only.
+int rgs_cpu_composite_fwd(const float* const* partials, int64_t K, const float* bg, int64_t H, int64_t W,
+                          int64_t row0, int64_t row1, float* image, float* trans, void*) {
+    (void)H;
+#pragma omp parallel for
+    for (int64_t y = row0; y < row1; ++y)
+        for (int64_t x = 0; x < W; ++x) {
+            int64_t pid = y * W + x;
+            float C[3], T;
+            rgs_composite_pixel_fwd(partials, (int)K, pid, bg, C, T);
+            image[pid] = C[0]; image[H * W + pid] = C[1]; image[2 * H * W + pid] = C[2];
+            trans[pid] = T;
+        }
+    return 0;
+}
+
+// g_image: (3,H,W) dL/dimage; grads: K pointers to (H,W,4) buffers receiving dL/dC_k, dL/dT_k.
+int rgs_cpu_composite_bwd(const float* const* partials, float* const* grads, int64_t K, const float* bg,
+                          int64_t H, int64_t W, int64_t row0, int64_t row1, const float* g_image, void*) {
+#pragma omp parallel for
+    for (int64_t y = row0; y < row1; ++y)
+        for (int64_t x = 0; x < W; ++x) {
+            int64_t pid = y * W + x;
+            float g[3] = {g_image[pid], g_image[H * W + pid], g_image[2 * H * W + pid]};
+            rgs_composite_pixel_bwd(partials, grads, (int)K, pid, bg, g);
+        }
+    return 0;
+}
+
+// SSIM statistics pass: for rows [row0,row1) computes the SSIM map sum, the L1 sum and the three
+// derivative maps (dmu, dsig1, dsig12; each (3,H,W)) that the second pass convolves.
+// sums[0] += sum |img-gt| ; sums[1] += sum ssim_map ; sums[2] += sum (img-gt)^2
+int rgs_cpu_ssim_fwd(const float* img, const float* gt, int64_t H, int64_t W, int64_t row0, int64_t row1,
+                     int64_t srow0, int64_t srow1, float* dmaps, double* sums, void*) {
+    float gw[11];
+    rgs_gauss_window(gw);
+    double l1 = 0, ss = 0, l2 = 0;
+#pragma omp parallel for reduction(+ : l1, ss, l2)
+    for (int64_t y = row0; y < row1; ++y)
+        for (int c = 0; c < 3; ++c)
+            for (int64_t x = 0; x < W; ++x) {
+                const float* a = img + c * H * W; const float* b = gt + c * H * W;
+                float mu1 = 0, mu2 = 0, e11 = 0, e22 = 0, e12 = 0;
+                for (int dy = -5; dy <= 5; ++dy) {
+                    int64_t yy = y + dy; if (yy < 0 || yy >= H) continue;
+                    for (int dx = -5; dx <= 5; ++dx) {
+                        int64_t xx = x + dx; if (xx < 0 || xx >= W) continue;
+                        float wgt = gw[dy + 5] * gw[dx + 5];
+                        float p = a[yy * W + xx], q = b[yy * W + xx];
+                        mu1 += wgt * p; mu2 += wgt * q; e11 += wgt * p * p; e22 += wgt * q * q; e12 += wgt * p * q;
+                    }
+                }
+                float d[3];
+                float s = rgs_ssim_pixel(mu1, mu2, e11, e22, e12, d);
+                int64_t pid = c * H * W + y * W + x;
+                if (dmaps) { dmaps[pid] = d[0]; dmaps[3 * H * W + pid] = d[1]; dmaps[6 * H * W + pid] = d[2]; }
+                if (y >= srow0 && y < srow1) {
+                    float diff = a[y * W + x] - b[y * W + x];
+                    l1 += std::fabs(diff); ss += s; l2 += (double)diff * diff;
+                }
+            }
+    sums[0] += l1; sums[1] += ss; sums[2] += l2;
+    return 0;
+}
+
+// Second pass: g_image = w_l1 * sign(img-gt) + w_ssim * d(-SSIM mean)/dimg on rows [row0,row1);
+// w_l1 = (1-lambda)/(3HW), w_ssim = lambda/(3HW) are passed pre-multiplied by the caller.
+int rgs_cpu_ssim_bwd(const float* img, const float* gt, const float* dmaps, int64_t H, int64_t W, int64_t row0,
+                     int64_t row1, int64_t vrow0, int64_t vrow1, double w_l1, double w_ssim, float* g_image, void*) {
+    float gw[11];
+    rgs_gauss_window(gw);
+#pragma omp parallel for
+    for (int64_t y = row0; y < row1; ++y)
+        for (int c = 0; c < 3; ++c)
+            for (int64_t x = 0; x < W; ++x) {
+                const float* dm = dmaps + c * H * W;
+                float s0 = 0, s1 = 0, s2 = 0;
+                for (int dy = -5; dy <= 5; ++dy) {
+                    int64_t yy = y + dy; if (yy < vrow0 || yy >= vrow1) continue;
+                    for (int dx = -5; dx <= 5; ++dx) {
+                        int64_t xx = x + dx; if (xx < 0 || xx >= W) continue;
+                        float wgt = gw[dy + 5] * gw[dx + 5];
+                        s0 += wgt * dm[yy * W + xx]; s1 += wgt * dm[3 * H * W + yy * W + xx];
+                        s2 += wgt * dm[6 * H * W + yy * W + xx];
+                    }
+                }
+                int64_t pid = c * H * W + y * W + x;
+                float p = img[pid], q = gt[pid];
+                float dssim = s0 + 2.0f * p * s1 + q * s2;  // d(sum ssim)/d img
+                float diff = p - q;
+                float sgn = diff > 0.f ? 1.f : (diff < 0.f ? -1.f : 0.f);
+                g_image[pid] = (float)w_l1 * sgn - (float)w_ssim * dssim;
+            }
+    return 0;
+}
+
+}  // extern "C"

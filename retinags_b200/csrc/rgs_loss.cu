@@ -1,0 +1,247 @@
+// sm_100a kernels for ordered compositing of partial images and the fused L1 + D-SSIM loss with
+// its hand-written backward (fp32 SIMT path; the tensor-core SSIM filter lives in rgs_ssim_tc.cu).
+//
+// Replaces, in the reference: the ATen chain of parallel_utils/basic_parallel_trainer/
+// result_aggregator.py:244-259 (cat / cumprod / weighted sums + autograd) and the five depthwise
+// cuDNN convolutions of utils/loss_utils.py:43-63 (+ five more in autograd's backward).
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "rgs_api.h"
+#include "rgs_cuda_common.cuh"
+#include "rgs_loss_math.h"
+
+struct RgsPartialPtrs { const float* p[RGS_MAX_PARTIALS]; };
+struct RgsGradPtrs { float* p[RGS_MAX_PARTIALS]; };
+
+__global__ void __launch_bounds__(256) rgs_composite_fwd_kernel(const __grid_constant__ RgsPartialPtrs parts, int K,
+                                                                float bg0, float bg1, float bg2, int64_t H, int64_t W,
+                                                                int64_t row0, int64_t row1, float* __restrict__ image,
+                                                                float* __restrict__ trans) {
+    const int64_t n = (row1 - row0) * W;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t pid = row0 * W + i;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, t = 1.f;
+        for (int k = 0; k < K; ++k) {
+            const float4 q = reinterpret_cast<const float4*>(parts.p[k])[pid];
+            a0 += t * q.x; a1 += t * q.y; a2 += t * q.z;
+            t *= q.w;
+        }
+        image[pid] = a0 + bg0 * t;
+        image[H * W + pid] = a1 + bg1 * t;
+        image[2 * H * W + pid] = a2 + bg2 * t;
+        trans[pid] = t;
+    }
+}
+
+__global__ void __launch_bounds__(256) rgs_composite_bwd_kernel(const __grid_constant__ RgsPartialPtrs parts,
+                                                                const __grid_constant__ RgsGradPtrs grads, int K,
+                                                                float bg0, float bg1, float bg2, int64_t H, int64_t W,
+                                                                int64_t row0, int64_t row1,
+                                                                const float* __restrict__ g_image) {
+    const int64_t n = (row1 - row0) * W;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t pid = row0 * W + i;
+        const float g0 = g_image[pid], g1 = g_image[H * W + pid], g2 = g_image[2 * H * W + pid];
+        float tpre[RGS_MAX_PARTIALS];
+        float t = 1.f;
+        for (int k = 0; k < K; ++k) { tpre[k] = t; t *= parts.p[k][4 * pid + 3]; }
+        float s = bg0 * g0 + bg1 * g1 + bg2 * g2;
+        for (int k = K - 1; k >= 0; --k) {
+            const float4 q = reinterpret_cast<const float4*>(parts.p[k])[pid];
+            const float tp = tpre[k];
+            reinterpret_cast<float4*>(grads.p[k])[pid] = make_float4(tp * g0, tp * g1, tp * g2, tp * s);
+            s = q.x * g0 + q.y * g1 + q.z * g2 + q.w * s;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SSIM: 32x32 output tile per block and channel, separable 11-tap filter through shared memory
+// ---------------------------------------------------------------------------------------------
+#define ST 32
+#define SH_ 42  // ST + 10
+
+__device__ __forceinline__ void ssim_window(float* g) { rgs_gauss_window(g); }
+
+__global__ void __launch_bounds__(256) rgs_ssim_fwd_kernel(const float* __restrict__ img, const float* __restrict__ gt,
+                                                           int H, int W, int crow0, int crow1, int srow0, int srow1,
+                                                           float* __restrict__ dmaps, double* __restrict__ sums) {
+    __shared__ float in1[SH_][SH_ + 1], in2[SH_][SH_ + 1];
+    __shared__ float hb[5][SH_][ST];
+    __shared__ float red[3][8];
+    float gw[11];
+    ssim_window(gw);
+    const int c = blockIdx.z;
+    const int x0 = blockIdx.x * ST, y0 = crow0 + blockIdx.y * ST;
+    const float* a = img + (size_t)c * H * W;
+    const float* b = gt + (size_t)c * H * W;
+    for (int idx = threadIdx.x; idx < SH_ * SH_; idx += 256) {
+        const int r = idx / SH_, q = idx % SH_;
+        const int y = y0 + r - 5, x = x0 + q - 5;
+        const bool in = y >= 0 && y < H && x >= 0 && x < W;
+        in1[r][q] = in ? a[(size_t)y * W + x] : 0.f;
+        in2[r][q] = in ? b[(size_t)y * W + x] : 0.f;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < SH_ * ST; idx += 256) {
+        const int r = idx / ST, q = idx % ST;
+        float m1 = 0, m2 = 0, e11 = 0, e22 = 0, e12 = 0;
+#pragma unroll
+        for (int k = 0; k < 11; ++k) {
+            const float p = in1[r][q + k], v = in2[r][q + k], w = gw[k];
+            m1 += w * p; m2 += w * v; e11 += w * p * p; e22 += w * v * v; e12 += w * p * v;
+        }
+        hb[0][r][q] = m1; hb[1][r][q] = m2; hb[2][r][q] = e11; hb[3][r][q] = e22; hb[4][r][q] = e12;
+    }
+    __syncthreads();
+    float l1 = 0.f, ss = 0.f, l2 = 0.f;
+    const int q = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = (threadIdx.x >> 5) + 8 * i;
+        const int y = y0 + r, x = x0 + q;
+        if (y < crow1 && y < H && x < W) {
+            float m[5] = {0, 0, 0, 0, 0};
+#pragma unroll
+            for (int k = 0; k < 11; ++k) {
+                const float w = gw[k];
+#pragma unroll
+                for (int j = 0; j < 5; ++j) m[j] += w * hb[j][r + k][q];
+            }
+            float d[3];
+            const float s = rgs_ssim_pixel(m[0], m[1], m[2], m[3], m[4], d);
+            const size_t pid = (size_t)c * H * W + (size_t)y * W + x;
+            const size_t plane = (size_t)3 * H * W;
+            dmaps[pid] = d[0]; dmaps[plane + pid] = d[1]; dmaps[2 * plane + pid] = d[2];
+            if (y >= srow0 && y < srow1) {
+                const float diff = in1[r + 5][q + 5] - in2[r + 5][q + 5];
+                l1 += fabsf(diff); ss += s; l2 += diff * diff;
+            }
+        }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        l1 += __shfl_xor_sync(0xffffffffu, l1, d);
+        ss += __shfl_xor_sync(0xffffffffu, ss, d);
+        l2 += __shfl_xor_sync(0xffffffffu, l2, d);
+    }
+    if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = l1; red[1][threadIdx.x >> 5] = ss; red[2][threadIdx.x >> 5] = l2; }
+    __syncthreads();
+    if (threadIdx.x < 3) {
+        double t = 0;
+        for (int w = 0; w < 8; ++w) t += (double)red[threadIdx.x][w];
+        atomicAdd(&sums[threadIdx.x], t);
+    }
+}
+
+__global__ void __launch_bounds__(256) rgs_ssim_bwd_kernel(const float* __restrict__ img, const float* __restrict__ gt,
+                                                           const float* __restrict__ dmaps, int H, int W, int row0,
+                                                           int row1, int vrow0, int vrow1, float w_l1, float w_ssim,
+                                                           float* __restrict__ g_image) {
+    __shared__ float in[3][SH_][SH_ + 1];
+    __shared__ float hb[3][SH_][ST];
+    float gw[11];
+    ssim_window(gw);
+    const int c = blockIdx.z;
+    const int x0 = blockIdx.x * ST, y0 = row0 + blockIdx.y * ST;
+    const size_t plane = (size_t)3 * H * W;
+    const float* dm = dmaps + (size_t)c * H * W;
+    for (int idx = threadIdx.x; idx < SH_ * SH_; idx += 256) {
+        const int r = idx / SH_, q = idx % SH_;
+        const int y = y0 + r - 5, x = x0 + q - 5;
+        // derivative maps exist only on rows [vrow0, vrow1); outside the image they are zero padding
+        const bool ok = y >= vrow0 && y < vrow1 && x >= 0 && x < W;
+        const size_t o = (size_t)y * W + x;
+        in[0][r][q] = ok ? dm[o] : 0.f;
+        in[1][r][q] = ok ? dm[plane + o] : 0.f;
+        in[2][r][q] = ok ? dm[2 * plane + o] : 0.f;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < SH_ * ST; idx += 256) {
+        const int r = idx / ST, q = idx % ST;
+        float s0 = 0, s1 = 0, s2 = 0;
+#pragma unroll
+        for (int k = 0; k < 11; ++k) {
+            const float w = gw[k];
+            s0 += w * in[0][r][q + k]; s1 += w * in[1][r][q + k]; s2 += w * in[2][r][q + k];
+        }
+        hb[0][r][q] = s0; hb[1][r][q] = s1; hb[2][r][q] = s2;
+    }
+    __syncthreads();
+    const int q = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = (threadIdx.x >> 5) + 8 * i;
+        const int y = y0 + r, x = x0 + q;
+        if (y < row1 && y < H && x < W) {
+            float s0 = 0, s1 = 0, s2 = 0;
+#pragma unroll
+            for (int k = 0; k < 11; ++k) {
+                const float w = gw[k];
+                s0 += w * hb[0][r + k][q]; s1 += w * hb[1][r + k][q]; s2 += w * hb[2][r + k][q];
+            }
+            const size_t pid = (size_t)c * H * W + (size_t)y * W + x;
+            const float p = img[pid], v = gt[pid];
+            const float dssim = s0 + 2.0f * p * s1 + v * s2;
+            const float diff = p - v;
+            const float sgn = diff > 0.f ? 1.f : (diff < 0.f ? -1.f : 0.f);
+            g_image[pid] = w_l1 * sgn - w_ssim * dssim;
+        }
+    }
+}
+
+extern "C" {
+
+int rgs_cuda_composite_fwd(const float* const* partials, int64_t K, const float* bg, int64_t H, int64_t W,
+                           int64_t row0, int64_t row1, float* image, float* trans, void* stream) {
+    if (K < 0 || K > RGS_MAX_PARTIALS) return 12;
+    if (row1 <= row0) return 0;
+    RgsPartialPtrs pp;
+    for (int k = 0; k < K; ++k) pp.p[k] = partials[k];
+    const int64_t n = (row1 - row0) * W;
+    const int64_t want = (n + 255) / 256;
+    const unsigned blocks = (unsigned)(want > 148 * 32 ? 148 * 32 : want);
+    rgs_composite_fwd_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(pp, (int)K, bg[0], bg[1], bg[2], H, W, row0, row1,
+                                                                      image, trans);
+    return (int)cudaGetLastError();
+}
+
+int rgs_cuda_composite_bwd(const float* const* partials, float* const* grads, int64_t K, const float* bg, int64_t H,
+                           int64_t W, int64_t row0, int64_t row1, const float* g_image, void* stream) {
+    if (K < 0 || K > RGS_MAX_PARTIALS) return 12;
+    if (row1 <= row0) return 0;
+    RgsPartialPtrs pp;
+    RgsGradPtrs gp;
+    for (int k = 0; k < K; ++k) { pp.p[k] = partials[k]; gp.p[k] = grads[k]; }
+    const int64_t n = (row1 - row0) * W;
+    const int64_t want = (n + 255) / 256;
+    const unsigned blocks = (unsigned)(want > 148 * 32 ? 148 * 32 : want);
+    rgs_composite_bwd_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(pp, gp, (int)K, bg[0], bg[1], bg[2], H, W, row0,
+                                                                      row1, g_image);
+    return (int)cudaGetLastError();
+}
+
+// Statistics pass on rows [crow0,crow1) (derivative maps written there); the loss sums count rows
+// [srow0,srow1) only. sums: 3 doubles on the device: sum|d|, sum ssim, sum d^2 (accumulated).
+int rgs_cuda_ssim_fwd(const float* img, const float* gt, int64_t H, int64_t W, int64_t crow0, int64_t crow1,
+                      int64_t srow0, int64_t srow1, float* dmaps, double* sums, void* stream) {
+    if (crow1 <= crow0) return 0;
+    dim3 grid((unsigned)((W + ST - 1) / ST), (unsigned)((crow1 - crow0 + ST - 1) / ST), 3);
+    rgs_ssim_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(img, gt, (int)H, (int)W, (int)crow0, (int)crow1,
+                                                                (int)srow0, (int)srow1, dmaps, sums);
+    return (int)cudaGetLastError();
+}
+
+// Gradient pass on rows [row0,row1); derivative maps are valid on rows [vrow0,vrow1).
+int rgs_cuda_ssim_bwd(const float* img, const float* gt, const float* dmaps, int64_t H, int64_t W, int64_t row0,
+                      int64_t row1, int64_t vrow0, int64_t vrow1, double w_l1, double w_ssim, float* g_image,
+                      void* stream) {
+    if (row1 <= row0) return 0;
+    dim3 grid((unsigned)((W + ST - 1) / ST), (unsigned)((row1 - row0 + ST - 1) / ST), 3);
+    rgs_ssim_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(img, gt, dmaps, (int)H, (int)W, (int)row0, (int)row1,
+                                                                (int)vrow0, (int)vrow1, (float)w_l1, (float)w_ssim,
+                                                                g_image);
+    return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,0 +1,392 @@
+// sm_100a rasteriser kernels: projection + SH + instance emission, tile blend forward/backward,
+// per-Gaussian geometry backward.
+//
+// Design notes (what differs from the reference's
+// rasterization_kernels/diff-gaussian-rasterization-half-gaussian/cuda_rasterizer_hgs/{forward,backward,
+// rasterizer_impl}.cu):
+//  * projection, tile counting, the prefix sum over tile counts and duplicate-with-keys are ONE
+//    kernel: a block aggregates its instance count, reserves a range of the key buffer with one
+//    atomic and emits directly. No per-Gaussian count/offset arrays, no separate scan, and the
+//    instance total stays on the device (the reference copies it to the host,
+//    rasterizer_impl.cu:286-287).
+//  * visible splats are compacted into 48-byte records; everything downstream is sized by the
+//    number of visible splats, not by the number of Gaussians.
+//  * the blend kernels stage the depth-sorted splat records of a tile into shared memory with
+//    bulk asynchronous copies (cp.async.bulk, completion on an mbarrier), double buffered.
+//  * the blend backward reduces the nine per-splat gradients over the warp and issues one
+//    vector reduction per warp instead of nine atomics per pixel (backward.cu:576-619).
+//  * every wait on an mbarrier is bounded; on expiry the block records a status word and leaves.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "rgs_api.h"
+#include "rgs_cuda_common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// project + emit
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rgs_project_emit_kernel(
+    const __grid_constant__ RgsCamera cam, const RgsSegment seg, const int64_t id_base, RgsSplat* __restrict__ splats,
+    int32_t* __restrict__ vis_ids, uint32_t* __restrict__ aux, const uint32_t cap_vis, uint64_t* __restrict__ keys,
+    uint32_t* __restrict__ vals, const uint32_t cap_inst, uint32_t* __restrict__ counters) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    bool ok = false;
+    RgsSplat sp;
+    RgsRect rc;
+    int radius = 0;
+    unsigned clamped = 0;
+    if (i < seg.count) {
+        float p[3] = {seg.xyz[3 * i], seg.xyz[3 * i + 1], seg.xyz[3 * i + 2]};
+        float s[3] = {seg.scale[3 * i], seg.scale[3 * i + 1], seg.scale[3 * i + 2]};
+        float4 q4 = reinterpret_cast<const float4*>(seg.rot)[i];
+        float q[4] = {q4.x, q4.y, q4.z, q4.w};
+        ok = rgs_project(cam, p, s, q, seg.opacity[i], seg.sh + 48 * i, sp, rc, radius, clamped);
+    }
+    uint32_t cnt = ok ? (uint32_t)((rc.x1 - rc.x0) * (rc.y1 - rc.y0)) : 0u;
+    // block-wide exclusive scans of (visible, instances)
+    __shared__ uint32_t warp_cnt[8], warp_vis[8];
+    __shared__ uint32_t base_cnt, base_vis;
+    __shared__ int drop;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    uint32_t incl = cnt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        uint32_t n = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += n;
+    }
+    const uint32_t vmask = __ballot_sync(0xffffffffu, ok);
+    if (lane == 31) { warp_cnt[wid] = incl; warp_vis[wid] = __popc(vmask); }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t tc = 0, tv = 0;
+        for (int w = 0; w < 8; ++w) { uint32_t c = warp_cnt[w]; warp_cnt[w] = tc; tc += c;
+                                      uint32_t v = warp_vis[w]; warp_vis[w] = tv; tv += v; }
+        uint32_t bc = 0, bv = 0;
+        int d = 0;
+        if (tv) {
+            bc = atomicAdd(&counters[RGS_CNT_INST], tc);
+            bv = atomicAdd(&counters[RGS_CNT_VIS], tv);
+            // unsigned wrap of the instance counter also counts as overflow
+            if (bc + tc > cap_inst || bc + tc < bc || bv + tv > cap_vis) { atomicExch(&counters[RGS_CNT_OVERFLOW], 1u); d = 1; }
+        }
+        base_cnt = bc; base_vis = bv; drop = d;
+    }
+    __syncthreads();
+    if (!ok || drop) return;
+    const uint32_t slot = base_vis + warp_vis[wid] + __popc(vmask & ((1u << lane) - 1u));
+    uint32_t off = base_cnt + warp_cnt[wid] + (incl - cnt);
+    float4* dst = reinterpret_cast<float4*>(splats + slot);
+    dst[0] = make_float4(sp.px, sp.py, sp.ca, sp.cb);
+    dst[1] = make_float4(sp.cc, sp.opacity, sp.r, sp.g);
+    dst[2] = make_float4(sp.b, sp.w, sp.depth, 0.f);
+    vis_ids[slot] = (int32_t)(id_base + i);
+    aux[slot] = ((uint32_t)radius << 3) | clamped;
+    const uint64_t dbits = (uint64_t)__float_as_uint(sp.depth);
+    for (int y = rc.y0; y < rc.y1; ++y)
+        for (int x = rc.x0; x < rc.x1; ++x) {
+            keys[off] = ((uint64_t)(uint32_t)(y * cam.tiles_x + x) << 32) | dbits;
+            vals[off] = slot;
+            ++off;
+        }
+}
+
+// ---------------------------------------------------------------------------------------------
+// blend forward
+// ---------------------------------------------------------------------------------------------
+#define BLEND_BATCH 256
+#define RGS_WAIT_LIMIT (1u << 22)
+
+struct BlendSmem {
+    RgsSplat buf[2][BLEND_BATCH];
+    unsigned long long bar[2];
+};
+
+// Issue the gather of one batch: every thread copies the 48-byte record of one sorted instance.
+__device__ __forceinline__ void blend_issue(BlendSmem& sm, int stage, const RgsSplat* __restrict__ splats,
+                                            const uint32_t* __restrict__ vals, int first, int count, bool reverse,
+                                            int range_end) {
+    const int t = threadIdx.x;
+    if (t == 0) rgs_mbar_expect_tx(&sm.bar[stage], (uint32_t)count * (uint32_t)sizeof(RgsSplat));
+    if (t < count) {
+        const int idx = reverse ? (range_end - 1 - first - t) : (first + t);
+        const uint32_t slot = vals[idx];
+        rgs_bulk_g2s(&sm.buf[stage][t], splats + slot, (uint32_t)sizeof(RgsSplat), &sm.bar[stage]);
+    }
+}
+
+__global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
+    const __grid_constant__ RgsCamera cam, const int2* __restrict__ ranges, const uint32_t* __restrict__ vals,
+    const RgsSplat* __restrict__ splats, float4* __restrict__ out, float* __restrict__ depth,
+    int32_t* __restrict__ n_contrib, uint32_t* __restrict__ counters) {
+    __shared__ __align__(128) BlendSmem sm;
+    const int tid = threadIdx.x;
+    const int lx = tid & 15, ly = tid >> 4;
+    const int px = blockIdx.x * RGS_TILE + lx, py = blockIdx.y * RGS_TILE + ly;
+    const bool inside = px < cam.W && py < cam.H;
+    const int tile = blockIdx.y * cam.tiles_x + blockIdx.x;
+    int2 range = ranges[tile];
+    if (counters[RGS_CNT_OVERFLOW]) range = make_int2(0, 0);
+    const int total = range.y - range.x;
+    const int rounds = (total + BLEND_BATCH - 1) / BLEND_BATCH;
+    if (tid == 0) { rgs_mbar_init(&sm.bar[0], 1); rgs_mbar_init(&sm.bar[1], 1); rgs_fence_mbar_init(); }
+    __syncthreads();
+
+    const float pixx = (float)px, pixy = (float)py;
+    RgsPixelRay ray;
+    rgs_pixel_ray(cam, pixx, pixy, ray);
+    RgsPixelState st;
+    rgs_pixel_init(st);
+    st.done = !inside;
+
+    if (rounds > 0) blend_issue(sm, 0, splats, vals, range.x, min(BLEND_BATCH, total), false, range.y);
+    int pending = rounds > 0 ? 0 : -1;  // stage with a copy in flight that has not been waited for
+    bool failed = false;
+    for (int b = 0; b < rounds; ++b) {
+        const int stage = b & 1;
+        const int cnt = min(BLEND_BATCH, total - b * BLEND_BATCH);
+        if (b + 1 < rounds) {
+            rgs_fence_proxy_async();
+            blend_issue(sm, stage ^ 1, splats, vals, range.x + (b + 1) * BLEND_BATCH,
+                        min(BLEND_BATCH, total - (b + 1) * BLEND_BATCH), false, range.y);
+        }
+        if (!rgs_mbar_wait(&sm.bar[stage], (b >> 1) & 1, RGS_WAIT_LIMIT)) failed = true;
+        pending = (b + 1 < rounds) ? (stage ^ 1) : -1;
+        if (!failed) {
+            for (int j = 0; j < cnt && !st.done; ++j)
+                rgs_blend_fwd_step(cam, ray, pixx, pixy, sm.buf[stage][j], st);
+        }
+        // also the barrier that frees this stage for the copy issued two rounds later
+        const int ndone = __syncthreads_count(st.done || failed);
+        if (ndone == 256) {
+            if (pending >= 0) rgs_mbar_wait(&sm.bar[pending], ((b + 1) >> 1) & 1, RGS_WAIT_LIMIT);
+            break;
+        }
+    }
+    if (failed && tid == 0) atomicExch(&counters[RGS_CNT_STATUS], 1u);
+    if (inside) {
+        const int64_t pid = (int64_t)py * cam.W + px;
+        out[pid] = make_float4(st.C[0], st.C[1], st.C[2], st.T);
+        if (depth) depth[pid] = st.D;
+        n_contrib[pid] = st.last;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// blend backward
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    return v;
+}
+
+__global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
+    const __grid_constant__ RgsCamera cam, const int2* __restrict__ ranges, const uint32_t* __restrict__ vals,
+    const RgsSplat* __restrict__ splats, const float4* __restrict__ out, const int32_t* __restrict__ n_contrib,
+    const float4* __restrict__ grad_out, RgsSplatGrad* __restrict__ splat_grads, uint32_t* __restrict__ counters) {
+    __shared__ __align__(128) BlendSmem sm;
+    __shared__ uint32_t sm_slot[2][BLEND_BATCH];
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int lx = tid & 15, ly = tid >> 4;
+    const int px = blockIdx.x * RGS_TILE + lx, py = blockIdx.y * RGS_TILE + ly;
+    const bool inside = px < cam.W && py < cam.H;
+    const int tile = blockIdx.y * cam.tiles_x + blockIdx.x;
+    int2 range = ranges[tile];
+    if (counters[RGS_CNT_OVERFLOW]) range = make_int2(0, 0);
+    const int64_t pid = (int64_t)py * cam.W + px;
+    const int last = inside ? n_contrib[pid] : 0;
+    // only the first max(last) instances of the tile contributed to any pixel
+    __shared__ int sm_max_last;
+    if (tid == 0) { sm_max_last = 0; rgs_mbar_init(&sm.bar[0], 1); rgs_mbar_init(&sm.bar[1], 1); rgs_fence_mbar_init(); }
+    __syncthreads();
+    {
+        int m = last;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, d));
+        if (lane == 0) atomicMax(&sm_max_last, m);
+    }
+    __syncthreads();
+    const int total = min(sm_max_last, range.y - range.x);
+    const int range_end = range.x + total;  // replay [range.x, range_end) back to front
+    const int rounds = (total + BLEND_BATCH - 1) / BLEND_BATCH;
+
+    const float pixx = (float)px, pixy = (float)py;
+    RgsPixelRay ray;
+    rgs_pixel_ray(cam, pixx, pixy, ray);
+    RgsPixelBwd st;
+    {
+        float4 o = inside ? out[pid] : make_float4(0.f, 0.f, 0.f, 1.f);
+        float4 g = inside ? grad_out[pid] : make_float4(0.f, 0.f, 0.f, 0.f);
+        float gC[3] = {g.x, g.y, g.z};
+        rgs_pixel_bwd_init(st, o.w, gC, g.w);
+    }
+    auto issue = [&](int b) {
+        const int stage = b & 1;
+        const int cnt = min(BLEND_BATCH, total - b * BLEND_BATCH);
+        if (tid == 0) rgs_mbar_expect_tx(&sm.bar[stage], (uint32_t)cnt * (uint32_t)sizeof(RgsSplat));
+        if (tid < cnt) {
+            const uint32_t slot = vals[range_end - 1 - b * BLEND_BATCH - tid];
+            sm_slot[stage][tid] = slot;
+            rgs_bulk_g2s(&sm.buf[stage][tid], splats + slot, (uint32_t)sizeof(RgsSplat), &sm.bar[stage]);
+        }
+    };
+    if (rounds > 0) issue(0);
+    bool failed = false;
+    int contributor = total;  // 1-based index of the instance about to be visited
+    for (int b = 0; b < rounds; ++b) {
+        const int stage = b & 1;
+        const int cnt = min(BLEND_BATCH, total - b * BLEND_BATCH);
+        if (b + 1 < rounds) { rgs_fence_proxy_async(); issue(b + 1); }
+        if (!rgs_mbar_wait(&sm.bar[stage], (b >> 1) & 1, RGS_WAIT_LIMIT)) failed = true;
+        __syncthreads();  // sm_slot of this stage is visible to all
+        if (!failed) {
+            for (int j = 0; j < cnt; ++j, --contributor) {
+                RgsSplatGrad g;
+                bool hit = false;
+                if (contributor <= last) hit = rgs_blend_bwd_step(cam, ray, pixx, pixy, sm.buf[stage][j], st, g);
+                if (!__any_sync(0xffffffffu, hit)) continue;
+                float v[9] = {g.dpx, g.dpy, g.dca, g.dcb, g.dcc, g.dopacity, g.dr, g.dg, g.db};
+#pragma unroll
+                for (int k = 0; k < 9; ++k) v[k] = warp_sum(hit ? v[k] : 0.f);
+                if (lane == 0) {
+                    float4* dst = reinterpret_cast<float4*>(splat_grads + sm_slot[stage][j]);
+                    atomicAdd(dst, make_float4(v[0], v[1], v[2], v[3]));
+                    atomicAdd(dst + 1, make_float4(v[4], v[5], v[6], v[7]));
+                    atomicAdd(reinterpret_cast<float*>(dst + 2), v[8]);
+                }
+            }
+        }
+        __syncthreads();  // frees this stage for the copy issued two rounds later
+    }
+    if (failed && tid == 0) atomicExch(&counters[RGS_CNT_STATUS], 2u);
+}
+
+// ---------------------------------------------------------------------------------------------
+// geometry backward: one thread per visible splat
+// ---------------------------------------------------------------------------------------------
+struct RgsSegments { RgsSegment s[4]; int n; };
+
+__global__ void __launch_bounds__(128) rgs_geom_bwd_kernel(
+    const __grid_constant__ RgsCamera cam, const __grid_constant__ RgsSegments segs,
+    const uint32_t* __restrict__ counters, const int32_t* __restrict__ vis_ids, const uint32_t* __restrict__ aux,
+    const RgsSplatGrad* __restrict__ splat_grads) {
+    if (counters[RGS_CNT_OVERFLOW]) return;
+    const uint32_t n_vis = counters[RGS_CNT_VIS];
+    for (uint32_t slot = blockIdx.x * blockDim.x + threadIdx.x; slot < n_vis; slot += gridDim.x * blockDim.x) {
+        int64_t i = vis_ids[slot];
+        int sidx = 0;
+        while (sidx < segs.n - 1 && i >= segs.s[sidx].count) { i -= segs.s[sidx].count; ++sidx; }
+        const RgsSegment& sg = segs.s[sidx];
+        const uint32_t a = aux[slot];
+        const float4* gsrc = reinterpret_cast<const float4*>(splat_grads + slot);
+        float4 g0 = gsrc[0], g1 = gsrc[1], g2 = gsrc[2];
+        RgsSplatGrad g;
+        g.dpx = g0.x; g.dpy = g0.y; g.dca = g0.z; g.dcb = g0.w;
+        g.dcc = g1.x; g.dopacity = g1.y; g.dr = g1.z; g.dg = g1.w;
+        g.db = g2.x; g.ddepth = g2.y; g.pad0 = 0.f; g.pad1 = 0.f;
+        float p[3] = {sg.xyz[3 * i], sg.xyz[3 * i + 1], sg.xyz[3 * i + 2]};
+        float s[3] = {sg.scale[3 * i], sg.scale[3 * i + 1], sg.scale[3 * i + 2]};
+        float4 q4 = reinterpret_cast<const float4*>(sg.rot)[i];
+        float q[4] = {q4.x, q4.y, q4.z, q4.w};
+        float gx[3] = {0.f, 0.f, 0.f}, gs[3] = {0.f, 0.f, 0.f}, gq[4] = {0.f, 0.f, 0.f, 0.f}, go[1] = {0.f};
+        float gsh[48];
+#pragma unroll
+        for (int k = 0; k < 48; ++k) gsh[k] = 0.f;
+        const float nrm = rgs_project_bwd(cam, p, s, q, sg.opacity[i], sg.sh + 48 * i, a & 7u, g, gx, gsh, gs, gq, go);
+        if (sg.g_xyz) { sg.g_xyz[3 * i] += gx[0]; sg.g_xyz[3 * i + 1] += gx[1]; sg.g_xyz[3 * i + 2] += gx[2]; }
+        if (sg.g_scale) { sg.g_scale[3 * i] += gs[0]; sg.g_scale[3 * i + 1] += gs[1]; sg.g_scale[3 * i + 2] += gs[2]; }
+        if (sg.g_rot) {
+            float4* d = reinterpret_cast<float4*>(sg.g_rot) + i;
+            float4 o = *d;
+            o.x += gq[0]; o.y += gq[1]; o.z += gq[2]; o.w += gq[3];
+            *d = o;
+        }
+        if (sg.g_opacity) sg.g_opacity[i] += go[0];
+        if (sg.g_sh) {
+            const int nc4 = ((cam.sh_degree + 1) * (cam.sh_degree + 1) * 3 + 3) / 4;
+            float4* d = reinterpret_cast<float4*>(sg.g_sh + 48 * i);
+#pragma unroll
+            for (int k = 0; k < 12; ++k) {
+                if (k < nc4) {
+                    float4 o = d[k];
+                    o.x += gsh[4 * k]; o.y += gsh[4 * k + 1]; o.z += gsh[4 * k + 2]; o.w += gsh[4 * k + 3];
+                    d[k] = o;
+                }
+            }
+        }
+        if (sg.g_mean2d) { sg.g_mean2d[2 * i] = g.dpx * 0.5f * cam.W; sg.g_mean2d[2 * i + 1] = g.dpy * 0.5f * cam.H; }
+        if (sg.stat_grad) sg.stat_grad[i] += nrm;
+        if (sg.stat_denom) sg.stat_denom[i] += 1.0f;
+        if (sg.stat_maxrad) sg.stat_maxrad[i] = fmaxf(sg.stat_maxrad[i], (float)(a >> 3));
+    }
+}
+
+__global__ void rgs_scatter_radii_kernel(const uint32_t* __restrict__ counters, const int32_t* __restrict__ vis_ids,
+                                         const uint32_t* __restrict__ aux, int64_t id_base, int64_t count,
+                                         int32_t* __restrict__ radii) {
+    if (counters[RGS_CNT_OVERFLOW]) return;
+    const uint32_t n_vis = counters[RGS_CNT_VIS];
+    for (uint32_t s = blockIdx.x * blockDim.x + threadIdx.x; s < n_vis; s += gridDim.x * blockDim.x) {
+        int64_t i = (int64_t)vis_ids[s] - id_base;
+        if (i >= 0 && i < count) radii[i] = (int32_t)(aux[s] >> 3);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host entry points
+// ---------------------------------------------------------------------------------------------
+extern "C" {
+
+int rgs_cuda_project_emit(const RgsCamera* cam, const RgsSegment* seg, int64_t id_base, RgsSplat* splats,
+                          int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint64_t* keys, uint32_t* vals,
+                          int64_t cap_inst, int32_t* counters, void* stream) {
+    if (seg->count <= 0) return 0;
+    if (cap_inst > 0xfffffff0ll || cap_vis > 0x7ffffff0ll) return 10;
+    const unsigned blocks = (unsigned)((seg->count + 255) / 256);
+    rgs_project_emit_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
+        *cam, *seg, id_base, splats, vis_ids, aux, (uint32_t)cap_vis, keys, vals, (uint32_t)cap_inst,
+        reinterpret_cast<uint32_t*>(counters));
+    return (int)cudaGetLastError();
+}
+
+int rgs_cuda_blend_fwd(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
+                       float* out, float* depth, int32_t* n_contrib, int32_t* counters, void* stream) {
+    dim3 grid(cam->tiles_x, cam->tiles_y);
+    rgs_blend_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
+        *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<float4*>(out), depth, n_contrib,
+        reinterpret_cast<uint32_t*>(counters));
+    return (int)cudaGetLastError();
+}
+
+int rgs_cuda_blend_bwd(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
+                       const float* out, const int32_t* n_contrib, const float* grad_out, RgsSplatGrad* splat_grads,
+                       int32_t* counters, void* stream) {
+    dim3 grid(cam->tiles_x, cam->tiles_y);
+    rgs_blend_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
+        *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
+        reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters));
+    return (int)cudaGetLastError();
+}
+
+int rgs_cuda_geom_bwd(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg, const int32_t* counters,
+                      const RgsSplat* splats, const int32_t* vis_ids, const uint32_t* aux,
+                      const RgsSplatGrad* splat_grads, int64_t cap_vis, void* stream) {
+    (void)splats;
+    if (nseg < 1 || nseg > 4) return 11;
+    RgsSegments s;
+    s.n = (int)nseg;
+    for (int k = 0; k < (int)nseg; ++k) s.s[k] = segs[k];
+    const int64_t want = (cap_vis + 127) / 128;
+    const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > 148 * 16 ? 148 * 16 : want));
+    rgs_geom_bwd_kernel<<<blocks, 128, 0, (cudaStream_t)stream>>>(*cam, s, reinterpret_cast<const uint32_t*>(counters),
+                                                                 vis_ids, aux, splat_grads);
+    return (int)cudaGetLastError();
+}
+
+int rgs_cuda_scatter_radii(const int32_t* counters, const int32_t* vis_ids, const uint32_t* aux, int64_t id_base,
+                           int64_t count, int32_t* radii, void* stream) {
+    rgs_scatter_radii_kernel<<<148 * 4, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const uint32_t*>(counters),
+                                                                         vis_ids, aux, id_base, count, radii);
+    return (int)cudaGetLastError();
+}
+
+}  // extern "C"

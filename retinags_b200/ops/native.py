@@ -1,0 +1,159 @@
+"""ctypes binding of the native libraries (``librgs_cpu.so`` / ``librgs_cuda.so``).
+
+Every entry point exists twice with the same argument list: ``rgs_cpu_<name>`` works on host
+pointers, ``rgs_cuda_<name>`` on device pointers and takes the CUDA stream as its last argument
+(the CPU twin ignores it).  :func:`call` picks the twin from the device of the tensors involved.
+On a machine with a GPU the CUDA library is mandatory: a missing ``librgs_cuda.so`` raises instead
+of silently falling back to another implementation.
+
+Counterpart in the reference: the pybind extension
+``rasterization_kernels/diff-gaussian-rasterization-half-gaussian/ext.cpp:15-19``.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+
+import torch
+
+from .. import _build
+
+_LOCK = threading.Lock()
+_LIBS: dict[str, ctypes.CDLL] = {}
+
+# signature alphabet: p = pointer, i = int64, f = double
+SIGNATURES = {
+    "project_emit": "ppipppippipp",
+    "sort_ranges": "ppppipippp",
+    "blend_fwd": "ppppppppp",
+    "blend_bwd": "pppppppppp",
+    "geom_bwd": "ppipppppip",
+    "scatter_radii": "pppiipp",
+    "adam": "ppppiipfffipp",
+    "composite_fwd": "pipiiiippp",
+    "composite_bwd": "ppipiiiipp",
+    "ssim_fwd": "ppiiiiiippp",
+    "ssim_bwd": "pppiiiiiiffpp",
+}
+
+_CTYPE = {"p": ctypes.c_void_p, "i": ctypes.c_int64, "f": ctypes.c_double}
+
+
+class RgsCamera(ctypes.Structure):
+    """Mirror of ``struct RgsCamera`` (csrc/rgs_math.h)."""
+
+    _fields_ = [
+        ("view", ctypes.c_float * 16),
+        ("proj", ctypes.c_float * 16),
+        ("c2w", ctypes.c_float * 16),
+        ("campos", ctypes.c_float * 3),
+        ("tan_fovx", ctypes.c_float),
+        ("tan_fovy", ctypes.c_float),
+        ("focal_x", ctypes.c_float),
+        ("focal_y", ctypes.c_float),
+        ("W", ctypes.c_int),
+        ("H", ctypes.c_int),
+        ("tiles_x", ctypes.c_int),
+        ("tiles_y", ctypes.c_int),
+        ("box_lo", ctypes.c_float * 3),
+        ("box_hi", ctypes.c_float * 3),
+        ("bg", ctypes.c_float * 3),
+        ("sh_degree", ctypes.c_int),
+        ("scale_modifier", ctypes.c_float),
+        ("raw_params", ctypes.c_int),
+        ("tight_rect", ctypes.c_int),
+    ]
+
+
+class RgsSegment(ctypes.Structure):
+    """Mirror of ``struct RgsSegment`` (csrc/rgs_api.h)."""
+
+    _fields_ = [(n, ctypes.c_void_p) for n in (
+        "xyz", "sh", "scale", "rot", "opacity", "g_xyz", "g_sh", "g_scale", "g_rot", "g_opacity",
+        "g_mean2d", "stat_grad", "stat_denom", "stat_maxrad")] + [("count", ctypes.c_int64)]
+
+
+CNT_VIS, CNT_INST, CNT_OVERFLOW, CNT_STATUS, CNT_WORDS = 0, 1, 2, 3, 8
+SPLAT_FLOATS = 12
+
+
+def cuda_required() -> bool:
+    return torch.cuda.is_available()
+
+
+def lib(kind: str) -> ctypes.CDLL:
+    """Load (building first when stale) ``librgs_<kind>.so``; kind is "cpu" or "cuda"."""
+    with _LOCK:
+        if kind in _LIBS:
+            return _LIBS[kind]
+        if kind == "cpu":
+            path = _build.build_cpu()
+        elif kind == "cuda":
+            path = _build.LIB / "librgs_cuda.so"
+            if not path.exists() or _build._stale(path, [_build.CSRC / s for s in _build.CUDA_SOURCES
+                                                          if (_build.CSRC / s).exists()]):
+                path = _build.build_cuda()
+        else:
+            raise ValueError(kind)
+        handle = ctypes.CDLL(str(path))
+        _LIBS[kind] = handle
+        return handle
+
+
+def _fn(kind: str, name: str, sig: str | None = None):
+    handle = lib(kind)
+    full = f"rgs_{kind}_{name}"
+    fn = getattr(handle, full)
+    if not getattr(fn, "_rgs_ready", False):
+        sig = sig if sig is not None else SIGNATURES[name]
+        fn.argtypes = [_CTYPE[c] for c in sig]
+        fn.restype = ctypes.c_int
+        fn._rgs_ready = True
+    return fn
+
+
+def ptr(x):
+    """Raw address of a tensor / ctypes object / None."""
+    if x is None:
+        return None
+    if isinstance(x, torch.Tensor):
+        return x.data_ptr()
+    if isinstance(x, (ctypes.Structure, ctypes.Array)):
+        return ctypes.addressof(x)
+    if isinstance(x, int):
+        return x
+    raise TypeError(type(x))
+
+
+def stream_ptr(device: torch.device):
+    if device.type != "cuda":
+        return None
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def call(name: str, device: torch.device, *args, sig: str | None = None) -> None:
+    """Invoke ``rgs_<cpu|cuda>_<name>(*args, stream)`` and raise on a non-zero status."""
+    kind = "cuda" if device.type == "cuda" else "cpu"
+    fn = _fn(kind, name, sig)
+    conv = []
+    for a in args:
+        if isinstance(a, (torch.Tensor, ctypes.Structure, ctypes.Array)) or a is None:
+            conv.append(ptr(a))
+        else:
+            conv.append(a)
+    if kind == "cuda":
+        with torch.cuda.device(device):
+            rc = fn(*conv, stream_ptr(device))
+    else:
+        rc = fn(*conv, None)
+    if rc != 0:
+        raise RuntimeError(f"rgs_{kind}_{name} failed with status {rc}")
+
+
+def pointer_array(tensors) -> ctypes.Array:
+    """Host array of raw addresses (for entry points that take a list of buffers)."""
+    arr = (ctypes.c_void_p * max(len(tensors), 1))()
+    for i, t in enumerate(tensors):
+        arr[i] = ptr(t)
+    return arr

@@ -1,0 +1,375 @@
+"""Render tasks: one (camera, sub-model) rasterisation through the native kernels.
+
+``RenderTask`` owns every buffer of one render (compacted splat records, sorted instance list,
+tile ranges, per-pixel contributor counts, splat gradients) so that nothing is allocated inside
+the step once capacities have settled; the reference allocates outputs plus three byte buffers on
+every call (``rasterize_points.cu:71-83``) and blocks the host on the instance count
+(``rasterizer_impl.cu:286-287``).  Capacities are high-water marks: the kernels count what they
+*would* have needed and raise an overflow word instead of writing out of bounds; the host reads
+the counters when it next synchronises anyway and grows the buffers.
+
+``rasterize_gaussians`` is the autograd entry point with the argument list of the reference's
+``GaussianRasterizer.forward`` (``diff_gaussian_rasterization_half_gaussian/__init__.py:199-232``):
+activated means/scales/rotations/opacities/SHs in, premultiplied colour, depth and alpha out.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..data.cameras import Camera
+from . import native
+from .native import CNT_INST, CNT_OVERFLOW, CNT_STATUS, CNT_VIS, CNT_WORDS, RgsCamera, RgsSegment
+
+TILE = 16
+INF = float("inf")
+
+
+def make_camera(cam: Camera, sh_degree: int, box_lo=None, box_hi=None, raw_params: bool = True,
+                tight_rect: bool = True, scale_modifier: float = 1.0, bg=(0.0, 0.0, 0.0)) -> RgsCamera:
+    """Fill the by-value camera/sub-model descriptor the kernels take."""
+    c = RgsCamera()
+    c.view[:] = cam.world_view_transform.reshape(-1).tolist()
+    c.proj[:] = cam.full_proj_transform.reshape(-1).tolist()
+    c.c2w[:] = cam.view_world_transform.reshape(-1).tolist()
+    c.campos[:] = cam.camera_center.tolist()
+    c.tan_fovx, c.tan_fovy = cam.tan_fovx, cam.tan_fovy
+    c.focal_x = cam.width / (2.0 * cam.tan_fovx)
+    c.focal_y = cam.height / (2.0 * cam.tan_fovy)
+    c.W, c.H = cam.width, cam.height
+    c.tiles_x = (cam.width + TILE - 1) // TILE
+    c.tiles_y = (cam.height + TILE - 1) // TILE
+    lo = [-INF] * 3 if box_lo is None else [float(v) for v in box_lo]
+    hi = [INF] * 3 if box_hi is None else [float(v) for v in box_hi]
+    c.box_lo[:] = lo
+    c.box_hi[:] = hi
+    c.bg[:] = [float(v) for v in bg]
+    c.sh_degree = int(sh_degree)
+    c.scale_modifier = float(scale_modifier)
+    c.raw_params = 1 if raw_params else 0
+    c.tight_rect = 1 if tight_rect else 0
+    return c
+
+
+@dataclass
+class Segment:
+    """A block of Gaussians read by a render (own or borrowed), with optional gradient sinks."""
+
+    xyz: torch.Tensor
+    sh: torch.Tensor
+    scale: torch.Tensor
+    rot: torch.Tensor
+    opacity: torch.Tensor
+    g_xyz: torch.Tensor | None = None
+    g_sh: torch.Tensor | None = None
+    g_scale: torch.Tensor | None = None
+    g_rot: torch.Tensor | None = None
+    g_opacity: torch.Tensor | None = None
+    g_mean2d: torch.Tensor | None = None
+    stat_grad: torch.Tensor | None = None
+    stat_denom: torch.Tensor | None = None
+    stat_maxrad: torch.Tensor | None = None
+
+    @property
+    def count(self) -> int:
+        return int(self.xyz.shape[0])
+
+    def struct(self, with_grads: bool = True) -> RgsSegment:
+        s = RgsSegment()
+        for name in ("xyz", "sh", "scale", "rot", "opacity"):
+            t = getattr(self, name)
+            assert t.is_contiguous() and t.dtype == torch.float32, name
+            setattr(s, name, t.data_ptr())
+        for name in ("g_xyz", "g_sh", "g_scale", "g_rot", "g_opacity", "g_mean2d", "stat_grad", "stat_denom",
+                     "stat_maxrad"):
+            t = getattr(self, name) if with_grads else None
+            if t is not None:
+                assert t.is_contiguous() and t.dtype == torch.float32, name
+            setattr(s, name, None if t is None else t.data_ptr())
+        s.count = self.count
+        return s
+
+
+class SortScratch:
+    """Ping-pong buffers and histogram scratch of the radix sort, shared by all tasks of a device."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.cap = 0
+        self.keys_tmp = self.vals_tmp = self.words = None
+
+    def ensure(self, cap_inst: int):
+        if cap_inst <= self.cap:
+            return
+        kind = "cuda" if self.device.type == "cuda" else "cpu"
+        fn = getattr(native.lib(kind), f"rgs_{kind}_sort_scratch_words")
+        fn.argtypes = [ctypes.c_int64]
+        fn.restype = ctypes.c_int64
+        words = int(fn(cap_inst))
+        self.keys_tmp = torch.empty(cap_inst, dtype=torch.int64, device=self.device)
+        self.vals_tmp = torch.empty(cap_inst, dtype=torch.int32, device=self.device)
+        self.words = torch.empty(words, dtype=torch.int32, device=self.device)
+        self.cap = cap_inst
+
+
+_SCRATCH: dict[str, SortScratch] = {}
+
+
+def sort_scratch(device: torch.device) -> SortScratch:
+    key = str(device)
+    if key not in _SCRATCH:
+        _SCRATCH[key] = SortScratch(device)
+    return _SCRATCH[key]
+
+
+class RenderTask:
+    """State of one rasterisation, kept between forward and backward."""
+
+    def __init__(self, device, inst_per_gaussian: float = 4.0, min_inst: int = 1 << 16):
+        self.device = torch.device(device)
+        self.inst_per_gaussian = inst_per_gaussian
+        self.min_inst = min_inst
+        self.cap_vis = 0
+        self.cap_inst = 0
+        self.hw = (0, 0)
+        self.cam: RgsCamera | None = None
+        self.counters = torch.zeros(CNT_WORDS, dtype=torch.int32, device=self.device)
+        self._host_counters = torch.zeros(CNT_WORDS, dtype=torch.int32)
+        if self.device.type == "cuda":
+            self._host_counters = self._host_counters.pin_memory()
+        self._event = None
+        self.splats = self.vis_ids = self.aux = self.keys = self.vals = self.ranges = None
+        self.out = self.depth = self.n_contrib = self.splat_grads = None
+        self.total_count = 0
+
+    # -- buffers ------------------------------------------------------------------------------
+    def _ensure(self, n_gauss: int, H: int, W: int, want_depth: bool):
+        dev = self.device
+        if n_gauss > self.cap_vis:
+            self.cap_vis = max(int(n_gauss), 1)
+            self.splats = torch.empty(self.cap_vis, native.SPLAT_FLOATS, dtype=torch.float32, device=dev)
+            self.vis_ids = torch.empty(self.cap_vis, dtype=torch.int32, device=dev)
+            self.aux = torch.empty(self.cap_vis, dtype=torch.int32, device=dev)
+            self.splat_grads = torch.empty(self.cap_vis, native.SPLAT_FLOATS, dtype=torch.float32, device=dev)
+        want_inst = max(int(n_gauss * self.inst_per_gaussian), self.min_inst)
+        if self.cap_inst == 0:
+            self._grow_inst(want_inst)
+        if (H, W) != self.hw:
+            self.hw = (H, W)
+            tiles = ((H + TILE - 1) // TILE) * ((W + TILE - 1) // TILE)
+            self.ranges = torch.zeros(tiles, 2, dtype=torch.int32, device=dev)
+            self.out = torch.empty(H, W, 4, dtype=torch.float32, device=dev)
+            self.n_contrib = torch.empty(H, W, dtype=torch.int32, device=dev)
+            self.depth = None
+        if want_depth and self.depth is None:
+            self.depth = torch.empty(H, W, dtype=torch.float32, device=dev)
+
+    def _grow_inst(self, cap: int):
+        cap = int(min(max(cap, self.min_inst), 0xFFFFFF00))
+        self.cap_inst = cap
+        self.keys = torch.empty(cap, dtype=torch.int64, device=self.device)
+        self.vals = torch.empty(cap, dtype=torch.int32, device=self.device)
+        sort_scratch(self.device).ensure(cap)
+
+    # -- forward ------------------------------------------------------------------------------
+    def forward(self, cam: RgsCamera, segments: list[Segment], want_depth: bool = False, out: torch.Tensor | None = None,
+                check: bool = False) -> torch.Tensor:
+        """Rasterise ``segments`` for ``cam``; returns the (H,W,4) premultiplied RGB + T image.
+
+        ``out`` lets the caller provide the destination (for instance a slot of a compositing
+        buffer).  With ``check`` the counters are read back (host sync) and the render is repeated
+        with larger buffers when the instance capacity was exceeded.
+        """
+        H, W = cam.H, cam.W
+        self.cam = cam
+        self.total_count = sum(s.count for s in segments)
+        self._ensure(self.total_count, H, W, want_depth)
+        while True:
+            dst = self.out if out is None else out
+            self.counters.zero_()
+            base = 0
+            for seg in segments:
+                if seg.count:
+                    native.call("project_emit", self.device, cam, seg.struct(False), base, self.splats, self.vis_ids,
+                                self.aux, self.cap_vis, self.keys, self.vals, self.cap_inst, self.counters)
+                base += seg.count
+            sc = sort_scratch(self.device)
+            sc.ensure(self.cap_inst)
+            native.call("sort_ranges", self.device, self.keys, self.vals, sc.keys_tmp, sc.vals_tmp, self.cap_inst,
+                        self.counters, cam.tiles_x * cam.tiles_y, self.ranges, sc.words)
+            native.call("blend_fwd", self.device, cam, self.ranges, self.vals, self.splats, dst,
+                        self.depth if want_depth else None, self.n_contrib, self.counters)
+            self.last_out = dst
+            if not check:
+                self._record_counters()
+                return dst
+            cnt = self.counters.tolist()
+            if cnt[CNT_STATUS]:
+                raise RuntimeError(f"rasteriser wait expired (status {cnt[CNT_STATUS]})")
+            if not cnt[CNT_OVERFLOW]:
+                self.n_vis, self.n_inst = cnt[CNT_VIS], cnt[CNT_INST]
+                return dst
+            need = cnt[CNT_INST] & 0xFFFFFFFF
+            self._grow_inst(int(need * 1.25) + 1024)
+
+    def _record_counters(self):
+        if self.device.type == "cuda":
+            self._host_counters.copy_(self.counters, non_blocking=True)
+            self._event = torch.cuda.Event()
+            self._event.record(torch.cuda.current_stream(self.device))
+        else:
+            self._host_counters.copy_(self.counters)
+
+    def poll(self) -> dict:
+        """Counters of the last unchecked forward (call after the stream was synchronised).
+
+        Grows the instance buffers when the last render overflowed or came close; returns the
+        counters so that the caller can decide to redo the step.
+        """
+        if self._event is not None:
+            self._event.synchronize()
+            self._event = None
+        c = self._host_counters.tolist()
+        info = dict(n_vis=c[CNT_VIS], n_inst=c[CNT_INST] & 0xFFFFFFFF, overflow=bool(c[CNT_OVERFLOW]), status=c[CNT_STATUS])
+        if info["status"]:
+            raise RuntimeError(f"rasteriser wait expired (status {info['status']})")
+        if info["overflow"] or info["n_inst"] > 0.8 * self.cap_inst:
+            self._grow_inst(int(info["n_inst"] * 1.5) + 1024)
+        return info
+
+    # -- backward -----------------------------------------------------------------------------
+    def backward(self, grad_out: torch.Tensor, segments: list[Segment]):
+        """Accumulate parameter gradients of the last forward. ``grad_out`` is (H,W,4): dL/dC, dL/dT."""
+        cam = self.cam
+        assert grad_out.is_contiguous() and grad_out.shape == (cam.H, cam.W, 4)
+        self.splat_grads.zero_()
+        native.call("blend_bwd", self.device, cam, self.ranges, self.vals, self.splats, self.last_out, self.n_contrib,
+                    grad_out, self.splat_grads, self.counters)
+        structs = (RgsSegment * len(segments))(*[s.struct(True) for s in segments])
+        native.call("geom_bwd", self.device, cam, structs, len(segments), self.counters, self.splats, self.vis_ids,
+                    self.aux, self.splat_grads, self.cap_vis)
+
+    def radii(self, segment_index: int, segments: list[Segment]) -> torch.Tensor:
+        base = sum(s.count for s in segments[:segment_index])
+        cnt = segments[segment_index].count
+        r = torch.zeros(cnt, dtype=torch.int32, device=self.device)
+        native.call("scatter_radii", self.device, self.counters, self.vis_ids, self.aux, base, cnt, r)
+        return r
+
+
+# ---------------------------------------------------------------------------------------------
+# autograd entry point with the reference's interface
+# ---------------------------------------------------------------------------------------------
+@dataclass
+class GaussianRasterizationSettings:
+    """Field-for-field equivalent of the reference's settings tuple
+    (``diff_gaussian_rasterization_half_gaussian/__init__.py:166-181``)."""
+
+    image_height: int
+    image_width: int
+    tanfovx: float
+    tanfovy: float
+    bg: torch.Tensor
+    scale_modifier: float
+    viewmatrix: torch.Tensor
+    projmatrix: torch.Tensor
+    projmatrix_inv: torch.Tensor  # view->world, transposed storage
+    range_low: torch.Tensor
+    range_up: torch.Tensor
+    sh_degree: int
+    campos: torch.Tensor
+    prefiltered: bool = False
+    debug: bool = False
+
+
+def _settings_camera(st: GaussianRasterizationSettings) -> RgsCamera:
+    c = RgsCamera()
+    c.view[:] = st.viewmatrix.detach().cpu().reshape(-1).tolist()
+    c.proj[:] = st.projmatrix.detach().cpu().reshape(-1).tolist()
+    c.c2w[:] = st.projmatrix_inv.detach().cpu().reshape(-1).tolist()
+    c.campos[:] = st.campos.detach().cpu().reshape(-1).tolist()
+    c.tan_fovx, c.tan_fovy = st.tanfovx, st.tanfovy
+    c.focal_x = st.image_width / (2.0 * st.tanfovx)
+    c.focal_y = st.image_height / (2.0 * st.tanfovy)
+    c.W, c.H = st.image_width, st.image_height
+    c.tiles_x = (st.image_width + TILE - 1) // TILE
+    c.tiles_y = (st.image_height + TILE - 1) // TILE
+    c.box_lo[:] = st.range_low.detach().cpu().reshape(-1).tolist()
+    c.box_hi[:] = st.range_up.detach().cpu().reshape(-1).tolist()
+    c.bg[:] = st.bg.detach().cpu().reshape(-1).tolist()
+    c.sh_degree = st.sh_degree
+    c.scale_modifier = st.scale_modifier
+    c.raw_params = 0
+    c.tight_rect = 1
+    return c
+
+
+class _Rasterize(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, means3D, means2D, shs, opacities, scales, rotations, settings):
+        dev = means3D.device
+        cam = _settings_camera(settings)
+        seg = Segment(means3D.contiguous(), shs.contiguous().view(-1, 48), scales.contiguous(), rotations.contiguous(),
+                      opacities.contiguous().view(-1, 1))
+        if shs.shape[1] != 16:
+            full = torch.zeros(shs.shape[0], 16, 3, dtype=shs.dtype, device=dev)
+            full[:, : shs.shape[1]] = shs
+            seg.sh = full.view(-1, 48)
+        task = RenderTask(dev)
+        out = task.forward(cam, [seg], want_depth=True, check=True)
+        bg = settings.bg.to(dev).view(1, 1, 3)
+        color = (out[..., :3] + out[..., 3:4] * bg).permute(2, 0, 1).contiguous()
+        alpha = (1.0 - out[..., 3]).unsqueeze(0)
+        depth = task.depth.unsqueeze(0).clone()
+        radii = task.radii(0, [seg])
+        ctx.task, ctx.seg, ctx.settings, ctx.n_sh = task, seg, settings, shs.shape[1]
+        ctx.mark_non_differentiable(radii)
+        return color, depth, alpha, radii
+
+    @staticmethod
+    def backward(ctx, g_color, g_depth, g_alpha, _g_radii):
+        task, seg, st = ctx.task, ctx.seg, ctx.settings
+        dev = seg.xyz.device
+        H, W = st.image_height, st.image_width
+        bg = st.bg.to(dev).view(3, 1, 1)
+        grad = torch.zeros(H, W, 4, dtype=torch.float32, device=dev)
+        if g_color is not None:
+            grad[..., :3] = g_color.permute(1, 2, 0)
+            grad[..., 3] = (g_color * bg).sum(0)
+        if g_alpha is not None:
+            grad[..., 3] -= g_alpha[0]
+        n = seg.count
+        seg.g_xyz = torch.zeros(n, 3, device=dev)
+        seg.g_sh = torch.zeros(n, 48, device=dev)
+        seg.g_scale = torch.zeros(n, 3, device=dev)
+        seg.g_rot = torch.zeros(n, 4, device=dev)
+        seg.g_opacity = torch.zeros(n, 1, device=dev)
+        seg.g_mean2d = torch.zeros(n, 2, device=dev)
+        task.backward(grad.contiguous(), [seg])
+        g_means2D = torch.zeros(n, 3, device=dev)
+        g_means2D[:, :2] = seg.g_mean2d
+        g_sh = seg.g_sh.view(n, 16, 3)[:, : ctx.n_sh]
+        return seg.g_xyz, g_means2D, g_sh, seg.g_opacity, seg.g_scale, seg.g_rot, None
+
+
+def rasterize_gaussians(means3D, means2D, shs, opacities, scales, rotations, settings: GaussianRasterizationSettings):
+    """(color (3,H,W), depth (1,H,W), alpha (1,H,W), radii (P)) for activated inputs."""
+    return _Rasterize.apply(means3D, means2D, shs, opacities, scales, rotations, settings)
+
+
+class GaussianRasterizer(torch.nn.Module):
+    """Module wrapper with the call signature of the reference's ``GaussianRasterizer``."""
+
+    def __init__(self, raster_settings: GaussianRasterizationSettings):
+        super().__init__()
+        self.raster_settings = raster_settings
+
+    def forward(self, means3D, means2D, opacities, shs=None, colors_precomp=None, scales=None, rotations=None,
+                cov3D_precomp=None):
+        if shs is None or colors_precomp is not None or cov3D_precomp is not None:
+            raise NotImplementedError("only the SH + scale/rotation path exists (the one the reference's trainer uses)")
+        return rasterize_gaussians(means3D, means2D, shs, opacities, scales, rotations, self.raster_settings)

@@ -1,0 +1,125 @@
+"""Native CPU rasteriser (shared math with the sm_100a kernels) against the PyTorch oracle."""
+import pytest
+import torch
+
+from helpers import activated, native_render, oracle_render, small_scene
+from retinags_b200.ops import oracle, rasterize
+
+
+@pytest.mark.parametrize("deg", [0, 1, 3])
+def test_forward_matches_oracle(deg):
+    g, cams = small_scene(sh_degree=deg)
+    for cam in cams[:2]:
+        out, task, _, _ = native_render(g, cam, deg, want_depth=True)
+        C, T, D, info = oracle_render(g, cam, deg)
+        assert task.n_vis > 50
+        torch.testing.assert_close(out[..., :3].permute(2, 0, 1), C, atol=2e-5, rtol=1e-4)
+        torch.testing.assert_close(out[..., 3], T, atol=2e-5, rtol=1e-4)
+        torch.testing.assert_close(task.depth, D, atol=1e-4, rtol=1e-4)
+
+
+def test_tight_rect_is_exact():
+    g, cams = small_scene(n=1500)
+    a, ta, _, _ = native_render(g, cams[0], 3, tight=True)
+    b, tb, _, _ = native_render(g, cams[0], 3, tight=False)
+    assert torch.equal(a, b)
+    assert ta.n_inst < tb.n_inst
+
+
+def test_box_split_composites_to_whole():
+    g, cams = small_scene(n=1500)
+    big = 1e9
+    whole, _, _, _ = native_render(g, cams[1], 3)
+    left, _, _, _ = native_render(g, cams[1], 3, box=([-big, -big, -big], [0.1, big, big]))
+    right, _, _, _ = native_render(g, cams[1], 3, box=([0.1, -big, -big], [big, big, big]))
+    # which half is in front depends on the camera; composite both orders and take the matching one
+    def over(f, b):
+        return f[..., :3] + f[..., 3:4] * b[..., :3], f[..., 3] * b[..., 3]
+    center = cams[1].camera_center
+    first, second = (left, right) if center[0] <= 0.1 else (right, left)
+    C, T = over(first, second)
+    # the sort order inside one pixel differs only by which sub-model a splat belongs to, so the
+    # composite equals the whole render up to float rounding, except where the T<1e-4 stop differs
+    # (a pixel that stops in the whole render may keep blending across the two halves: |dT| < 1e-3)
+    torch.testing.assert_close(C, whole[..., :3], atol=1e-3, rtol=0)
+    torch.testing.assert_close(T, whole[..., 3], atol=1e-3, rtol=0)
+    assert ((T - whole[..., 3]).abs() > 1e-5).float().mean() < 0.02
+
+
+def test_backward_matches_autograd():
+    deg = 3
+    g, cams = small_scene(n=400, seed=5)
+    cam = cams[0]
+    box = ([-0.3, -1e9, -1e9], [1e9, 1e9, 1e9])
+    a = activated(g)
+    leaves = {k: v.clone().requires_grad_(True) for k, v in a.items()}
+    C, T, D, _ = oracle.rasterize(cam, leaves["xyz"], leaves["sh"].view(-1, 16, 3), leaves["opacity"], leaves["scale"],
+                                  leaves["rot"], deg, box[0], box[1])
+    gen = torch.Generator().manual_seed(0)
+    wC = torch.randn(C.shape, generator=gen)
+    wT = torch.randn(T.shape, generator=gen)
+    ((C * wC).sum() + (T * wT).sum()).backward()
+
+    out, task, seg, c = native_render(a, cam, deg, box=box, raw=False)
+    n = seg.count
+    for name, w in (("g_xyz", 3), ("g_sh", 48), ("g_scale", 3), ("g_rot", 4), ("g_opacity", 1), ("g_mean2d", 2)):
+        setattr(seg, name, torch.zeros(n, w))
+    grad = torch.cat([wC.permute(1, 2, 0), wT[..., None]], dim=-1).contiguous()
+    task.backward(grad, [seg])
+    for name, key in (("g_xyz", "xyz"), ("g_sh", "sh"), ("g_scale", "scale"), ("g_rot", "rot"), ("g_opacity", "opacity")):
+        ref = leaves[key].grad
+        got = getattr(seg, name)
+        scale = ref.abs().max().item() + 1e-12
+        err = (got - ref).abs().max().item() / scale
+        assert err < 2e-3, (name, err, scale)
+
+
+def test_raw_param_gradients():
+    """Gradients with respect to raw parameters == autograd through the activations."""
+    deg = 2
+    g, cams = small_scene(n=300, seed=9, sh_degree=deg)
+    cam = cams[2]
+    leaves = {k: v.clone().requires_grad_(True) for k, v in g.items()}
+    act = activated(leaves)
+    C, T, D, _ = oracle.rasterize(cam, act["xyz"], act["sh"].view(-1, 16, 3), act["opacity"], act["scale"], act["rot"], deg)
+    gen = torch.Generator().manual_seed(1)
+    wC = torch.randn(C.shape, generator=gen)
+    ((C * wC).sum()).backward()
+    out, task, seg, c = native_render(g, cam, deg, raw=True)
+    n = seg.count
+    for name, w in (("g_xyz", 3), ("g_sh", 48), ("g_scale", 3), ("g_rot", 4), ("g_opacity", 1)):
+        setattr(seg, name, torch.zeros(n, w))
+    seg.stat_grad = torch.zeros(n)
+    seg.stat_denom = torch.zeros(n)
+    seg.stat_maxrad = torch.zeros(n)
+    grad = torch.cat([wC.permute(1, 2, 0), torch.zeros(C.shape[1], C.shape[2], 1)], dim=-1).contiguous()
+    task.backward(grad, [seg])
+    for name, key in (("g_xyz", "xyz"), ("g_sh", "sh"), ("g_scale", "scale"), ("g_rot", "rot"), ("g_opacity", "opacity")):
+        ref = leaves[key].grad
+        got = getattr(seg, name)
+        scale = ref.abs().max().item() + 1e-12
+        assert (got - ref).abs().max().item() / scale < 2e-3, name
+    assert int(seg.stat_denom.sum()) == task.n_vis
+    assert seg.stat_maxrad.max() > 0
+
+
+def test_autograd_function_interface():
+    g, cams = small_scene(n=300, seed=11)
+    cam = cams[0]
+    a = activated(g)
+    st = rasterize.GaussianRasterizationSettings(
+        image_height=cam.height, image_width=cam.width, tanfovx=cam.tan_fovx, tanfovy=cam.tan_fovy,
+        bg=torch.tensor([0.2, 0.3, 0.4]), scale_modifier=1.0, viewmatrix=torch.tensor(cam.world_view_transform),
+        projmatrix=torch.tensor(cam.full_proj_transform), projmatrix_inv=torch.tensor(cam.view_world_transform),
+        range_low=torch.tensor([-1e9] * 3), range_up=torch.tensor([1e9] * 3), sh_degree=3,
+        campos=torch.tensor(cam.camera_center))
+    xyz = a["xyz"].clone().requires_grad_(True)
+    m2d = torch.zeros(xyz.shape[0], 3, requires_grad=True)
+    color, depth, alpha, radii = rasterize.GaussianRasterizer(st)(
+        xyz, m2d, a["opacity"], shs=a["sh"].view(-1, 16, 3), scales=a["scale"], rotations=a["rot"])
+    C, T, D, info = oracle_render(g, cam, 3)
+    torch.testing.assert_close(color, C + T[None] * st.bg.view(3, 1, 1), atol=2e-5, rtol=1e-4)
+    torch.testing.assert_close(alpha[0], 1 - T, atol=2e-5, rtol=1e-4)
+    assert torch.equal(radii > 0, info["radii"] > 0)
+    color.sum().backward()
+    assert xyz.grad.abs().sum() > 0 and m2d.grad.abs().sum() > 0
