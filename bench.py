@@ -1,0 +1,192 @@
+#!/usr/bin/env python
+"""Headline benchmark: training views/s at 62.9M Gaussians, 1600x1036, on N B200s of one node.
+
+Own arm (default): the framework's trainer on a seeded synthetic cluster scene (random-init
+Gaussians, SH degree 3, fp32), 2^k sub-models for N = 2^k GPUs (strong scaling: the scene is fixed),
+two views per step.  Reference arm (``--impl reference``): the unmodified reference installed
+under ``baseline/_ref`` run through its own trainer on the same synthetic scene written to disk.
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--gaussians", type=int, default=62_900_000)
+    ap.add_argument("--width", type=int, default=1600)
+    ap.add_argument("--height", type=int, default=1036)
+    ap.add_argument("--batch", type=int, default=2, help="views per step (MAX_BATCH_SIZE of the 8-GPU config)")
+    ap.add_argument("--gt-gaussians", type=int, default=6_000_000)
+    ap.add_argument("--transport", default="auto", choices=["auto", "peer", "nccl"])
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0])); smax.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def run_own(args):
+    import torch
+    import torch.distributed as dist
+
+    from retinags_b200.bench_session import BenchSession
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    sess = BenchSession(device=device, rank=rank, world=world, n_gaussians=args.gaussians, width=args.width,
+                        height=args.height, batch=args.batch, n_views=(args.steps + args.warmup) * args.batch,
+                        gt_gaussians=args.gt_gaussians, transport=args.transport, seed=args.seed)
+    # ---- device-timed region ------------------------------------------------------------------
+    for i in range(args.warmup):
+        sess.step(i)
+        sess.settle()
+    sess.sync()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    sess.reset_launch_count()
+    sess.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        sess.step(args.warmup + i)
+    ev1.record()
+    sess.barrier()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1)
+    launches = sess.launch_count()
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    overflow = sess.settle()
+    # ---- end-to-end region: public Trainer API, pinned-host inputs in, loss out, every step ------
+    e2e = None
+    if not args.no_e2e:
+        sess.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        h2d = d2h = 0
+        for i in range(args.steps):
+            loss, bi, bo = sess.step_e2e(args.warmup + i)
+            h2d, d2h = bi, bo
+        torch.cuda.synchronize()
+        sess.barrier()
+        wall = time.perf_counter() - t0
+        tw = torch.tensor([wall], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(tw, op=dist.ReduceOp.MAX)
+        wall = float(tw.item())
+        e2e = {"value": args.steps * args.batch / wall, "unit": "views/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "last_loss": loss}
+    if rank == 0:
+        value = args.steps * args.batch / (ms / 1e3)
+        out = {
+            "metric": "train views/s (62.9M GS, 1600x1036)", "value": value, "unit": "views/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+            "impl": "own",
+            "config": {"model": "3DGS SH-3, seeded 64-cluster mixture in a 20-unit box", "gaussians": args.gaussians,
+                       "global_batch": args.batch, "resolution": [args.width, args.height],
+                       "submodels": sess.n_models, "bvh_depth": sess.bvh_depth,
+                       "parallelism": f"spatial-mp{world}", "transport": sess.transport_name,
+                       "l2": "inputs larger than L2 (parameter blocks of >= 1.8 GB per GPU are streamed every step)",
+                       "visible_splats_per_view": sess.last_info.get("n_vis"),
+                       "instances_per_view": sess.last_info.get("n_inst"), "overflow_in_timed_region": overflow},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    from baseline import reference_arm
+    reference_arm.main(args)
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_own(a)

@@ -1,0 +1,198 @@
+"""Benchmark session: the flagship training step on a seeded synthetic scene.
+
+Builds, on every rank, the part of the scene that the rank hosts (cluster-mixture Gaussians cut by
+the kd/BVH partition into one sub-model per GPU), renders ground-truth images from an independent
+seeded scene into pinned host memory, and exposes ``step`` (device-timed loop) and ``step_e2e``
+(host-timed loop that also reads the loss back).  The work per step is exactly the trainer's
+``StepEngine.train_step``: ground-truth upload, render of every visible local sub-model, compositing,
+L1 + D-SSIM loss, backward, fused Adam on every sub-model.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .data import synthetic
+from .engine import StepEngine
+from .models.gaussians import GaussianStore
+from .ops import native
+from .ops.rasterize import RenderTask, Segment, make_camera
+from .parallel.compositing import LocalTransport, TorchDistTransport, band_rows
+from .parallel.partition import BvhTree, Grid3D, assign_models, load_histogram
+
+CHUNK = 4_000_000
+
+
+class ClusterScene:
+    """Seeded mixture of anisotropic 3D clusters, sampled in chunks so that no rank ever holds more than
+    one chunk besides its own sub-models."""
+
+    def __init__(self, seed: int, device, n_clusters: int = 64, box: float = 20.0):
+        self.seed, self.device, self.box = seed, device, box
+        g = torch.Generator(device=device)
+        g.manual_seed(seed + 101)
+        self.centers = (torch.rand(n_clusters, 3, device=device, generator=g) - 0.5) * box * 0.8
+        self.centers[:, 2] = self.centers[:, 2].abs() * 0.5
+        self.axes = 0.3 + 1.7 * torch.rand(n_clusters, 3, device=device, generator=g)
+        q, _ = torch.linalg.qr(torch.randn(n_clusters, 3, 3, device=device, generator=g))
+        self.rot = q
+
+    def means(self, n: int, chunk: int) -> torch.Tensor:
+        g = torch.Generator(device=self.device)
+        g.manual_seed(self.seed * 7919 + 13 * chunk + 1)
+        which = torch.randint(0, self.centers.shape[0], (n,), device=self.device, generator=g)
+        local = torch.randn(n, 3, device=self.device, generator=g) * self.axes[which]
+        pts = torch.einsum("nij,nj->ni", self.rot[which], local) + self.centers[which]
+        return pts.clamp_(-self.box / 2, self.box / 2)
+
+    def gaussians(self, n: int, chunk: int, sh_degree: int = 3) -> dict:
+        return synthetic.random_gaussians(n, self.means(n, chunk), self.seed * 104729 + chunk, self.device, sh_degree)
+
+
+def chunks_of(n: int):
+    k = 0
+    while n > 0:
+        m = min(n, CHUNK)
+        yield k, m
+        n -= m
+        k += 1
+
+
+class BenchSession:
+    def __init__(self, device, rank: int, world: int, n_gaussians: int, width: int, height: int, batch: int,
+                 n_views: int, gt_gaussians: int, transport: str = "auto", seed: int = 0, sh_degree: int = 3,
+                 grid=(2048, 2048, 1)):
+        self.device = torch.device(device)
+        self.rank, self.world, self.batch = rank, world, batch
+        self.sh_degree = sh_degree
+        self.bvh_depth = int(round(math.log2(world)))
+        assert 2 ** self.bvh_depth == world, "world size must be a power of two"
+        scene = ClusterScene(seed, self.device)
+        # ---- partition from the load histogram of all positions -------------------------------
+        half = scene.box / 2
+        g3 = Grid3D(np.array([-half] * 3), np.array([half] * 3), grid)
+        hist = torch.zeros(grid, dtype=torch.float32, device=self.device)
+        for k, m in chunks_of(n_gaussians):
+            hist += load_histogram(scene.means(m, k), g3)
+        g3.load = hist.double().cpu().numpy()
+        self.tree = BvhTree.build(g3, self.bvh_depth, (0, 1))
+        self.n_models = len(self.tree.leaves)
+        self.model2rank = assign_models(self.n_models, world)
+        lo, hi = self.tree.leaf_boxes_world(open_border=True)
+        local = [m for m in range(self.n_models) if self.model2rank[m] == rank]
+        counts = {m: 0 for m in local}
+        # ---- fill the local sub-models chunk by chunk -------------------------------------------
+        self.stores = {m: GaussianStore(max(4, int(n_gaussians / self.n_models * 1.15)), self.device, sh_degree,
+                                        lo[m], hi[m], m) for m in local}
+        for st in self.stores.values():
+            st.active_sh_degree = sh_degree
+        for k, mcount in chunks_of(n_gaussians):
+            g = scene.gaussians(mcount, k, sh_degree)
+            ids = self.tree.label(g["xyz"])
+            for m in local:
+                sel = (ids == m).nonzero(as_tuple=True)[0]
+                if sel.numel():
+                    self.stores[m].append_new({name: v[sel] for name, v in g.items()})
+            del g, ids
+        torch.cuda.empty_cache() if self.device.type == "cuda" else None
+        # ---- cameras, relation, ground truth -----------------------------------------------------
+        self.cams = synthetic.hemisphere_cameras(max(n_views, 1), 8.0, width, height, 50.0, seed)
+        self.relation = self.tree.relation(self.cams, 0.01, 1000.0)
+        self._render_ground_truth(seed, gt_gaussians, sh_degree)
+        # ---- engine ---------------------------------------------------------------------------
+        self.transport_name = "local"
+        tr = LocalTransport(self.device)
+        if world > 1:
+            want = transport
+            if want in ("auto", "peer"):
+                try:
+                    from .parallel.peer import PeerTransport
+                    tr = PeerTransport(self.device)
+                    self.transport_name = "peer (kernel stores into peer-mapped slots, flag barrier)"
+                except Exception as exc:  # pragma: no cover - depends on the box
+                    if want == "peer":
+                        raise
+                    if rank == 0:
+                        print(f"[bench] peer transport unavailable ({exc!r}); using torch.distributed send/recv",
+                              flush=True)
+                    tr = TorchDistTransport(self.device)
+                    self.transport_name = "nccl send/recv"
+            else:
+                tr = TorchDistTransport(self.device)
+                self.transport_name = "nccl send/recv"
+        self.engine = StepEngine(self.stores, self.model2rank, self.device, tr)
+        extent = 1.1 * 8.0
+        self.lrs = (1.6e-4 * extent, 2.5e-3, 2.5e-3 / 20.0, 5e-3, 1e-3, 5e-2)
+        self.last_info: dict = {}
+        self._launch_base = 0
+
+    # -- ground truth -----------------------------------------------------------------------------
+    def _render_ground_truth(self, seed: int, gt_gaussians: int, sh_degree: int):
+        """Targets come from an independent seeded scene; each view is rendered once and parked in pinned
+        host memory (only the rows this rank owns, plus the SSIM halo, are uploaded per step)."""
+        scene = ClusterScene(seed + 1, self.device)
+        parts = [scene.gaussians(m, k, sh_degree) for k, m in chunks_of(gt_gaussians)]
+        g = {name: torch.cat([p[name] for p in parts]) for name in parts[0]}
+        seg = Segment(g["xyz"], g["sh"], g["scale"], g["rot"], g["opacity"])
+        task = RenderTask(self.device)
+        pin = self.device.type == "cuda"
+        for cam in self.cams:
+            c = make_camera(cam, sh_degree)
+            out = task.forward(c, [seg], check=True)
+            img = out[..., :3].permute(2, 0, 1).contiguous().cpu()
+            cam.image = img.pin_memory() if pin else img
+        del task, seg, g, parts
+        from .ops import rasterize
+        rasterize._SCRATCH.clear()
+        if pin:
+            torch.cuda.empty_cache()
+
+    # -- steps ------------------------------------------------------------------------------------
+    def _batch(self, i: int):
+        idx = [(i * self.batch + j) % len(self.cams) for j in range(self.batch)]
+        return [self.cams[k] for k in idx], self.relation[idx]
+
+    def step(self, i: int):
+        cams, rel = self._batch(i)
+        return self.engine.train_step(cams, rel, self.sh_degree, self.lrs)
+
+    def step_e2e(self, i: int):
+        cams, rel = self._batch(i)
+        res = self.engine.train_step(cams, rel, self.sh_degree, self.lrs)
+        sums = torch.stack(res.sums).cpu()  # device -> host read of the step's loss sums
+        loss = 0.0
+        for p, s in zip(res.plans, sums):
+            npx = 3.0 * p.H * p.W
+            b = p.bands[self.rank]
+            # this rank's share of (1-lambda) L1 + lambda (1 - SSIM); shares of all ranks add up to the loss
+            loss += (0.8 * float(s[0]) + 0.2 * (3.0 * (b[1] - b[0]) * p.W - float(s[1]))) / npx
+        h2d = 0
+        for p in res.plans:
+            b = p.bands[self.rank]
+            if b[1] > b[0]:
+                h2d += 3 * (min(p.H, b[1] + 5) - max(0, b[0] - 5)) * p.W * 4
+        return loss, h2d, int(sums.numel() * 8)
+
+    def settle(self) -> bool:
+        """Synchronise and let every render task look at its counters (grows buffers after an overflow)."""
+        self.sync()
+        info = self.engine.poll()
+        self.last_info = info
+        return bool(info["overflow"])
+
+    def sync(self):
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+
+    def barrier(self):
+        if self.world > 1:
+            dist.barrier()
+
+    def reset_launch_count(self):
+        self._launch_base = native.launch_count()
+
+    def launch_count(self) -> int:
+        return native.launch_count() - self._launch_base

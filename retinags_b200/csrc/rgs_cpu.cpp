@@ -6,6 +6,7 @@
 // The reference has no CPU path at all (its rasteriser is CUDA-only:
 // rasterization_kernels/diff-gaussian-rasterization-half-gaussian/cuda_rasterizer_hgs/).
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <numeric>
 #include <vector>
@@ -16,7 +17,7 @@ extern "C" {
 
 int rgs_cpu_project_emit(const RgsCamera* cam, const RgsSegment* seg, int64_t id_base, RgsSplat* splats,
                          int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint64_t* keys, uint32_t* vals,
-                         int64_t cap_inst, int32_t* counters, void*) {
+                         int64_t cap_inst, int32_t* counters, RgsSplatGrad* splat_grads, void*) {
     int64_t n_vis = counters[RGS_CNT_VIS], n_inst = counters[RGS_CNT_INST];
     for (int64_t i = 0; i < seg->count; ++i) {
         RgsSplat sp; RgsRect rc; int radius; unsigned clamped;
@@ -32,6 +33,7 @@ int rgs_cpu_project_emit(const RgsCamera* cam, const RgsSegment* seg, int64_t id
         splats[slot] = sp;
         vis_ids[slot] = (int32_t)(id_base + i);
         aux[slot] = ((uint32_t)radius << 3) | clamped;
+        if (splat_grads) std::memset(&splat_grads[slot], 0, sizeof(RgsSplatGrad));
         uint32_t dbits; std::memcpy(&dbits, &sp.depth, 4);
         for (int y = rc.y0; y < rc.y1; ++y)
             for (int x = rc.x0; x < rc.x1; ++x) {
@@ -182,8 +184,8 @@ int rgs_cpu_scatter_radii(const int32_t* counters, const int32_t* vis_ids, const
 // Fused Adam over the grouped parameter block. The block holds five groups of `cap` rows each:
 // xyz(3) sh(48) scale(3) rot(4) opacity(1); only the first `count` rows of each group are live.
 // `skip` (optional int32) != 0 turns the whole update into a no-op (overflow-guarded commit).
-int rgs_cpu_adam(float* p, const float* g, float* m, float* v, int64_t count, int64_t cap, const double* lrs,
-                 double beta1, double beta2, double eps, int64_t step, const int32_t* skip, void*) {
+int rgs_cpu_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t cap, const double* lrs,
+                 double beta1, double beta2, double eps, int64_t step, int64_t zero_grad, const int32_t* skip, void*) {
     if (skip && skip[RGS_CNT_OVERFLOW]) return 0;
     const int widths[5] = {3, 48, 3, 4, 1};
     float bc1 = (float)(1.0 - std::pow(beta1, (double)step));
@@ -204,6 +206,7 @@ int rgs_cpu_adam(float* p, const float* g, float* m, float* v, int64_t count, in
             }
             int64_t k = off + e;
             rgs_adam_elem(p[k], g[k], m[k], v[k], lr, (float)beta1, (float)beta2, (float)eps, bc1, bc2s);
+            if (zero_grad) g[k] = 0.f;
         }
         off += cap * w;
     }

@@ -27,7 +27,8 @@
 __global__ void __launch_bounds__(256) rgs_project_emit_kernel(
     const __grid_constant__ RgsCamera cam, const RgsSegment seg, const int64_t id_base, RgsSplat* __restrict__ splats,
     int32_t* __restrict__ vis_ids, uint32_t* __restrict__ aux, const uint32_t cap_vis, uint64_t* __restrict__ keys,
-    uint32_t* __restrict__ vals, const uint32_t cap_inst, uint32_t* __restrict__ counters) {
+    uint32_t* __restrict__ vals, const uint32_t cap_inst, uint32_t* __restrict__ counters,
+    RgsSplatGrad* __restrict__ splat_grads) {
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
     bool ok = false;
     RgsSplat sp;
@@ -80,6 +81,10 @@ __global__ void __launch_bounds__(256) rgs_project_emit_kernel(
     dst[2] = make_float4(sp.b, sp.w, sp.depth, 0.f);
     vis_ids[slot] = (int32_t)(id_base + i);
     aux[slot] = ((uint32_t)radius << 3) | clamped;
+    if (splat_grads) {  // the backward accumulates into this record: clear it here, no separate memset
+        float4* gz = reinterpret_cast<float4*>(splat_grads + slot);
+        gz[0] = make_float4(0.f, 0.f, 0.f, 0.f); gz[1] = gz[0]; gz[2] = gz[0];
+    }
     const uint64_t dbits = (uint64_t)__float_as_uint(sp.depth);
     for (int y = rc.y0; y < rc.y1; ++y)
         for (int x = rc.x0; x < rc.x1; ++x) {
@@ -338,13 +343,13 @@ extern "C" {
 
 int rgs_cuda_project_emit(const RgsCamera* cam, const RgsSegment* seg, int64_t id_base, RgsSplat* splats,
                           int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint64_t* keys, uint32_t* vals,
-                          int64_t cap_inst, int32_t* counters, void* stream) {
+                          int64_t cap_inst, int32_t* counters, RgsSplatGrad* splat_grads, void* stream) {
     if (seg->count <= 0) return 0;
     if (cap_inst > 0xfffffff0ll || cap_vis > 0x7ffffff0ll) return 10;
     const unsigned blocks = (unsigned)((seg->count + 255) / 256);
     rgs_project_emit_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
         *cam, *seg, id_base, splats, vis_ids, aux, (uint32_t)cap_vis, keys, vals, (uint32_t)cap_inst,
-        reinterpret_cast<uint32_t*>(counters));
+        reinterpret_cast<uint32_t*>(counters), splat_grads);
     return (int)cudaGetLastError();
 }
 

@@ -1,0 +1,190 @@
+"""One training / rendering step over the sub-models hosted by this rank.
+
+``StepEngine`` is the per-rank executor underneath the trainer: given the cameras of a batch and the
+camera->sub-model relation it renders every visible local sub-model, hands the partial images to
+the compositing transport, composites and evaluates the loss on the row bands this rank owns,
+routes ``dL/d(partial)`` back, runs the rasteriser backward and applies one fused Adam update per
+sub-model.  It corresponds to steps 1-10 of the reference's iteration
+(``parallel_utils/basic_parallel_trainer/trainer4tree_partition.py:606-669``), with the six
+blocking exchange phases reduced to two and no host synchronisation inside a step.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from .data.cameras import Camera
+from .models.gaussians import GaussianStore
+from .ops.loss import CompositeLoss
+from .ops.rasterize import RenderTask, Segment, make_camera
+from .parallel.compositing import LocalTransport, ViewPlan, band_rows, extended
+
+
+@dataclass
+class StepResult:
+    sums: list            # per view: device tensor (3,) float64 of loss sums over this rank's band
+    plans: list
+    overflow: bool = False
+    info: dict = field(default_factory=dict)
+
+
+class StepEngine:
+    def __init__(self, stores: dict[int, GaussianStore], model2rank: list[int], device, transport=None,
+                 lambda_dssim: float = 0.2, background=(0.0, 0.0, 0.0), tight_rect: bool = True,
+                 borrow=None):
+        self.stores = stores
+        self.model2rank = list(model2rank)
+        self.device = torch.device(device)
+        self.transport = transport if transport is not None else LocalTransport(device)
+        self.rank, self.world = self.transport.rank, self.transport.world
+        self.lambda_dssim = lambda_dssim
+        self.background = tuple(background)
+        self.tight_rect = tight_rect
+        self.borrow = borrow  # optional BorderExchange (parallel/border.py)
+        self._tasks: dict = {}
+        self._grads: dict = {}
+        self._closs: dict = {}
+        self._gt: dict = {}
+
+    # -- pools ----------------------------------------------------------------------------------
+    def _task(self, view: int, mid: int) -> RenderTask:
+        key = (view, mid)
+        if key not in self._tasks:
+            self._tasks[key] = RenderTask(self.device)
+        return self._tasks[key]
+
+    def _grad(self, view: int, mid: int, H: int, W: int) -> torch.Tensor:
+        key = (view, mid)
+        g = self._grads.get(key)
+        if g is None or g.shape[:2] != (H, W):
+            g = torch.zeros(H, W, 4, dtype=torch.float32, device=self.device)
+            self._grads[key] = g
+        return g
+
+    def _loss(self, view: int, H: int, W: int) -> CompositeLoss:
+        cl = self._closs.get(view)
+        if cl is None or (cl.H, cl.W) != (H, W):
+            cl = CompositeLoss(self.device, H, W)
+            self._closs[view] = cl
+        return cl
+
+    def _gt_rows(self, view: int, cam: Camera, rows: tuple[int, int]) -> torch.Tensor:
+        """Device (3,H,W) buffer with the ground truth uploaded on ``rows`` only (pinned host -> device)."""
+        H, W = cam.height, cam.width
+        buf = self._gt.get(view)
+        if buf is None or buf.shape != (3, H, W):
+            buf = torch.zeros(3, H, W, dtype=torch.float32, device=self.device)
+            self._gt[view] = buf
+        if cam.image is not None and rows[1] > rows[0]:
+            src = cam.image
+            if src.device == buf.device:
+                buf[:, rows[0]:rows[1]].copy_(src[:, rows[0]:rows[1]])
+            else:
+                buf[:, rows[0]:rows[1]].copy_(src[:, rows[0]:rows[1]], non_blocking=True)
+        return buf
+
+    # -- segments -------------------------------------------------------------------------------
+    def _segments(self, mid: int, with_grads: bool) -> list[Segment]:
+        segs = [self.stores[mid].segment(with_grads=with_grads)]
+        if self.borrow is not None:
+            b = self.borrow.segment(mid, with_grads=with_grads)
+            if b is not None and b.count:
+                segs.append(b)
+        return segs
+
+    def plan(self, cams: list[Camera], relations) -> list[ViewPlan]:
+        """``relations[i][m]`` = front-to-back position of sub-model m for camera i, or -1 (invisible)."""
+        plans = []
+        for i, cam in enumerate(cams):
+            rel = [int(v) for v in relations[i]]
+            vis = sorted((r, m) for m, r in enumerate(rel) if r >= 0)
+            models = [m for _, m in vis]
+            plans.append(ViewPlan(i, cam.height, cam.width, models, [self.model2rank[m] for m in models],
+                                  band_rows(cam.height, self.world)))
+        return plans
+
+    # -- forward --------------------------------------------------------------------------------
+    def render_partials(self, cams: list[Camera], plans: list[ViewPlan], sh_degree: int, want_depth: bool = False,
+                        check: bool = False) -> dict:
+        local_out: dict[int, dict[int, torch.Tensor]] = {}
+        for p, cam in zip(plans, cams):
+            local_out[p.view] = {}
+            for m, r in zip(p.models, p.ranks):
+                if r != self.rank:
+                    continue
+                st = self.stores[m]
+                c = make_camera(cam, sh_degree, st.box_lo, st.box_hi, raw_params=True, tight_rect=self.tight_rect)
+                task = self._task(p.view, m)
+                dst = self.transport.render_target(p, m) if hasattr(self.transport, "render_target") else None
+                local_out[p.view][m] = task.forward(c, self._segments(m, False), want_depth=want_depth, out=dst,
+                                                    check=check)
+        return local_out
+
+    def render(self, cams: list[Camera], relations, sh_degree: int, background=None):
+        """Eval-time render: returns per view the composited (3,H,W) image rows this rank owns
+        (``image``, ``rows``) -- with world size 1 that is the whole image."""
+        bg = self.background if background is None else background
+        plans = self.plan(cams, relations)
+        if self.borrow is not None:
+            self.borrow.refresh(self.stores, need_grads=False)
+        local_out = self.render_partials(cams, plans, sh_degree, check=True)
+        slots = self.transport.exchange_partials(plans, local_out)
+        out = []
+        for p in plans:
+            cl = self._loss(p.view, p.H, p.W)
+            b = p.bands[self.rank]
+            cl.composite(slots[p.view], bg, b[0], b[1])
+            out.append(dict(image=cl.image, trans=cl.trans, rows=b, partials=local_out[p.view], plan=p))
+        return out
+
+    # -- training step --------------------------------------------------------------------------
+    def train_step(self, cams: list[Camera], relations, sh_degree: int, lrs, optimizer_step: bool = True,
+                   background=None) -> StepResult:
+        bg = self.background if background is None else background
+        plans = self.plan(cams, relations)
+        if self.borrow is not None:
+            self.borrow.refresh(self.stores, need_grads=True)
+        local_out = self.render_partials(cams, plans, sh_degree)
+        slots = self.transport.exchange_partials(plans, local_out)
+        local_grad = {p.view: {m: self._grad(p.view, m, p.H, p.W) for m, r in zip(p.models, p.ranks) if r == self.rank}
+                      for p in plans}
+        gslots = self.transport.grad_slots(plans, local_grad)
+        sums = []
+        for p, cam in zip(plans, cams):
+            cl = self._loss(p.view, p.H, p.W)
+            b = p.bands[self.rank]
+            if b[1] <= b[0]:
+                sums.append(torch.zeros(3, dtype=torch.float64, device=self.device))
+                continue
+            e = (max(0, b[0] - 10), min(p.H, b[1] + 10))
+            gt = self._gt_rows(p.view, cam, (max(0, b[0] - 5), min(p.H, b[1] + 5)))
+            cl.composite(slots[p.view], bg, e[0], e[1])
+            sums.append(cl.loss(gt, self.lambda_dssim, b[0], b[1]).clone())
+            cl.backward(slots[p.view], gslots[p.view], bg, b[0], b[1])
+        self.transport.return_grads(plans, gslots, local_grad)
+        for p in plans:
+            for m, r in zip(p.models, p.ranks):
+                if r == self.rank:
+                    self._task(p.view, m).backward(local_grad[p.view][m], self._segments(m, True))
+        if self.borrow is not None:
+            self.borrow.return_grads(self.stores)
+        if optimizer_step:
+            self.optimizer_step(lrs, plans)
+        return StepResult(sums=sums, plans=plans)
+
+    def optimizer_step(self, lrs, plans=None):
+        for m, st in self.stores.items():
+            st.adam_step(lrs)
+
+    def poll(self) -> dict:
+        """After a host synchronisation: read the counters of all tasks (grows buffers when needed)."""
+        info = dict(overflow=False, n_vis=0, n_inst=0)
+        for task in self._tasks.values():
+            if task.cam is None:
+                continue
+            c = task.poll()
+            info["overflow"] |= c["overflow"]
+            info["n_vis"] += c["n_vis"]
+            info["n_inst"] += c["n_inst"]
+        return info

@@ -1,0 +1,84 @@
+"""Compositing of partial images and the fused L1 + D-SSIM loss, through the native kernels.
+
+``CompositeLoss`` owns the per-view buffers (composited image, total transmittance, SSIM derivative
+maps, image gradient, loss sums) and exposes three steps, each restricted to a band of image rows
+so that several ranks can each own a band of the same view:
+
+1. ``composite``   ordered front-to-back "over" of K partial (H,W,4) images
+2. ``loss``        L1 and SSIM statistics + derivative maps, then d(loss)/d(image)
+3. ``backward``    d(loss)/d(partial_k) for every partial (dC_k = T_<k g, dT_k = T_<k S_k.g)
+
+The reference performs 1 with ATen ops (``result_aggregator.py:244-259``), 2 with cuDNN
+convolutions (``utils/loss_utils.py:17-63``) and leaves 3 and the backward of 2 to autograd.
+The loss per image is ``(1-lambda) L1 + lambda (1 - SSIM)``; losses of the images of a batch are
+summed (``trainer4tree_partition.py:450-454``).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import native
+
+HALO = 5  # SSIM window radius
+
+
+class CompositeLoss:
+    def __init__(self, device, H: int, W: int):
+        self.device = torch.device(device)
+        self.H, self.W = H, W
+        dev = self.device
+        self.image = torch.zeros(3, H, W, dtype=torch.float32, device=dev)
+        self.trans = torch.ones(H, W, dtype=torch.float32, device=dev)
+        self.dmaps = torch.zeros(9, H, W, dtype=torch.float32, device=dev)
+        self.g_image = torch.zeros(3, H, W, dtype=torch.float32, device=dev)
+        self.sums = torch.zeros(3, dtype=torch.float64, device=dev)
+
+    @staticmethod
+    def _bg(bg):
+        return (ctypes.c_float * 3)(*[float(v) for v in bg])
+
+    def composite(self, partials: list[torch.Tensor], bg, row0: int = 0, row1: int | None = None):
+        """Composite rows [row0,row1) of the ordered partials into ``self.image`` / ``self.trans``."""
+        row1 = self.H if row1 is None else row1
+        for p in partials:
+            assert p.is_contiguous() and p.shape[-1] == 4
+        ptrs = native.pointer_array(partials)
+        native.call("composite_fwd", self.device, ptrs, len(partials), self._bg(bg), self.H, self.W, row0, row1,
+                    self.image, self.trans)
+        return self.image, self.trans
+
+    def loss(self, gt: torch.Tensor, lambda_dssim: float = 0.2, row0: int = 0, row1: int | None = None,
+             weight: float = 1.0):
+        """Loss statistics and d(loss)/d(image) for rows [row0,row1) of the composited image.
+
+        The image must be composited on rows [row0-10, row1+10) (clipped to the image).  Returns the
+        device tensor of accumulated sums (sum|d|, sum ssim, sum d^2) over the band; the loss value
+        is ``loss_from_sums``.  ``weight`` scales the gradient (1 = summed per-image losses).
+        """
+        H, W = self.H, self.W
+        row1 = H if row1 is None else row1
+        assert gt.is_contiguous() and gt.shape == (3, H, W)
+        c0, c1 = max(0, row0 - HALO), min(H, row1 + HALO)
+        self.sums.zero_()
+        native.call("ssim_fwd", self.device, self.image, gt, H, W, c0, c1, row0, row1, self.dmaps, self.sums)
+        npx = 3.0 * H * W
+        native.call("ssim_bwd", self.device, self.image, gt, self.dmaps, H, W, row0, row1, c0, c1,
+                    weight * (1.0 - lambda_dssim) / npx, weight * lambda_dssim / npx, self.g_image)
+        return self.sums
+
+    def loss_from_sums(self, sums, lambda_dssim: float = 0.2) -> dict:
+        s = sums.tolist() if isinstance(sums, torch.Tensor) else list(sums)
+        npx = 3.0 * self.H * self.W
+        l1, ssim, mse = s[0] / npx, s[1] / npx, s[2] / npx
+        return dict(l1=l1, ssim=ssim, mse=mse, loss=(1.0 - lambda_dssim) * l1 + lambda_dssim * (1.0 - ssim))
+
+    def backward(self, partials: list[torch.Tensor], grads: list[torch.Tensor], bg, row0: int = 0,
+                 row1: int | None = None):
+        """Write d(loss)/d(partial_k) on rows [row0,row1) into ``grads[k]`` ((H,W,4): dC, dT)."""
+        row1 = self.H if row1 is None else row1
+        pp = native.pointer_array(partials)
+        gp = native.pointer_array(grads)
+        native.call("composite_bwd", self.device, pp, gp, len(partials), self._bg(bg), self.H, self.W, row0, row1,
+                    self.g_image)

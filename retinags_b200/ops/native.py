@@ -24,13 +24,13 @@ _LIBS: dict[str, ctypes.CDLL] = {}
 
 # signature alphabet: p = pointer, i = int64, f = double
 SIGNATURES = {
-    "project_emit": "ppipppippipp",
+    "project_emit": "ppipppippippp",
     "sort_ranges": "ppppipippp",
     "blend_fwd": "ppppppppp",
     "blend_bwd": "pppppppppp",
     "geom_bwd": "ppipppppip",
     "scatter_radii": "pppiipp",
-    "adam": "ppppiipfffipp",
+    "adam": "ppppiipfffiipp",
     "composite_fwd": "pipiiiippp",
     "composite_bwd": "ppipiiiipp",
     "ssim_fwd": "ppiiiiiippp",
@@ -132,9 +132,30 @@ def stream_ptr(device: torch.device):
     return torch.cuda.current_stream(device).cuda_stream
 
 
+# kernels launched by one call of an entry point (the radix sort's count depends on the tile count)
+_KERNELS = {"project_emit": 1, "blend_fwd": 1, "blend_bwd": 1, "geom_bwd": 1, "scatter_radii": 1, "adam": 1,
+            "composite_fwd": 1, "composite_bwd": 1, "ssim_fwd": 1, "ssim_bwd": 1}
+_LAUNCHES = [0]
+
+
+def launch_count() -> int:
+    """Number of kernels of the CUDA library launched so far by this process."""
+    return _LAUNCHES[0]
+
+
+def _count_launches(name: str, args) -> int:
+    if name == "sort_ranges":
+        tiles = max(int(args[6]), 1)
+        bits = 32 + max(tiles - 1, 0).bit_length()
+        return 3 * ((bits + 7) // 8) + 1
+    return _KERNELS.get(name, 1)
+
+
 def call(name: str, device: torch.device, *args, sig: str | None = None) -> None:
     """Invoke ``rgs_<cpu|cuda>_<name>(*args, stream)`` and raise on a non-zero status."""
     kind = "cuda" if device.type == "cuda" else "cpu"
+    if kind == "cuda":
+        _LAUNCHES[0] += _count_launches(name, args)
     fn = _fn(kind, name, sig)
     conv = []
     for a in args:

@@ -195,7 +195,8 @@ class RenderTask:
             for seg in segments:
                 if seg.count:
                     native.call("project_emit", self.device, cam, seg.struct(False), base, self.splats, self.vis_ids,
-                                self.aux, self.cap_vis, self.keys, self.vals, self.cap_inst, self.counters)
+                                self.aux, self.cap_vis, self.keys, self.vals, self.cap_inst, self.counters,
+                                self.splat_grads)
                 base += seg.count
             sc = sort_scratch(self.device)
             sc.ensure(self.cap_inst)
@@ -246,7 +247,6 @@ class RenderTask:
         """Accumulate parameter gradients of the last forward. ``grad_out`` is (H,W,4): dL/dC, dL/dT."""
         cam = self.cam
         assert grad_out.is_contiguous() and grad_out.shape == (cam.H, cam.W, 4)
-        self.splat_grads.zero_()
         native.call("blend_bwd", self.device, cam, self.ranges, self.vals, self.splats, self.last_out, self.n_contrib,
                     grad_out, self.splat_grads, self.counters)
         structs = (RgsSegment * len(segments))(*[s.struct(True) for s in segments])

@@ -1,0 +1,139 @@
+"""sm_100a kernels against the native CPU backend / PyTorch references (needs a B200)."""
+import pytest
+import torch
+
+from helpers import native_render, small_scene
+from retinags_b200.data import synthetic
+from retinags_b200.models.gaussians import GaussianStore
+from retinags_b200.ops import native, rasterize
+from retinags_b200.ops.loss import CompositeLoss
+
+pytestmark = pytest.mark.gpu
+
+
+def _scene(n=40000, w=320, h=208, deg=3, seed=4):
+    g = synthetic.uniform_gaussians(n, seed, sh_degree=deg, log_scale_mean=-3.6)
+    cams = synthetic.ring_cameras(3, 3.0, w, h)
+    return g, cams
+
+
+def test_cuda_library_is_loaded():
+    lib = native.lib("cuda")
+    assert hasattr(lib, "rgs_cuda_blend_fwd")
+
+
+@pytest.mark.parametrize("deg,box", [(3, (None, None)), (1, ([-0.2, -1e9, -1e9], [1e9, 0.3, 1e9]))])
+def test_raster_forward_matches_cpu(deg, box):
+    g, cams = _scene(deg=deg)
+    for cam in cams[:2]:
+        ref, tr, _, _ = native_render(g, cam, deg, box=box, device="cpu", want_depth=True)
+        out, tg, _, _ = native_render(g, cam, deg, box=box, device="cuda", want_depth=True)
+        assert tg.n_vis == tr.n_vis and tg.n_inst == tr.n_inst
+        torch.testing.assert_close(out.cpu(), ref, atol=3e-5, rtol=1e-4)
+        torch.testing.assert_close(tg.depth.cpu(), tr.depth, atol=2e-4, rtol=1e-4)
+        assert torch.equal(tg.n_contrib.cpu(), tr.n_contrib) or \
+            (tg.n_contrib.cpu() != tr.n_contrib).float().mean() < 1e-3
+
+
+def test_raster_small_capacity_regrows():
+    g, cams = _scene(n=20000)
+    seg = rasterize.Segment(*(g[k].cuda().contiguous() for k in ("xyz", "sh", "scale", "rot", "opacity")))
+    task = rasterize.RenderTask("cuda", inst_per_gaussian=0.01, min_inst=256)
+    c = rasterize.make_camera(cams[0], 3)
+    out = task.forward(c, [seg], check=True)
+    ref, _, _, _ = native_render(g, cams[0], 3, device="cpu")
+    torch.testing.assert_close(out.cpu(), ref, atol=3e-5, rtol=1e-4)
+
+
+def test_raster_backward_matches_cpu():
+    deg = 3
+    g, cams = _scene(n=20000, w=160, h=112)
+    cam = cams[1]
+    gen = torch.Generator().manual_seed(0)
+    grad = torch.randn(cam.height, cam.width, 4, generator=gen)
+    res = {}
+    for dev in ("cpu", "cuda"):
+        out, task, seg, c = native_render(g, cam, deg, device=dev)
+        n = seg.count
+        for name, w in (("g_xyz", 3), ("g_sh", 48), ("g_scale", 3), ("g_rot", 4), ("g_opacity", 1), ("g_mean2d", 2)):
+            setattr(seg, name, torch.zeros(n, w, device=dev))
+        seg.stat_grad = torch.zeros(n, device=dev)
+        seg.stat_denom = torch.zeros(n, device=dev)
+        seg.stat_maxrad = torch.zeros(n, device=dev)
+        task.backward(grad.to(dev).contiguous(), [seg])
+        res[dev] = seg
+    for name in ("g_xyz", "g_sh", "g_scale", "g_rot", "g_opacity", "g_mean2d", "stat_grad", "stat_denom", "stat_maxrad"):
+        a, b = getattr(res["cuda"], name).cpu(), getattr(res["cpu"], name)
+        scale = b.abs().max().item() + 1e-12
+        assert (a - b).abs().max().item() / scale < 5e-3, name
+
+
+def test_radix_sort_matches_torch():
+    dev = torch.device("cuda")
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    for n, tiles in ((1, 7), (4097, 1000), (1_000_003, 6500), (3_000_000, 70000)):
+        tile = torch.randint(0, tiles, (n,), device=dev, generator=gen, dtype=torch.int64)
+        depth = torch.rand(n, device=dev, generator=gen) * 10 + 0.2
+        keys = (tile << 32) | depth.view(torch.int32).to(torch.int64)
+        vals = torch.arange(n, device=dev, dtype=torch.int32)
+        cap = n + 123
+        kbuf = torch.zeros(cap, dtype=torch.int64, device=dev); kbuf[:n] = keys
+        vbuf = torch.zeros(cap, dtype=torch.int32, device=dev); vbuf[:n] = vals
+        counters = torch.zeros(native.CNT_WORDS, dtype=torch.int32, device=dev)
+        counters[native.CNT_INST] = n
+        sc = rasterize.sort_scratch(dev)
+        sc.ensure(cap)
+        ranges = torch.zeros(tiles, 2, dtype=torch.int32, device=dev)
+        native.call("sort_ranges", dev, kbuf, vbuf, sc.keys_tmp, sc.vals_tmp, cap, counters, tiles, ranges, sc.words)
+        order = torch.sort(keys, stable=True).indices.to(torch.int32)
+        assert torch.equal(vbuf[:n], order)
+        sorted_tiles = tile[order.long()]
+        counts = torch.bincount(sorted_tiles, minlength=tiles)
+        ends = torch.cumsum(counts, 0)
+        starts = ends - counts
+        nz = counts > 0
+        assert torch.equal(ranges[nz, 0].long(), starts[nz]) and torch.equal(ranges[nz, 1].long(), ends[nz])
+        assert int(ranges[~nz].abs().sum()) == 0
+
+
+def test_loss_kernels_match_cpu():
+    H, W, K = 200, 333, 3
+    gen = torch.Generator().manual_seed(0)
+    parts = []
+    for _ in range(K):
+        T = torch.rand(H, W, 1, generator=gen) * 0.9 + 0.05
+        parts.append(torch.cat([torch.rand(H, W, 3, generator=gen) * (1 - T), T], -1).contiguous())
+    gt = torch.rand(3, H, W, generator=gen)
+    bg = (0.1, 0.0, 0.3)
+    res = {}
+    for dev in ("cpu", "cuda"):
+        cl = CompositeLoss(dev, H, W)
+        p = [x.to(dev) for x in parts]
+        cl.composite(p, bg)
+        sums = cl.loss(gt.to(dev), 0.2).cpu()
+        grads = [torch.zeros_like(x) for x in p]
+        cl.backward(p, grads, bg)
+        res[dev] = (cl.image.cpu(), sums, cl.g_image.cpu(), [x.cpu() for x in grads])
+    torch.testing.assert_close(res["cuda"][0], res["cpu"][0], atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(res["cuda"][1], res["cpu"][1], atol=1e-2, rtol=1e-5)
+    torch.testing.assert_close(res["cuda"][2], res["cpu"][2], atol=1e-9, rtol=2e-3)
+    for a, b in zip(res["cuda"][3], res["cpu"][3]):
+        torch.testing.assert_close(a, b, atol=1e-9, rtol=2e-3)
+
+
+def test_adam_matches_cpu():
+    g = synthetic.uniform_gaussians(1001, 1, sh_degree=3)
+    lrs = (1.6e-4, 2.5e-3, 1.25e-4, 5e-3, 1e-3, 5e-2)
+    stores = {}
+    for dev in ("cpu", "cuda"):
+        st = GaussianStore(1001, dev)
+        st.set_params({k: v.to(dev) for k, v in g.items()})
+        gen = torch.Generator().manual_seed(3)
+        for _ in range(3):
+            st.grads.copy_((torch.randn(st.grads.shape, generator=gen) * 1e-3).to(dev))
+            st.adam_step(lrs)
+        stores[dev] = st
+    torch.testing.assert_close(stores["cuda"].records().cpu(), stores["cpu"].records(), atol=2e-6, rtol=1e-5)
+    torch.testing.assert_close(stores["cuda"].records("exp_avg_sq").cpu(), stores["cpu"].records("exp_avg_sq"),
+                               atol=1e-12, rtol=1e-5)
+    assert float(stores["cuda"].grads.abs().sum()) == 0.0

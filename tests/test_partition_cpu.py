@@ -1,0 +1,117 @@
+"""kd/BVH partition, relation and balancer."""
+import numpy as np
+import torch
+
+from retinags_b200.data import synthetic
+from retinags_b200.parallel.balancer import WorkloadBalancer
+from retinags_b200.parallel.partition import BvhTree, Grid3D, assign_models, frustum_overlaps_boxes, load_histogram
+from retinags_b200.utils.general import is_interval_in_batch, is_point_in_batch, expon_lr
+
+
+def _tree(depth=3, n=20000, seed=0, grid=(64, 64, 1)):
+    pts = synthetic.cluster_means(n, seed).numpy()
+    g = Grid3D.from_points(pts, grid)
+    g.accumulate(pts)
+    return BvhTree.build(g, depth, (0, 1)), pts
+
+
+def test_tree_balance_and_cover():
+    tree, pts = _tree()
+    assert len(tree.leaves) == 8
+    assert sum(l.size for l in tree.leaves) == tree.nodes[""].size
+    ids = tree.label(torch.as_tensor(pts, dtype=torch.float32))
+    counts = torch.bincount(ids, minlength=8).float()
+    assert counts.min() > 0.5 * counts.mean() and counts.max() < 1.6 * counts.mean()
+    lo, hi = tree.leaf_boxes_world(open_border=True)
+    p = torch.as_tensor(pts, dtype=torch.float32)
+    for m in range(8):
+        inside = ((p > torch.as_tensor(lo[m], dtype=torch.float32)) & (p <= torch.as_tensor(hi[m], dtype=torch.float32))).all(1)
+        assert torch.equal(inside, ids == m)
+
+
+def test_tree_pickle_roundtrip(tmp_path):
+    tree, _ = _tree(depth=2)
+    f = tmp_path / "tree_0.txt"
+    tree.save(str(f))
+    import pickle
+    raw = pickle.load(open(f, "rb"))
+    assert "grid_info" in raw and "" in raw and "01" in raw and len(raw[""]) == 3
+    t2 = BvhTree.load(str(f))
+    assert [l.path for l in t2.leaves] == [l.path for l in tree.leaves]
+    np.testing.assert_array_equal(t2.leaf_boxes_grid(), tree.leaf_boxes_grid())
+    assert t2.nodes[""].split_position == tree.nodes[""].split_position
+
+
+def test_rebuild_avoids_old_split():
+    tree, pts = _tree(depth=1)
+    t2 = BvhTree.build(tree.grid, 1, (0, 1), previous=tree, rng=np.random.default_rng(1))
+    assert t2.nodes[""].split_position != tree.nodes[""].split_position
+
+
+def test_relation_order_and_visibility():
+    tree, pts = _tree(depth=2, grid=(32, 32, 1))
+    cams = synthetic.hemisphere_cameras(12, 8.0, 160, 104)
+    rel = tree.relation(cams, 0.01, 1000.0)
+    lo, hi = tree.leaf_boxes_world()
+    centers = 0.5 * (lo + hi)
+    for i, cam in enumerate(cams):
+        vis = rel[i] >= 0
+        assert vis.any()
+        # brute force: sample points in each box, check if any projects inside the frustum
+        c = np.asarray(cam.camera_center)
+        # order: the leaf containing the camera column (x,y) must come first among visible ones when inside
+        order = tree.order_for(c)
+        assert sorted(order) == list(range(4))
+        # front-to-back consistency: for each internal node the near child precedes the far child
+        root = tree.nodes[""]
+        near_is_right = c[root.split_dim] > tree.split_world(root)
+        right_ids = [m for m, l in enumerate(tree.leaves) if l.path[0] == "1"]
+        left_ids = [m for m, l in enumerate(tree.leaves) if l.path[0] == "0"]
+        if near_is_right:
+            assert max(order[m] for m in right_ids) < min(order[m] for m in left_ids)
+        else:
+            assert max(order[m] for m in left_ids) < min(order[m] for m in right_ids)
+
+
+def test_frustum_box_test_against_sampling():
+    cams = synthetic.ring_cameras(6, 4.0, 96, 64)
+    rng = np.random.default_rng(0)
+    lo = rng.uniform(-6, 4, size=(200, 3))
+    hi = lo + rng.uniform(0.2, 3, size=(200, 3))
+    for cam in cams[:3]:
+        got = frustum_overlaps_boxes(cam, lo, hi, 0.1, 5.0)
+        w2c_t = np.asarray(cam.world_view_transform, dtype=np.float64)
+        for m in range(200):
+            pts = rng.uniform(lo[m], hi[m], size=(4000, 3))
+            v = np.concatenate([pts, np.ones((4000, 1))], 1) @ w2c_t
+            inside = (v[:, 2] > 0.1) & (v[:, 2] < 5.0) & (np.abs(v[:, 0]) < cam.tan_fovx * v[:, 2]) & \
+                (np.abs(v[:, 1]) < cam.tan_fovy * v[:, 2])
+            if inside.any():
+                assert got[m]  # a sampled hit implies overlap (the exact test may also see thin overlaps)
+
+
+def test_histogram_matches_numpy():
+    tree, pts = _tree(depth=1, grid=(16, 8, 1))
+    h = load_histogram(torch.as_tensor(pts, dtype=torch.float32), tree.grid)
+    np.testing.assert_allclose(h.numpy(), tree.grid.load, atol=0)
+
+
+def test_balancer_limits():
+    rel = np.array([[0, 1, -1, -1], [0, 1, 2, 3], [-1, -1, 0, 1], [0, -1, -1, 1], [1, 0, 2, 3]])
+    b = WorkloadBalancer(2, assign_models(4, 2))
+    groups = b.groups(rel, [0, 1, 2, 3, 4], max_task=3, max_batch=2)
+    assert sum(len(g) for g in groups) == 5 and [i for g in groups for i in g] == [0, 1, 2, 3, 4]
+    for g in groups:
+        assert len(g) <= 2
+        load = sum(b.load_per_rank(rel[i]) for i in g)
+        assert len(g) == 1 or (load <= 3).all()
+
+
+def test_interval_helpers():
+    assert not is_interval_in_batch(0, 4, 100)
+    assert is_interval_in_batch(100, 1, 100) and not is_interval_in_batch(101, 1, 100)
+    assert is_interval_in_batch(98, 4, 100) and not is_interval_in_batch(101, 4, 100)
+    assert is_interval_in_batch(100, 4, 100)
+    assert is_point_in_batch(10, 4, 13) and not is_point_in_batch(10, 4, 14)
+    assert abs(expon_lr(0, 1.6e-4, 1.6e-6, max_steps=30000) - 1.6e-4) < 1e-12
+    assert abs(expon_lr(30000, 1.6e-4, 1.6e-6, max_steps=30000) - 1.6e-6) < 1e-12
