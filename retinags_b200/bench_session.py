@@ -61,16 +61,36 @@ def chunks_of(n: int):
         k += 1
 
 
+class UniformScene:
+    """Gaussians uniform in [-1,1]^3 with the plumbing-test statistics (log-scale N(-4,.5), SH degree 1)."""
+
+    box = 2.0
+
+    def __init__(self, seed: int, device):
+        self.seed, self.device = seed, device
+
+    def means(self, n: int, chunk: int) -> torch.Tensor:
+        g = torch.Generator(device=self.device)
+        g.manual_seed(self.seed * 7919 + 13 * chunk + 1)
+        return torch.rand(n, 3, device=self.device, generator=g) * 2 - 1
+
+    def gaussians(self, n: int, chunk: int, sh_degree: int = 1) -> dict:
+        return synthetic.random_gaussians(n, self.means(n, chunk), self.seed * 104729 + chunk, self.device, sh_degree)
+
+
 class BenchSession:
     def __init__(self, device, rank: int, world: int, n_gaussians: int, width: int, height: int, batch: int,
                  n_views: int, gt_gaussians: int, transport: str = "auto", seed: int = 0, sh_degree: int = 3,
-                 grid=(2048, 2048, 1)):
+                 grid=(2048, 2048, 1), bvh_depth: int | None = None, scene_kind: str = "cluster",
+                 borrow: bool = True, borrow_refresh: int = 1, group=None):
         self.device = torch.device(device)
         self.rank, self.world, self.batch = rank, world, batch
         self.sh_degree = sh_degree
-        self.bvh_depth = int(round(math.log2(world)))
-        assert 2 ** self.bvh_depth == world, "world size must be a power of two"
-        scene = ClusterScene(seed, self.device)
+        self.bvh_depth = int(round(math.log2(world))) if bvh_depth is None else bvh_depth
+        assert 2 ** self.bvh_depth >= world, "need at least one sub-model per rank"
+        make_scene = ClusterScene if scene_kind == "cluster" else UniformScene
+        self._make_scene = make_scene
+        scene = make_scene(seed, self.device)
         # ---- partition from the load histogram of all positions -------------------------------
         half = scene.box / 2
         g3 = Grid3D(np.array([-half] * 3), np.array([half] * 3), grid)
@@ -99,7 +119,10 @@ class BenchSession:
             del g, ids
         torch.cuda.empty_cache() if self.device.type == "cuda" else None
         # ---- cameras, relation, ground truth -----------------------------------------------------
-        self.cams = synthetic.hemisphere_cameras(max(n_views, 1), 8.0, width, height, 50.0, seed)
+        if scene_kind == "cluster":
+            self.cams = synthetic.hemisphere_cameras(max(n_views, 1), 8.0, width, height, 50.0, seed)
+        else:
+            self.cams = synthetic.ring_cameras(max(n_views, 1), 3.0, width, height, 60.0)
         self.relation = self.tree.relation(self.cams, 0.01, 1000.0)
         self._render_ground_truth(seed, gt_gaussians, sh_degree)
         # ---- engine ---------------------------------------------------------------------------
@@ -110,7 +133,7 @@ class BenchSession:
             if want in ("auto", "peer"):
                 try:
                     from .parallel.peer import PeerTransport
-                    tr = PeerTransport(self.device)
+                    tr = PeerTransport(self.device, group)
                     self.transport_name = "peer (kernel stores into peer-mapped slots, flag barrier)"
                 except Exception as exc:  # pragma: no cover - depends on the box
                     if want == "peer":
@@ -118,12 +141,16 @@ class BenchSession:
                     if rank == 0:
                         print(f"[bench] peer transport unavailable ({exc!r}); using torch.distributed send/recv",
                               flush=True)
-                    tr = TorchDistTransport(self.device)
-                    self.transport_name = "nccl send/recv"
+                    tr = TorchDistTransport(self.device, group)
+                    self.transport_name = "torch.distributed send/recv"
             else:
-                tr = TorchDistTransport(self.device)
-                self.transport_name = "nccl send/recv"
-        self.engine = StepEngine(self.stores, self.model2rank, self.device, tr)
+                tr = TorchDistTransport(self.device, group)
+                self.transport_name = "torch.distributed send/recv"
+        self.border = None
+        if borrow and self.n_models > 1:
+            from .parallel.border import BorderExchange
+            self.border = BorderExchange(lo, hi, self.model2rank, rank, world, self.device, group, borrow_refresh)
+        self.engine = StepEngine(self.stores, self.model2rank, self.device, tr, borrow=self.border)
         extent = 1.1 * 8.0
         self.lrs = (1.6e-4 * extent, 2.5e-3, 2.5e-3 / 20.0, 5e-3, 1e-3, 5e-2)
         self.last_info: dict = {}
@@ -133,7 +160,7 @@ class BenchSession:
     def _render_ground_truth(self, seed: int, gt_gaussians: int, sh_degree: int):
         """Targets come from an independent seeded scene; each view is rendered once and parked in pinned
         host memory (only the rows this rank owns, plus the SSIM halo, are uploaded per step)."""
-        scene = ClusterScene(seed + 1, self.device)
+        scene = self._make_scene(seed + 1, self.device)
         parts = [scene.gaussians(m, k, sh_degree) for k, m in chunks_of(gt_gaussians)]
         g = {name: torch.cat([p[name] for p in parts]) for name in parts[0]}
         seg = Segment(g["xyz"], g["sh"], g["scale"], g["rot"], g["opacity"])
@@ -190,6 +217,11 @@ class BenchSession:
     def barrier(self):
         if self.world > 1:
             dist.barrier()
+
+    def render_view(self, i: int):
+        """Composited image rows owned by this rank for camera ``i`` (eval path)."""
+        out = self.engine.render([self.cams[i]], self.relation[[i]], self.sh_degree)[0]
+        return out["image"], out["rows"], out["trans"]
 
     def reset_launch_count(self):
         self._launch_base = native.launch_count()

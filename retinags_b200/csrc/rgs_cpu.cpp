@@ -98,6 +98,17 @@ int rgs_cpu_blend_fwd(const RgsCamera* cam, const int32_t* ranges, const uint32_
     return 0;
 }
 
+// CPU twin of the fused push (used by the loopback tests): copies the rows after the render.
+int rgs_cpu_blend_fwd_push(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
+                           float* out, float* depth, int32_t* n_contrib, int32_t* counters, int64_t n_dst,
+                           const int32_t* row0, const int32_t* row1, float* const* dst, void* stream) {
+    rgs_cpu_blend_fwd(cam, ranges, vals, splats, out, depth, n_contrib, counters, stream);
+    for (int64_t o = 0; o < n_dst; ++o)
+        if (row1[o] > row0[o])
+            std::memcpy(dst[o], out + (int64_t)row0[o] * cam->W * 4, (size_t)(row1[o] - row0[o]) * cam->W * 16);
+    return 0;
+}
+
 // grad_out: (H,W,4) = dL/dC (rgb), dL/dT. splat_grads[n_vis] must be zeroed by the caller.
 int rgs_cpu_blend_bwd(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
                       const float* out, const int32_t* n_contrib, const float* grad_out, RgsSplatGrad* splat_grads,

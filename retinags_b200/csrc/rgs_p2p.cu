@@ -1,0 +1,98 @@
+// Peer-to-peer plumbing of the fused compositing path: CUDA IPC allocation/mapping of the
+// per-rank exchange region and the flag kernels that order producers and consumers across GPUs.
+//
+// The reference moves partial images and their gradients with NCCL send/recv batches followed by
+// a device-wide synchronise (parallel_utils/communicate_utils/core.py:37-65). Here the bytes are
+// stored by the producing kernels themselves (rgs_raster.cu: blend epilogue; rgs_loss.cu:
+// compositing backward) through peer-mapped pointers over NVLink; what remains is ordering:
+//   signal: after its producing kernels, a rank release-stores an epoch number into its word of
+//           every peer's flag array (system scope);
+//   wait:   before its consuming kernels, a rank acquire-loads its own flag array until every
+//           word has reached the epoch. The wait is bounded by a cycle budget; on expiry it writes
+//           a status word that the host checks, and returns normally.
+// Plain peer stores/loads only: no multimem, no multicast, no TMA on peer memory.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+#include "rgs_api.h"
+#include "rgs_cuda_common.cuh"
+
+struct RgsPeerFlagPtrs { uint32_t* p[16]; };
+
+__global__ void rgs_p2p_signal_kernel(const __grid_constant__ RgsPeerFlagPtrs flags, int world, int my_rank,
+                                      uint32_t epoch) {
+    const int o = threadIdx.x;
+    if (o < world) {
+        __threadfence_system();
+        rgs_st_release_sys(flags.p[o] + my_rank, epoch);
+    }
+}
+
+__global__ void rgs_p2p_wait_kernel(const uint32_t* __restrict__ my_flags, int world, uint32_t epoch,
+                                    long long budget_cycles, uint32_t* __restrict__ status) {
+    const int r = threadIdx.x;
+    if (r >= world) return;
+    const long long t0 = clock64();
+    while (true) {
+        const uint32_t v = rgs_ld_acquire_sys(my_flags + r);
+        if ((int32_t)(v - epoch) >= 0) break;
+        if (clock64() - t0 > budget_cycles) {
+            atomicExch(status, 0x100u | (uint32_t)r);  // gave up waiting for rank r
+            break;
+        }
+        __nanosleep(200);
+    }
+    __threadfence_system();
+}
+
+extern "C" {
+
+int rgs_cuda_ipc_alloc(int64_t bytes, void** out) {
+    void* p = nullptr;
+    RGS_CUDA_CHECK(cudaMalloc(&p, (size_t)bytes));
+    RGS_CUDA_CHECK(cudaMemset(p, 0, (size_t)bytes));
+    RGS_CUDA_CHECK(cudaDeviceSynchronize());
+    *out = p;
+    return 0;
+}
+
+int rgs_cuda_ipc_free(void* p) { return (int)cudaFree(p); }
+
+int rgs_cuda_ipc_get_handle(void* p, char* out64) {
+    cudaIpcMemHandle_t h;
+    RGS_CUDA_CHECK(cudaIpcGetMemHandle(&h, p));
+    static_assert(sizeof(h) == 64, "handle size");
+    memcpy(out64, &h, 64);
+    return 0;
+}
+
+int rgs_cuda_ipc_open(const char* in64, void** out) {
+    cudaIpcMemHandle_t h;
+    memcpy(&h, in64, 64);
+    void* p = nullptr;
+    RGS_CUDA_CHECK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *out = p;
+    return 0;
+}
+
+int rgs_cuda_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+
+// flag_ptrs: `world` device pointers (host array): the flag array of every rank as mapped here.
+int rgs_cuda_p2p_signal(uint32_t* const* flag_ptrs, int64_t world, int64_t my_rank, int64_t epoch, void* stream) {
+    if (world < 1 || world > 16) return 14;
+    RgsPeerFlagPtrs f;
+    for (int i = 0; i < world; ++i) f.p[i] = flag_ptrs[i];
+    rgs_p2p_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, (int)world, (int)my_rank, (uint32_t)epoch);
+    return (int)cudaGetLastError();
+}
+
+int rgs_cuda_p2p_wait(const uint32_t* my_flags, int64_t world, int64_t epoch, int64_t budget_cycles, int32_t* status,
+                      void* stream) {
+    if (world < 1 || world > 16) return 14;
+    rgs_p2p_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(my_flags, (int)world, (uint32_t)epoch,
+                                                           (long long)budget_cycles,
+                                                           reinterpret_cast<uint32_t*>(status));
+    return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -98,6 +98,7 @@ __global__ void __launch_bounds__(256) rgs_project_emit_kernel(
 // blend forward
 // ---------------------------------------------------------------------------------------------
 #define BLEND_BATCH 256
+#define RGS_MAX_PUSH 16
 #define RGS_WAIT_LIMIT (1u << 22)
 
 struct BlendSmem {
@@ -118,10 +119,19 @@ __device__ __forceinline__ void blend_issue(BlendSmem& sm, int stage, const RgsS
     }
 }
 
+// Destinations of the fused push: for every owner rank the rows [row0,row1) it needs of this partial and
+// the (possibly peer-mapped) base of its slot, which holds exactly those rows.
+struct RgsPushPlan {
+    int n;
+    int row0[RGS_MAX_PUSH];
+    int row1[RGS_MAX_PUSH];
+    float4* dst[RGS_MAX_PUSH];
+};
+
 __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
     const __grid_constant__ RgsCamera cam, const int2* __restrict__ ranges, const uint32_t* __restrict__ vals,
     const RgsSplat* __restrict__ splats, float4* __restrict__ out, float* __restrict__ depth,
-    int32_t* __restrict__ n_contrib, uint32_t* __restrict__ counters) {
+    int32_t* __restrict__ n_contrib, uint32_t* __restrict__ counters, const __grid_constant__ RgsPushPlan push) {
     __shared__ __align__(128) BlendSmem sm;
     const int tid = threadIdx.x;
     const int lx = tid & 15, ly = tid >> 4;
@@ -169,9 +179,15 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
     if (failed && tid == 0) atomicExch(&counters[RGS_CNT_STATUS], 1u);
     if (inside) {
         const int64_t pid = (int64_t)py * cam.W + px;
-        out[pid] = make_float4(st.C[0], st.C[1], st.C[2], st.T);
+        const float4 val = make_float4(st.C[0], st.C[1], st.C[2], st.T);
+        out[pid] = val;
         if (depth) depth[pid] = st.D;
         n_contrib[pid] = st.last;
+        // epilogue push: the finished pixel goes straight into the slot of every rank that composites
+        // this row (plain stores; the destination may be another GPU's memory mapped over NVLink)
+        for (int o = 0; o < push.n; ++o)
+            if (py >= push.row0[o] && py < push.row1[o])
+                push.dst[o][(int64_t)(py - push.row0[o]) * cam.W + px] = val;
     }
 }
 
@@ -356,9 +372,27 @@ int rgs_cuda_project_emit(const RgsCamera* cam, const RgsSegment* seg, int64_t i
 int rgs_cuda_blend_fwd(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
                        float* out, float* depth, int32_t* n_contrib, int32_t* counters, void* stream) {
     dim3 grid(cam->tiles_x, cam->tiles_y);
+    RgsPushPlan push;
+    push.n = 0;
     rgs_blend_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
         *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<float4*>(out), depth, n_contrib,
-        reinterpret_cast<uint32_t*>(counters));
+        reinterpret_cast<uint32_t*>(counters), push);
+    return (int)cudaGetLastError();
+}
+
+// Blend forward with the fused push: besides the local (H,W,4) image, rows [row0[o],row1[o]) are stored
+// into dst[o] for o < n_dst (slot bases, local or peer-mapped).
+int rgs_cuda_blend_fwd_push(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
+                            float* out, float* depth, int32_t* n_contrib, int32_t* counters, int64_t n_dst,
+                            const int32_t* row0, const int32_t* row1, float* const* dst, void* stream) {
+    if (n_dst < 0 || n_dst > RGS_MAX_PUSH) return 15;
+    dim3 grid(cam->tiles_x, cam->tiles_y);
+    RgsPushPlan push;
+    push.n = (int)n_dst;
+    for (int o = 0; o < n_dst; ++o) { push.row0[o] = row0[o]; push.row1[o] = row1[o]; push.dst[o] = reinterpret_cast<float4*>(dst[o]); }
+    rgs_blend_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
+        *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<float4*>(out), depth, n_contrib,
+        reinterpret_cast<uint32_t*>(counters), push);
     return (int)cudaGetLastError();
 }
 

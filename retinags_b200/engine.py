@@ -116,9 +116,9 @@ class StepEngine:
                 st = self.stores[m]
                 c = make_camera(cam, sh_degree, st.box_lo, st.box_hi, raw_params=True, tight_rect=self.tight_rect)
                 task = self._task(p.view, m)
-                dst = self.transport.render_target(p, m) if hasattr(self.transport, "render_target") else None
-                local_out[p.view][m] = task.forward(c, self._segments(m, False), want_depth=want_depth, out=dst,
-                                                    check=check)
+                push = self.transport.push_plan(p, m) if hasattr(self.transport, "push_plan") else None
+                local_out[p.view][m] = task.forward(c, self._segments(m, False), want_depth=want_depth, check=check,
+                                                    push=push)
         return local_out
 
     def render(self, cams: list[Camera], relations, sh_degree: int, background=None):
@@ -126,6 +126,7 @@ class StepEngine:
         (``image``, ``rows``) -- with world size 1 that is the whole image."""
         bg = self.background if background is None else background
         plans = self.plan(cams, relations)
+        self._prepare_transport(plans)
         if self.borrow is not None:
             self.borrow.refresh(self.stores, need_grads=False)
         local_out = self.render_partials(cams, plans, sh_degree, check=True)
@@ -136,19 +137,28 @@ class StepEngine:
             b = p.bands[self.rank]
             cl.composite(slots[p.view], bg, b[0], b[1])
             out.append(dict(image=cl.image, trans=cl.trans, rows=b, partials=local_out[p.view], plan=p))
+        self.transport.barrier()  # slots may be overwritten by the next render only after everyone composited
         return out
+
+    def _prepare_transport(self, plans):
+        if hasattr(self.transport, "prepare") and plans:
+            self.transport.prepare(plans, len(self.model2rank), self.model2rank)
 
     # -- training step --------------------------------------------------------------------------
     def train_step(self, cams: list[Camera], relations, sh_degree: int, lrs, optimizer_step: bool = True,
                    background=None) -> StepResult:
         bg = self.background if background is None else background
         plans = self.plan(cams, relations)
+        self._prepare_transport(plans)
         if self.borrow is not None:
             self.borrow.refresh(self.stores, need_grads=True)
         local_out = self.render_partials(cams, plans, sh_degree)
         slots = self.transport.exchange_partials(plans, local_out)
-        local_grad = {p.view: {m: self._grad(p.view, m, p.H, p.W) for m, r in zip(p.models, p.ranks) if r == self.rank}
-                      for p in plans}
+        if hasattr(self.transport, "local_grad_images"):
+            local_grad = self.transport.local_grad_images(plans)
+        else:
+            local_grad = {p.view: {m: self._grad(p.view, m, p.H, p.W) for m, r in zip(p.models, p.ranks)
+                                   if r == self.rank} for p in plans}
         gslots = self.transport.grad_slots(plans, local_grad)
         sums = []
         for p, cam in zip(plans, cams):

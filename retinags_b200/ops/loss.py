@@ -42,8 +42,8 @@ class CompositeLoss:
     def composite(self, partials: list[torch.Tensor], bg, row0: int = 0, row1: int | None = None):
         """Composite rows [row0,row1) of the ordered partials into ``self.image`` / ``self.trans``."""
         row1 = self.H if row1 is None else row1
-        for p in partials:
-            assert p.is_contiguous() and p.shape[-1] == 4
+        for p in partials:  # tensors, or raw (virtual full-height) base addresses
+            assert isinstance(p, int) or (p.is_contiguous() and p.shape[-1] == 4)
         ptrs = native.pointer_array(partials)
         native.call("composite_fwd", self.device, ptrs, len(partials), self._bg(bg), self.H, self.W, row0, row1,
                     self.image, self.trans)

@@ -27,6 +27,7 @@ SIGNATURES = {
     "project_emit": "ppipppippippp",
     "sort_ranges": "ppppipippp",
     "blend_fwd": "ppppppppp",
+    "blend_fwd_push": "ppppppppipppp",
     "blend_bwd": "pppppppppp",
     "geom_bwd": "ppipppppip",
     "scatter_radii": "pppiipp",

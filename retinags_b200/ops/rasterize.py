@@ -177,11 +177,11 @@ class RenderTask:
 
     # -- forward ------------------------------------------------------------------------------
     def forward(self, cam: RgsCamera, segments: list[Segment], want_depth: bool = False, out: torch.Tensor | None = None,
-                check: bool = False) -> torch.Tensor:
+                check: bool = False, push=None) -> torch.Tensor:
         """Rasterise ``segments`` for ``cam``; returns the (H,W,4) premultiplied RGB + T image.
 
-        ``out`` lets the caller provide the destination (for instance a slot of a compositing
-        buffer).  With ``check`` the counters are read back (host sync) and the render is repeated
+        ``out`` lets the caller provide the destination; ``push`` = (n, row0[], row1[], dst[]) makes the
+        blend epilogue also store row ranges into compositing slots (local or peer-mapped).  With ``check`` the counters are read back (host sync) and the render is repeated
         with larger buffers when the instance capacity was exceeded.
         """
         H, W = cam.H, cam.W
@@ -202,8 +202,13 @@ class RenderTask:
             sc.ensure(self.cap_inst)
             native.call("sort_ranges", self.device, self.keys, self.vals, sc.keys_tmp, sc.vals_tmp, self.cap_inst,
                         self.counters, cam.tiles_x * cam.tiles_y, self.ranges, sc.words)
-            native.call("blend_fwd", self.device, cam, self.ranges, self.vals, self.splats, dst,
-                        self.depth if want_depth else None, self.n_contrib, self.counters)
+            if push is None:
+                native.call("blend_fwd", self.device, cam, self.ranges, self.vals, self.splats, dst,
+                            self.depth if want_depth else None, self.n_contrib, self.counters)
+            else:  # (n, row0[], row1[], dst[]): also store the rows into the owners' compositing slots
+                native.call("blend_fwd_push", self.device, cam, self.ranges, self.vals, self.splats, dst,
+                            self.depth if want_depth else None, self.n_contrib, self.counters, push[0], push[1],
+                            push[2], push[3])
             self.last_out = dst
             if not check:
                 self._record_counters()

@@ -28,3 +28,12 @@ def oracle_render(g, cam, sh_degree, box=(None, None)):
     a = activated(g)
     return oracle.rasterize(cam, a["xyz"], a["sh"].view(-1, 16, 3), a["opacity"], a["scale"], a["rot"], sh_degree,
                             box[0], box[1])
+
+
+def assert_mostly_close(a, b, atol, rtol, max_frac=2e-4, hard_atol=5e-3):
+    """Element-wise closeness that tolerates a handful of pixels where the T < 1e-4 stop rule or the 1/255
+    alpha reject flips between two float evaluation orders (FMA contraction differs between nvcc and g++)."""
+    diff = (a - b).abs()
+    bad = diff > (atol + rtol * b.abs())
+    assert bad.float().mean().item() <= max_frac, f"{int(bad.sum())} of {bad.numel()} elements differ"
+    assert diff.max().item() <= hard_atol, f"max abs diff {diff.max().item()}"
