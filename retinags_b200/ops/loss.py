@@ -68,6 +68,15 @@ class CompositeLoss:
                     weight * (1.0 - lambda_dssim) / npx, weight * lambda_dssim / npx, self.g_image)
         return self.sums
 
+    def stats(self, gt: torch.Tensor, row0: int = 0, row1: int | None = None):
+        """Loss statistics only (no gradient): accumulated (sum|d|, sum ssim, sum d^2) over rows [row0,row1)."""
+        H, W = self.H, self.W
+        row1 = H if row1 is None else row1
+        c0, c1 = max(0, row0), min(H, row1)
+        self.sums.zero_()
+        native.call("ssim_fwd", self.device, self.image, gt, H, W, c0, c1, row0, row1, self.dmaps, self.sums)
+        return self.sums
+
     def loss_from_sums(self, sums, lambda_dssim: float = 0.2) -> dict:
         s = sums.tolist() if isinstance(sums, torch.Tensor) else list(sums)
         npx = 3.0 * self.H * self.W
