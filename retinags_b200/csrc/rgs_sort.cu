@@ -187,6 +187,7 @@ __global__ void rgs_tile_ranges_kernel(const uint64_t* __restrict__ keys, const 
     }
 }
 
+#ifndef RGS_SORT_KERNELS_ONLY  // the kernels above are also compiled into rgs_noalloc.cu (own namespace)
 extern "C" {
 
 // Number of uint32 words of scratch needed for a capacity of cap_inst pairs.
@@ -227,3 +228,4 @@ int rgs_cuda_sort_ranges(uint64_t* keys, uint32_t* vals, uint64_t* keys_tmp, uin
 }
 
 }  // extern "C"
+#endif  // RGS_SORT_KERNELS_ONLY

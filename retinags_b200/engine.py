@@ -135,7 +135,8 @@ class StepEngine:
         for p in plans:
             cl = self._loss(p.view, p.H, p.W)
             b = p.bands[self.rank]
-            cl.composite(slots[p.view], bg, b[0], b[1])
+            if b[1] > b[0]:  # five more rows on each side so that SSIM windows of the band are complete
+                cl.composite(slots[p.view], bg, max(0, b[0] - 5), min(p.H, b[1] + 5))
             out.append(dict(image=cl.image, trans=cl.trans, rows=b, partials=local_out[p.view], plan=p))
         self.transport.barrier()  # slots may be overwritten by the next render only after everyone composited
         return out

@@ -1,0 +1,80 @@
+"""End-to-end trainer on CPU: train from a point cloud with densification, checkpoint, resume, eval."""
+import glob
+import os
+
+import numpy as np
+import torch
+
+from retinags_b200.config import build_parser
+from retinags_b200.data.synthetic_scene import build_synthetic_scene
+from retinags_b200.models import ply_io
+from retinags_b200.trainer import Trainer
+
+
+def _trainer(tmp, extra=(), scene=None):
+    parser, lp, op, pp = build_parser()
+    argv = ["-m", str(tmp), "--bvh_depth", "1", "--MAX_BATCH_SIZE", "2", "--MAX_LOAD", "4", "--device", "cpu",
+            "--densify_from_iter", "4", "--densification_interval", "6", "--opacity_reset_interval", "1000",
+            "--densify_until_iter", "40", "--quiet", "--EVAL_PSNR_INTERVAL", "2", "--eval"] + list(extra)
+    args = parser.parse_args(argv)
+    scene = scene or build_synthetic_scene("uniform:n=4000:w=96:h=64:views=10:test=2:init=1500:deg=1", device=torch.device("cpu"))
+    return Trainer(args, lp.extract(args), op.extract(args), pp.extract(args), scene=scene), scene
+
+
+def test_train_checkpoint_resume_eval(tmp_path):
+    tr, scene = _trainer(tmp_path, ["--epochs", "3"])
+    assert sorted(tr.stores) == [0, 1]
+    n0 = sum(s.count for s in tr.stores.values())
+    assert n0 == 1500
+    before = tr.eval()
+    tr.train()
+    after = tr.eval()
+    assert after["test"]["psnr"] > before["test"]["psnr"] + 0.5
+    assert after["train"]["l1"] < before["train"]["l1"]
+    n1 = sum(s.count for s in tr.stores.values())
+    assert n1 != n0  # densification/pruning changed the point count
+    it = tr.iteration
+    ck = os.path.join(tmp_path, "rank_0", "point_cloud", f"iteration_{it}")
+    assert os.path.exists(os.path.join(ck, "point_cloud_0.ply")) and os.path.exists(os.path.join(ck, "adam_1.pt"))
+    assert os.path.exists(os.path.join(ck, "tree_0.txt"))
+    whole = os.path.join(tmp_path, "point_cloud", f"iteration_{it}", "point_cloud.ply")
+    g = ply_io.load_gaussians(whole)
+    assert g["xyz"].shape[0] == n1
+    names = ply_io.read_ply_vertices(whole).dtype.names
+    assert list(names[:9]) == ["x", "y", "z", "nx", "ny", "nz", "f_dc_0", "f_dc_1", "f_dc_2"] and len(names) == 62
+    # resume from the merged model with a different partition depth (whole-model mode)
+    tr2, _ = _trainer(tmp_path, ["--epochs", "3", "--bvh_depth", "2"], scene)
+    assert tr2.iteration == it and sum(s.count for s in tr2.stores.values()) == n1 and tr2.n_models == 4
+    r2 = tr2.eval()
+    assert abs(r2["test"]["psnr"] - after["test"]["psnr"]) < 0.3
+    # resume from the per-sub-model files, Adam moments included
+    tr3, _ = _trainer(tmp_path, ["--epochs", "4", "--SPLIT_MODEL"], scene)
+    assert tr3.iteration == it and {m: s.count for m, s in tr3.stores.items()} == {m: s.count for m, s in tr.stores.items()}
+    assert float(tr3.stores[0].exp_avg_sq.abs().sum()) > 0
+    torch.testing.assert_close(tr3.stores[0].records("exp_avg"), tr.stores[0].records("exp_avg"))
+    tr3.train()
+    assert tr3.iteration > it
+
+
+def test_repartition_keeps_every_gaussian(tmp_path):
+    tr, _ = _trainer(tmp_path, ["--epochs", "1"])
+    n = sum(s.count for s in tr.stores.values())
+    for st in tr.stores.values():
+        st.exp_avg.uniform_()
+    rec_before = torch.cat([s.migration_records() for s in tr.stores.values()])
+    # move everything so that the old partition is unbalanced, then rebalance
+    for st in tr.stores.values():
+        st.views()["xyz"][:, 0] += 0.35
+    rec_before = torch.cat([s.migration_records() for s in tr.stores.values()])
+    tr._repartition()
+    assert sum(s.count for s in tr.stores.values()) == n
+    rec_after = torch.cat([s.migration_records() for s in tr.stores.values()])
+    a = rec_before[torch.argsort(rec_before[:, 0])]
+    b = rec_after[torch.argsort(rec_after[:, 0])]
+    torch.testing.assert_close(a, b)
+    lo, hi = tr.boxes
+    for m, st in tr.stores.items():
+        p = st.xyz
+        assert bool(((p > torch.tensor(lo[m], dtype=torch.float32)) & (p <= torch.tensor(hi[m], dtype=torch.float32))).all())
+    counts = [s.count for s in tr.stores.values()]
+    assert min(counts) > 0.6 * max(counts)
