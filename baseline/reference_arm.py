@@ -227,26 +227,30 @@ def main(args):
     if why:
         print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
         return
-    import torch
-
     world = args.gpus
     if int(os.environ.get("RANK", "0")) != 0:
         return  # launched under torchrun: rank 0 drives the reference's own torchrun below
     prepare_tree()
-    device = torch.device("cuda", 0)
     n_iter = args.warmup + args.steps + 1
     n_views = n_iter * args.batch + 2 * args.batch
-    root = os.environ.get("RGS_REF_WORKDIR", "/tmp/rgs_reference_arm") + f"_{args.gaussians}_{args.width}x{args.height}"
-    try:
-        data_dir, model_dir = write_scene(root, args, n_views, device)
-    except Exception as exc:  # disk or memory of the box
-        print(json.dumps({"impl": "reference", "unavailable": f"could not write the synthetic scene: {exc!r}"[:300]}), flush=True)
+    root = os.environ.get("RGS_REF_WORKDIR", "/tmp/rgs_reference_arm") + f"_{args.gaussians}_{args.width}x{args.height}_{n_views}"
+    data_dir, model_dir = os.path.join(root, "data"), os.path.join(root, "model")
+    # the scene is written by a child process so that no CUDA context of this driver stays on GPU 0
+    child_env = {k: v for k, v in os.environ.items() if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE")}
+    wr = subprocess.run([sys.executable, os.path.abspath(__file__), "--write-scene", root, str(n_views), str(args.gaussians),
+                         str(args.width), str(args.height), str(args.gt_gaussians), str(args.seed)], env=child_env,
+                        capture_output=True, text=True)
+    if wr.returncode != 0:
+        print(json.dumps({"impl": "reference", "unavailable": ("could not write the synthetic scene: " + wr.stderr[-300:]).replace("\n", " | ")}),
+              flush=True)
         return
     for d in glob.glob(os.path.join(model_dir, "rank_*")):
         shutil.rmtree(d, ignore_errors=True)
     depth = max(0, world.bit_length() - 1)
     env = dict(os.environ)
     env["PYTHONPATH"] = os.pathsep.join([SHIMS, REF, SRC, env.get("PYTHONPATH", "")])
+    # allocator hint that torch's own out-of-memory message recommends; the reference's code is untouched
+    env.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
     for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_PORT", "MASTER_ADDR", "TORCHELASTIC_RUN_ID", "GROUP_RANK",
               "LOCAL_WORLD_SIZE", "ROLE_RANK", "ROLE_WORLD_SIZE", "GROUP_WORLD_SIZE", "TORCHELASTIC_RESTART_COUNT",
               "TORCHELASTIC_MAX_RESTARTS", "TORCHELASTIC_USE_AGENT_STORE", "TORCH_NCCL_ASYNC_ERROR_HANDLING"):
@@ -284,11 +288,17 @@ def main(args):
                 proc.kill()
     log.close()
     if not stamps or not all(len(v) >= need for v in stamps.values()):
-        tail = open(os.path.join(root, "reference_run.log")).read()[-600:].replace("\n", " | ")
         dbg = ""
-        for fn in glob.glob(os.path.join(SRC, "debugger", "debug_0_*.txt")):
-            dbg = open(fn).read()[-500:].replace("\n", " | ")
-        print(json.dumps({"impl": "reference", "unavailable": f"reference run recorded too few iterations: {tail} {dbg}"[:900]}),
+        for fn in sorted(glob.glob(os.path.join(SRC, "debugger", "debug_*.txt"))):
+            txt = open(fn).read()
+            if "Error" in txt or "error" in txt:
+                dbg = txt[-400:].replace("\n", " | ")
+        got = min((len(v) for v in stamps.values()), default=0)
+        partial = ""
+        if got >= 3:
+            per = max((v[got - 1][1] - v[1][1]) / (got - 2) for v in stamps.values())
+            partial = f" (the {got - 2} iterations it completed after the first took {1e3 * per:.0f} ms each)"
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference stopped after {got} of {need} iterations{partial}: {dbg}"[:900]}),
               flush=True)
         return
     W, K = args.warmup, args.steps
@@ -308,6 +318,13 @@ def main(args):
 
 if __name__ == "__main__":
     sys.path.insert(0, os.path.dirname(HERE))
+    if len(sys.argv) > 1 and sys.argv[1] == "--write-scene":
+        import argparse
+        import torch
+        ns = argparse.Namespace(gaussians=int(sys.argv[4]), width=int(sys.argv[5]), height=int(sys.argv[6]),
+                                gt_gaussians=int(sys.argv[7]), seed=int(sys.argv[8]))
+        write_scene(sys.argv[2], ns, int(sys.argv[3]), torch.device("cuda", 0))
+        sys.exit(0)
     import bench
     a = bench.parse_args()
     main(a)

@@ -22,6 +22,7 @@ CPU_SOURCES = ["rgs_cpu.cpp", "rgs_host.cpp"]
 CUDA_SOURCES = [
     "rgs_raster.cu",
     "rgs_sort.cu",
+    "rgs_binning.cu",
     "rgs_loss.cu",
     "rgs_model.cu",
     "rgs_p2p.cu",

@@ -173,7 +173,7 @@ class BenchSession:
             cam.image = img.pin_memory() if pin else img
         del task, seg, g, parts
         from .ops import rasterize
-        rasterize._SCRATCH.clear()
+        rasterize.release_scratch()
         if pin:
             torch.cuda.empty_cache()
 

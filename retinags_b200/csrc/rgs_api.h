@@ -31,6 +31,9 @@ struct RgsSegment {
     float* stat_grad;      // (count) += |screen gradient|, optional
     float* stat_denom;     // (count) += 1 for every view in which the Gaussian is visible, optional
     float* stat_maxrad;    // (count) = max(., radius), optional
+    uint8_t* touched;      // (count) optional: 1 once a gradient row was written this step. Rows with 0 are
+                           // known to hold zero gradients, so the first writer stores instead of adding and
+                           // the optimiser neither reads nor clears them.
     int64_t count;
 };
 

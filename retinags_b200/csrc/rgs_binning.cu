@@ -1,0 +1,473 @@
+// Depth-ordered tile binning for sm_100a.
+//
+// The reference sorts every (tile, splat) instance by a 64-bit (tile | depth) key with
+// cub::DeviceRadixSort (rasterizer_impl.cu:298-317): 6 radix passes over ~10^8 pairs of 12 bytes.
+// Here the order is produced in two much cheaper steps that give the identical result:
+//   1. the *visible splats* (10x fewer than instances) are sorted by depth: 4 passes over 8-byte pairs;
+//   2. instances are emitted in that order (a block scan fused into the emission gives every splat its
+//      output range, the instance total stays on the device), then ONE stable radix sort on the tile id
+//      alone (ceil(log2(tiles)/8) = 2 passes, 8-byte pairs) groups them by tile while keeping the depth
+//      order inside each tile, because an LSD radix sort is stable.
+// All kernels read their element counts from device memory; no kernel waits on another block.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "rgs_api.h"
+#include "rgs_cuda_common.cuh"
+
+#define BS_THREADS 256
+#define BS_ITEMS 16
+#define BS_CHUNK (BS_THREADS * BS_ITEMS)
+#define BS_WARPS (BS_THREADS / 32)
+#define BS_WARP_SPAN (32 * BS_ITEMS)
+
+// ---------------------------------------------------------------------------------------------
+// projection to slots (no instance emission)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rgs_project_slots_kernel(
+    const __grid_constant__ RgsCamera cam, const RgsSegment seg, const int64_t id_base, RgsSplat* __restrict__ splats,
+    int32_t* __restrict__ vis_ids, uint32_t* __restrict__ aux, const uint32_t cap_vis, uint32_t* __restrict__ slot_depth,
+    uint2* __restrict__ slot_rect, uint32_t* __restrict__ counters, RgsSplatGrad* __restrict__ splat_grads) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    bool ok = false;
+    RgsSplat sp;
+    RgsRect rc;
+    int radius = 0;
+    unsigned clamped = 0;
+    if (i < seg.count) {
+        float p[3] = {seg.xyz[3 * i], seg.xyz[3 * i + 1], seg.xyz[3 * i + 2]};
+        float s[3] = {seg.scale[3 * i], seg.scale[3 * i + 1], seg.scale[3 * i + 2]};
+        float4 q4 = reinterpret_cast<const float4*>(seg.rot)[i];
+        float q[4] = {q4.x, q4.y, q4.z, q4.w};
+        ok = rgs_project(cam, p, s, q, seg.opacity[i], seg.sh + 48 * i, sp, rc, radius, clamped);
+    }
+    __shared__ uint32_t warp_vis[8];
+    __shared__ uint32_t base_vis;
+    __shared__ int drop;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const uint32_t vmask = __ballot_sync(0xffffffffu, ok);
+    if (lane == 0) warp_vis[wid] = __popc(vmask);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t tv = 0;
+        for (int w = 0; w < 8; ++w) { uint32_t v = warp_vis[w]; warp_vis[w] = tv; tv += v; }
+        uint32_t bv = 0;
+        int d = 0;
+        if (tv) {
+            bv = atomicAdd(&counters[RGS_CNT_VIS], tv);
+            if (bv + tv > cap_vis) { atomicExch(&counters[RGS_CNT_OVERFLOW], 1u); d = 1; }
+        }
+        base_vis = bv; drop = d;
+    }
+    __syncthreads();
+    if (!ok || drop) return;
+    const uint32_t slot = base_vis + warp_vis[wid] + __popc(vmask & ((1u << lane) - 1u));
+    float4* dst = reinterpret_cast<float4*>(splats + slot);
+    dst[0] = make_float4(sp.px, sp.py, sp.ca, sp.cb);
+    dst[1] = make_float4(sp.cc, sp.opacity, sp.r, sp.g);
+    dst[2] = make_float4(sp.b, sp.w, sp.depth, 0.f);
+    vis_ids[slot] = (int32_t)(id_base + i);
+    aux[slot] = ((uint32_t)radius << 3) | clamped;
+    slot_depth[slot] = __float_as_uint(sp.depth);
+    slot_rect[slot] = make_uint2((uint32_t)rc.x0 | ((uint32_t)rc.y0 << 16), (uint32_t)rc.x1 | ((uint32_t)rc.y1 << 16));
+    if (splat_grads) {
+        float4* gz = reinterpret_cast<float4*>(splat_grads + slot);
+        gz[0] = make_float4(0.f, 0.f, 0.f, 0.f); gz[1] = gz[0]; gz[2] = gz[0];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// radix sort of (u32 key, u32 value) pairs; count read from counters[which]
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t bs_count(const uint32_t* counters, int which, uint32_t cap) {
+    if (counters[RGS_CNT_OVERFLOW]) return 0u;
+    const uint32_t n = counters[which];
+    return n < cap ? n : cap;
+}
+
+// When keys_in is null the key of element i is gathered as key_src[vals_in[i]] / the value is i itself
+// (first pass of the depth sort: keys live in slot order, values are the slots).
+__global__ void __launch_bounds__(BS_THREADS) rgs_bs_hist_kernel(const uint32_t* __restrict__ keys,
+                                                                const uint32_t* __restrict__ counters, int which,
+                                                                uint32_t cap, int shift, uint32_t* __restrict__ hist,
+                                                                uint32_t nchunks_cap) {
+    __shared__ uint32_t sh[BS_WARPS][256];
+    const uint32_t n = bs_count(counters, which, cap);
+    const uint32_t nchunks = (n + BS_CHUNK - 1) / BS_CHUNK;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        for (int k = threadIdx.x; k < BS_WARPS * 256; k += BS_THREADS) (&sh[0][0])[k] = 0;
+        __syncthreads();
+        const uint32_t base = c * BS_CHUNK + wid * BS_WARP_SPAN;
+#pragma unroll 4
+        for (int r = 0; r < BS_ITEMS; ++r) {
+            const uint32_t idx = base + r * 32 + lane;
+            const bool valid = idx < n;
+            const uint32_t digit = valid ? ((keys[idx] >> shift) & 0xffu) : 0xffffffffu;
+            const uint32_t m = __match_any_sync(0xffffffffu, digit);
+            if (valid && lane == (__ffs(m) - 1)) sh[wid][digit] += __popc(m);
+            __syncwarp();
+        }
+        __syncthreads();
+        uint32_t tot = 0;
+#pragma unroll
+        for (int w = 0; w < BS_WARPS; ++w) tot += sh[w][threadIdx.x];
+        hist[(size_t)threadIdx.x * nchunks_cap + c] = tot;
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(256) rgs_bs_scan_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ totals,
+                                                          const uint32_t* __restrict__ counters, int which, uint32_t cap,
+                                                          uint32_t nchunks_cap) {
+    __shared__ uint32_t warp_tot[8];
+    __shared__ uint32_t carry_s;
+    const uint32_t n = bs_count(counters, which, cap);
+    const uint32_t nchunks = (n + BS_CHUNK - 1) / BS_CHUNK;
+    uint32_t* row = hist + (size_t)blockIdx.x * nchunks_cap;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry_s = 0;
+    __syncthreads();
+    for (uint32_t start = 0; start < nchunks; start += 256 * 4) {
+        const uint32_t i0 = start + threadIdx.x * 4;
+        uint32_t v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = (i0 + k < nchunks) ? row[i0 + k] : 0u;
+        const uint32_t mine = v[0] + v[1] + v[2] + v[3];
+        uint32_t incl = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += t;
+        }
+        if (lane == 31) warp_tot[wid] = incl;
+        __syncthreads();
+        uint32_t wbase = 0;
+        for (int w = 0; w < wid; ++w) wbase += warp_tot[w];
+        uint32_t run = carry_s + wbase + incl - mine;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (i0 + k < nchunks) row[i0 + k] = run;
+            run += v[k];
+        }
+        __syncthreads();
+        if (threadIdx.x == 255) carry_s = run;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) totals[blockIdx.x] = carry_s;
+}
+
+__global__ void __launch_bounds__(BS_THREADS) rgs_bs_scatter_kernel(
+    const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ keys_out,
+    uint32_t* __restrict__ vals_out, const uint32_t* __restrict__ counters, int which, uint32_t cap, int shift,
+    const uint32_t* __restrict__ hist, const uint32_t* __restrict__ totals, uint32_t nchunks_cap, int iota_vals) {
+    __shared__ uint32_t sh[BS_WARPS][256];
+    __shared__ uint32_t digit_base[256];
+    __shared__ uint32_t warp_tot[8];
+    const uint32_t n = bs_count(counters, which, cap);
+    const uint32_t nchunks = (n + BS_CHUNK - 1) / BS_CHUNK;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    {
+        const uint32_t t = totals[threadIdx.x];
+        uint32_t incl = t;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            uint32_t u = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += u;
+        }
+        if (lane == 31) warp_tot[wid] = incl;
+        __syncthreads();
+        uint32_t wbase = 0;
+        for (int w = 0; w < wid; ++w) wbase += warp_tot[w];
+        digit_base[threadIdx.x] = wbase + incl - t;
+    }
+    __syncthreads();
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        for (int k = threadIdx.x; k < BS_WARPS * 256; k += BS_THREADS) (&sh[0][0])[k] = 0;
+        __syncthreads();
+        const uint32_t base = c * BS_CHUNK + wid * BS_WARP_SPAN;
+        uint32_t key[BS_ITEMS], val[BS_ITEMS], rank[BS_ITEMS];
+#pragma unroll
+        for (int r = 0; r < BS_ITEMS; ++r) {
+            const uint32_t idx = base + r * 32 + lane;
+            const bool valid = idx < n;
+            key[r] = valid ? keys_in[idx] : 0xffffffffu;
+            val[r] = valid ? (iota_vals ? idx : vals_in[idx]) : 0u;
+        }
+#pragma unroll
+        for (int r = 0; r < BS_ITEMS; ++r) {
+            const uint32_t idx = base + r * 32 + lane;
+            const bool valid = idx < n;
+            const uint32_t digit = valid ? ((key[r] >> shift) & 0xffu) : 0xffffffffu;
+            const uint32_t m = __match_any_sync(0xffffffffu, digit);
+            const int leader = __ffs(m) - 1;
+            uint32_t pre = 0;
+            if (valid && lane == leader) { pre = sh[wid][digit]; sh[wid][digit] = pre + __popc(m); }
+            pre = __shfl_sync(0xffffffffu, pre, leader);
+            rank[r] = pre + __popc(m & lt_mask);
+            __syncwarp();
+        }
+        __syncthreads();
+        {
+            const int d = threadIdx.x;
+            uint32_t run = hist[(size_t)d * nchunks_cap + c] + digit_base[d];
+#pragma unroll
+            for (int w = 0; w < BS_WARPS; ++w) { uint32_t t = sh[w][d]; sh[w][d] = run; run += t; }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < BS_ITEMS; ++r) {
+            const uint32_t idx = base + r * 32 + lane;
+            if (idx < n) {
+                const uint32_t digit = (key[r] >> shift) & 0xffu;
+                const uint32_t dst = sh[wid][digit] + rank[r];
+                if (dst < cap) { keys_out[dst] = key[r]; vals_out[dst] = val[r]; }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// instance emission in depth order: per-segment counts -> scan of segment sums -> emit
+// ---------------------------------------------------------------------------------------------
+#define EM_SEG 1024  // splats per segment (256 threads x 4)
+
+__device__ __forceinline__ uint32_t rect_count(uint2 r) {
+    const uint32_t w = (r.y & 0xffffu) - (r.x & 0xffffu), h = (r.y >> 16) - (r.x >> 16);
+    return w * h;
+}
+
+__global__ void __launch_bounds__(256) rgs_emit_count_kernel(const uint32_t* __restrict__ order,
+                                                             const uint2* __restrict__ slot_rect,
+                                                             const uint32_t* __restrict__ counters, uint32_t cap_vis,
+                                                             uint32_t* __restrict__ seg_sums) {
+    __shared__ uint32_t red[8];
+    const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);
+    const uint32_t nseg = (n + EM_SEG - 1) / EM_SEG;
+    for (uint32_t s = blockIdx.x; s < nseg; s += gridDim.x) {
+        uint32_t sum = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t i = s * EM_SEG + k * 256 + threadIdx.x;
+            if (i < n) sum += rect_count(slot_rect[order[i]]);
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t t = 0;
+            for (int w = 0; w < 8; ++w) t += red[w];
+            seg_sums[s] = t;
+        }
+        __syncthreads();
+    }
+}
+
+// single block: exclusive scan of the segment sums in place; total -> counters[CNT_INST], overflow flag.
+__global__ void __launch_bounds__(1024) rgs_emit_scan_kernel(uint32_t* __restrict__ seg_sums, uint32_t* __restrict__ counters,
+                                                             uint32_t cap_vis, uint32_t cap_inst) {
+    __shared__ uint32_t warp_tot[32];
+    __shared__ unsigned long long carry_s;  // 64-bit so that a total beyond 2^32 is seen as an overflow, not a wrap
+    const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);
+    const uint32_t nseg = (n + EM_SEG - 1) / EM_SEG;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry_s = 0;
+    __syncthreads();
+    unsigned long long total64 = 0;
+    for (uint32_t start = 0; start < nseg; start += 1024) {
+        const uint32_t i = start + threadIdx.x;
+        const uint32_t v = i < nseg ? seg_sums[i] : 0u;
+        uint32_t incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += t;
+        }
+        if (lane == 31) warp_tot[wid] = incl;
+        __syncthreads();
+        uint32_t wbase = 0;
+        for (int w = 0; w < wid; ++w) wbase += warp_tot[w];
+        const uint32_t excl = (uint32_t)carry_s + wbase + incl - v;
+        if (i < nseg) seg_sums[i] = excl;
+        __syncthreads();
+        if (threadIdx.x == 1023) { total64 = carry_s + wbase + incl; carry_s = total64; }
+        __syncthreads();
+    }
+    if (threadIdx.x == 1023) {
+        const unsigned long long tot = nseg ? total64 : 0ull;
+        counters[RGS_CNT_INST] = tot > 0xffffffffull ? 0xffffffffu : (uint32_t)tot;
+        if (tot > (unsigned long long)cap_inst) atomicExch(&counters[RGS_CNT_OVERFLOW], 1u);
+    }
+}
+
+#define EM_BIG 96  // splats covering more tiles than this are emitted by the whole block
+
+__global__ void __launch_bounds__(256) rgs_emit_kernel(const uint32_t* __restrict__ order, const uint2* __restrict__ slot_rect,
+                                                       const uint32_t* __restrict__ counters, uint32_t cap_vis,
+                                                       const uint32_t* __restrict__ seg_excl, uint32_t* __restrict__ tile_keys,
+                                                       uint32_t* __restrict__ vals, uint32_t cap_inst, int tiles_x) {
+    __shared__ uint32_t warp_tot[8];
+    __shared__ uint32_t big_slot[EM_SEG], big_base[EM_SEG];
+    __shared__ uint2 big_rect[EM_SEG];
+    __shared__ uint32_t n_big;
+    // an overflow flagged by the scan kernel zeroes the count here, so nothing is written
+    const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);
+    const uint32_t nseg = (n + EM_SEG - 1) / EM_SEG;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    for (uint32_t s = blockIdx.x; s < nseg; s += gridDim.x) {
+        if (threadIdx.x == 0) n_big = 0;
+        // thread t owns elements s*1024 + 4t .. 4t+3 (consecutive, so the scan order is the element order)
+        uint32_t slot[4], cnt[4];
+        uint2 rect[4];
+        uint32_t mine = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t i = s * EM_SEG + threadIdx.x * 4 + k;
+            if (i < n) { slot[k] = order[i]; rect[k] = slot_rect[slot[k]]; cnt[k] = rect_count(rect[k]); }
+            else { slot[k] = 0; rect[k] = make_uint2(0, 0); cnt[k] = 0; }
+            mine += cnt[k];
+        }
+        uint32_t incl = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += t;
+        }
+        if (lane == 31) warp_tot[wid] = incl;
+        __syncthreads();
+        uint32_t wbase = 0;
+        for (int w = 0; w < wid; ++w) wbase += warp_tot[w];
+        uint32_t base = seg_excl[s] + wbase + incl - mine;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (cnt[k] > EM_BIG) {
+                const uint32_t j = atomicAdd(&n_big, 1u);
+                big_slot[j] = slot[k]; big_base[j] = base; big_rect[j] = rect[k];
+            } else if (cnt[k]) {
+                const int x0 = rect[k].x & 0xffff, y0 = rect[k].x >> 16, x1 = rect[k].y & 0xffff, y1 = rect[k].y >> 16;
+                uint32_t o = base;
+                for (int y = y0; y < y1; ++y)
+                    for (int x = x0; x < x1; ++x, ++o)
+                        if (o < cap_inst) { tile_keys[o] = (uint32_t)(y * tiles_x + x); vals[o] = slot[k]; }
+            }
+            base += cnt[k];
+        }
+        __syncthreads();
+        const uint32_t nb = n_big;
+        for (uint32_t j = 0; j < nb; ++j) {
+            const uint2 r = big_rect[j];
+            const int x0 = r.x & 0xffff, y0 = r.x >> 16, x1 = r.y & 0xffff;
+            const int w = x1 - x0;
+            const uint32_t c = rect_count(r), b0 = big_base[j], sl = big_slot[j];
+            for (uint32_t t = threadIdx.x; t < c; t += 256) {
+                const uint32_t o = b0 + t;
+                if (o < cap_inst) { tile_keys[o] = (uint32_t)((y0 + (int)(t / w)) * tiles_x + x0 + (int)(t % w)); vals[o] = sl; }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void rgs_bs_tile_ranges_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ counters,
+                                          uint32_t cap, int2* __restrict__ ranges, uint32_t num_tiles,
+                                          const uint32_t* __restrict__ vals_src, uint32_t* __restrict__ vals_dst) {
+    const uint32_t n = bs_count(counters, RGS_CNT_INST, cap);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const uint32_t t = keys[i];
+        if (vals_dst) vals_dst[i] = vals_src[i];
+        if (t >= num_tiles) continue;
+        if (i == 0 || keys[i - 1] != t) ranges[t].x = (int)i;
+        if (i == n - 1 || keys[i + 1] != t) ranges[t].y = (int)(i + 1);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------------------------
+static inline uint32_t chunks_of(int64_t n) { int64_t c = (n + BS_CHUNK - 1) / BS_CHUNK; return (uint32_t)(c > 0 ? c : 1); }
+
+static void bs_sort(const uint32_t* keys_first, uint32_t* ka, uint32_t* va, uint32_t* kb, uint32_t* vb, const uint32_t* cnt,
+                    int which, uint32_t cap, int npass, uint32_t* hist, uint32_t* totals, int iota_first, cudaStream_t st,
+                    uint32_t** k_out, uint32_t** v_out) {
+    const uint32_t nchunks_cap = chunks_of(cap);
+    const unsigned grid = nchunks_cap < 148u * 8u ? nchunks_cap : 148u * 8u;
+    const uint32_t* kin = keys_first;
+    uint32_t* vin = va;
+    uint32_t *kout = kb, *vout = vb;
+    for (int p = 0; p < npass; ++p) {
+        rgs_bs_hist_kernel<<<grid, BS_THREADS, 0, st>>>(kin, cnt, which, cap, 8 * p, hist, nchunks_cap);
+        rgs_bs_scan_kernel<<<256, 256, 0, st>>>(hist, totals, cnt, which, cap, nchunks_cap);
+        rgs_bs_scatter_kernel<<<grid, BS_THREADS, 0, st>>>(kin, vin, kout, vout, cnt, which, cap, 8 * p, hist, totals,
+                                                            nchunks_cap, (p == 0 && iota_first) ? 1 : 0);
+        // ping-pong: after the first pass the input buffers are (ka, va) / (kb, vb) alternately
+        kin = kout; vin = vout;
+        if (kout == kb) { kout = ka; vout = va; } else { kout = kb; vout = vb; }
+    }
+    *k_out = const_cast<uint32_t*>(kin);
+    *v_out = vin;
+}
+
+extern "C" {
+
+int rgs_cuda_project_slots(const RgsCamera* cam, const RgsSegment* seg, int64_t id_base, RgsSplat* splats,
+                           int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint32_t* slot_depth, uint32_t* slot_rect,
+                           int32_t* counters, RgsSplatGrad* splat_grads, void* stream) {
+    if (seg->count <= 0) return 0;
+    if (cap_vis > 0x7ffffff0ll || cam->tiles_x > 65535 || cam->tiles_y > 65535) return 10;
+    const unsigned blocks = (unsigned)((seg->count + 255) / 256);
+    rgs_project_slots_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
+        *cam, *seg, id_base, splats, vis_ids, aux, (uint32_t)cap_vis, slot_depth, reinterpret_cast<uint2*>(slot_rect),
+        reinterpret_cast<uint32_t*>(counters), splat_grads);
+    return (int)cudaGetLastError();
+}
+
+// words of uint32 scratch for capacities (cap_vis, cap_inst)
+int64_t rgs_cuda_bin_scratch_words(int64_t cap_vis, int64_t cap_inst) {
+    const int64_t cap = cap_vis > cap_inst ? cap_vis : cap_inst;
+    return 256 * (int64_t)chunks_of(cap) + 256 + (cap_vis + EM_SEG - 1) / EM_SEG + 16;
+}
+
+// Depth-order the visible slots, emit instances in that order, group them by tile.
+//   slot_depth/slot_rect: per slot, from rgs_cuda_project_slots
+//   vis_a/vis_b (u32[cap_vis] x4: key/value ping-pong)  inst_keys/inst_vals/inst_keys_tmp/inst_vals_tmp (u32[cap_inst])
+// Result: inst_vals holds the slots grouped by tile in depth order, ranges[tile] = [start,end).
+int rgs_cuda_bin_instances(const uint32_t* slot_depth, const uint32_t* slot_rect, int64_t cap_vis, uint32_t* vis_ka,
+                           uint32_t* vis_va, uint32_t* vis_kb, uint32_t* vis_vb, uint32_t* inst_keys, uint32_t* inst_vals,
+                           uint32_t* inst_keys_tmp, uint32_t* inst_vals_tmp, int64_t cap_inst, int32_t* counters,
+                           int64_t tiles_x, int64_t num_tiles, int32_t* ranges, uint32_t* scratch, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cap_inst > 0xfffffe00ll) return 10;
+    uint32_t* cnt = reinterpret_cast<uint32_t*>(counters);
+    const int64_t cap = cap_vis > cap_inst ? cap_vis : cap_inst;
+    uint32_t* hist = scratch;
+    uint32_t* totals = scratch + 256 * (size_t)chunks_of(cap);
+    uint32_t* seg_sums = totals + 256;
+    // 1. depth sort of the slots (values start as 0..n-1 == the slots themselves)
+    uint32_t *dk, *order;
+    bs_sort(slot_depth, vis_ka, vis_va, vis_kb, vis_vb, cnt, RGS_CNT_VIS, (uint32_t)cap_vis, 4, hist, totals, 1, st, &dk,
+            &order);
+    // 2. emission in depth order
+    const uint32_t nseg_cap = (uint32_t)((cap_vis + EM_SEG - 1) / EM_SEG);
+    const unsigned egrid = nseg_cap < 148u * 8u ? (nseg_cap ? nseg_cap : 1u) : 148u * 8u;
+    rgs_emit_count_kernel<<<egrid, 256, 0, st>>>(order, reinterpret_cast<const uint2*>(slot_rect), cnt, (uint32_t)cap_vis,
+                                                 seg_sums);
+    rgs_emit_scan_kernel<<<1, 1024, 0, st>>>(seg_sums, cnt, (uint32_t)cap_vis, (uint32_t)cap_inst);
+    rgs_emit_kernel<<<egrid, 256, 0, st>>>(order, reinterpret_cast<const uint2*>(slot_rect), cnt, (uint32_t)cap_vis, seg_sums,
+                                           inst_keys, inst_vals, (uint32_t)cap_inst, (int)tiles_x);
+    // 3. stable sort by tile id
+    int tile_bits = 0;
+    while ((1ll << tile_bits) < num_tiles) ++tile_bits;
+    const int npass = tile_bits <= 8 ? 1 : (tile_bits + 7) / 8;
+    uint32_t *tk, *tv;
+    bs_sort(inst_keys, inst_keys, inst_vals, inst_keys_tmp, inst_vals_tmp, cnt, RGS_CNT_INST, (uint32_t)cap_inst, npass, hist,
+            totals, 0, st, &tk, &tv);
+    RGS_CUDA_CHECK(cudaMemsetAsync(ranges, 0, (size_t)num_tiles * 8, st));
+    const bool in_tmp = (tv != inst_vals);
+    rgs_bs_tile_ranges_kernel<<<148 * 8, 256, 0, st>>>(tk, cnt, (uint32_t)cap_inst, reinterpret_cast<int2*>(ranges),
+                                                       (uint32_t)num_tiles, in_tmp ? tv : nullptr, in_tmp ? inst_vals : nullptr);
+    return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -49,6 +49,61 @@ int rgs_cpu_project_emit(const RgsCamera* cam, const RgsSegment* seg, int64_t id
 }
 
 int64_t rgs_cpu_sort_scratch_words(int64_t) { return 1; }
+int64_t rgs_cpu_bin_scratch_words(int64_t, int64_t) { return 1; }
+
+// CPU twins of the depth-ordered binning (rgs_binning.cu)
+int rgs_cpu_project_slots(const RgsCamera* cam, const RgsSegment* seg, int64_t id_base, RgsSplat* splats,
+                          int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint32_t* slot_depth, uint32_t* slot_rect,
+                          int32_t* counters, RgsSplatGrad* splat_grads, void*) {
+    int64_t n_vis = counters[RGS_CNT_VIS];
+    for (int64_t i = 0; i < seg->count; ++i) {
+        RgsSplat sp; RgsRect rc; int radius; unsigned clamped;
+        if (!rgs_project(*cam, seg->xyz + 3 * i, seg->scale + 3 * i, seg->rot + 4 * i, seg->opacity[i],
+                         seg->sh + 48 * i, sp, rc, radius, clamped))
+            continue;
+        if (n_vis >= cap_vis) { counters[RGS_CNT_OVERFLOW] = 1; continue; }
+        int64_t slot = n_vis++;
+        splats[slot] = sp;
+        vis_ids[slot] = (int32_t)(id_base + i);
+        aux[slot] = ((uint32_t)radius << 3) | clamped;
+        std::memcpy(&slot_depth[slot], &sp.depth, 4);
+        slot_rect[2 * slot] = (uint32_t)rc.x0 | ((uint32_t)rc.y0 << 16);
+        slot_rect[2 * slot + 1] = (uint32_t)rc.x1 | ((uint32_t)rc.y1 << 16);
+        if (splat_grads) std::memset(&splat_grads[slot], 0, sizeof(RgsSplatGrad));
+    }
+    counters[RGS_CNT_VIS] = (int32_t)n_vis;
+    return 0;
+}
+
+int rgs_cpu_bin_instances(const uint32_t* slot_depth, const uint32_t* slot_rect, int64_t cap_vis, uint32_t*, uint32_t*,
+                          uint32_t*, uint32_t*, uint32_t* inst_keys, uint32_t* inst_vals, uint32_t*, uint32_t*,
+                          int64_t cap_inst, int32_t* counters, int64_t tiles_x, int64_t num_tiles, int32_t* ranges,
+                          uint32_t*, void*) {
+    (void)cap_vis;
+    std::memset(ranges, 0, num_tiles * 8);
+    if (counters[RGS_CNT_OVERFLOW]) return 0;
+    const int64_t n = counters[RGS_CNT_VIS];
+    std::vector<uint32_t> order(n);
+    std::iota(order.begin(), order.end(), 0u);
+    std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return slot_depth[a] < slot_depth[b]; });
+    std::vector<std::pair<uint32_t, uint32_t>> inst;
+    for (int64_t i = 0; i < n; ++i) {
+        const uint32_t s = order[i], lo = slot_rect[2 * s], hi = slot_rect[2 * s + 1];
+        for (uint32_t y = lo >> 16; y < (hi >> 16); ++y)
+            for (uint32_t x = lo & 0xffff; x < (hi & 0xffff); ++x) inst.emplace_back((uint32_t)(y * tiles_x + x), s);
+    }
+    counters[RGS_CNT_INST] = (int32_t)std::min<size_t>(inst.size(), 0x7fffffff);
+    if ((int64_t)inst.size() > cap_inst) { counters[RGS_CNT_OVERFLOW] = 1; return 0; }
+    std::stable_sort(inst.begin(), inst.end(), [](const std::pair<uint32_t, uint32_t>& a, const std::pair<uint32_t, uint32_t>& b) { return a.first < b.first; });
+    const int64_t m = (int64_t)inst.size();
+    for (int64_t i = 0; i < m; ++i) {
+        inst_keys[i] = inst[i].first; inst_vals[i] = inst[i].second;
+        const uint32_t t = inst[i].first;
+        if (i == 0 || inst[i - 1].first != t) ranges[2 * t] = (int32_t)i;
+        if (i == m - 1 || inst[i + 1].first != t) ranges[2 * t + 1] = (int32_t)(i + 1);
+    }
+    return 0;
+}
 
 // Sorts the instances by (tile, depth) and writes [start,end) per tile. The sorted lists end up in
 // keys/vals (the *_tmp buffers are scratch, as for the GPU sort).
@@ -165,6 +220,7 @@ int rgs_cpu_geom_bwd(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg,
         float radius = (float)(aux[slot] >> 3);
         float nrm = rgs_project_bwd(*cam, sg->xyz + 3 * i, sg->scale + 3 * i, sg->rot + 4 * i, sg->opacity[i],
                                     sg->sh + 48 * i, clamped, splat_grads[slot], gx, gsh, gs, gq, go);
+        if (sg->touched) sg->touched[i] = 1;
         if (sg->g_xyz) for (int k = 0; k < 3; ++k) sg->g_xyz[3 * i + k] += gx[k];
         if (sg->g_sh) for (int k = 0; k < 48; ++k) sg->g_sh[48 * i + k] += gsh[k];
         if (sg->g_scale) for (int k = 0; k < 3; ++k) sg->g_scale[3 * i + k] += gs[k];
@@ -196,7 +252,8 @@ int rgs_cpu_scatter_radii(const int32_t* counters, const int32_t* vis_ids, const
 // xyz(3) sh(48) scale(3) rot(4) opacity(1); only the first `count` rows of each group are live.
 // `skip` (optional int32) != 0 turns the whole update into a no-op (overflow-guarded commit).
 int rgs_cpu_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t cap, const double* lrs,
-                 double beta1, double beta2, double eps, int64_t step, int64_t zero_grad, const int32_t* skip, void*) {
+                 double beta1, double beta2, double eps, int64_t step, int64_t zero_grad, const int32_t* skip,
+                 const uint8_t* touched, void*) {
     if (skip && skip[RGS_CNT_OVERFLOW]) return 0;
     const int widths[5] = {3, 48, 3, 4, 1};
     float bc1 = (float)(1.0 - std::pow(beta1, (double)step));
@@ -216,8 +273,10 @@ int rgs_cpu_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t 
                 default: lr = (float)lrs[RGS_LR_OPACITY]; break;
             }
             int64_t k = off + e;
-            rgs_adam_elem(p[k], g[k], m[k], v[k], lr, (float)beta1, (float)beta2, (float)eps, bc1, bc2s);
-            if (zero_grad) g[k] = 0.f;
+            const bool t = touched ? touched[e / w] != 0 : true;
+            if (!t && m[k] == 0.f && v[k] == 0.f) continue;  // zero gradient, zero moments: the update is exactly zero
+            rgs_adam_elem(p[k], t ? g[k] : 0.f, m[k], v[k], lr, (float)beta1, (float)beta2, (float)eps, bc1, bc2s);
+            if (zero_grad && t) g[k] = 0.f;
         }
         off += cap * w;
     }

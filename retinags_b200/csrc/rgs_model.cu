@@ -25,7 +25,8 @@ __global__ void __launch_bounds__(256) rgs_adam_kernel(float* __restrict__ p, fl
                                                        float* __restrict__ v, int64_t count, int64_t cap,
                                                        const __grid_constant__ RgsLrTable lrs, float beta1, float beta2,
                                                        float eps, float bc1, float bc2s, int zero_grad,
-                                                       const uint32_t* __restrict__ skip) {
+                                                       const uint32_t* __restrict__ skip,
+                                                       const uint8_t* __restrict__ touched) {
     if (skip && skip[RGS_CNT_OVERFLOW]) return;
     const int widths[5] = {3, 48, 3, 4, 1};
     int64_t nvec[5], voff[5], goff[5];
@@ -44,8 +45,18 @@ __global__ void __launch_bounds__(256) rgs_adam_kernel(float* __restrict__ p, fl
         const int64_t e0 = (t - voff[grp]) * 4, live = count * w;
         const int64_t base = goff[grp] + e0;
         if (e0 + 3 < live) {
-            float4 P = *reinterpret_cast<float4*>(p + base), G = *reinterpret_cast<float4*>(g + base);
+            // rows whose `touched` byte is 0 hold zero gradients: skip the gradient read and clear, and when the
+            // moments are zero as well the whole update is exactly zero and nothing is written
+            bool any = true;
+            if (touched) {
+                any = touched[e0 / w] | touched[(e0 + 1) / w] | touched[(e0 + 2) / w] | touched[(e0 + 3) / w];
+            }
             float4 M = *reinterpret_cast<float4*>(m + base), V = *reinterpret_cast<float4*>(v + base);
+            float4 G = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (any) G = *reinterpret_cast<float4*>(g + base);
+            else if (M.x == 0.f && M.y == 0.f && M.z == 0.f && M.w == 0.f && V.x == 0.f && V.y == 0.f && V.z == 0.f && V.w == 0.f)
+                continue;
+            float4 P = *reinterpret_cast<float4*>(p + base);
             const int c0 = (int)(e0 % w);
             rgs_adam_elem(P.x, G.x, M.x, V.x, adam_lr(lrs, grp, c0 % w), beta1, beta2, eps, bc1, bc2s);
             rgs_adam_elem(P.y, G.y, M.y, V.y, adam_lr(lrs, grp, (c0 + 1) % w), beta1, beta2, eps, bc1, bc2s);
@@ -54,13 +65,15 @@ __global__ void __launch_bounds__(256) rgs_adam_kernel(float* __restrict__ p, fl
             *reinterpret_cast<float4*>(p + base) = P;
             *reinterpret_cast<float4*>(m + base) = M;
             *reinterpret_cast<float4*>(v + base) = V;
-            if (zero_grad) *reinterpret_cast<float4*>(g + base) = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (zero_grad && any) *reinterpret_cast<float4*>(g + base) = make_float4(0.f, 0.f, 0.f, 0.f);
         } else {
             for (int k = 0; k < 4 && e0 + k < live; ++k) {
                 const int col = (int)((e0 + k) % w);
-                rgs_adam_elem(p[base + k], g[base + k], m[base + k], v[base + k], adam_lr(lrs, grp, col), beta1, beta2,
-                              eps, bc1, bc2s);
-                if (zero_grad) g[base + k] = 0.f;
+                const bool t = touched ? touched[(e0 + k) / w] != 0 : true;
+                if (!t && m[base + k] == 0.f && v[base + k] == 0.f) continue;
+                rgs_adam_elem(p[base + k], t ? g[base + k] : 0.f, m[base + k], v[base + k], adam_lr(lrs, grp, col), beta1,
+                              beta2, eps, bc1, bc2s);
+                if (zero_grad && t) g[base + k] = 0.f;
             }
         }
     }
@@ -69,7 +82,8 @@ __global__ void __launch_bounds__(256) rgs_adam_kernel(float* __restrict__ p, fl
 extern "C" {
 
 int rgs_cuda_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t cap, const double* lrs, double beta1,
-                  double beta2, double eps, int64_t step, int64_t zero_grad, const int32_t* skip, void* stream) {
+                  double beta2, double eps, int64_t step, int64_t zero_grad, const int32_t* skip, const uint8_t* touched,
+                  void* stream) {
     if (count <= 0) return 0;
     if (cap % 4 != 0) return 13;
     RgsLrTable t;
@@ -81,7 +95,7 @@ int rgs_cuda_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t
     const unsigned blocks = (unsigned)(want > 148 * 64 ? 148 * 64 : want);
     rgs_adam_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, count, cap, t, (float)beta1, (float)beta2,
                                                              (float)eps, bc1, bc2s, (int)zero_grad,
-                                                             reinterpret_cast<const uint32_t*>(skip));
+                                                             reinterpret_cast<const uint32_t*>(skip), touched);
     return (int)cudaGetLastError();
 }
 

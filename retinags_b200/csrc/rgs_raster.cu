@@ -313,22 +313,31 @@ __global__ void __launch_bounds__(128) rgs_geom_bwd_kernel(
 #pragma unroll
         for (int k = 0; k < 48; ++k) gsh[k] = 0.f;
         const float nrm = rgs_project_bwd(cam, p, s, q, sg.opacity[i], sg.sh + 48 * i, a & 7u, g, gx, gsh, gs, gq, go);
-        if (sg.g_xyz) { sg.g_xyz[3 * i] += gx[0]; sg.g_xyz[3 * i + 1] += gx[1]; sg.g_xyz[3 * i + 2] += gx[2]; }
-        if (sg.g_scale) { sg.g_scale[3 * i] += gs[0]; sg.g_scale[3 * i + 1] += gs[1]; sg.g_scale[3 * i + 2] += gs[2]; }
+        // first writer of this row in this step stores, later ones (other views of the batch) add
+        bool first = false;
+        if (sg.touched) { first = sg.touched[i] == 0; if (first) sg.touched[i] = 1; }
+        if (sg.g_xyz) {
+            if (first) { sg.g_xyz[3 * i] = gx[0]; sg.g_xyz[3 * i + 1] = gx[1]; sg.g_xyz[3 * i + 2] = gx[2]; }
+            else { sg.g_xyz[3 * i] += gx[0]; sg.g_xyz[3 * i + 1] += gx[1]; sg.g_xyz[3 * i + 2] += gx[2]; }
+        }
+        if (sg.g_scale) {
+            if (first) { sg.g_scale[3 * i] = gs[0]; sg.g_scale[3 * i + 1] = gs[1]; sg.g_scale[3 * i + 2] = gs[2]; }
+            else { sg.g_scale[3 * i] += gs[0]; sg.g_scale[3 * i + 1] += gs[1]; sg.g_scale[3 * i + 2] += gs[2]; }
+        }
         if (sg.g_rot) {
             float4* d = reinterpret_cast<float4*>(sg.g_rot) + i;
-            float4 o = *d;
+            float4 o = first ? make_float4(0.f, 0.f, 0.f, 0.f) : *d;
             o.x += gq[0]; o.y += gq[1]; o.z += gq[2]; o.w += gq[3];
             *d = o;
         }
-        if (sg.g_opacity) sg.g_opacity[i] += go[0];
+        if (sg.g_opacity) { if (first) sg.g_opacity[i] = go[0]; else sg.g_opacity[i] += go[0]; }
         if (sg.g_sh) {
             const int nc4 = ((cam.sh_degree + 1) * (cam.sh_degree + 1) * 3 + 3) / 4;
             float4* d = reinterpret_cast<float4*>(sg.g_sh + 48 * i);
 #pragma unroll
             for (int k = 0; k < 12; ++k) {
                 if (k < nc4) {
-                    float4 o = d[k];
+                    float4 o = first ? make_float4(0.f, 0.f, 0.f, 0.f) : d[k];
                     o.x += gsh[4 * k]; o.y += gsh[4 * k + 1]; o.z += gsh[4 * k + 2]; o.w += gsh[4 * k + 3];
                     d[k] = o;
                 }

@@ -45,6 +45,7 @@ class GaussianStore:
         self.step = 0
         self.params = self.grads = self.exp_avg = self.exp_avg_sq = None
         self.grad_accum = self.denom = self.max_radii = None
+        self.touched = None  # uint8 per row: a gradient was written this step (rows with 0 hold zero gradients)
         self._alloc(_round_cap(capacity))
 
     # -- storage --------------------------------------------------------------------------------
@@ -60,9 +61,13 @@ class GaussianStore:
         self.grad_accum = torch.zeros(cap, dtype=torch.float32, device=dev)
         self.denom = torch.zeros(cap, dtype=torch.float32, device=dev)
         self.max_radii = torch.zeros(cap, dtype=torch.float32, device=dev)
+        # gradients do not survive a reallocation: the invariant "untouched rows are zero" restarts
+        self.touched = torch.zeros(cap, dtype=torch.uint8, device=dev)
         if old[0] is not None and old[5] > 0:
             n, ocap = old[5], old[4]
-            for new_buf, old_buf in zip((self.params, self.grads, self.exp_avg, self.exp_avg_sq), old[:4]):
+            for new_buf, old_buf in zip((self.params, None, self.exp_avg, self.exp_avg_sq), old[:4]):
+                if new_buf is None:
+                    continue
                 for (_, nv), (_, ov) in zip(self._views(new_buf, cap, n), self._views(old_buf, ocap, n)):
                     nv.copy_(ov)
             for nb, ob in zip((self.grad_accum, self.denom, self.max_radii), old_stats):
@@ -91,6 +96,7 @@ class GaussianStore:
             v.copy_(g[name].reshape(n, -1).to(self.device))
         for which in ("grads", "exp_avg", "exp_avg_sq"):
             getattr(self, which).zero_()
+        self.touched.zero_()
         self.reset_stats()
 
     def reset_stats(self):
@@ -111,6 +117,7 @@ class GaussianStore:
         if with_grads:
             g = self.views("grads")
             seg.g_xyz, seg.g_sh, seg.g_scale, seg.g_rot, seg.g_opacity = g["xyz"], g["sh"], g["scale"], g["rot"], g["opacity"]
+            seg.touched = self.touched[:self.count]
             if with_stats:
                 seg.stat_grad = self.grad_accum[:self.count]
                 seg.stat_denom = self.denom[:self.count]
@@ -155,7 +162,8 @@ class GaussianStore:
         """Keep the selected rows (stable order) in all buffers and statistics."""
         idx = mask_or_index.nonzero(as_tuple=True)[0] if mask_or_index.dtype == torch.bool else mask_or_index
         n = int(idx.numel())
-        for which in ("params", "grads", "exp_avg", "exp_avg_sq"):
+        self.zero_grad()  # surgery drops the gradients of the step
+        for which in ("params", "exp_avg", "exp_avg_sq"):
             buf = getattr(self, which)
             full = dict(self._views(buf, self.cap, self.cap))
             for name in NAMES:
@@ -191,10 +199,21 @@ class GaussianStore:
         import ctypes
         arr = (ctypes.c_double * 6)(*[float(x) for x in lrs])
         native.call("adam", self.device, self.params, self.grads, self.exp_avg, self.exp_avg_sq, self.count, self.cap, arr,
-                    float(beta1), float(beta2), float(eps), self.step, 1 if zero_grad else 0, skip)
+                    float(beta1), float(beta2), float(eps), self.step, 1 if zero_grad else 0, skip,
+                    self.touched if zero_grad else None)
+        if zero_grad:
+            self.touched.zero_()
+
+    def mark_touched(self, index: torch.Tensor | None = None):
+        """Declare that gradient rows were written outside the render kernels (all rows when ``index`` is None)."""
+        if index is None:
+            self.touched[:self.count] = 1
+        else:
+            self.touched[index] = 1
 
     def zero_grad(self):
         self.grads.zero_()
+        self.touched.zero_()
 
     # -- optimiser state files ------------------------------------------------------------------
     def optimizer_state_dict(self, lrs=None) -> dict:

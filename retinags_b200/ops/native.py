@@ -26,12 +26,14 @@ _LIBS: dict[str, ctypes.CDLL] = {}
 SIGNATURES = {
     "project_emit": "ppipppippippp",
     "sort_ranges": "ppppipippp",
+    "project_slots": "ppipppippppp",
+    "bin_instances": "ppippppppppipiippp",
     "blend_fwd": "ppppppppp",
     "blend_fwd_push": "ppppppppipppp",
     "blend_bwd": "pppppppppp",
     "geom_bwd": "ppipppppip",
     "scatter_radii": "pppiipp",
-    "adam": "ppppiipfffiipp",
+    "adam": "ppppiipfffiippp",
     "composite_fwd": "pipiiiippp",
     "composite_bwd": "ppipiiiipp",
     "ssim_fwd": "ppiiiiiippp",
@@ -72,7 +74,7 @@ class RgsSegment(ctypes.Structure):
 
     _fields_ = [(n, ctypes.c_void_p) for n in (
         "xyz", "sh", "scale", "rot", "opacity", "g_xyz", "g_sh", "g_scale", "g_rot", "g_opacity",
-        "g_mean2d", "stat_grad", "stat_denom", "stat_maxrad")] + [("count", ctypes.c_int64)]
+        "g_mean2d", "stat_grad", "stat_denom", "stat_maxrad", "touched")] + [("count", ctypes.c_int64)]
 
 
 CNT_VIS, CNT_INST, CNT_OVERFLOW, CNT_STATUS, CNT_WORDS = 0, 1, 2, 3, 8
@@ -149,6 +151,9 @@ def _count_launches(name: str, args) -> int:
         tiles = max(int(args[6]), 1)
         bits = 32 + max(tiles - 1, 0).bit_length()
         return 3 * ((bits + 7) // 8) + 1
+    if name == "bin_instances":
+        tiles = max(int(args[14]), 1)
+        return 3 * 4 + 3 + 3 * max(1, (max(tiles - 1, 0).bit_length() + 7) // 8) + 1
     return _KERNELS.get(name, 1)
 
 

@@ -73,6 +73,7 @@ class Segment:
     stat_grad: torch.Tensor | None = None
     stat_denom: torch.Tensor | None = None
     stat_maxrad: torch.Tensor | None = None
+    touched: torch.Tensor | None = None  # uint8 (count): see RgsSegment.touched
 
     @property
     def count(self) -> int:
@@ -90,6 +91,10 @@ class Segment:
             if t is not None:
                 assert t.is_contiguous() and t.dtype == torch.float32, name
             setattr(s, name, None if t is None else t.data_ptr())
+        tt = self.touched if with_grads else None
+        if tt is not None:
+            assert tt.is_contiguous() and tt.dtype == torch.uint8
+        s.touched = None if tt is None else tt.data_ptr()
         s.count = self.count
         return s
 
@@ -116,7 +121,52 @@ class SortScratch:
         self.cap = cap_inst
 
 
+class BinScratch:
+    """Transient buffers of the depth-ordered binning (rgs_binning.cu), shared by all tasks of a device."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.cap_vis = self.cap_inst = 0
+        self.words_n = 0
+
+    def ensure(self, cap_vis: int, cap_inst: int):
+        dev = self.device
+        grown = False
+        if cap_vis > self.cap_vis:
+            self.cap_vis = cap_vis
+            self.slot_depth = torch.empty(cap_vis, dtype=torch.int32, device=dev)
+            self.slot_rect = torch.empty(cap_vis, dtype=torch.int64, device=dev)
+            self.vis = [torch.empty(cap_vis, dtype=torch.int32, device=dev) for _ in range(4)]
+            grown = True
+        if cap_inst > self.cap_inst:
+            self.cap_inst = cap_inst
+            self.inst_keys = torch.empty(cap_inst, dtype=torch.int32, device=dev)
+            self.inst_keys_tmp = torch.empty(cap_inst, dtype=torch.int32, device=dev)
+            self.inst_vals_tmp = torch.empty(cap_inst, dtype=torch.int32, device=dev)
+            grown = True
+        if grown:
+            kind = "cuda" if dev.type == "cuda" else "cpu"
+            fn = getattr(native.lib(kind), f"rgs_{kind}_bin_scratch_words")
+            fn.argtypes = [ctypes.c_int64, ctypes.c_int64]
+            fn.restype = ctypes.c_int64
+            self.words = torch.empty(int(fn(self.cap_vis, self.cap_inst)), dtype=torch.int32, device=dev)
+
+
 _SCRATCH: dict[str, SortScratch] = {}
+_BIN_SCRATCH: dict[str, BinScratch] = {}
+
+
+def bin_scratch(device: torch.device) -> BinScratch:
+    key = str(device)
+    if key not in _BIN_SCRATCH:
+        _BIN_SCRATCH[key] = BinScratch(device)
+    return _BIN_SCRATCH[key]
+
+
+def release_scratch():
+    """Drop the shared sort/binning buffers (they are re-created on demand)."""
+    _SCRATCH.clear()
+    _BIN_SCRATCH.clear()
 
 
 def sort_scratch(device: torch.device) -> SortScratch:
@@ -129,8 +179,11 @@ def sort_scratch(device: torch.device) -> SortScratch:
 class RenderTask:
     """State of one rasterisation, kept between forward and backward."""
 
-    def __init__(self, device, inst_per_gaussian: float = 4.0, min_inst: int = 1 << 16):
+    def __init__(self, device, inst_per_gaussian: float = 4.0, min_inst: int = 1 << 16, binning: str = "depth_first"):
         self.device = torch.device(device)
+        # "depth_first": sort visible splats by depth, emit in order, 2-pass tile sort (rgs_binning.cu);
+        # "keyed": emit 64-bit (tile|depth) keys and sort them in 6 passes (rgs_raster.cu + rgs_sort.cu)
+        self.binning = binning
         self.inst_per_gaussian = inst_per_gaussian
         self.min_inst = min_inst
         self.cap_vis = 0
@@ -171,9 +224,10 @@ class RenderTask:
     def _grow_inst(self, cap: int):
         cap = int(min(max(cap, self.min_inst), 0xFFFFFF00))
         self.cap_inst = cap
-        self.keys = torch.empty(cap, dtype=torch.int64, device=self.device)
         self.vals = torch.empty(cap, dtype=torch.int32, device=self.device)
-        sort_scratch(self.device).ensure(cap)
+        if self.binning == "keyed":
+            self.keys = torch.empty(cap, dtype=torch.int64, device=self.device)
+            sort_scratch(self.device).ensure(cap)
 
     # -- forward ------------------------------------------------------------------------------
     def forward(self, cam: RgsCamera, segments: list[Segment], want_depth: bool = False, out: torch.Tensor | None = None,
@@ -192,16 +246,28 @@ class RenderTask:
             dst = self.out if out is None else out
             self.counters.zero_()
             base = 0
-            for seg in segments:
-                if seg.count:
-                    native.call("project_emit", self.device, cam, seg.struct(False), base, self.splats, self.vis_ids,
-                                self.aux, self.cap_vis, self.keys, self.vals, self.cap_inst, self.counters,
-                                self.splat_grads)
-                base += seg.count
-            sc = sort_scratch(self.device)
-            sc.ensure(self.cap_inst)
-            native.call("sort_ranges", self.device, self.keys, self.vals, sc.keys_tmp, sc.vals_tmp, self.cap_inst,
-                        self.counters, cam.tiles_x * cam.tiles_y, self.ranges, sc.words)
+            if self.binning == "keyed":
+                for seg in segments:
+                    if seg.count:
+                        native.call("project_emit", self.device, cam, seg.struct(False), base, self.splats, self.vis_ids,
+                                    self.aux, self.cap_vis, self.keys, self.vals, self.cap_inst, self.counters,
+                                    self.splat_grads)
+                    base += seg.count
+                sc = sort_scratch(self.device)
+                sc.ensure(self.cap_inst)
+                native.call("sort_ranges", self.device, self.keys, self.vals, sc.keys_tmp, sc.vals_tmp, self.cap_inst,
+                            self.counters, cam.tiles_x * cam.tiles_y, self.ranges, sc.words)
+            else:
+                bs = bin_scratch(self.device)
+                bs.ensure(self.cap_vis, self.cap_inst)
+                for seg in segments:
+                    if seg.count:
+                        native.call("project_slots", self.device, cam, seg.struct(False), base, self.splats, self.vis_ids,
+                                    self.aux, self.cap_vis, bs.slot_depth, bs.slot_rect, self.counters, self.splat_grads)
+                    base += seg.count
+                native.call("bin_instances", self.device, bs.slot_depth, bs.slot_rect, self.cap_vis, bs.vis[0], bs.vis[1],
+                            bs.vis[2], bs.vis[3], bs.inst_keys, self.vals, bs.inst_keys_tmp, bs.inst_vals_tmp,
+                            self.cap_inst, self.counters, cam.tiles_x, cam.tiles_y * cam.tiles_x, self.ranges, bs.words)
             if push is None:
                 native.call("blend_fwd", self.device, cam, self.ranges, self.vals, self.splats, dst,
                             self.depth if want_depth else None, self.n_contrib, self.counters)

@@ -192,3 +192,4 @@ class BorderExchange:
             gv[name].index_add_(0, idx, g[:, off:off + w])
             off += w
         store.grad_accum[:store.count].index_add_(0, idx, g[:, off])
+        store.mark_touched(idx)

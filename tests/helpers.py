@@ -16,9 +16,10 @@ def activated(g):
                 rot=g["rot"] / g["rot"].norm(dim=1, keepdim=True), opacity=torch.sigmoid(g["opacity"]))
 
 
-def native_render(g, cam, sh_degree, box=(None, None), raw=True, tight=True, device="cpu", want_depth=False):
+def native_render(g, cam, sh_degree, box=(None, None), raw=True, tight=True, device="cpu", want_depth=False,
+                  binning="depth_first"):
     seg = rasterize.Segment(*(g[k].to(device).contiguous() for k in ("xyz", "sh", "scale", "rot", "opacity")))
-    task = rasterize.RenderTask(device)
+    task = rasterize.RenderTask(device, binning=binning)
     c = rasterize.make_camera(cam, sh_degree, box[0], box[1], raw_params=raw, tight_rect=tight)
     out = task.forward(c, [seg], want_depth=want_depth, check=True)
     return out, task, seg, c

@@ -18,6 +18,13 @@ def test_forward_matches_oracle(deg):
         torch.testing.assert_close(task.depth, D, atol=1e-4, rtol=1e-4)
 
 
+def test_binning_variants_agree():
+    g, cams = small_scene(n=1500)
+    a, ta, _, _ = native_render(g, cams[2], 3, binning="depth_first")
+    b, tb, _, _ = native_render(g, cams[2], 3, binning="keyed")
+    assert torch.equal(a, b) and ta.n_inst == tb.n_inst and torch.equal(ta.n_contrib, tb.n_contrib)
+
+
 def test_tight_rect_is_exact():
     g, cams = small_scene(n=1500)
     a, ta, _, _ = native_render(g, cams[0], 3, tight=True)

@@ -31,6 +31,7 @@ def test_adam_matches_torch():
         f_rest.grad = gr[:, 1:].clone()
         gv["sh"].copy_(gr.view(n, 48))
         opt.step()
+        st.mark_touched()
         st.adam_step(lrs)
         assert float(st.grads.abs().sum()) == 0.0
     p = st.views()
@@ -73,3 +74,32 @@ def test_records_and_surgery():
     st2.set_params({k: v for k, v in st.views().items()})
     st2.load_optimizer_state_dict(sd)
     torch.testing.assert_close(st2.records("exp_avg"), st.records("exp_avg"))
+
+
+def test_untouched_rows_follow_dense_adam():
+    """Rows without a gradient this step still decay their moments and move by momentum, exactly like dense Adam
+    with a zero gradient; rows that never had a gradient are skipped and stay put."""
+    g = synthetic.uniform_gaussians(12, 4, sh_degree=3)
+    lrs = (1e-3,) * 6
+    a, b = GaussianStore(12, "cpu"), GaussianStore(12, "cpu")
+    a.set_params(g); b.set_params(g)
+    gen = torch.Generator().manual_seed(0)
+    rows = torch.tensor([0, 3, 7])
+    for step in range(4):
+        full = torch.randn(12, 59, generator=gen) * 1e-2
+        if step >= 2:
+            full[:] = 0  # later steps: nobody visible
+        for st in (a, b):
+            gv = st.views("grads")
+            off = 0
+            for name, w in zip(("xyz", "sh", "scale", "rot", "opacity"), (3, 48, 3, 4, 1)):
+                gv[name][rows] = full[rows, off:off + w]
+                off += w
+        a.mark_touched()            # dense: every row is read
+        if step < 2:
+            b.mark_touched(rows)    # sparse bookkeeping: only rows that received a gradient
+        a.adam_step(lrs); b.adam_step(lrs)
+    torch.testing.assert_close(a.records(), b.records(), atol=0, rtol=0)
+    torch.testing.assert_close(a.records("exp_avg"), b.records("exp_avg"), atol=0, rtol=0)
+    untouched = torch.tensor([1, 2, 4, 5, 6, 8, 9, 10, 11])
+    torch.testing.assert_close(b.records()[untouched], torch.cat([g[k] for k in ("xyz", "sh", "scale", "rot", "opacity")], 1)[untouched])
