@@ -37,6 +37,7 @@ def parse_args():
     ap.add_argument("--transport", default="auto", choices=["auto", "peer", "nccl"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--phases", action="store_true", help="also time the phases of a step (extra loop, after the timed one)")
     return ap.parse_args()
 
 
@@ -46,11 +47,14 @@ class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    # nvidia-smi stalls the GPU for ~0.1 s while it attaches, so the sampler is started before the warm-up
+    # steps and only the samples taken between mark_begin() and stop() are used.
 
     def __init__(self, index: int):
         self.index = index
         self.proc = None
-        self.lines: list[str] = []
+        self.lines: list[tuple[float, str]] = []
+        self.t_begin = 0.0
 
     def start(self):
         try:
@@ -64,7 +68,10 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def mark_begin(self):
+        self.t_begin = time.time()
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -77,7 +84,9 @@ class ClockSampler:
             self.proc.kill()
         sm, smax, reasons, power = [], [], set(), []
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for ln in self.lines:
+        for stamp, ln in self.lines:
+            if stamp < self.t_begin:
+                continue
             parts = [x.strip() for x in ln.split(",")]
             if len(parts) < 8:
                 continue
@@ -114,13 +123,14 @@ def run_own(args):
                         height=args.height, batch=args.batch, n_views=(args.steps + args.warmup) * args.batch,
                         gt_gaussians=args.gt_gaussians, transport=args.transport, seed=args.seed)
     # ---- device-timed region ------------------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for i in range(args.warmup):
         sess.step(i)
         sess.settle()
     sess.sync()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    sampler.mark_begin()
     sess.reset_launch_count()
     sess.barrier()
     torch.cuda.synchronize()
@@ -158,6 +168,14 @@ def run_own(args):
         wall = float(tw.item())
         e2e = {"value": args.steps * args.batch / wall, "unit": "views/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "last_loss": loss}
+    phases = None
+    if args.phases:
+        sess.engine.timer.enabled = True
+        sess.engine.timer.reset()
+        for i in range(args.steps):
+            sess.step(args.warmup + i)
+        phases = sess.engine.timer.table(args.steps)
+        sess.engine.timer.enabled = False
     if rank == 0:
         value = args.steps * args.batch / (ms / 1e3)
         out = {
@@ -172,7 +190,7 @@ def run_own(args):
                        "l2": "inputs larger than L2 (parameter blocks of >= 1.8 GB per GPU are streamed every step)",
                        "visible_splats_per_view": sess.last_info.get("n_vis"),
                        "instances_per_view": sess.last_info.get("n_inst"), "overflow_in_timed_region": overflow},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "phases_ms_per_step_max_over_ranks": phases,
         }
         print(json.dumps(out), flush=True)
     if world > 1:

@@ -302,22 +302,21 @@ __global__ void __launch_bounds__(1024) rgs_emit_scan_kernel(uint32_t* __restric
     }
 }
 
-#define EM_BIG 96  // splats covering more tiles than this are emitted by the whole block
-
+// Emission: a block scans the tile counts of its 1024 depth-ordered splats, parks (slot, rect, base) in
+// shared memory, then every warp walks its 128 splats and the 32 lanes write one splat's tiles together
+// (consecutive lanes -> consecutive instances: coalesced stores instead of one long loop per thread).
 __global__ void __launch_bounds__(256) rgs_emit_kernel(const uint32_t* __restrict__ order, const uint2* __restrict__ slot_rect,
                                                        const uint32_t* __restrict__ counters, uint32_t cap_vis,
                                                        const uint32_t* __restrict__ seg_excl, uint32_t* __restrict__ tile_keys,
                                                        uint32_t* __restrict__ vals, uint32_t cap_inst, int tiles_x) {
     __shared__ uint32_t warp_tot[8];
-    __shared__ uint32_t big_slot[EM_SEG], big_base[EM_SEG];
-    __shared__ uint2 big_rect[EM_SEG];
-    __shared__ uint32_t n_big;
+    __shared__ uint32_t s_slot[EM_SEG], s_base[EM_SEG];
+    __shared__ uint2 s_rect[EM_SEG];
     // an overflow flagged by the scan kernel zeroes the count here, so nothing is written
     const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);
     const uint32_t nseg = (n + EM_SEG - 1) / EM_SEG;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     for (uint32_t s = blockIdx.x; s < nseg; s += gridDim.x) {
-        if (threadIdx.x == 0) n_big = 0;
         // thread t owns elements s*1024 + 4t .. 4t+3 (consecutive, so the scan order is the element order)
         uint32_t slot[4], cnt[4];
         uint2 rect[4];
@@ -342,28 +341,22 @@ __global__ void __launch_bounds__(256) rgs_emit_kernel(const uint32_t* __restric
         uint32_t base = seg_excl[s] + wbase + incl - mine;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            if (cnt[k] > EM_BIG) {
-                const uint32_t j = atomicAdd(&n_big, 1u);
-                big_slot[j] = slot[k]; big_base[j] = base; big_rect[j] = rect[k];
-            } else if (cnt[k]) {
-                const int x0 = rect[k].x & 0xffff, y0 = rect[k].x >> 16, x1 = rect[k].y & 0xffff, y1 = rect[k].y >> 16;
-                uint32_t o = base;
-                for (int y = y0; y < y1; ++y)
-                    for (int x = x0; x < x1; ++x, ++o)
-                        if (o < cap_inst) { tile_keys[o] = (uint32_t)(y * tiles_x + x); vals[o] = slot[k]; }
-            }
+            const int e = threadIdx.x * 4 + k;
+            s_slot[e] = slot[k]; s_base[e] = base; s_rect[e] = rect[k];
             base += cnt[k];
         }
         __syncthreads();
-        const uint32_t nb = n_big;
-        for (uint32_t j = 0; j < nb; ++j) {
-            const uint2 r = big_rect[j];
-            const int x0 = r.x & 0xffff, y0 = r.x >> 16, x1 = r.y & 0xffff;
-            const int w = x1 - x0;
-            const uint32_t c = rect_count(r), b0 = big_base[j], sl = big_slot[j];
-            for (uint32_t t = threadIdx.x; t < c; t += 256) {
+        for (int j = 0; j < EM_SEG / 8; ++j) {
+            const int e = wid * (EM_SEG / 8) + j;
+            const uint2 r = s_rect[e];
+            const uint32_t c = rect_count(r);
+            if (c == 0) continue;
+            const int x0 = r.x & 0xffff, y0 = r.x >> 16, w = (int)(r.y & 0xffff) - x0;
+            const uint32_t b0 = s_base[e], sl = s_slot[e];
+            for (uint32_t t = lane; t < c; t += 32) {
                 const uint32_t o = b0 + t;
-                if (o < cap_inst) { tile_keys[o] = (uint32_t)((y0 + (int)(t / w)) * tiles_x + x0 + (int)(t % w)); vals[o] = sl; }
+                const uint32_t ty = t / (uint32_t)w, tx = t - ty * (uint32_t)w;
+                if (o < cap_inst) { tile_keys[o] = (uint32_t)((y0 + (int)ty) * tiles_x + x0 + (int)tx); vals[o] = sl; }
             }
         }
         __syncthreads();

@@ -256,8 +256,8 @@ int rgs_cpu_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t 
                  const uint8_t* touched, void*) {
     if (skip && skip[RGS_CNT_OVERFLOW]) return 0;
     const int widths[5] = {3, 48, 3, 4, 1};
-    float bc1 = (float)(1.0 - std::pow(beta1, (double)step));
-    float bc2s = (float)std::sqrt(1.0 - std::pow(beta2, (double)step));
+    float bc1 = (float)(1.0 / (1.0 - std::pow(beta1, (double)step)));
+    float bc2s = (float)(1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step)));
     int64_t off = 0;
     for (int grp = 0; grp < 5; ++grp) {
         int w = widths[grp];

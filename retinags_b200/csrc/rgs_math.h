@@ -553,11 +553,11 @@ RGS_HD bool rgs_blend_bwd_step(const RgsCamera& cam, const RgsPixelRay& ray, flo
 // Adam over the parameter block
 // ------------------------------------------------------------------------------------------
 RGS_HD void rgs_adam_elem(float& p, float g, float& m, float& v, float lr, float beta1, float beta2, float eps,
-                          float bc1, float bc2_sqrt) {
+                          float inv_bc1, float inv_bc2_sqrt) {
     // torch.optim.Adam: m = b1 m + (1-b1) g ; v = b2 v + (1-b2) g^2 ;
-    // p -= lr / bc1 * m / (sqrt(v)/sqrt(bc2) + eps)
+    // p -= lr / bc1 * m / (sqrt(v)/sqrt(bc2) + eps); the two bias corrections arrive as reciprocals
     m = beta1 * m + (1.0f - beta1) * g;
     v = beta2 * v + (1.0f - beta2) * g * g;
-    float denom = sqrtf(v) / bc2_sqrt + eps;
-    p -= (lr / bc1) * (m / denom);
+    const float denom = sqrtf(v) * inv_bc2_sqrt + eps;
+    p -= (lr * inv_bc1) * (m / denom);
 }

@@ -21,6 +21,51 @@ __device__ __forceinline__ float adam_lr(const RgsLrTable& t, int grp, int col) 
     }
 }
 
+// Update of one float4 (or the ragged tail) of a column group of compile-time width W, so that the row / column
+// arithmetic is multiplications by constants instead of 64-bit divisions.
+template <int W, int GRP>
+__device__ __forceinline__ void adam_vec(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
+                                         float* __restrict__ v, int64_t e0, int64_t live, int64_t goff,
+                                         const RgsLrTable& lrs, float beta1, float beta2, float eps, float bc1, float bc2s,
+                                         int zero_grad, const uint8_t* __restrict__ touched) {
+    const int64_t base = goff + e0;
+    if (e0 + 3 < live) {
+        // rows whose `touched` byte is 0 hold zero gradients: skip the gradient read and clear, and when the
+        // moments are zero as well the whole update is exactly zero and nothing is written
+        bool any = true;
+        if (touched) {
+            const int64_t r0 = e0 / W, r3 = (e0 + 3) / W;
+            any = touched[r0] != 0;
+            if (W < 4) { any = any || touched[(e0 + 1) / W] || touched[(e0 + 2) / W]; }
+            if (r3 != r0) any = any || touched[r3];
+        }
+        float4 M = *reinterpret_cast<float4*>(m + base), V = *reinterpret_cast<float4*>(v + base);
+        float4 G = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (any) G = *reinterpret_cast<float4*>(g + base);
+        else if (M.x == 0.f && M.y == 0.f && M.z == 0.f && M.w == 0.f && V.x == 0.f && V.y == 0.f && V.z == 0.f && V.w == 0.f)
+            return;
+        float4 P = *reinterpret_cast<float4*>(p + base);
+        const int c0 = (int)(e0 % W);
+        rgs_adam_elem(P.x, G.x, M.x, V.x, adam_lr(lrs, GRP, c0 % W), beta1, beta2, eps, bc1, bc2s);
+        rgs_adam_elem(P.y, G.y, M.y, V.y, adam_lr(lrs, GRP, (c0 + 1) % W), beta1, beta2, eps, bc1, bc2s);
+        rgs_adam_elem(P.z, G.z, M.z, V.z, adam_lr(lrs, GRP, (c0 + 2) % W), beta1, beta2, eps, bc1, bc2s);
+        rgs_adam_elem(P.w, G.w, M.w, V.w, adam_lr(lrs, GRP, (c0 + 3) % W), beta1, beta2, eps, bc1, bc2s);
+        *reinterpret_cast<float4*>(p + base) = P;
+        *reinterpret_cast<float4*>(m + base) = M;
+        *reinterpret_cast<float4*>(v + base) = V;
+        if (zero_grad && any) *reinterpret_cast<float4*>(g + base) = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+        for (int k = 0; k < 4 && e0 + k < live; ++k) {
+            const int col = (int)((e0 + k) % W);
+            const bool t = touched ? touched[(e0 + k) / W] != 0 : true;
+            if (!t && m[base + k] == 0.f && v[base + k] == 0.f) continue;
+            rgs_adam_elem(p[base + k], t ? g[base + k] : 0.f, m[base + k], v[base + k], adam_lr(lrs, GRP, col), beta1, beta2,
+                          eps, bc1, bc2s);
+            if (zero_grad && t) g[base + k] = 0.f;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) rgs_adam_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
                                                        float* __restrict__ v, int64_t count, int64_t cap,
                                                        const __grid_constant__ RgsLrTable lrs, float beta1, float beta2,
@@ -28,54 +73,16 @@ __global__ void __launch_bounds__(256) rgs_adam_kernel(float* __restrict__ p, fl
                                                        const uint32_t* __restrict__ skip,
                                                        const uint8_t* __restrict__ touched) {
     if (skip && skip[RGS_CNT_OVERFLOW]) return;
-    const int widths[5] = {3, 48, 3, 4, 1};
-    int64_t nvec[5], voff[5], goff[5];
-    int64_t tv = 0, to = 0;
-#pragma unroll
-    for (int k = 0; k < 5; ++k) {
-        nvec[k] = (count * widths[k] + 3) / 4;
-        voff[k] = tv; goff[k] = to;
-        tv += nvec[k]; to += cap * widths[k];
-    }
+    // vector ranges of the five groups: xyz(3) sh(48) scale(3) rot(4) opacity(1)
+    const int64_t n0 = (count * 3 + 3) / 4, n1 = count * 12, n2 = n0, n3 = count, n4 = (count + 3) / 4;
+    const int64_t v1 = n0, v2 = v1 + n1, v3 = v2 + n2, v4 = v3 + n3, tv = v4 + n4;
+    const int64_t o1 = cap * 3, o2 = o1 + cap * 48, o3 = o2 + cap * 3, o4 = o3 + cap * 4;
     for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < tv; t += (int64_t)gridDim.x * blockDim.x) {
-        int grp = 0;
-#pragma unroll
-        for (int k = 1; k < 5; ++k) if (t >= voff[k]) grp = k;
-        const int w = widths[grp];
-        const int64_t e0 = (t - voff[grp]) * 4, live = count * w;
-        const int64_t base = goff[grp] + e0;
-        if (e0 + 3 < live) {
-            // rows whose `touched` byte is 0 hold zero gradients: skip the gradient read and clear, and when the
-            // moments are zero as well the whole update is exactly zero and nothing is written
-            bool any = true;
-            if (touched) {
-                any = touched[e0 / w] | touched[(e0 + 1) / w] | touched[(e0 + 2) / w] | touched[(e0 + 3) / w];
-            }
-            float4 M = *reinterpret_cast<float4*>(m + base), V = *reinterpret_cast<float4*>(v + base);
-            float4 G = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (any) G = *reinterpret_cast<float4*>(g + base);
-            else if (M.x == 0.f && M.y == 0.f && M.z == 0.f && M.w == 0.f && V.x == 0.f && V.y == 0.f && V.z == 0.f && V.w == 0.f)
-                continue;
-            float4 P = *reinterpret_cast<float4*>(p + base);
-            const int c0 = (int)(e0 % w);
-            rgs_adam_elem(P.x, G.x, M.x, V.x, adam_lr(lrs, grp, c0 % w), beta1, beta2, eps, bc1, bc2s);
-            rgs_adam_elem(P.y, G.y, M.y, V.y, adam_lr(lrs, grp, (c0 + 1) % w), beta1, beta2, eps, bc1, bc2s);
-            rgs_adam_elem(P.z, G.z, M.z, V.z, adam_lr(lrs, grp, (c0 + 2) % w), beta1, beta2, eps, bc1, bc2s);
-            rgs_adam_elem(P.w, G.w, M.w, V.w, adam_lr(lrs, grp, (c0 + 3) % w), beta1, beta2, eps, bc1, bc2s);
-            *reinterpret_cast<float4*>(p + base) = P;
-            *reinterpret_cast<float4*>(m + base) = M;
-            *reinterpret_cast<float4*>(v + base) = V;
-            if (zero_grad && any) *reinterpret_cast<float4*>(g + base) = make_float4(0.f, 0.f, 0.f, 0.f);
-        } else {
-            for (int k = 0; k < 4 && e0 + k < live; ++k) {
-                const int col = (int)((e0 + k) % w);
-                const bool t = touched ? touched[(e0 + k) / w] != 0 : true;
-                if (!t && m[base + k] == 0.f && v[base + k] == 0.f) continue;
-                rgs_adam_elem(p[base + k], t ? g[base + k] : 0.f, m[base + k], v[base + k], adam_lr(lrs, grp, col), beta1,
-                              beta2, eps, bc1, bc2s);
-                if (zero_grad && t) g[base + k] = 0.f;
-            }
-        }
+        if (t < v1) adam_vec<3, 0>(p, g, m, v, t * 4, count * 3, 0, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched);
+        else if (t < v2) adam_vec<48, 1>(p, g, m, v, (t - v1) * 4, count * 48, o1, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched);
+        else if (t < v3) adam_vec<3, 2>(p, g, m, v, (t - v2) * 4, count * 3, o2, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched);
+        else if (t < v4) adam_vec<4, 3>(p, g, m, v, (t - v3) * 4, count * 4, o3, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched);
+        else adam_vec<1, 4>(p, g, m, v, (t - v4) * 4, count, o4, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched);
     }
 }
 
@@ -88,8 +95,8 @@ int rgs_cuda_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t
     if (cap % 4 != 0) return 13;
     RgsLrTable t;
     for (int k = 0; k < 6; ++k) t.lr[k] = (float)lrs[k];
-    const float bc1 = (float)(1.0 - pow(beta1, (double)step));
-    const float bc2s = (float)sqrt(1.0 - pow(beta2, (double)step));
+    const float bc1 = (float)(1.0 / (1.0 - pow(beta1, (double)step)));       // reciprocal bias corrections
+    const float bc2s = (float)(1.0 / sqrt(1.0 - pow(beta2, (double)step)));
     const int64_t tv = (count * 59 + 3) / 4 + 5;
     const int64_t want = (tv + 255) / 256;
     const unsigned blocks = (unsigned)(want > 148 * 64 ? 148 * 64 : want);

@@ -19,6 +19,7 @@ from .models.gaussians import GaussianStore
 from .ops.loss import CompositeLoss
 from .ops.rasterize import RenderTask, Segment, make_camera
 from .parallel.compositing import LocalTransport, ViewPlan, band_rows, extended
+from .utils.profiler import PhaseTimer
 
 
 @dataclass
@@ -42,6 +43,7 @@ class StepEngine:
         self.background = tuple(background)
         self.tight_rect = tight_rect
         self.borrow = borrow  # optional BorderExchange (parallel/border.py)
+        self.timer = PhaseTimer(self.device, enabled=False)
         self._tasks: dict = {}
         self._grads: dict = {}
         self._closs: dict = {}
@@ -149,12 +151,16 @@ class StepEngine:
     def train_step(self, cams: list[Camera], relations, sh_degree: int, lrs, optimizer_step: bool = True,
                    background=None) -> StepResult:
         bg = self.background if background is None else background
+        T = self.timer.phase
         plans = self.plan(cams, relations)
         self._prepare_transport(plans)
         if self.borrow is not None:
-            self.borrow.refresh(self.stores, need_grads=True)
-        local_out = self.render_partials(cams, plans, sh_degree)
-        slots = self.transport.exchange_partials(plans, local_out)
+            with T("border_exchange"):
+                self.borrow.refresh(self.stores, need_grads=True)
+        with T("render_forward"):
+            local_out = self.render_partials(cams, plans, sh_degree)
+        with T("exchange_partials"):
+            slots = self.transport.exchange_partials(plans, local_out)
         if hasattr(self.transport, "local_grad_images"):
             local_grad = self.transport.local_grad_images(plans)
         else:
@@ -162,31 +168,36 @@ class StepEngine:
                                    if r == self.rank} for p in plans}
         gslots = self.transport.grad_slots(plans, local_grad)
         sums = []
-        for p, cam in zip(plans, cams):
-            cl = self._loss(p.view, p.H, p.W)
-            b = p.bands[self.rank]
-            if b[1] <= b[0]:
-                sums.append(torch.zeros(3, dtype=torch.float64, device=self.device))
-                continue
-            e = (max(0, b[0] - 10), min(p.H, b[1] + 10))
-            gt = self._gt_rows(p.view, cam, (max(0, b[0] - 5), min(p.H, b[1] + 5)))
-            cl.composite(slots[p.view], bg, e[0], e[1])
-            sums.append(cl.loss(gt, self.lambda_dssim, b[0], b[1]).clone())
-            cl.backward(slots[p.view], gslots[p.view], bg, b[0], b[1])
-        self.transport.return_grads(plans, gslots, local_grad)
-        for p in plans:
-            for m, r in zip(p.models, p.ranks):
-                if r == self.rank:
-                    self._task(p.view, m).backward(local_grad[p.view][m], self._segments(m, True))
+        with T("composite_loss"):
+            for p, cam in zip(plans, cams):
+                cl = self._loss(p.view, p.H, p.W)
+                b = p.bands[self.rank]
+                if b[1] <= b[0]:
+                    sums.append(torch.zeros(3, dtype=torch.float64, device=self.device))
+                    continue
+                e = (max(0, b[0] - 10), min(p.H, b[1] + 10))
+                gt = self._gt_rows(p.view, cam, (max(0, b[0] - 5), min(p.H, b[1] + 5)))
+                cl.composite(slots[p.view], bg, e[0], e[1])
+                sums.append(cl.loss(gt, self.lambda_dssim, b[0], b[1]).clone())
+                cl.backward(slots[p.view], gslots[p.view], bg, b[0], b[1])
+        with T("return_grads"):
+            self.transport.return_grads(plans, gslots, local_grad)
+        with T("render_backward"):
+            for p in plans:
+                for m, r in zip(p.models, p.ranks):
+                    if r == self.rank:
+                        self._task(p.view, m).backward(local_grad[p.view][m], self._segments(m, True))
         if self.borrow is not None:
-            self.borrow.return_grads(self.stores)
+            with T("border_return"):
+                self.borrow.return_grads(self.stores)
         if optimizer_step:
             self.optimizer_step(lrs, plans)
         return StepResult(sums=sums, plans=plans)
 
     def optimizer_step(self, lrs, plans=None):
-        for m, st in self.stores.items():
-            st.adam_step(lrs)
+        with self.timer.phase("adam"):
+            for m, st in self.stores.items():
+                st.adam_step(lrs)
 
     def poll(self) -> dict:
         """After a host synchronisation: read the counters of all tasks (grows buffers when needed)."""

@@ -1,0 +1,75 @@
+"""Per-phase timing and tracing.
+
+``PhaseTimer`` brackets the phases of a step with CUDA events on the launching stream (no host
+synchronisation until the numbers are read) and NVTX ranges, so a step can be read in a profiler timeline or
+reduced to a per-phase table (maximum over ranks for multi-GPU numbers).  On CPU ranks it falls back to
+``time.perf_counter``.  The reference only has a whole-iteration CUDA-event timer
+(``trainer4tree_partition.py:590,613,641-643``) and an unused ``NaiveTimer`` (``utils/workload_utils.py:61-81``).
+"""
+from __future__ import annotations
+
+import contextlib
+import time
+from collections import defaultdict
+
+import torch
+
+
+class PhaseTimer:
+    def __init__(self, device, enabled: bool = False, nvtx: bool = True):
+        self.device = torch.device(device)
+        self.enabled = enabled
+        self.cuda = self.device.type == "cuda"
+        self.nvtx = nvtx and self.cuda
+        self._pending: list[tuple[str, object, object]] = []
+        self.totals: dict[str, float] = defaultdict(float)
+        self.counts: dict[str, int] = defaultdict(int)
+
+    @contextlib.contextmanager
+    def phase(self, name: str):
+        if not self.enabled:
+            yield
+            return
+        if self.nvtx:
+            torch.cuda.nvtx.range_push(name)
+        if self.cuda:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(torch.cuda.current_stream(self.device))
+        else:
+            a, b = time.perf_counter(), None
+        try:
+            yield
+        finally:
+            if self.cuda:
+                b.record(torch.cuda.current_stream(self.device))
+                self._pending.append((name, a, b))
+            else:
+                self.totals[name] += (time.perf_counter() - a) * 1e3
+                self.counts[name] += 1
+            if self.nvtx:
+                torch.cuda.nvtx.range_pop()
+
+    def collect(self) -> dict[str, float]:
+        """Fold the pending event pairs into ``totals`` (synchronises the device once)."""
+        if self.cuda and self._pending:
+            torch.cuda.synchronize(self.device)
+            for name, a, b in self._pending:
+                self.totals[name] += a.elapsed_time(b)
+                self.counts[name] += 1
+            self._pending.clear()
+        return dict(self.totals)
+
+    def reset(self):
+        self._pending.clear()
+        self.totals.clear()
+        self.counts.clear()
+
+    def table(self, steps: int = 1, group=None) -> dict[str, float]:
+        """ms per step and phase; with a process group the maximum over ranks."""
+        tot = self.collect()
+        names = sorted(tot)
+        vals = torch.tensor([tot[n] / max(steps, 1) for n in names], dtype=torch.float64,
+                            device=self.device if self.cuda else "cpu")
+        if group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()):
+            torch.distributed.all_reduce(vals, op=torch.distributed.ReduceOp.MAX, group=group)
+        return {n: float(v) for n, v in zip(names, vals.tolist())}

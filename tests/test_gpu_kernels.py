@@ -40,8 +40,8 @@ def test_binning_variants_agree_on_gpu():
         a, ta, _, _ = native_render(g, cam, 3, device="cuda", binning="depth_first")
         b, tb, _, _ = native_render(g, cam, 3, device="cuda", binning="keyed")
         assert ta.n_vis == tb.n_vis and ta.n_inst == tb.n_inst
-        # equal depths may be ordered differently by the two pipelines (slot numbering differs): allow rounding
-        assert_mostly_close(a, b, atol=1e-6, rtol=1e-5)
+        # splats of exactly equal depth are ordered by slot number, which differs between the pipelines
+        assert_mostly_close(a, b, atol=1e-5, rtol=1e-4, max_frac=1e-2)
         ref, tr, _, _ = native_render(g, cam, 3, device="cpu", binning="depth_first")
         assert tr.n_inst == ta.n_inst
         assert_mostly_close(a.cpu(), ref, atol=3e-5, rtol=1e-4)
