@@ -45,6 +45,7 @@ def main(argv=None) -> int:
     dbg.addHandler(logging.FileHandler(f"debugger/debug_{rank}_{time.strftime('%Y_%m_%d_%H')}.txt", mode="a"))
     dbg.setLevel(logging.INFO)
     code = 0
+    trainer = None
     try:
         from .trainer import Trainer
         scene = None
@@ -58,9 +59,11 @@ def main(argv=None) -> int:
             trainer.train()
         if rank == 0 and not args.quiet:
             print("\nTraining complete." if not args.EVAL_ONLY else "\nEvaluation complete.")
-    except Exception:
+    except Exception as exc:
         dbg.error(traceback.format_exc())
         traceback.print_exc()
+        if trainer is not None and getattr(trainer, "watchdog", None) is not None:
+            trainer.watchdog.report_failure(repr(exc))  # peers stop at their next step instead of hanging
         code = 1
     finally:
         if dist.is_initialized():

@@ -113,6 +113,15 @@ class Trainer:
         self.test_rlt = self._relation(self.test_dataset, "testset_relation.pt")
         self._gen = torch.Generator(device=self.device)
         self._gen.manual_seed(1234 + self.rank)
+        self.watchdog = None
+        if self.world > 1 and getattr(args, "WATCHDOG_TIMEOUT", 120.0) > 0:
+            from .parallel.watchdog import Watchdog
+            try:
+                base = dist.distributed_c10d._get_default_store()
+                self.watchdog = Watchdog(dist.PrefixStore("rgs_watchdog", base), self.rank, self.world, interval=2.0,
+                                         timeout=float(getattr(args, "WATCHDOG_TIMEOUT", 120.0))).start()
+            except Exception as exc:  # a backend without a reachable store: run without host heartbeats
+                self.logger.warning("watchdog disabled: %r", exc)
 
     # ------------------------------------------------------------------------------------------------
     # set-up helpers
@@ -321,6 +330,8 @@ class Trainer:
             for st in self.stores.values():
                 st.active_sh_degree = sh_deg
             for ids in groups:
+                if self.watchdog is not None:
+                    self.watchdog.check()  # a dead peer is noticed here, before the next kernels and collectives
                 cams = self._fetch(self.train_dataset, ids)
                 bs = len(cams)
                 t0 = time.perf_counter()

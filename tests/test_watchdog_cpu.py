@@ -1,0 +1,73 @@
+"""Failure detection on the host: heartbeats over a torch.distributed store, faults injected by the test."""
+import os
+import sys
+import time
+
+import pytest
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from retinags_b200.parallel.watchdog import PeerFailure, Watchdog
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_silent_peer_is_detected():
+    store = dist.HashStore()
+    a = Watchdog(store, 0, 2, interval=0.05, timeout=0.4).start()
+    b = Watchdog(store, 1, 2, interval=0.05, timeout=0.4).start()
+    time.sleep(0.3)
+    a.check(); b.check()          # both alive
+    b.stop()                      # rank 1 goes silent (no kernel, no collective in flight)
+    deadline = time.time() + 5
+    while a.failed is None and time.time() < deadline:
+        time.sleep(0.05)
+    with pytest.raises(PeerFailure, match="rank 1"):
+        a.check()
+    a.stop()
+
+
+def test_reported_failure_propagates_immediately():
+    store = dist.HashStore()
+    hits = []
+    a = Watchdog(store, 0, 2, interval=0.05, timeout=60.0, on_failure=hits.append).start()
+    b = Watchdog(store, 1, 2, interval=0.05, timeout=60.0).start()
+    b.report_failure("ValueError: boom")
+    deadline = time.time() + 5
+    while a.failed is None and time.time() < deadline:
+        time.sleep(0.05)
+    with pytest.raises(PeerFailure, match="boom"):
+        a.check()
+    assert hits and "boom" in hits[0]
+    a.stop(); b.stop()
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=__import__("datetime").timedelta(seconds=30))
+    wd = Watchdog(store, rank, world, interval=0.1, timeout=1.0).start()
+    try:
+        for step in range(100):
+            wd.check()
+            if rank == 1 and step == 3:
+                raise RuntimeError("injected fault on rank 1")  # raised between steps
+            time.sleep(0.1)
+        result = "finished"
+    except PeerFailure as exc:
+        result = f"peer failure: {exc}"
+    except RuntimeError as exc:
+        wd.report_failure(repr(exc))
+        result = "raised"
+        time.sleep(1.0)  # keep the store reachable until the peers have read the report
+    open(os.path.join(out_dir, f"r{rank}.txt"), "w").write(result)
+    wd.stop()
+
+
+@pytest.mark.timeout(120)
+def test_rank_that_raises_stops_the_others(tmp_path):
+    port = 29900 + os.getpid() % 90
+    mp.spawn(_worker, args=(3, port, str(tmp_path)), nprocs=3, join=True)
+    res = [open(os.path.join(tmp_path, f"r{r}.txt")).read() for r in range(3)]
+    assert res[1] == "raised"
+    assert res[0].startswith("peer failure") and "injected fault" in res[0]
+    assert res[2].startswith("peer failure")
