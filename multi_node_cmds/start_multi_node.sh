@@ -11,7 +11,7 @@ GPUS_PER_NODE=${GPUS_PER_NODE:-8}
 REPO=${REPO:-$(cd "$(dirname "$0")/.." && pwd)}
 NNODES=${#HOSTS[@]}
 for i in "${!HOSTS[@]}"; do
-  ssh "${HOSTS[$i]}" "cd $REPO && NCCL_SOCKET_TIMEOUT=60000 nohup python -m torch.distributed.run --nnodes=$NNODES \
+  ssh "${HOSTS[$i]}" "cd $REPO && NCCL_SOCKET_TIMEOUT=60000 nohup setsid python -m torch.distributed.run --nnodes=$NNODES \
     --node_rank=$i --nproc_per_node=$GPUS_PER_NODE --master_addr=$MASTER_ADDR --master_port=$MASTER_PORT main.py $* \
     > train_node$i.log 2>&1 & echo \$! > torchrun_$i.pid" &
 done

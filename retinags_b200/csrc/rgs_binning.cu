@@ -76,6 +76,134 @@ __global__ void __launch_bounds__(256) rgs_project_slots_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------
+// two-phase projection: a cheap conservative cull over all Gaussians, then the full projection on survivors
+// ---------------------------------------------------------------------------------------------
+// Phase 1 reads 24 bytes per Gaussian (position, scale) and keeps a Gaussian unless it is provably culled by
+// the exact projection: behind the near plane, or its screen rectangle (centre +- an upper bound of the
+// 3-sigma radius) misses the image. The radius bound uses ||J W||_2 <= ||J||_F with the clamped Jacobian of
+// rgs_ewa and the largest scale; it is never smaller than the exact radius, so no visible splat is lost.
+__global__ void __launch_bounds__(256) rgs_cull_kernel(const __grid_constant__ RgsCamera cam, const float* __restrict__ xyz,
+                                                       const float* __restrict__ scale, int64_t count, int64_t id_base,
+                                                       uint32_t* __restrict__ cand, uint32_t cap_cand,
+                                                       uint32_t* __restrict__ counters) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    bool keep = false;
+    if (i < count) {
+        const float p[3] = {xyz[3 * i], xyz[3 * i + 1], xyz[3 * i + 2]};
+        float t[3];
+        rgs_view_point(cam.view, p, t);
+        if (t[2] > RGS_NEAR_Z) {
+            float s0 = scale[3 * i], s1 = scale[3 * i + 1], s2 = scale[3 * i + 2];
+            if (cam.raw_params) { s0 = expf(s0); s1 = expf(s1); s2 = expf(s2); }
+            const float smax = fmaxf(s0, fmaxf(s1, s2)) * cam.scale_modifier;
+            const float tz = t[2], itz = 1.0f / tz;
+            const float limx = 1.3f * cam.tan_fovx, limy = 1.3f * cam.tan_fovy;
+            const float ax = fminf(limx, fabsf(t[0] * itz)), ay = fminf(limy, fabsf(t[1] * itz));
+            const float fx = cam.focal_x * itz, fy = cam.focal_y * itz;
+            const float jf2 = fx * fx * (1.0f + ax * ax) + fy * fy * (1.0f + ay * ay);
+            // +0.3 low-pass, +0.32 because rgs_project floors the eigenvalue discriminant at 0.1 (sqrt(0.1) < 0.32)
+            const float rad = ceilf(3.0f * sqrtf(smax * smax * jf2 + 0.62f)) * 1.0001f + 1.0f;
+            const float* m = cam.proj;
+            const float hx = m[0] * p[0] + m[4] * p[1] + m[8] * p[2] + m[12];
+            const float hy = m[1] * p[0] + m[5] * p[1] + m[9] * p[2] + m[13];
+            const float hw = m[3] * p[0] + m[7] * p[1] + m[11] * p[2] + m[15];
+            const float pw = 1.0f / (hw + 0.0000001f);
+            const float px = rgs_ndc2pix(hx * pw, cam.W), py = rgs_ndc2pix(hy * pw, cam.H);
+            // same rectangle rule as rgs_project, with the enlarged radius; NaNs fall through as "keep"
+            keep = !(px + rad + RGS_TILE - 1 < 0.0f || px - rad >= (float)(cam.tiles_x * RGS_TILE) ||
+                     py + rad + RGS_TILE - 1 < 0.0f || py - rad >= (float)(cam.tiles_y * RGS_TILE));
+        }
+    }
+    __shared__ uint32_t warp_n[8];
+    __shared__ uint32_t base_s;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const uint32_t mask = __ballot_sync(0xffffffffu, keep);
+    if (lane == 0) warp_n[wid] = __popc(mask);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t tot = 0;
+        for (int w = 0; w < 8; ++w) { uint32_t v = warp_n[w]; warp_n[w] = tot; tot += v; }
+        uint32_t b = 0;
+        if (tot) {
+            b = atomicAdd(&counters[RGS_CNT_CAND], tot);
+            if (b + tot > cap_cand) { atomicExch(&counters[RGS_CNT_OVERFLOW], 1u); b = 0xffffffffu; }
+        }
+        base_s = b;
+    }
+    __syncthreads();
+    if (keep && base_s != 0xffffffffu) cand[base_s + warp_n[wid] + __popc(mask & ((1u << lane) - 1u))] = (uint32_t)(id_base + i);
+}
+
+struct RgsSegs4 { RgsSegment s[4]; int n; };
+
+// Phase 2: full projection of the candidates (dense: every thread has work).
+__global__ void __launch_bounds__(256) rgs_project_cand_kernel(
+    const __grid_constant__ RgsCamera cam, const __grid_constant__ RgsSegs4 segs, const uint32_t* __restrict__ cand,
+    uint32_t cap_cand, RgsSplat* __restrict__ splats, int32_t* __restrict__ vis_ids, uint32_t* __restrict__ aux,
+    const uint32_t cap_vis, uint32_t* __restrict__ slot_depth, uint2* __restrict__ slot_rect, uint32_t* __restrict__ counters,
+    RgsSplatGrad* __restrict__ splat_grads) {
+    __shared__ uint32_t warp_vis[8];
+    __shared__ uint32_t base_vis;
+    __shared__ int drop;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    uint32_t n = counters[RGS_CNT_OVERFLOW] ? 0u : counters[RGS_CNT_CAND];
+    if (n > cap_cand) n = cap_cand;
+    const uint32_t nblk = (n + 255) / 256;
+    for (uint32_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
+        const uint32_t c = blk * 256 + threadIdx.x;
+        bool ok = false;
+        RgsSplat sp;
+        RgsRect rc;
+        int radius = 0;
+        unsigned clamped = 0;
+        uint32_t gid = 0;
+        if (c < n) {
+            gid = cand[c];
+            int64_t i = gid;
+            int sidx = 0;
+            while (sidx < segs.n - 1 && i >= segs.s[sidx].count) { i -= segs.s[sidx].count; ++sidx; }
+            const RgsSegment& seg = segs.s[sidx];
+            float p[3] = {seg.xyz[3 * i], seg.xyz[3 * i + 1], seg.xyz[3 * i + 2]};
+            float s[3] = {seg.scale[3 * i], seg.scale[3 * i + 1], seg.scale[3 * i + 2]};
+            float4 q4 = reinterpret_cast<const float4*>(seg.rot)[i];
+            float q[4] = {q4.x, q4.y, q4.z, q4.w};
+            ok = rgs_project(cam, p, s, q, seg.opacity[i], seg.sh + 48 * i, sp, rc, radius, clamped);
+        }
+        const uint32_t vmask = __ballot_sync(0xffffffffu, ok);
+        if (lane == 0) warp_vis[wid] = __popc(vmask);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t tv = 0;
+            for (int w = 0; w < 8; ++w) { uint32_t v = warp_vis[w]; warp_vis[w] = tv; tv += v; }
+            uint32_t bv = 0;
+            int d = 0;
+            if (tv) {
+                bv = atomicAdd(&counters[RGS_CNT_VIS], tv);
+                if (bv + tv > cap_vis) { atomicExch(&counters[RGS_CNT_OVERFLOW], 1u); d = 1; }
+            }
+            base_vis = bv; drop = d;
+        }
+        __syncthreads();
+        if (ok && !drop) {
+            const uint32_t slot = base_vis + warp_vis[wid] + __popc(vmask & ((1u << lane) - 1u));
+            float4* dst = reinterpret_cast<float4*>(splats + slot);
+            dst[0] = make_float4(sp.px, sp.py, sp.ca, sp.cb);
+            dst[1] = make_float4(sp.cc, sp.opacity, sp.r, sp.g);
+            dst[2] = make_float4(sp.b, sp.w, sp.depth, 0.f);
+            vis_ids[slot] = (int32_t)gid;
+            aux[slot] = ((uint32_t)radius << 3) | clamped;
+            slot_depth[slot] = __float_as_uint(sp.depth);
+            slot_rect[slot] = make_uint2((uint32_t)rc.x0 | ((uint32_t)rc.y0 << 16), (uint32_t)rc.x1 | ((uint32_t)rc.y1 << 16));
+            if (splat_grads) {
+                float4* gz = reinterpret_cast<float4*>(splat_grads + slot);
+                gz[0] = make_float4(0.f, 0.f, 0.f, 0.f); gz[1] = gz[0]; gz[2] = gz[0];
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // radix sort of (u32 key, u32 value) pairs; count read from counters[which]
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t bs_count(const uint32_t* counters, int which, uint32_t cap) {
@@ -413,6 +541,34 @@ int rgs_cuda_project_slots(const RgsCamera* cam, const RgsSegment* seg, int64_t 
     rgs_project_slots_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
         *cam, *seg, id_base, splats, vis_ids, aux, (uint32_t)cap_vis, slot_depth, reinterpret_cast<uint2*>(slot_rect),
         reinterpret_cast<uint32_t*>(counters), splat_grads);
+    return (int)cudaGetLastError();
+}
+
+// Two-phase variant of rgs_cuda_project_slots over up to 4 segments: cull all, then project the survivors.
+// `cand` holds cap_cand uint32 candidate ids (scratch owned by the caller).
+int rgs_cuda_project_slots2(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg, uint32_t* cand, int64_t cap_cand,
+                            RgsSplat* splats, int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint32_t* slot_depth,
+                            uint32_t* slot_rect, int32_t* counters, RgsSplatGrad* splat_grads, void* stream) {
+    if (nseg < 1 || nseg > 4) return 11;
+    if (cap_vis > 0x7ffffff0ll || cap_cand > 0x7ffffff0ll || cam->tiles_x > 65535 || cam->tiles_y > 65535) return 10;
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t* cnt = reinterpret_cast<uint32_t*>(counters);
+    RgsSegs4 s4;
+    s4.n = (int)nseg;
+    int64_t base = 0;
+    for (int k = 0; k < (int)nseg; ++k) {
+        s4.s[k] = segs[k];
+        if (segs[k].count > 0) {
+            const unsigned blocks = (unsigned)((segs[k].count + 255) / 256);
+            rgs_cull_kernel<<<blocks, 256, 0, st>>>(*cam, segs[k].xyz, segs[k].scale, segs[k].count, base, cand,
+                                                    (uint32_t)cap_cand, cnt);
+        }
+        base += segs[k].count;
+    }
+    const int64_t want = (cap_cand + 255) / 256;
+    const unsigned grid = (unsigned)(want < 1 ? 1 : (want > 148 * 8 ? 148 * 8 : want));
+    rgs_project_cand_kernel<<<grid, 256, 0, st>>>(*cam, s4, cand, (uint32_t)cap_cand, splats, vis_ids, aux, (uint32_t)cap_vis,
+                                                  slot_depth, reinterpret_cast<uint2*>(slot_rect), cnt, splat_grads);
     return (int)cudaGetLastError();
 }
 

@@ -75,6 +75,17 @@ int rgs_cpu_project_slots(const RgsCamera* cam, const RgsSegment* seg, int64_t i
     return 0;
 }
 
+int rgs_cpu_project_slots2(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg, uint32_t*, int64_t,
+                           RgsSplat* splats, int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint32_t* slot_depth,
+                           uint32_t* slot_rect, int32_t* counters, RgsSplatGrad* splat_grads, void* stream) {
+    int64_t base = 0;
+    for (int64_t k = 0; k < nseg; ++k) {
+        rgs_cpu_project_slots(cam, &segs[k], base, splats, vis_ids, aux, cap_vis, slot_depth, slot_rect, counters, splat_grads, stream);
+        base += segs[k].count;
+    }
+    return 0;
+}
+
 int rgs_cpu_bin_instances(const uint32_t* slot_depth, const uint32_t* slot_rect, int64_t cap_vis, uint32_t*, uint32_t*,
                           uint32_t*, uint32_t*, uint32_t* inst_keys, uint32_t* inst_vals, uint32_t*, uint32_t*,
                           int64_t cap_inst, int32_t* counters, int64_t tiles_x, int64_t num_tiles, int32_t* ranges,

@@ -54,6 +54,7 @@ class StepEngine:
         key = (view, mid)
         if key not in self._tasks:
             self._tasks[key] = RenderTask(self.device)
+        self._tasks[key].timer = self.timer if self.timer.enabled else None
         return self._tasks[key]
 
     def _grad(self, view: int, mid: int, H: int, W: int) -> torch.Tensor:

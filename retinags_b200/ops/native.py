@@ -27,6 +27,7 @@ SIGNATURES = {
     "project_emit": "ppipppippippp",
     "sort_ranges": "ppppipippp",
     "project_slots": "ppipppippppp",
+    "project_slots2": "ppipipppippppp",
     "bin_instances": "ppippppppppipiippp",
     "blend_fwd": "ppppppppp",
     "blend_fwd_push": "ppppppppipppp",
@@ -136,7 +137,7 @@ def stream_ptr(device: torch.device):
 
 
 # kernels launched by one call of an entry point (the radix sort's count depends on the tile count)
-_KERNELS = {"project_emit": 1, "blend_fwd": 1, "blend_bwd": 1, "geom_bwd": 1, "scatter_radii": 1, "adam": 1,
+_KERNELS = {"project_slots": 1, "project_slots2": 2, "project_emit": 1, "blend_fwd": 1, "blend_bwd": 1, "geom_bwd": 1, "scatter_radii": 1, "adam": 1,
             "composite_fwd": 1, "composite_bwd": 1, "ssim_fwd": 1, "ssim_bwd": 1}
 _LAUNCHES = [0]
 

@@ -198,6 +198,11 @@ class RenderTask:
         self.splats = self.vis_ids = self.aux = self.keys = self.vals = self.ranges = None
         self.out = self.depth = self.n_contrib = self.splat_grads = None
         self.total_count = 0
+        self.timer = None  # optional utils.profiler.PhaseTimer for per-kernel-group timing
+
+    def _phase(self, name: str):
+        import contextlib
+        return self.timer.phase(name) if self.timer is not None else contextlib.nullcontext()
 
     # -- buffers ------------------------------------------------------------------------------
     def _ensure(self, n_gauss: int, H: int, W: int, want_depth: bool):
@@ -260,21 +265,26 @@ class RenderTask:
             else:
                 bs = bin_scratch(self.device)
                 bs.ensure(self.cap_vis, self.cap_inst)
-                for seg in segments:
-                    if seg.count:
-                        native.call("project_slots", self.device, cam, seg.struct(False), base, self.splats, self.vis_ids,
-                                    self.aux, self.cap_vis, bs.slot_depth, bs.slot_rect, self.counters, self.splat_grads)
-                    base += seg.count
-                native.call("bin_instances", self.device, bs.slot_depth, bs.slot_rect, self.cap_vis, bs.vis[0], bs.vis[1],
-                            bs.vis[2], bs.vis[3], bs.inst_keys, self.vals, bs.inst_keys_tmp, bs.inst_vals_tmp,
-                            self.cap_inst, self.counters, cam.tiles_x, cam.tiles_y * cam.tiles_x, self.ranges, bs.words)
-            if push is None:
-                native.call("blend_fwd", self.device, cam, self.ranges, self.vals, self.splats, dst,
-                            self.depth if want_depth else None, self.n_contrib, self.counters)
-            else:  # (n, row0[], row1[], dst[]): also store the rows into the owners' compositing slots
-                native.call("blend_fwd_push", self.device, cam, self.ranges, self.vals, self.splats, dst,
-                            self.depth if want_depth else None, self.n_contrib, self.counters, push[0], push[1],
-                            push[2], push[3])
+                # two-phase projection: conservative cull of everything, full projection of the survivors;
+                # the candidate list reuses a ping-pong buffer of the depth sort (free until then)
+                structs = (RgsSegment * len(segments))(*[s.struct(False) for s in segments])
+                with self._phase("fwd.project"):
+                    native.call("project_slots2", self.device, cam, structs, len(segments), bs.vis[3], self.cap_vis,
+                                self.splats, self.vis_ids, self.aux, self.cap_vis, bs.slot_depth, bs.slot_rect,
+                                self.counters, self.splat_grads)
+                with self._phase("fwd.binning"):
+                    native.call("bin_instances", self.device, bs.slot_depth, bs.slot_rect, self.cap_vis, bs.vis[0],
+                                bs.vis[1], bs.vis[2], bs.vis[3], bs.inst_keys, self.vals, bs.inst_keys_tmp,
+                                bs.inst_vals_tmp, self.cap_inst, self.counters, cam.tiles_x, cam.tiles_y * cam.tiles_x,
+                                self.ranges, bs.words)
+            with self._phase("fwd.blend"):
+                if push is None:
+                    native.call("blend_fwd", self.device, cam, self.ranges, self.vals, self.splats, dst,
+                                self.depth if want_depth else None, self.n_contrib, self.counters)
+                else:  # (n, row0[], row1[], dst[]): also store the rows into the owners' compositing slots
+                    native.call("blend_fwd_push", self.device, cam, self.ranges, self.vals, self.splats, dst,
+                                self.depth if want_depth else None, self.n_contrib, self.counters, push[0], push[1],
+                                push[2], push[3])
             self.last_out = dst
             if not check:
                 self._record_counters()
@@ -318,11 +328,13 @@ class RenderTask:
         """Accumulate parameter gradients of the last forward. ``grad_out`` is (H,W,4): dL/dC, dL/dT."""
         cam = self.cam
         assert grad_out.is_contiguous() and grad_out.shape == (cam.H, cam.W, 4)
-        native.call("blend_bwd", self.device, cam, self.ranges, self.vals, self.splats, self.last_out, self.n_contrib,
-                    grad_out, self.splat_grads, self.counters)
+        with self._phase("bwd.blend"):
+            native.call("blend_bwd", self.device, cam, self.ranges, self.vals, self.splats, self.last_out, self.n_contrib,
+                        grad_out, self.splat_grads, self.counters)
         structs = (RgsSegment * len(segments))(*[s.struct(True) for s in segments])
-        native.call("geom_bwd", self.device, cam, structs, len(segments), self.counters, self.splats, self.vis_ids,
-                    self.aux, self.splat_grads, self.cap_vis)
+        with self._phase("bwd.geometry"):
+            native.call("geom_bwd", self.device, cam, structs, len(segments), self.counters, self.splats, self.vis_ids,
+                        self.aux, self.splat_grads, self.cap_vis)
 
     def radii(self, segment_index: int, segments: list[Segment]) -> torch.Tensor:
         base = sum(s.count for s in segments[:segment_index])

@@ -44,7 +44,7 @@ def test_binning_variants_agree_on_gpu():
         assert_mostly_close(a, b, atol=1e-5, rtol=1e-4, max_frac=1e-2)
         ref, tr, _, _ = native_render(g, cam, 3, device="cpu", binning="depth_first")
         assert tr.n_inst == ta.n_inst
-        assert_mostly_close(a.cpu(), ref, atol=3e-5, rtol=1e-4)
+        assert_mostly_close(a.cpu(), ref, atol=3e-5, rtol=1e-4, max_frac=5e-3)
 
 
 def test_raster_small_capacity_regrows():
