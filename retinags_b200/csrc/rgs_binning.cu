@@ -20,13 +20,25 @@
 #define BS_WARPS (BS_THREADS / 32)
 #define BS_WARP_SPAN (32 * BS_ITEMS)
 
+// number of tiles of the rectangle that hold at least one contributing pixel (all of them without tight_rect)
+__device__ __forceinline__ uint32_t count_hit_tiles(const RgsCamera& cam, const RgsSplat& sp, const RgsRect& rc) {
+    if (!cam.tight_rect) return (uint32_t)((rc.x1 - rc.x0) * (rc.y1 - rc.y0));
+    const float bound = rgs_alpha_bound(sp.opacity);
+    uint32_t n = 0;
+    for (int y = rc.y0; y < rc.y1; ++y)
+        for (int x = rc.x0; x < rc.x1; ++x)
+            n += rgs_tile_hit(sp.px, sp.py, sp.ca, sp.cb, sp.cc, bound, x, y, cam.W, cam.H) ? 1u : 0u;
+    return n;
+}
+
 // ---------------------------------------------------------------------------------------------
 // projection to slots (no instance emission)
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) rgs_project_slots_kernel(
     const __grid_constant__ RgsCamera cam, const RgsSegment seg, const int64_t id_base, RgsSplat* __restrict__ splats,
     int32_t* __restrict__ vis_ids, uint32_t* __restrict__ aux, const uint32_t cap_vis, uint32_t* __restrict__ slot_depth,
-    uint2* __restrict__ slot_rect, uint32_t* __restrict__ counters, RgsSplatGrad* __restrict__ splat_grads) {
+    uint2* __restrict__ slot_rect, uint32_t* __restrict__ slot_cnt, uint32_t* __restrict__ counters,
+    RgsSplatGrad* __restrict__ splat_grads) {
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
     bool ok = false;
     RgsSplat sp;
@@ -69,6 +81,7 @@ __global__ void __launch_bounds__(256) rgs_project_slots_kernel(
     aux[slot] = ((uint32_t)radius << 3) | clamped;
     slot_depth[slot] = __float_as_uint(sp.depth);
     slot_rect[slot] = make_uint2((uint32_t)rc.x0 | ((uint32_t)rc.y0 << 16), (uint32_t)rc.x1 | ((uint32_t)rc.y1 << 16));
+    slot_cnt[slot] = count_hit_tiles(cam, sp, rc);
     if (splat_grads) {
         float4* gz = reinterpret_cast<float4*>(splat_grads + slot);
         gz[0] = make_float4(0.f, 0.f, 0.f, 0.f); gz[1] = gz[0]; gz[2] = gz[0];
@@ -140,8 +153,8 @@ struct RgsSegs4 { RgsSegment s[4]; int n; };
 __global__ void __launch_bounds__(256) rgs_project_cand_kernel(
     const __grid_constant__ RgsCamera cam, const __grid_constant__ RgsSegs4 segs, const uint32_t* __restrict__ cand,
     uint32_t cap_cand, RgsSplat* __restrict__ splats, int32_t* __restrict__ vis_ids, uint32_t* __restrict__ aux,
-    const uint32_t cap_vis, uint32_t* __restrict__ slot_depth, uint2* __restrict__ slot_rect, uint32_t* __restrict__ counters,
-    RgsSplatGrad* __restrict__ splat_grads) {
+    const uint32_t cap_vis, uint32_t* __restrict__ slot_depth, uint2* __restrict__ slot_rect, uint32_t* __restrict__ slot_cnt,
+    uint32_t* __restrict__ counters, RgsSplatGrad* __restrict__ splat_grads) {
     __shared__ uint32_t warp_vis[8];
     __shared__ uint32_t base_vis;
     __shared__ int drop;
@@ -194,6 +207,7 @@ __global__ void __launch_bounds__(256) rgs_project_cand_kernel(
             aux[slot] = ((uint32_t)radius << 3) | clamped;
             slot_depth[slot] = __float_as_uint(sp.depth);
             slot_rect[slot] = make_uint2((uint32_t)rc.x0 | ((uint32_t)rc.y0 << 16), (uint32_t)rc.x1 | ((uint32_t)rc.y1 << 16));
+            slot_cnt[slot] = count_hit_tiles(cam, sp, rc);
             if (splat_grads) {
                 float4* gz = reinterpret_cast<float4*>(splat_grads + slot);
                 gz[0] = make_float4(0.f, 0.f, 0.f, 0.f); gz[1] = gz[0]; gz[2] = gz[0];
@@ -367,7 +381,7 @@ __device__ __forceinline__ uint32_t rect_count(uint2 r) {
 }
 
 __global__ void __launch_bounds__(256) rgs_emit_count_kernel(const uint32_t* __restrict__ order,
-                                                             const uint2* __restrict__ slot_rect,
+                                                             const uint32_t* __restrict__ slot_cnt,
                                                              const uint32_t* __restrict__ counters, uint32_t cap_vis,
                                                              uint32_t* __restrict__ seg_sums) {
     __shared__ uint32_t red[8];
@@ -378,7 +392,7 @@ __global__ void __launch_bounds__(256) rgs_emit_count_kernel(const uint32_t* __r
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const uint32_t i = s * EM_SEG + k * 256 + threadIdx.x;
-            if (i < n) sum += rect_count(slot_rect[order[i]]);
+            if (i < n) sum += slot_cnt[order[i]];
         }
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
@@ -431,12 +445,14 @@ __global__ void __launch_bounds__(1024) rgs_emit_scan_kernel(uint32_t* __restric
 }
 
 // Emission: a block scans the tile counts of its 1024 depth-ordered splats, parks (slot, rect, base) in
-// shared memory, then every warp walks its 128 splats and the 32 lanes write one splat's tiles together
+// shared memory, then every warp walks its 128 splats and the 32 lanes test/write one splat's tiles together
 // (consecutive lanes -> consecutive instances: coalesced stores instead of one long loop per thread).
-__global__ void __launch_bounds__(256) rgs_emit_kernel(const uint32_t* __restrict__ order, const uint2* __restrict__ slot_rect,
+__global__ void __launch_bounds__(256) rgs_emit_kernel(const __grid_constant__ RgsCamera cam, const uint32_t* __restrict__ order,
+                                                       const uint2* __restrict__ slot_rect, const uint32_t* __restrict__ slot_cnt,
+                                                       const RgsSplat* __restrict__ splats,
                                                        const uint32_t* __restrict__ counters, uint32_t cap_vis,
                                                        const uint32_t* __restrict__ seg_excl, uint32_t* __restrict__ tile_keys,
-                                                       uint32_t* __restrict__ vals, uint32_t cap_inst, int tiles_x) {
+                                                       uint32_t* __restrict__ vals, uint32_t cap_inst) {
     __shared__ uint32_t warp_tot[8];
     __shared__ uint32_t s_slot[EM_SEG], s_base[EM_SEG];
     __shared__ uint2 s_rect[EM_SEG];
@@ -444,6 +460,7 @@ __global__ void __launch_bounds__(256) rgs_emit_kernel(const uint32_t* __restric
     const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);
     const uint32_t nseg = (n + EM_SEG - 1) / EM_SEG;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int tiles_x = cam.tiles_x;
     for (uint32_t s = blockIdx.x; s < nseg; s += gridDim.x) {
         // thread t owns elements s*1024 + 4t .. 4t+3 (consecutive, so the scan order is the element order)
         uint32_t slot[4], cnt[4];
@@ -452,7 +469,7 @@ __global__ void __launch_bounds__(256) rgs_emit_kernel(const uint32_t* __restric
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const uint32_t i = s * EM_SEG + threadIdx.x * 4 + k;
-            if (i < n) { slot[k] = order[i]; rect[k] = slot_rect[slot[k]]; cnt[k] = rect_count(rect[k]); }
+            if (i < n) { slot[k] = order[i]; rect[k] = slot_rect[slot[k]]; cnt[k] = slot_cnt[slot[k]]; }
             else { slot[k] = 0; rect[k] = make_uint2(0, 0); cnt[k] = 0; }
             mine += cnt[k];
         }
@@ -470,7 +487,8 @@ __global__ void __launch_bounds__(256) rgs_emit_kernel(const uint32_t* __restric
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int e = threadIdx.x * 4 + k;
-            s_slot[e] = slot[k]; s_base[e] = base; s_rect[e] = rect[k];
+            s_slot[e] = slot[k]; s_base[e] = base;
+            s_rect[e] = cnt[k] ? rect[k] : make_uint2(0, 0);  // nothing to emit -> empty rectangle
             base += cnt[k];
         }
         __syncthreads();
@@ -480,11 +498,34 @@ __global__ void __launch_bounds__(256) rgs_emit_kernel(const uint32_t* __restric
             const uint32_t c = rect_count(r);
             if (c == 0) continue;
             const int x0 = r.x & 0xffff, y0 = r.x >> 16, w = (int)(r.y & 0xffff) - x0;
-            const uint32_t b0 = s_base[e], sl = s_slot[e];
-            for (uint32_t t = lane; t < c; t += 32) {
-                const uint32_t o = b0 + t;
-                const uint32_t ty = t / (uint32_t)w, tx = t - ty * (uint32_t)w;
-                if (o < cap_inst) { tile_keys[o] = (uint32_t)((y0 + (int)ty) * tiles_x + x0 + (int)tx); vals[o] = sl; }
+            const uint32_t sl = s_slot[e];
+            uint32_t o = s_base[e];
+            if (!cam.tight_rect) {
+                for (uint32_t t = lane; t < c; t += 32) {
+                    const uint32_t ty = t / (uint32_t)w, tx = t - ty * (uint32_t)w;
+                    if (o + t < cap_inst) { tile_keys[o + t] = (uint32_t)((y0 + (int)ty) * tiles_x + x0 + (int)tx); vals[o + t] = sl; }
+                }
+                continue;
+            }
+            // same test, same inputs as count_hit_tiles: the record written by the projection kernel
+            const float4 q0 = reinterpret_cast<const float4*>(splats + sl)[0];
+            const float2 q1 = reinterpret_cast<const float2*>(splats + sl)[2];
+            const float bound = rgs_alpha_bound(q1.y);
+            for (uint32_t t0 = 0; t0 < c; t0 += 32) {
+                const uint32_t t = t0 + lane;
+                bool hit = false;
+                uint32_t key = 0;
+                if (t < c) {
+                    const uint32_t ty = t / (uint32_t)w, tx = t - ty * (uint32_t)w;
+                    hit = rgs_tile_hit(q0.x, q0.y, q0.z, q0.w, q1.x, bound, x0 + (int)tx, y0 + (int)ty, cam.W, cam.H);
+                    key = (uint32_t)((y0 + (int)ty) * tiles_x + x0 + (int)tx);
+                }
+                const uint32_t m = __ballot_sync(0xffffffffu, hit);
+                if (hit) {
+                    const uint32_t dst = o + __popc(m & ((1u << lane) - 1u));
+                    if (dst < cap_inst) { tile_keys[dst] = key; vals[dst] = sl; }
+                }
+                o += __popc(m);
             }
         }
         __syncthreads();
@@ -534,13 +575,13 @@ extern "C" {
 
 int rgs_cuda_project_slots(const RgsCamera* cam, const RgsSegment* seg, int64_t id_base, RgsSplat* splats,
                            int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint32_t* slot_depth, uint32_t* slot_rect,
-                           int32_t* counters, RgsSplatGrad* splat_grads, void* stream) {
+                           uint32_t* slot_cnt, int32_t* counters, RgsSplatGrad* splat_grads, void* stream) {
     if (seg->count <= 0) return 0;
     if (cap_vis > 0x7ffffff0ll || cam->tiles_x > 65535 || cam->tiles_y > 65535) return 10;
     const unsigned blocks = (unsigned)((seg->count + 255) / 256);
     rgs_project_slots_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
         *cam, *seg, id_base, splats, vis_ids, aux, (uint32_t)cap_vis, slot_depth, reinterpret_cast<uint2*>(slot_rect),
-        reinterpret_cast<uint32_t*>(counters), splat_grads);
+        slot_cnt, reinterpret_cast<uint32_t*>(counters), splat_grads);
     return (int)cudaGetLastError();
 }
 
@@ -548,7 +589,8 @@ int rgs_cuda_project_slots(const RgsCamera* cam, const RgsSegment* seg, int64_t 
 // `cand` holds cap_cand uint32 candidate ids (scratch owned by the caller).
 int rgs_cuda_project_slots2(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg, uint32_t* cand, int64_t cap_cand,
                             RgsSplat* splats, int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint32_t* slot_depth,
-                            uint32_t* slot_rect, int32_t* counters, RgsSplatGrad* splat_grads, void* stream) {
+                            uint32_t* slot_rect, uint32_t* slot_cnt, int32_t* counters, RgsSplatGrad* splat_grads,
+                            void* stream) {
     if (nseg < 1 || nseg > 4) return 11;
     if (cap_vis > 0x7ffffff0ll || cap_cand > 0x7ffffff0ll || cam->tiles_x > 65535 || cam->tiles_y > 65535) return 10;
     cudaStream_t st = (cudaStream_t)stream;
@@ -568,7 +610,7 @@ int rgs_cuda_project_slots2(const RgsCamera* cam, const RgsSegment* segs, int64_
     const int64_t want = (cap_cand + 255) / 256;
     const unsigned grid = (unsigned)(want < 1 ? 1 : (want > 148 * 8 ? 148 * 8 : want));
     rgs_project_cand_kernel<<<grid, 256, 0, st>>>(*cam, s4, cand, (uint32_t)cap_cand, splats, vis_ids, aux, (uint32_t)cap_vis,
-                                                  slot_depth, reinterpret_cast<uint2*>(slot_rect), cnt, splat_grads);
+                                                  slot_depth, reinterpret_cast<uint2*>(slot_rect), slot_cnt, cnt, splat_grads);
     return (int)cudaGetLastError();
 }
 
@@ -582,7 +624,8 @@ int64_t rgs_cuda_bin_scratch_words(int64_t cap_vis, int64_t cap_inst) {
 //   slot_depth/slot_rect: per slot, from rgs_cuda_project_slots
 //   vis_a/vis_b (u32[cap_vis] x4: key/value ping-pong)  inst_keys/inst_vals/inst_keys_tmp/inst_vals_tmp (u32[cap_inst])
 // Result: inst_vals holds the slots grouped by tile in depth order, ranges[tile] = [start,end).
-int rgs_cuda_bin_instances(const uint32_t* slot_depth, const uint32_t* slot_rect, int64_t cap_vis, uint32_t* vis_ka,
+int rgs_cuda_bin_instances(const RgsCamera* cam, const RgsSplat* splats, const uint32_t* slot_depth, const uint32_t* slot_rect,
+                           const uint32_t* slot_cnt, int64_t cap_vis, uint32_t* vis_ka,
                            uint32_t* vis_va, uint32_t* vis_kb, uint32_t* vis_vb, uint32_t* inst_keys, uint32_t* inst_vals,
                            uint32_t* inst_keys_tmp, uint32_t* inst_vals_tmp, int64_t cap_inst, int32_t* counters,
                            int64_t tiles_x, int64_t num_tiles, int32_t* ranges, uint32_t* scratch, void* stream) {
@@ -600,11 +643,11 @@ int rgs_cuda_bin_instances(const uint32_t* slot_depth, const uint32_t* slot_rect
     // 2. emission in depth order
     const uint32_t nseg_cap = (uint32_t)((cap_vis + EM_SEG - 1) / EM_SEG);
     const unsigned egrid = nseg_cap < 148u * 8u ? (nseg_cap ? nseg_cap : 1u) : 148u * 8u;
-    rgs_emit_count_kernel<<<egrid, 256, 0, st>>>(order, reinterpret_cast<const uint2*>(slot_rect), cnt, (uint32_t)cap_vis,
-                                                 seg_sums);
+    rgs_emit_count_kernel<<<egrid, 256, 0, st>>>(order, slot_cnt, cnt, (uint32_t)cap_vis, seg_sums);
     rgs_emit_scan_kernel<<<1, 1024, 0, st>>>(seg_sums, cnt, (uint32_t)cap_vis, (uint32_t)cap_inst);
-    rgs_emit_kernel<<<egrid, 256, 0, st>>>(order, reinterpret_cast<const uint2*>(slot_rect), cnt, (uint32_t)cap_vis, seg_sums,
-                                           inst_keys, inst_vals, (uint32_t)cap_inst, (int)tiles_x);
+    rgs_emit_kernel<<<egrid, 256, 0, st>>>(*cam, order, reinterpret_cast<const uint2*>(slot_rect), slot_cnt, splats, cnt,
+                                           (uint32_t)cap_vis, seg_sums, inst_keys, inst_vals, (uint32_t)cap_inst);
+    (void)tiles_x;
     // 3. stable sort by tile id
     int tile_bits = 0;
     while ((1ll << tile_bits) < num_tiles) ++tile_bits;

@@ -54,7 +54,7 @@ int64_t rgs_cpu_bin_scratch_words(int64_t, int64_t) { return 1; }
 // CPU twins of the depth-ordered binning (rgs_binning.cu)
 int rgs_cpu_project_slots(const RgsCamera* cam, const RgsSegment* seg, int64_t id_base, RgsSplat* splats,
                           int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint32_t* slot_depth, uint32_t* slot_rect,
-                          int32_t* counters, RgsSplatGrad* splat_grads, void*) {
+                          uint32_t* slot_cnt, int32_t* counters, RgsSplatGrad* splat_grads, void*) {
     int64_t n_vis = counters[RGS_CNT_VIS];
     for (int64_t i = 0; i < seg->count; ++i) {
         RgsSplat sp; RgsRect rc; int radius; unsigned clamped;
@@ -69,6 +69,12 @@ int rgs_cpu_project_slots(const RgsCamera* cam, const RgsSegment* seg, int64_t i
         std::memcpy(&slot_depth[slot], &sp.depth, 4);
         slot_rect[2 * slot] = (uint32_t)rc.x0 | ((uint32_t)rc.y0 << 16);
         slot_rect[2 * slot + 1] = (uint32_t)rc.x1 | ((uint32_t)rc.y1 << 16);
+        uint32_t hits = 0;
+        const float bound = rgs_alpha_bound(sp.opacity);
+        for (int y = rc.y0; y < rc.y1; ++y)
+            for (int x = rc.x0; x < rc.x1; ++x)
+                hits += (!cam->tight_rect || rgs_tile_hit(sp.px, sp.py, sp.ca, sp.cb, sp.cc, bound, x, y, cam->W, cam->H)) ? 1u : 0u;
+        slot_cnt[slot] = hits;
         if (splat_grads) std::memset(&splat_grads[slot], 0, sizeof(RgsSplatGrad));
     }
     counters[RGS_CNT_VIS] = (int32_t)n_vis;
@@ -77,16 +83,19 @@ int rgs_cpu_project_slots(const RgsCamera* cam, const RgsSegment* seg, int64_t i
 
 int rgs_cpu_project_slots2(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg, uint32_t*, int64_t,
                            RgsSplat* splats, int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint32_t* slot_depth,
-                           uint32_t* slot_rect, int32_t* counters, RgsSplatGrad* splat_grads, void* stream) {
+                           uint32_t* slot_rect, uint32_t* slot_cnt, int32_t* counters, RgsSplatGrad* splat_grads,
+                           void* stream) {
     int64_t base = 0;
     for (int64_t k = 0; k < nseg; ++k) {
-        rgs_cpu_project_slots(cam, &segs[k], base, splats, vis_ids, aux, cap_vis, slot_depth, slot_rect, counters, splat_grads, stream);
+        rgs_cpu_project_slots(cam, &segs[k], base, splats, vis_ids, aux, cap_vis, slot_depth, slot_rect, slot_cnt, counters,
+                              splat_grads, stream);
         base += segs[k].count;
     }
     return 0;
 }
 
-int rgs_cpu_bin_instances(const uint32_t* slot_depth, const uint32_t* slot_rect, int64_t cap_vis, uint32_t*, uint32_t*,
+int rgs_cpu_bin_instances(const RgsCamera* cam, const RgsSplat* splats, const uint32_t* slot_depth, const uint32_t* slot_rect,
+                          const uint32_t* slot_cnt, int64_t cap_vis, uint32_t*, uint32_t*,
                           uint32_t*, uint32_t*, uint32_t* inst_keys, uint32_t* inst_vals, uint32_t*, uint32_t*,
                           int64_t cap_inst, int32_t* counters, int64_t tiles_x, int64_t num_tiles, int32_t* ranges,
                           uint32_t*, void*) {
@@ -100,8 +109,13 @@ int rgs_cpu_bin_instances(const uint32_t* slot_depth, const uint32_t* slot_rect,
     std::vector<std::pair<uint32_t, uint32_t>> inst;
     for (int64_t i = 0; i < n; ++i) {
         const uint32_t s = order[i], lo = slot_rect[2 * s], hi = slot_rect[2 * s + 1];
+        if (slot_cnt[s] == 0) continue;
+        const RgsSplat& sp = splats[s];
+        const float bound = rgs_alpha_bound(sp.opacity);
         for (uint32_t y = lo >> 16; y < (hi >> 16); ++y)
-            for (uint32_t x = lo & 0xffff; x < (hi & 0xffff); ++x) inst.emplace_back((uint32_t)(y * tiles_x + x), s);
+            for (uint32_t x = lo & 0xffff; x < (hi & 0xffff); ++x)
+                if (!cam->tight_rect || rgs_tile_hit(sp.px, sp.py, sp.ca, sp.cb, sp.cc, bound, (int)x, (int)y, cam->W, cam->H))
+                    inst.emplace_back((uint32_t)(y * tiles_x + x), s);
     }
     counters[RGS_CNT_INST] = (int32_t)std::min<size_t>(inst.size(), 0x7fffffff);
     if ((int64_t)inst.size() > cap_inst) { counters[RGS_CNT_OVERFLOW] = 1; return 0; }

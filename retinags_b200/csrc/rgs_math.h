@@ -289,6 +289,34 @@ RGS_HD bool rgs_project(const RgsCamera& cam, const float* p, const float* s_in,
     return true;
 }
 
+// Exact tile culling. A splat contributes to a pixel only where alpha = o exp(-q/2) >= 1/255, i.e. where
+// q(d) = ca dx^2 + 2 cb dx dy + cc dy^2 <= 2 ln(255 o). The minimum of the convex form q over the rectangle of
+// pixel centres of a tile is 0 when the mean lies inside, else it is attained on one of the four edges (a 1-D
+// quadratic each). A tile whose minimum exceeds the bound holds no contributing pixel and can be skipped without
+// changing any output bit; a small margin absorbs rounding differences to the per-pixel evaluation.
+RGS_HD float rgs_edge_min(float a, float b2, float c, float fixed, float lo, float hi) {
+    // minimise a*fixed^2 + b2*fixed*t + c*t^2 over t in [lo, hi]
+    float t = -0.5f * b2 * fixed / c;
+    t = fminf(hi, fmaxf(lo, t));
+    return a * fixed * fixed + b2 * fixed * t + c * t * t;
+}
+
+RGS_HD bool rgs_tile_hit(float px, float py, float ca, float cb, float cc, float bound, int tx, int ty, int W, int H) {
+    const float x0 = (float)(tx * RGS_TILE), y0 = (float)(ty * RGS_TILE);
+    const float x1 = fminf(x0 + (RGS_TILE - 1), (float)(W - 1)), y1 = fminf(y0 + (RGS_TILE - 1), (float)(H - 1));
+    // d = mean - pixel: ranges of dx, dy over the tile
+    const float dx_lo = px - x1, dx_hi = px - x0, dy_lo = py - y1, dy_hi = py - y0;
+    if (dx_lo <= 0.0f && dx_hi >= 0.0f && dy_lo <= 0.0f && dy_hi >= 0.0f) return true;
+    const float b2 = 2.0f * cb;
+    float m = rgs_edge_min(ca, b2, cc, dx_lo, dy_lo, dy_hi);
+    m = fminf(m, rgs_edge_min(ca, b2, cc, dx_hi, dy_lo, dy_hi));
+    m = fminf(m, rgs_edge_min(cc, b2, ca, dy_lo, dx_lo, dx_hi));
+    m = fminf(m, rgs_edge_min(cc, b2, ca, dy_hi, dx_lo, dx_hi));
+    return !(m > bound * 1.0005f + 0.001f);
+}
+
+RGS_HD float rgs_alpha_bound(float opacity) { return 2.0f * logf(255.0f * opacity); }
+
 // Gradients of the image-space quantities of one splat, accumulated by the blend backward.
 // 12 floats so that three 16-byte vector reductions update one record.
 struct __attribute__((aligned(16))) RgsSplatGrad {

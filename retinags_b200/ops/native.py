@@ -26,9 +26,9 @@ _LIBS: dict[str, ctypes.CDLL] = {}
 SIGNATURES = {
     "project_emit": "ppipppippippp",
     "sort_ranges": "ppppipippp",
-    "project_slots": "ppipppippppp",
-    "project_slots2": "ppipipppippppp",
-    "bin_instances": "ppippppppppipiippp",
+    "project_slots": "ppipppipppppp",
+    "project_slots2": "ppipipppipppppp",
+    "bin_instances": "pppppippppppppipiippp",
     "blend_fwd": "ppppppppp",
     "blend_fwd_push": "ppppppppipppp",
     "blend_bwd": "pppppppppp",
@@ -153,7 +153,7 @@ def _count_launches(name: str, args) -> int:
         bits = 32 + max(tiles - 1, 0).bit_length()
         return 3 * ((bits + 7) // 8) + 1
     if name == "bin_instances":
-        tiles = max(int(args[14]), 1)
+        tiles = max(int(args[17]), 1)
         return 3 * 4 + 3 + 3 * max(1, (max(tiles - 1, 0).bit_length() + 7) // 8) + 1
     return _KERNELS.get(name, 1)
 

@@ -136,6 +136,7 @@ class BinScratch:
             self.cap_vis = cap_vis
             self.slot_depth = torch.empty(cap_vis, dtype=torch.int32, device=dev)
             self.slot_rect = torch.empty(cap_vis, dtype=torch.int64, device=dev)
+            self.slot_cnt = torch.empty(cap_vis, dtype=torch.int32, device=dev)
             self.vis = [torch.empty(cap_vis, dtype=torch.int32, device=dev) for _ in range(4)]
             grown = True
         if cap_inst > self.cap_inst:
@@ -271,9 +272,10 @@ class RenderTask:
                 with self._phase("fwd.project"):
                     native.call("project_slots2", self.device, cam, structs, len(segments), bs.vis[3], self.cap_vis,
                                 self.splats, self.vis_ids, self.aux, self.cap_vis, bs.slot_depth, bs.slot_rect,
-                                self.counters, self.splat_grads)
+                                bs.slot_cnt, self.counters, self.splat_grads)
                 with self._phase("fwd.binning"):
-                    native.call("bin_instances", self.device, bs.slot_depth, bs.slot_rect, self.cap_vis, bs.vis[0],
+                    native.call("bin_instances", self.device, cam, self.splats, bs.slot_depth, bs.slot_rect, bs.slot_cnt,
+                                self.cap_vis, bs.vis[0],
                                 bs.vis[1], bs.vis[2], bs.vis[3], bs.inst_keys, self.vals, bs.inst_keys_tmp,
                                 bs.inst_vals_tmp, self.cap_inst, self.counters, cam.tiles_x, cam.tiles_y * cam.tiles_x,
                                 self.ranges, bs.words)

@@ -39,7 +39,7 @@ def test_binning_variants_agree_on_gpu():
     for cam in cams[:2]:
         a, ta, _, _ = native_render(g, cam, 3, device="cuda", binning="depth_first")
         b, tb, _, _ = native_render(g, cam, 3, device="cuda", binning="keyed")
-        assert ta.n_vis == tb.n_vis and ta.n_inst == tb.n_inst
+        assert ta.n_vis == tb.n_vis and ta.n_inst <= tb.n_inst
         # splats of exactly equal depth are ordered by slot number, which differs between the pipelines
         assert_mostly_close(a, b, atol=1e-5, rtol=1e-4, max_frac=1e-2)
         ref, tr, _, _ = native_render(g, cam, 3, device="cpu", binning="depth_first")

@@ -22,7 +22,8 @@ def test_binning_variants_agree():
     g, cams = small_scene(n=1500)
     a, ta, _, _ = native_render(g, cams[2], 3, binning="depth_first")
     b, tb, _, _ = native_render(g, cams[2], 3, binning="keyed")
-    assert torch.equal(a, b) and ta.n_inst == tb.n_inst and torch.equal(ta.n_contrib, tb.n_contrib)
+    # the depth-first pipeline also drops tiles without a contributing pixel: fewer instances, same image
+    assert torch.equal(a, b) and ta.n_inst <= tb.n_inst and ta.n_vis == tb.n_vis
 
 
 def test_tight_rect_is_exact():
