@@ -36,6 +36,8 @@ def parse_args():
     ap.add_argument("--gt-gaussians", type=int, default=6_000_000)
     ap.add_argument("--transport", default="auto", choices=["auto", "peer", "nccl"])
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--borrow-refresh", type=int, default=8,
+                    help="steps between recomputations of the border-Gaussian selection (the rows are re-sent every step)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--phases", action="store_true", help="also time the phases of a step (extra loop, after the timed one)")
     return ap.parse_args()
@@ -121,7 +123,8 @@ def run_own(args):
         dist.init_process_group("nccl", device_id=device)
     sess = BenchSession(device=device, rank=rank, world=world, n_gaussians=args.gaussians, width=args.width,
                         height=args.height, batch=args.batch, n_views=(args.steps + args.warmup) * args.batch,
-                        gt_gaussians=args.gt_gaussians, transport=args.transport, seed=args.seed)
+                        gt_gaussians=args.gt_gaussians, transport=args.transport, seed=args.seed,
+                        borrow_refresh=args.borrow_refresh)
     # ---- device-timed region ------------------------------------------------------------------
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -187,6 +190,7 @@ def run_own(args):
                        "global_batch": args.batch, "resolution": [args.width, args.height],
                        "submodels": sess.n_models, "bvh_depth": sess.bvh_depth,
                        "parallelism": f"spatial-mp{world}", "transport": sess.transport_name,
+                       "border_selection_refresh_steps": sess.borrow_refresh if sess.n_models > 1 else None,
                        "l2": "inputs larger than L2 (parameter blocks of >= 1.8 GB per GPU are streamed every step)",
                        "visible_splats_per_view": sess.last_info.get("n_vis"),
                        "instances_per_view": sess.last_info.get("n_inst"), "overflow_in_timed_region": overflow},

@@ -26,6 +26,7 @@ CUDA_SOURCES = [
     "rgs_loss.cu",
     "rgs_model.cu",
     "rgs_p2p.cu",
+    "rgs_border.cu",
     "rgs_ssim_tc.cu",
     "rgs_noalloc.cu",
 ]

@@ -149,7 +149,12 @@ class BenchSession:
         self.border = None
         if borrow and self.n_models > 1:
             from .parallel.border import BorderExchange
-            self.border = BorderExchange(lo, hi, self.model2rank, rank, world, self.device, group, borrow_refresh)
+            if hasattr(tr, "push_plan"):  # peer transport: border rows travel by peer stores as well
+                from .parallel.peer_border import PeerBorderExchange
+                self.border = PeerBorderExchange(lo, hi, self.model2rank, rank, world, self.device, tr, group, borrow_refresh)
+            else:
+                self.border = BorderExchange(lo, hi, self.model2rank, rank, world, self.device, group, borrow_refresh)
+        self.borrow_refresh = borrow_refresh
         self.engine = StepEngine(self.stores, self.model2rank, self.device, tr, borrow=self.border)
         extent = 1.1 * 8.0
         self.lrs = (1.6e-4 * extent, 2.5e-3, 2.5e-3 / 20.0, 5e-3, 1e-3, 5e-2)

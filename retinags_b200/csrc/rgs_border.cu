@@ -1,0 +1,126 @@
+// Border-Gaussian exchange kernels for the peer-to-peer path.
+//
+// A sub-model lends the Gaussians whose extent reaches into a neighbour's box. The reference gathers them with
+// boolean masks, concatenates 62-float rows and ships them with NCCL send/recv in both directions every iteration
+// (parallel_utils/basic_parallel_trainer/result_aggregator.py:55-147, task_utils.py:230-362,
+// trainer4tree_partition.py:354-388,521-571). Here
+//   rgs_border_pack_kernel     gathers the selected rows from the owner's column groups and stores them straight
+//                              into the borrowing rank's segment (column groups in peer-mapped memory: what
+//                              arrives IS the render segment, nothing is unpacked);
+//   rgs_border_grad_push_kernel stores the gradients of the borrowed rows (59 parameter gradients + the
+//                              screen-gradient statistic) into the owner's return ring (peer-mapped);
+//   rgs_border_grad_add_kernel adds the returned rows into the owner's gradient block and marks them touched.
+// Plain peer stores only; ordering is by the epoch flags of rgs_p2p.cu.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "rgs_api.h"
+#include "rgs_cuda_common.cuh"
+
+struct RgsColumns { float* xyz; float* sh; float* scale; float* rot; float* opacity; };
+struct RgsConstColumns { const float* xyz; const float* sh; const float* scale; const float* rot; const float* opacity; };
+
+// 15 units per row: 12 float4 of SH, xyz, scale+opacity, rotation
+__global__ void __launch_bounds__(256) rgs_border_pack_kernel(const RgsConstColumns src, const int64_t* __restrict__ idx,
+                                                              int64_t n, const RgsColumns dst, int64_t dst_row0) {
+    const int64_t total = n * 15;
+    for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = u / 15;
+        const int k = (int)(u - r * 15);
+        const int64_t i = idx[r], o = dst_row0 + r;
+        if (k < 12) {
+            reinterpret_cast<float4*>(dst.sh + 48 * o)[k] = reinterpret_cast<const float4*>(src.sh + 48 * i)[k];
+        } else if (k == 12) {
+            dst.xyz[3 * o] = src.xyz[3 * i]; dst.xyz[3 * o + 1] = src.xyz[3 * i + 1]; dst.xyz[3 * o + 2] = src.xyz[3 * i + 2];
+        } else if (k == 13) {
+            dst.scale[3 * o] = src.scale[3 * i]; dst.scale[3 * o + 1] = src.scale[3 * i + 1]; dst.scale[3 * o + 2] = src.scale[3 * i + 2];
+            dst.opacity[o] = src.opacity[i];
+        } else {
+            reinterpret_cast<float4*>(dst.rot)[o] = reinterpret_cast<const float4*>(src.rot)[i];
+        }
+    }
+}
+
+// rows: (n, 60) row-major = [g_xyz 3, stat 1 | g_sh 48 | g_scale 3, g_opacity 1 | g_rot 4] (16-byte aligned groups)
+__global__ void __launch_bounds__(256) rgs_border_grad_push_kernel(const RgsConstColumns g, const float* __restrict__ stat,
+                                                                   int64_t row0, int64_t n, float* __restrict__ rows) {
+    const int64_t total = n * 15;
+    for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = u / 15;
+        const int k = (int)(u - r * 15);
+        const int64_t i = row0 + r;
+        float* o = rows + 60 * r;
+        if (k < 12) {
+            reinterpret_cast<float4*>(o + 4)[k] = reinterpret_cast<const float4*>(g.sh + 48 * i)[k];
+        } else if (k == 12) {
+            o[0] = g.xyz[3 * i]; o[1] = g.xyz[3 * i + 1]; o[2] = g.xyz[3 * i + 2]; o[3] = stat ? stat[i] : 0.f;
+        } else if (k == 13) {
+            o[52] = g.scale[3 * i]; o[53] = g.scale[3 * i + 1]; o[54] = g.scale[3 * i + 2]; o[55] = g.opacity[i];
+        } else {
+            reinterpret_cast<float4*>(o + 56)[0] = reinterpret_cast<const float4*>(g.rot)[i];
+        }
+    }
+}
+
+// inverse of the push layout: [xyz 3, stat 1 | sh 48 | scale 3, opacity 1 | rot 4]
+__global__ void __launch_bounds__(256) rgs_border_grad_add_kernel(const float* __restrict__ rows, const int64_t* __restrict__ idx,
+                                                                  int64_t n, const RgsColumns g, float* __restrict__ stat,
+                                                                  uint8_t* __restrict__ touched) {
+    const int64_t total = n * 15;
+    for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = u / 15;
+        const int k = (int)(u - r * 15);
+        const int64_t i = idx[r];
+        const float* o = rows + 60 * r;
+        if (k < 12) {
+            float4 a = reinterpret_cast<float4*>(g.sh + 48 * i)[k];
+            const float4 b = reinterpret_cast<const float4*>(o + 4)[k];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+            reinterpret_cast<float4*>(g.sh + 48 * i)[k] = a;
+        } else if (k == 12) {
+            g.xyz[3 * i] += o[0]; g.xyz[3 * i + 1] += o[1]; g.xyz[3 * i + 2] += o[2];
+            if (stat) stat[i] += o[3];
+            if (touched) touched[i] = 1;
+        } else if (k == 13) {
+            g.scale[3 * i] += o[52]; g.scale[3 * i + 1] += o[53]; g.scale[3 * i + 2] += o[54]; g.opacity[i] += o[55];
+        } else {
+            float4 a = reinterpret_cast<float4*>(g.rot)[i];
+            const float4 b = reinterpret_cast<const float4*>(o + 56)[0];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+            reinterpret_cast<float4*>(g.rot)[i] = a;
+        }
+    }
+}
+
+static inline unsigned border_grid(int64_t n) {
+    const int64_t want = (n * 15 + 255) / 256;
+    return (unsigned)(want < 1 ? 1 : (want > 148 * 16 ? 148 * 16 : want));
+}
+
+extern "C" {
+
+// src/dst: 5 pointers each (xyz, sh, scale, rot, opacity); dst may be peer-mapped.
+int rgs_cuda_border_pack(const float* const* src, const int64_t* idx, int64_t n, float* const* dst, int64_t dst_row0,
+                         void* stream) {
+    if (n <= 0) return 0;
+    RgsConstColumns s{src[0], src[1], src[2], src[3], src[4]};
+    RgsColumns d{dst[0], dst[1], dst[2], dst[3], dst[4]};
+    rgs_border_pack_kernel<<<border_grid(n), 256, 0, (cudaStream_t)stream>>>(s, idx, n, d, dst_row0);
+    return (int)cudaGetLastError();
+}
+
+int rgs_cuda_border_grad_push(const float* const* g, const float* stat, int64_t row0, int64_t n, float* rows, void* stream) {
+    if (n <= 0) return 0;
+    RgsConstColumns s{g[0], g[1], g[2], g[3], g[4]};
+    rgs_border_grad_push_kernel<<<border_grid(n), 256, 0, (cudaStream_t)stream>>>(s, stat, row0, n, rows);
+    return (int)cudaGetLastError();
+}
+
+int rgs_cuda_border_grad_add(const float* rows, const int64_t* idx, int64_t n, float* const* g, float* stat,
+                             uint8_t* touched, void* stream) {
+    if (n <= 0) return 0;
+    RgsColumns d{g[0], g[1], g[2], g[3], g[4]};
+    rgs_border_grad_add_kernel<<<border_grid(n), 256, 0, (cudaStream_t)stream>>>(rows, idx, n, d, stat, touched);
+    return (int)cudaGetLastError();
+}
+
+}  // extern "C"

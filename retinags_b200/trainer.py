@@ -267,8 +267,13 @@ class Trainer:
         lo, hi = self.boxes
         self.border = None
         if self.n_models > 1 and not a.NOT_SHRAE_GS_INFO:
-            self.border = BorderExchange(lo, hi, self.model2rank, self.rank, self.world, self.device, self.group,
-                                         getattr(a, "BORROW_REFRESH_INTERVAL", 1))
+            interval = getattr(a, "BORROW_REFRESH_INTERVAL", 1)
+            if hasattr(tr, "push_plan"):
+                from .parallel.peer_border import PeerBorderExchange
+                self.border = PeerBorderExchange(lo, hi, self.model2rank, self.rank, self.world, self.device, tr, self.group,
+                                                 interval)
+            else:
+                self.border = BorderExchange(lo, hi, self.model2rank, self.rank, self.world, self.device, self.group, interval)
         self.engine = StepEngine(self.stores, self.model2rank, self.device, tr, self.opt.lambda_dssim, self.background,
                                  borrow=self.border)
         self.balancer = WorkloadBalancer(self.world, self.model2rank)

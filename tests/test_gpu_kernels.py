@@ -167,8 +167,11 @@ def test_peer_transport_single_rank_equals_local():
         return BenchSession("cuda", 0, 1, 60000, 320, 208, batch=2, n_views=4, gt_gaussians=20000, seed=5, sh_degree=3,
                             grid=(64, 64, 1), bvh_depth=1)
     a, b = make(), make()
+    from retinags_b200.parallel.peer_border import PeerBorderExchange
     tr = PeerTransport(torch.device("cuda"))
     b.engine.transport = tr
+    lo, hi = b.tree.leaf_boxes_world(open_border=True)
+    b.engine.borrow = PeerBorderExchange(lo, hi, b.model2rank, 0, 1, torch.device("cuda"), tr, None, refresh_interval=1)
     ia, _, _ = a.render_view(1)
     ib, _, _ = b.render_view(1)
     torch.testing.assert_close(ia, ib, atol=1e-6, rtol=1e-5)
@@ -178,7 +181,9 @@ def test_peer_transport_single_rank_equals_local():
         assert abs(la - lb) < 1e-4 * max(1.0, abs(la))
     torch.cuda.synchronize()
     tr.check()
+    assert int(b.engine.borrow._counts.sum()) == int(a.border._counts.sum()) > 0
     for m in a.stores:
         ra, rb = a.stores[m].records(), b.stores[m].records()
         assert (ra - rb).abs().mean() < 1e-5
+    b.engine.borrow.close()
     tr.close()
