@@ -22,7 +22,7 @@
 
 // number of tiles of the rectangle that hold at least one contributing pixel (all of them without tight_rect)
 __device__ __forceinline__ uint32_t count_hit_tiles(const RgsCamera& cam, const RgsSplat& sp, const RgsRect& rc) {
-    if (!cam.tight_rect) return (uint32_t)((rc.x1 - rc.x0) * (rc.y1 - rc.y0));
+    if (cam.tight_rect < 2) return (uint32_t)((rc.x1 - rc.x0) * (rc.y1 - rc.y0));
     const float bound = rgs_alpha_bound(sp.opacity);
     uint32_t n = 0;
     for (int y = rc.y0; y < rc.y1; ++y)
@@ -500,7 +500,7 @@ __global__ void __launch_bounds__(256) rgs_emit_kernel(const __grid_constant__ R
             const int x0 = r.x & 0xffff, y0 = r.x >> 16, w = (int)(r.y & 0xffff) - x0;
             const uint32_t sl = s_slot[e];
             uint32_t o = s_base[e];
-            if (!cam.tight_rect) {
+            if (cam.tight_rect < 2) {
                 for (uint32_t t = lane; t < c; t += 32) {
                     const uint32_t ty = t / (uint32_t)w, tx = t - ty * (uint32_t)w;
                     if (o + t < cap_inst) { tile_keys[o + t] = (uint32_t)((y0 + (int)ty) * tiles_x + x0 + (int)tx); vals[o + t] = sl; }

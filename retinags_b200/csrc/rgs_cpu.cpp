@@ -73,7 +73,7 @@ int rgs_cpu_project_slots(const RgsCamera* cam, const RgsSegment* seg, int64_t i
         const float bound = rgs_alpha_bound(sp.opacity);
         for (int y = rc.y0; y < rc.y1; ++y)
             for (int x = rc.x0; x < rc.x1; ++x)
-                hits += (!cam->tight_rect || rgs_tile_hit(sp.px, sp.py, sp.ca, sp.cb, sp.cc, bound, x, y, cam->W, cam->H)) ? 1u : 0u;
+                hits += (cam->tight_rect < 2 || rgs_tile_hit(sp.px, sp.py, sp.ca, sp.cb, sp.cc, bound, x, y, cam->W, cam->H)) ? 1u : 0u;
         slot_cnt[slot] = hits;
         if (splat_grads) std::memset(&splat_grads[slot], 0, sizeof(RgsSplatGrad));
     }
@@ -114,7 +114,7 @@ int rgs_cpu_bin_instances(const RgsCamera* cam, const RgsSplat* splats, const ui
         const float bound = rgs_alpha_bound(sp.opacity);
         for (uint32_t y = lo >> 16; y < (hi >> 16); ++y)
             for (uint32_t x = lo & 0xffff; x < (hi & 0xffff); ++x)
-                if (!cam->tight_rect || rgs_tile_hit(sp.px, sp.py, sp.ca, sp.cb, sp.cc, bound, (int)x, (int)y, cam->W, cam->H))
+                if (cam->tight_rect < 2 || rgs_tile_hit(sp.px, sp.py, sp.ca, sp.cb, sp.cc, bound, (int)x, (int)y, cam->W, cam->H))
                     inst.emplace_back((uint32_t)(y * tiles_x + x), s);
     }
     counters[RGS_CNT_INST] = (int32_t)std::min<size_t>(inst.size(), 0x7fffffff);

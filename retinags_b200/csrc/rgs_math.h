@@ -51,7 +51,8 @@ struct RgsCamera {
     int sh_degree;    // active SH degree (0..3)
     float scale_modifier;
     int raw_params;   // 1: inputs are raw (log-scale, logit opacity, unnormalised quaternion)
-    int tight_rect;   // 1: shrink the tile rectangle to the alpha >= 1/255 extent (exact)
+    int tight_rect;   // 1: shrink the tile rectangle to the alpha >= 1/255 extent (exact); 2: additionally drop every
+                      //    tile of the rectangle that holds no contributing pixel (exact; depth-first binning only)
 };
 
 // Projected splat. 12 floats = three 16-byte vectors; this is the record the blend kernels stage

@@ -21,7 +21,11 @@ import torch
 
 from . import native
 
+import os
+
 HALO = 5  # SSIM window radius
+# statistics pass of SSIM on the tensor cores (csrc/rgs_ssim_tc.cu) instead of the fp32 SIMT kernel
+USE_TENSOR_CORES = os.environ.get("RGS_SSIM_TC", "0") == "1"
 
 
 class CompositeLoss:
@@ -34,6 +38,21 @@ class CompositeLoss:
         self.dmaps = torch.zeros(9, H, W, dtype=torch.float32, device=dev)
         self.g_image = torch.zeros(3, H, W, dtype=torch.float32, device=dev)
         self.sums = torch.zeros(3, dtype=torch.float64, device=dev)
+        self.status = torch.zeros(native.CNT_WORDS, dtype=torch.int32, device=dev)
+        self.tensor_cores = USE_TENSOR_CORES and self.device.type == "cuda" and self._tc_supported()
+
+    def _tc_supported(self) -> bool:
+        import ctypes
+        fn = native.lib("cuda").rgs_cuda_ssim_tc_supported
+        fn.argtypes, fn.restype = [ctypes.c_int64, ctypes.c_int64], ctypes.c_int
+        return bool(fn(self.H, self.W))
+
+    def _ssim_fwd(self, gt, c0, c1, r0, r1):
+        if self.tensor_cores:
+            native.call("ssim_fwd_tc", self.device, self.image, gt, self.H, self.W, c0, c1, r0, r1, self.dmaps, self.sums,
+                        self.status, sig="ppiiiiiipppp")
+        else:
+            native.call("ssim_fwd", self.device, self.image, gt, self.H, self.W, c0, c1, r0, r1, self.dmaps, self.sums)
 
     @staticmethod
     def _bg(bg):
@@ -62,7 +81,7 @@ class CompositeLoss:
         assert gt.is_contiguous() and gt.shape == (3, H, W)
         c0, c1 = max(0, row0 - HALO), min(H, row1 + HALO)
         self.sums.zero_()
-        native.call("ssim_fwd", self.device, self.image, gt, H, W, c0, c1, row0, row1, self.dmaps, self.sums)
+        self._ssim_fwd(gt, c0, c1, row0, row1)
         npx = 3.0 * H * W
         native.call("ssim_bwd", self.device, self.image, gt, self.dmaps, H, W, row0, row1, c0, c1,
                     weight * (1.0 - lambda_dssim) / npx, weight * lambda_dssim / npx, self.g_image)
@@ -74,7 +93,7 @@ class CompositeLoss:
         row1 = H if row1 is None else row1
         c0, c1 = max(0, row0), min(H, row1)
         self.sums.zero_()
-        native.call("ssim_fwd", self.device, self.image, gt, H, W, c0, c1, row0, row1, self.dmaps, self.sums)
+        self._ssim_fwd(gt, c0, c1, row0, row1)
         return self.sums
 
     def loss_from_sums(self, sums, lambda_dssim: float = 0.2) -> dict:

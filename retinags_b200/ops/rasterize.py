@@ -30,7 +30,7 @@ INF = float("inf")
 
 
 def make_camera(cam: Camera, sh_degree: int, box_lo=None, box_hi=None, raw_params: bool = True,
-                tight_rect: bool = True, scale_modifier: float = 1.0, bg=(0.0, 0.0, 0.0)) -> RgsCamera:
+                tight_rect: bool | int = True, scale_modifier: float = 1.0, bg=(0.0, 0.0, 0.0)) -> RgsCamera:
     """Fill the by-value camera/sub-model descriptor the kernels take."""
     c = RgsCamera()
     c.view[:] = cam.world_view_transform.reshape(-1).tolist()
@@ -51,7 +51,7 @@ def make_camera(cam: Camera, sh_degree: int, box_lo=None, box_hi=None, raw_param
     c.sh_degree = int(sh_degree)
     c.scale_modifier = float(scale_modifier)
     c.raw_params = 1 if raw_params else 0
-    c.tight_rect = 1 if tight_rect else 0
+    c.tight_rect = int(tight_rect)  # 0 off, 1 opacity-aware rectangle, 2 rectangle + per-tile test
     return c
 
 

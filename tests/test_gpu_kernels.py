@@ -47,6 +47,18 @@ def test_binning_variants_agree_on_gpu():
         assert_mostly_close(a.cpu(), ref, atol=3e-5, rtol=1e-4, max_frac=5e-3)
 
 
+def test_tile_culling_is_exact_on_gpu():
+    g, cams = _scene(n=60000)
+    seg = rasterize.Segment(*(g[k].cuda().contiguous() for k in ("xyz", "sh", "scale", "rot", "opacity")))
+    outs, insts = [], []
+    for mode in (1, 2):
+        task = rasterize.RenderTask("cuda")
+        out = task.forward(rasterize.make_camera(cams[1], 3, tight_rect=mode), [seg], check=True)
+        outs.append(out.clone()); insts.append(task.n_inst)
+    assert torch.equal(outs[0], outs[1])
+    assert insts[1] < insts[0]
+
+
 def test_raster_small_capacity_regrows():
     g, cams = _scene(n=20000)
     seg = rasterize.Segment(*(g[k].cuda().contiguous() for k in ("xyz", "sh", "scale", "rot", "opacity")))
@@ -187,3 +199,28 @@ def test_peer_transport_single_rank_equals_local():
         assert (ra - rb).abs().mean() < 1e-5
     b.engine.borrow.close()
     tr.close()
+
+
+def test_ssim_tensor_core_path_matches_simt():
+    """tcgen05/TMEM horizontal filter (3xTF32) against the fp32 SIMT statistics kernel."""
+    from retinags_b200.ops import loss as loss_mod
+    H, W = 300, 448
+    gen = torch.Generator().manual_seed(3)
+    img = torch.rand(3, H, W, generator=gen).cuda()
+    gt = (img.cpu() + 0.1 * torch.randn(3, H, W, generator=gen)).clamp(0, 1).cuda()
+    res = {}
+    for tc in (False, True):
+        cl = CompositeLoss("cuda", H, W)
+        cl.tensor_cores = tc and cl._tc_supported()
+        if tc:
+            assert cl.tensor_cores, "tensor-core SSIM path not available"
+        cl.image.copy_(img)
+        sums = cl.loss(gt, 0.2, 16, 280).clone()
+        torch.cuda.synchronize()
+        assert int(cl.status[0]) == 0, f"bounded wait expired in the tensor-core kernel (status {int(cl.status[0])})"
+        res[tc] = (sums.cpu(), cl.dmaps[:, 11:285].clone().cpu(), cl.g_image[:, 16:280].clone().cpu())
+    torch.testing.assert_close(res[True][0], res[False][0], atol=1e-2, rtol=2e-5)
+    d_ref = res[False][1]
+    assert (res[True][1] - d_ref).abs().max().item() <= 2e-3 * d_ref.abs().max().item()
+    g_ref = res[False][2]
+    assert (res[True][2] - g_ref).abs().max().item() <= 2e-3 * g_ref.abs().max().item()

@@ -30,8 +30,9 @@ def test_tight_rect_is_exact():
     g, cams = small_scene(n=1500)
     a, ta, _, _ = native_render(g, cams[0], 3, tight=True)
     b, tb, _, _ = native_render(g, cams[0], 3, tight=False)
-    assert torch.equal(a, b)
-    assert ta.n_inst < tb.n_inst
+    c, tc, _, _ = native_render(g, cams[0], 3, tight=2)  # per-tile test on top
+    assert torch.equal(a, b) and torch.equal(a, c)
+    assert tc.n_inst < ta.n_inst < tb.n_inst
 
 
 def test_box_split_composites_to_whole():
