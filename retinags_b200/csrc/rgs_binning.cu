@@ -14,11 +14,11 @@
 #include "rgs_api.h"
 #include "rgs_cuda_common.cuh"
 
+#include <stdlib.h>
+
 #define BS_THREADS 256
-#define BS_ITEMS 16
-#define BS_CHUNK (BS_THREADS * BS_ITEMS)
 #define BS_WARPS (BS_THREADS / 32)
-#define BS_WARP_SPAN (32 * BS_ITEMS)
+#define BS_MIN_ITEMS 8   // smallest per-thread item count any variant uses: sizes the histogram table
 
 // number of tiles of the rectangle that hold at least one contributing pixel (all of them without tight_rect)
 __device__ __forceinline__ uint32_t count_hit_tiles(const RgsCamera& cam, const RgsSplat& sp, const RgsRect& rc) {
@@ -228,10 +228,12 @@ __device__ __forceinline__ uint32_t bs_count(const uint32_t* counters, int which
 
 // When keys_in is null the key of element i is gathered as key_src[vals_in[i]] / the value is i itself
 // (first pass of the depth sort: keys live in slot order, values are the slots).
+template <int BS_ITEMS>
 __global__ void __launch_bounds__(BS_THREADS) rgs_bs_hist_kernel(const uint32_t* __restrict__ keys,
                                                                 const uint32_t* __restrict__ counters, int which,
                                                                 uint32_t cap, int shift, uint32_t* __restrict__ hist,
                                                                 uint32_t nchunks_cap) {
+    constexpr uint32_t BS_CHUNK = BS_THREADS * BS_ITEMS, BS_WARP_SPAN = 32 * BS_ITEMS;
     __shared__ uint32_t sh[BS_WARPS][256];
     const uint32_t n = bs_count(counters, which, cap);
     const uint32_t nchunks = (n + BS_CHUNK - 1) / BS_CHUNK;
@@ -260,11 +262,11 @@ __global__ void __launch_bounds__(BS_THREADS) rgs_bs_hist_kernel(const uint32_t*
 
 __global__ void __launch_bounds__(256) rgs_bs_scan_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ totals,
                                                           const uint32_t* __restrict__ counters, int which, uint32_t cap,
-                                                          uint32_t nchunks_cap) {
+                                                          uint32_t nchunks_cap, uint32_t chunk) {
     __shared__ uint32_t warp_tot[8];
     __shared__ uint32_t carry_s;
     const uint32_t n = bs_count(counters, which, cap);
-    const uint32_t nchunks = (n + BS_CHUNK - 1) / BS_CHUNK;
+    const uint32_t nchunks = (n + chunk - 1) / chunk;
     uint32_t* row = hist + (size_t)blockIdx.x * nchunks_cap;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     if (threadIdx.x == 0) carry_s = 0;
@@ -298,10 +300,12 @@ __global__ void __launch_bounds__(256) rgs_bs_scan_kernel(uint32_t* __restrict__
     if (threadIdx.x == 0) totals[blockIdx.x] = carry_s;
 }
 
+template <int BS_ITEMS>
 __global__ void __launch_bounds__(BS_THREADS) rgs_bs_scatter_kernel(
     const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ keys_out,
     uint32_t* __restrict__ vals_out, const uint32_t* __restrict__ counters, int which, uint32_t cap, int shift,
     const uint32_t* __restrict__ hist, const uint32_t* __restrict__ totals, uint32_t nchunks_cap, int iota_vals) {
+    constexpr uint32_t BS_CHUNK = BS_THREADS * BS_ITEMS, BS_WARP_SPAN = 32 * BS_ITEMS;
     __shared__ uint32_t sh[BS_WARPS][256];
     __shared__ uint32_t digit_base[256];
     __shared__ uint32_t warp_tot[8];
@@ -548,21 +552,48 @@ __global__ void rgs_bs_tile_ranges_kernel(const uint32_t* __restrict__ keys, con
 // ---------------------------------------------------------------------------------------------
 // host
 // ---------------------------------------------------------------------------------------------
-static inline uint32_t chunks_of(int64_t n) { int64_t c = (n + BS_CHUNK - 1) / BS_CHUNK; return (uint32_t)(c > 0 ? c : 1); }
+// table sizes assume the smallest chunk any variant uses
+static inline uint32_t chunks_of(int64_t n) {
+    const int64_t chunk = BS_THREADS * BS_MIN_ITEMS;
+    int64_t c = (n + chunk - 1) / chunk;
+    return (uint32_t)(c > 0 ? c : 1);
+}
+
+// items per thread of the sort kernels: 16 (4096-pair chunks) or 8 (2048-pair chunks, half the registers);
+// RGS_SORT_ITEMS selects the variant.
+static int sort_items() {
+    static int v = 0;
+    if (!v) {
+        const char* e = getenv("RGS_SORT_ITEMS");
+        v = (e && atoi(e) == 16) ? 16 : 8;
+    }
+    return v;
+}
+
+template <int ITEMS>
+static void bs_pass(const uint32_t* kin, const uint32_t* vin, uint32_t* kout, uint32_t* vout, const uint32_t* cnt, int which,
+                    uint32_t cap, int shift, uint32_t* hist, uint32_t* totals, uint32_t nchunks_cap, int iota, cudaStream_t st) {
+    const uint32_t chunk = BS_THREADS * ITEMS;
+    const uint32_t nch = (cap + chunk - 1) / chunk;
+    const unsigned grid = nch < 1u ? 1u : (nch < 148u * 8u ? nch : 148u * 8u);
+    rgs_bs_hist_kernel<ITEMS><<<grid, BS_THREADS, 0, st>>>(kin, cnt, which, cap, shift, hist, nchunks_cap);
+    rgs_bs_scan_kernel<<<256, 256, 0, st>>>(hist, totals, cnt, which, cap, nchunks_cap, chunk);
+    rgs_bs_scatter_kernel<ITEMS><<<grid, BS_THREADS, 0, st>>>(kin, vin, kout, vout, cnt, which, cap, shift, hist, totals,
+                                                              nchunks_cap, iota);
+}
 
 static void bs_sort(const uint32_t* keys_first, uint32_t* ka, uint32_t* va, uint32_t* kb, uint32_t* vb, const uint32_t* cnt,
                     int which, uint32_t cap, int npass, uint32_t* hist, uint32_t* totals, int iota_first, cudaStream_t st,
                     uint32_t** k_out, uint32_t** v_out) {
     const uint32_t nchunks_cap = chunks_of(cap);
-    const unsigned grid = nchunks_cap < 148u * 8u ? nchunks_cap : 148u * 8u;
     const uint32_t* kin = keys_first;
     uint32_t* vin = va;
     uint32_t *kout = kb, *vout = vb;
+    const int items = sort_items();
     for (int p = 0; p < npass; ++p) {
-        rgs_bs_hist_kernel<<<grid, BS_THREADS, 0, st>>>(kin, cnt, which, cap, 8 * p, hist, nchunks_cap);
-        rgs_bs_scan_kernel<<<256, 256, 0, st>>>(hist, totals, cnt, which, cap, nchunks_cap);
-        rgs_bs_scatter_kernel<<<grid, BS_THREADS, 0, st>>>(kin, vin, kout, vout, cnt, which, cap, 8 * p, hist, totals,
-                                                            nchunks_cap, (p == 0 && iota_first) ? 1 : 0);
+        const int iota = (p == 0 && iota_first) ? 1 : 0;
+        if (items == 16) bs_pass<16>(kin, vin, kout, vout, cnt, which, cap, 8 * p, hist, totals, nchunks_cap, iota, st);
+        else bs_pass<8>(kin, vin, kout, vout, cnt, which, cap, 8 * p, hist, totals, nchunks_cap, iota, st);
         // ping-pong: after the first pass the input buffers are (ka, va) / (kb, vb) alternately
         kin = kout; vin = vout;
         if (kout == kb) { kout = ka; vout = va; } else { kout = kb; vout = vb; }

@@ -333,9 +333,12 @@ struct __attribute__((aligned(16))) RgsSplatGrad {
 // (g_xyz[3], g_sh[48], g_scale[3], g_rot[4], g_opacity[1]); when cam.raw_params is set the
 // gradients are with respect to the raw parameters. Returns the norm of the NDC-scaled screen
 // gradient (the densification statistic).
+// When `g_sh` is null the SH gradients are not accumulated; the caller can form them itself from the basis
+// (`basis_out`, 16 values) and the clamped colour gradient (`gc_out`, 3 values): d/dsh[k][c] = basis[k] * gc[c].
 RGS_HD float rgs_project_bwd(const RgsCamera& cam, const float* p, const float* s_in, const float* q_in, float o_in,
                              const float* sh, unsigned clamped, const RgsSplatGrad& g, float* g_xyz, float* g_sh,
-                             float* g_scale, float* g_rot, float* g_opacity) {
+                             float* g_scale, float* g_rot, float* g_opacity, float* basis_out = nullptr,
+                             float* gc_out = nullptr) {
     float s[3], q[4], o, qn;
     rgs_activate(cam.raw_params, s_in, q_in, o_in, s, q, o, qn);
     RgsEwa e;
@@ -439,9 +442,11 @@ RGS_HD float rgs_project_bwd(const RgsCamera& cam, const float* p, const float* 
     int nc = (cam.sh_degree + 1) * (cam.sh_degree + 1);
     float gux = 0.f, guy = 0.f, guz = 0.f;
     RGS_UNROLL
+    if (gc_out) { gc_out[0] = gc0; gc_out[1] = gc1; gc_out[2] = gc2; }
     for (int k = 0; k < 16; ++k) {
+        if (basis_out) basis_out[k] = k < nc ? B[k] : 0.0f;
         if (k >= nc) continue;
-        g_sh[3 * k] += B[k] * gc0; g_sh[3 * k + 1] += B[k] * gc1; g_sh[3 * k + 2] += B[k] * gc2;
+        if (g_sh) { g_sh[3 * k] += B[k] * gc0; g_sh[3 * k + 1] += B[k] * gc1; g_sh[3 * k + 2] += B[k] * gc2; }
         float wsum = sh[3 * k] * gc0 + sh[3 * k + 1] * gc1 + sh[3 * k + 2] * gc2;
         gux += Bx[k] * wsum; guy += By[k] * wsum; guz += Bz[k] * wsum;
     }

@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
 // ---------------------------------------------------------------------------------------------
 struct RgsSegments { RgsSegment s[4]; int n; };
 
-__global__ void __launch_bounds__(128) rgs_geom_bwd_kernel(
+__global__ void __launch_bounds__(128, 8) rgs_geom_bwd_kernel(
     const __grid_constant__ RgsCamera cam, const __grid_constant__ RgsSegments segs,
     const uint32_t* __restrict__ counters, const int32_t* __restrict__ vis_ids, const uint32_t* __restrict__ aux,
     const RgsSplatGrad* __restrict__ splat_grads) {
@@ -309,10 +309,10 @@ __global__ void __launch_bounds__(128) rgs_geom_bwd_kernel(
         float4 q4 = reinterpret_cast<const float4*>(sg.rot)[i];
         float q[4] = {q4.x, q4.y, q4.z, q4.w};
         float gx[3] = {0.f, 0.f, 0.f}, gs[3] = {0.f, 0.f, 0.f}, gq[4] = {0.f, 0.f, 0.f, 0.f}, go[1] = {0.f};
-        float gsh[48];
-#pragma unroll
-        for (int k = 0; k < 48; ++k) gsh[k] = 0.f;
-        const float nrm = rgs_project_bwd(cam, p, s, q, sg.opacity[i], sg.sh + 48 * i, a & 7u, g, gx, gsh, gs, gq, go);
+        // SH gradients are outer products basis[k] * gc[c]: formed on the fly when written (no 48-float array)
+        float basis[16], gc[3];
+        const float nrm = rgs_project_bwd(cam, p, s, q, sg.opacity[i], sg.sh + 48 * i, a & 7u, g, gx, nullptr, gs, gq, go,
+                                          basis, gc);
         // first writer of this row in this step stores, later ones (other views of the batch) add
         bool first = false;
         if (sg.touched) { first = sg.touched[i] == 0; if (first) sg.touched[i] = 1; }
@@ -338,7 +338,11 @@ __global__ void __launch_bounds__(128) rgs_geom_bwd_kernel(
             for (int k = 0; k < 12; ++k) {
                 if (k < nc4) {
                     float4 o = first ? make_float4(0.f, 0.f, 0.f, 0.f) : d[k];
-                    o.x += gsh[4 * k]; o.y += gsh[4 * k + 1]; o.z += gsh[4 * k + 2]; o.w += gsh[4 * k + 3];
+                    // element e = 3*coef + channel
+                    o.x += basis[(4 * k) / 3] * gc[(4 * k) % 3];
+                    o.y += basis[(4 * k + 1) / 3] * gc[(4 * k + 1) % 3];
+                    o.z += basis[(4 * k + 2) / 3] * gc[(4 * k + 2) % 3];
+                    o.w += basis[(4 * k + 3) / 3] * gc[(4 * k + 3) % 3];
                     d[k] = o;
                 }
             }
