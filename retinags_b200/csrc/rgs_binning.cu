@@ -232,7 +232,7 @@ template <int BS_ITEMS>
 __global__ void __launch_bounds__(BS_THREADS) rgs_bs_hist_kernel(const uint32_t* __restrict__ keys,
                                                                 const uint32_t* __restrict__ counters, int which,
                                                                 uint32_t cap, int shift, uint32_t* __restrict__ hist,
-                                                                uint32_t nchunks_cap) {
+                                                                uint32_t nchunks_cap, int aggregate) {
     constexpr uint32_t BS_CHUNK = BS_THREADS * BS_ITEMS, BS_WARP_SPAN = 32 * BS_ITEMS;
     __shared__ uint32_t sh[BS_WARPS][256];
     const uint32_t n = bs_count(counters, which, cap);
@@ -247,9 +247,13 @@ __global__ void __launch_bounds__(BS_THREADS) rgs_bs_hist_kernel(const uint32_t*
             const uint32_t idx = base + r * 32 + lane;
             const bool valid = idx < n;
             const uint32_t digit = valid ? ((keys[idx] >> shift) & 0xffu) : 0xffffffffu;
-            const uint32_t m = __match_any_sync(0xffffffffu, digit);
-            if (valid && lane == (__ffs(m) - 1)) sh[wid][digit] += __popc(m);
-            __syncwarp();
+            if (aggregate) {  // digits repeat inside a warp (high bits of sorted-ish keys): one update per distinct digit
+                const uint32_t m = __match_any_sync(0xffffffffu, digit);
+                if (valid && lane == (__ffs(m) - 1)) sh[wid][digit] += __popc(m);
+                __syncwarp();
+            } else if (valid) {  // digits mostly distinct inside a warp: conflict-free shared atomics
+                atomicAdd(&sh[wid][digit], 1u);
+            }
         }
         __syncthreads();
         uint32_t tot = 0;
@@ -306,9 +310,12 @@ __global__ void __launch_bounds__(BS_THREADS) rgs_bs_scatter_kernel(
     uint32_t* __restrict__ vals_out, const uint32_t* __restrict__ counters, int which, uint32_t cap, int shift,
     const uint32_t* __restrict__ hist, const uint32_t* __restrict__ totals, uint32_t nchunks_cap, int iota_vals) {
     constexpr uint32_t BS_CHUNK = BS_THREADS * BS_ITEMS, BS_WARP_SPAN = 32 * BS_ITEMS;
-    __shared__ uint32_t sh[BS_WARPS][256];
-    __shared__ uint32_t digit_base[256];
+    __shared__ uint32_t sh[BS_WARPS][256];      // per-warp digit counts -> offsets of the warp inside the digit's run
+    __shared__ uint32_t digit_base[256];        // first output index of every digit (over the whole array)
+    __shared__ uint32_t local_start[256];       // first staged index of every digit inside this chunk
+    __shared__ uint32_t global_start[256];      // output index of the chunk's first element of every digit
     __shared__ uint32_t warp_tot[8];
+    __shared__ uint32_t stage_k[BS_CHUNK], stage_v[BS_CHUNK];
     const uint32_t n = bs_count(counters, which, cap);
     const uint32_t nchunks = (n + BS_CHUNK - 1) / BS_CHUNK;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -354,21 +361,44 @@ __global__ void __launch_bounds__(BS_THREADS) rgs_bs_scatter_kernel(
             __syncwarp();
         }
         __syncthreads();
+        // thread d: offsets of the warps inside digit d's run, the chunk's count of d, and a block scan of the counts
         {
             const int d = threadIdx.x;
-            uint32_t run = hist[(size_t)d * nchunks_cap + c] + digit_base[d];
+            uint32_t run = 0;
 #pragma unroll
             for (int w = 0; w < BS_WARPS; ++w) { uint32_t t = sh[w][d]; sh[w][d] = run; run += t; }
+            uint32_t incl = run;
+#pragma unroll
+            for (int dd = 1; dd < 32; dd <<= 1) {
+                uint32_t u = __shfl_up_sync(0xffffffffu, incl, dd);
+                if (lane >= dd) incl += u;
+            }
+            if (lane == 31) warp_tot[wid] = incl;
+            __syncthreads();
+            uint32_t wbase = 0;
+            for (int w = 0; w < wid; ++w) wbase += warp_tot[w];
+            local_start[d] = wbase + incl - run;
+            global_start[d] = hist[(size_t)d * nchunks_cap + c] + digit_base[d];
         }
         __syncthreads();
+        // stage the chunk in digit order
 #pragma unroll
         for (int r = 0; r < BS_ITEMS; ++r) {
             const uint32_t idx = base + r * 32 + lane;
             if (idx < n) {
                 const uint32_t digit = (key[r] >> shift) & 0xffu;
-                const uint32_t dst = sh[wid][digit] + rank[r];
-                if (dst < cap) { keys_out[dst] = key[r]; vals_out[dst] = val[r]; }
+                const uint32_t pos = local_start[digit] + sh[wid][digit] + rank[r];
+                stage_k[pos] = key[r]; stage_v[pos] = val[r];
             }
+        }
+        __syncthreads();
+        // consecutive threads now hold consecutive elements of a digit's run: stores come out in full sectors
+        const uint32_t chunk_n = min(BS_CHUNK, n - c * BS_CHUNK);
+        for (uint32_t i = threadIdx.x; i < chunk_n; i += BS_THREADS) {
+            const uint32_t k = stage_k[i];
+            const uint32_t digit = (k >> shift) & 0xffu;
+            const uint32_t dst = global_start[digit] + (i - local_start[digit]);
+            if (dst < cap) { keys_out[dst] = k; vals_out[dst] = stage_v[i]; }
         }
         __syncthreads();
     }
@@ -565,7 +595,7 @@ static int sort_items() {
     static int v = 0;
     if (!v) {
         const char* e = getenv("RGS_SORT_ITEMS");
-        v = (e && atoi(e) == 16) ? 16 : 8;
+        v = (e && atoi(e) == 8) ? 8 : 16;
     }
     return v;
 }
@@ -576,7 +606,9 @@ static void bs_pass(const uint32_t* kin, const uint32_t* vin, uint32_t* kout, ui
     const uint32_t chunk = BS_THREADS * ITEMS;
     const uint32_t nch = (cap + chunk - 1) / chunk;
     const unsigned grid = nch < 1u ? 1u : (nch < 148u * 8u ? nch : 148u * 8u);
-    rgs_bs_hist_kernel<ITEMS><<<grid, BS_THREADS, 0, st>>>(kin, cnt, which, cap, shift, hist, nchunks_cap);
+    // which == CNT_INST is the tile sort: its upper digit repeats inside a warp, everything else is close to random
+    const int aggregate = (which == RGS_CNT_INST && shift >= 8) ? 1 : 0;
+    rgs_bs_hist_kernel<ITEMS><<<grid, BS_THREADS, 0, st>>>(kin, cnt, which, cap, shift, hist, nchunks_cap, aggregate);
     rgs_bs_scan_kernel<<<256, 256, 0, st>>>(hist, totals, cnt, which, cap, nchunks_cap, chunk);
     rgs_bs_scatter_kernel<ITEMS><<<grid, BS_THREADS, 0, st>>>(kin, vin, kout, vout, cnt, which, cap, shift, hist, totals,
                                                               nchunks_cap, iota);
