@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(256) rgs_project_slots_kernel(
     float4* dst = reinterpret_cast<float4*>(splats + slot);
     dst[0] = make_float4(sp.px, sp.py, sp.ca, sp.cb);
     dst[1] = make_float4(sp.cc, sp.opacity, sp.r, sp.g);
-    dst[2] = make_float4(sp.b, sp.w, sp.depth, 0.f);
+    dst[2] = make_float4(sp.b, sp.w, sp.depth, sp.pmin);
     vis_ids[slot] = (int32_t)(id_base + i);
     aux[slot] = ((uint32_t)radius << 3) | clamped;
     slot_depth[slot] = __float_as_uint(sp.depth);
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(256) rgs_project_cand_kernel(
             float4* dst = reinterpret_cast<float4*>(splats + slot);
             dst[0] = make_float4(sp.px, sp.py, sp.ca, sp.cb);
             dst[1] = make_float4(sp.cc, sp.opacity, sp.r, sp.g);
-            dst[2] = make_float4(sp.b, sp.w, sp.depth, 0.f);
+            dst[2] = make_float4(sp.b, sp.w, sp.depth, sp.pmin);
             vis_ids[slot] = (int32_t)gid;
             aux[slot] = ((uint32_t)radius << 3) | clamped;
             slot_depth[slot] = __float_as_uint(sp.depth);

@@ -64,7 +64,7 @@ struct __attribute__((aligned(16))) RgsSplat {
     float r, g, b;
     float w;             // clip-space w == view-space z (projection has P[3][2] = 1)
     float depth;         // view-space z
-    float pad;
+    float pmin;          // powers below this give alpha < 1/255: lets the blend loops skip the exponential
 };
 
 struct RgsRect { int x0, y0, x1, y1; };
@@ -285,7 +285,10 @@ RGS_HD bool rgs_project(const RgsCamera& cam, const float* p, const float* s_in,
     out.ca = e.c * det_inv; out.cb = -e.b * det_inv; out.cc = e.a * det_inv;
     out.opacity = o;
     out.r = fmaxf(c0, 0.0f); out.g = fmaxf(c1, 0.0f); out.b = fmaxf(c2, 0.0f);
-    out.w = hw; out.depth = t[2]; out.pad = 0.0f;
+    out.w = hw; out.depth = t[2];
+    // alpha = o exp(power) < 1/255  <=>  power < -ln(255 o); slightly lowered so that the cheap test never rejects a
+    // pair the exact test would keep
+    out.pmin = -logf(255.0f * o) * 1.00001f - 0.00001f;
     radius = irad;
     return true;
 }
@@ -510,7 +513,7 @@ RGS_HD bool rgs_alpha(const RgsCamera& cam, const RgsPixelRay& ray, float pixx, 
                       float& alpha, float& G, float& dx, float& dy) {
     dx = sp.px - pixx; dy = sp.py - pixy;
     float power = -0.5f * (sp.ca * dx * dx + sp.cc * dy * dy) - sp.cb * dx * dy;
-    if (power > 0.0f) return false;
+    if (power > 0.0f || power < sp.pmin) return false;
     G = expf(power);
     alpha = fminf(RGS_ALPHA_MAX, sp.opacity * G);
     if (alpha < RGS_ALPHA_MIN) return false;

@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(256) rgs_project_emit_kernel(
     float4* dst = reinterpret_cast<float4*>(splats + slot);
     dst[0] = make_float4(sp.px, sp.py, sp.ca, sp.cb);
     dst[1] = make_float4(sp.cc, sp.opacity, sp.r, sp.g);
-    dst[2] = make_float4(sp.b, sp.w, sp.depth, 0.f);
+    dst[2] = make_float4(sp.b, sp.w, sp.depth, sp.pmin);
     vis_ids[slot] = (int32_t)(id_base + i);
     aux[slot] = ((uint32_t)radius << 3) | clamped;
     if (splat_grads) {  // the backward accumulates into this record: clear it here, no separate memset
@@ -265,15 +265,44 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
                 bool hit = false;
                 if (contributor <= last) hit = rgs_blend_bwd_step(cam, ray, pixx, pixy, sm.buf[stage][j], st, g);
                 if (!__any_sync(0xffffffffu, hit)) continue;
-                float v[9] = {g.dpx, g.dpy, g.dca, g.dcb, g.dcc, g.dopacity, g.dr, g.dg, g.db};
+                // Reduce 8 of the 9 values with a transposing butterfly: at every step a lane keeps half of its values
+                // and hands the other half to its partner, so the 8 sums cost 4+2+1+1+1 = 9 shuffles instead of 40;
+                // lane 4k ends up with the total of value k. The ninth value takes the plain 5-step reduction.
+                float v[8] = {g.dpx, g.dpy, g.dca, g.dcb, g.dcc, g.dopacity, g.dr, g.dg};
+                float v8 = hit ? g.db : 0.f;
+                if (!hit) {
 #pragma unroll
-                for (int k = 0; k < 9; ++k) v[k] = warp_sum(hit ? v[k] : 0.f);
-                if (lane == 0) {
-                    float4* dst = reinterpret_cast<float4*>(splat_grads + sm_slot[stage][j]);
-                    atomicAdd(dst, make_float4(v[0], v[1], v[2], v[3]));
-                    atomicAdd(dst + 1, make_float4(v[4], v[5], v[6], v[7]));
-                    atomicAdd(reinterpret_cast<float*>(dst + 2), v[8]);
+                    for (int k = 0; k < 8; ++k) v[k] = 0.f;
                 }
+                float w4[4], w2[2], w1;
+                {
+                    const bool up = lane & 16;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float send = up ? v[k] : v[k + 4], keep = up ? v[k + 4] : v[k];
+                        w4[k] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+                    }
+                }
+                {
+                    const bool up = lane & 8;
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const float send = up ? w4[k] : w4[k + 2], keep = up ? w4[k + 2] : w4[k];
+                        w2[k] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                    }
+                }
+                {
+                    const bool up = lane & 4;
+                    const float send = up ? w2[0] : w2[1], keep = up ? w2[1] : w2[0];
+                    w1 = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+                }
+                w1 += __shfl_xor_sync(0xffffffffu, w1, 2);
+                w1 += __shfl_xor_sync(0xffffffffu, w1, 1);
+                v8 = warp_sum(v8);
+                // value index held by this lane: bit 16 -> +4, bit 8 -> +2, bit 4 -> +1
+                float* dst = reinterpret_cast<float*>(splat_grads + sm_slot[stage][j]);
+                if ((lane & 3) == 0) atomicAdd(dst + (((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)), w1);
+                if (lane == 0) atomicAdd(dst + 8, v8);
             }
         }
         __syncthreads();  // frees this stage for the copy issued two rounds later
