@@ -27,6 +27,7 @@ CUDA_SOURCES = [
     "rgs_model.cu",
     "rgs_p2p.cu",
     "rgs_border.cu",
+    "rgs_aux.cu",
     "rgs_ssim_tc.cu",
     "rgs_noalloc.cu",
 ]

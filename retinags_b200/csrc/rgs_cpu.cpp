@@ -12,6 +12,7 @@
 #include <vector>
 #include "rgs_api.h"
 #include "rgs_loss_math.h"
+#include "rgs_knn.h"
 
 extern "C" {
 
@@ -406,6 +407,35 @@ int rgs_cpu_ssim_bwd(const float* img, const float* gt, const float* dmaps, int6
                 float sgn = diff > 0.f ? 1.f : (diff < 0.f ? -1.f : 0.f);
                 g_image[pid] = (float)w_l1 * sgn - (float)w_ssim * dssim;
             }
+    return 0;
+}
+
+// CPU twins of rgs_aux.cu
+int rgs_cpu_knn3(const RgsKnnGrid* g, const float* pts, const int32_t* cell_start, int64_t n, float* out, void*) {
+#pragma omp parallel for schedule(dynamic, 256)
+    for (int64_t i = 0; i < n; ++i) out[i] = rgs_knn3(*g, pts, cell_start, n, i);
+    return 0;
+}
+
+int rgs_cpu_histogram(const float* xyz, const float* weight, int64_t n, const double* lo, const double* voxel,
+                      const int64_t* dims, float* grid, void*) {
+    for (int64_t i = 0; i < n; ++i) {
+        int64_t c[3];
+        for (int a = 0; a < 3; ++a) {
+            int64_t v = (int64_t)std::floor((xyz[3 * i + a] - (float)lo[a]) / (float)voxel[a]);
+            c[a] = std::min<int64_t>(std::max<int64_t>(v, 0), dims[a] - 1);
+        }
+        grid[(c[0] * dims[1] + c[1]) * dims[2] + c[2]] += weight ? weight[i] : 1.0f;
+    }
+    return 0;
+}
+
+int rgs_cpu_mark_visible(const float* xyz, int64_t n, const RgsCamera* cam, uint8_t* out, void*) {
+    for (int64_t i = 0; i < n; ++i) {
+        float t[3];
+        rgs_view_point(cam->view, xyz + 3 * i, t);
+        out[i] = t[2] > RGS_NEAR_Z ? 1 : 0;
+    }
     return 0;
 }
 

@@ -458,3 +458,12 @@ class GaussianRasterizer(torch.nn.Module):
         if shs is None or colors_precomp is not None or cov3D_precomp is not None:
             raise NotImplementedError("only the SH + scale/rotation path exists (the one the reference's trainer uses)")
         return rasterize_gaussians(means3D, means2D, shs, opacities, scales, rotations, self.raster_settings)
+
+    def markVisible(self, positions: torch.Tensor) -> torch.Tensor:
+        """Boolean mask of the points in front of the near plane (``GaussianRasterizer.markVisible`` of the
+        reference, ``diff_gaussian_rasterization_half_gaussian/__init__.py:188-197``)."""
+        cam = _settings_camera(self.raster_settings)
+        pts = positions.detach().float().contiguous()
+        out = torch.zeros(pts.shape[0], dtype=torch.uint8, device=pts.device)
+        native.call("mark_visible", pts.device, pts, pts.shape[0], cam, out, sig="pippp")
+        return out.bool()

@@ -63,16 +63,20 @@ class Grid3D:
 def load_histogram(xyz: torch.Tensor, grid: Grid3D, weights: torch.Tensor | None = None) -> torch.Tensor:
     """Per-cell load of Gaussians resident on ``xyz.device`` (replaces the reference's CPU numba
     scatter-add ``accum_on_3Dgrid``, ``grid_utils/utils.py:140-151``).  Returns a float32 tensor of the grid's shape on
-    the same device, ready to be all-reduced."""
-    lo = torch.as_tensor(grid.range_low, dtype=torch.float32, device=xyz.device)
-    vs = torch.as_tensor(grid.voxel_size, dtype=torch.float32, device=xyz.device)
-    gs = torch.as_tensor(grid.grid_size, dtype=torch.int64, device=xyz.device)
-    idx = torch.floor((xyz - lo) / vs).to(torch.int64)
-    idx = torch.minimum(torch.clamp_min(idx, 0), gs - 1)
-    flat = (idx[:, 0] * gs[1] + idx[:, 1]) * gs[2] + idx[:, 2]
-    n = int(np.prod(grid.grid_size))
-    h = torch.bincount(flat, weights=weights, minlength=n) if flat.numel() else torch.zeros(n, device=xyz.device)
-    return h.to(torch.float32).view(*grid.grid_size)
+    the same device, ready to be all-reduced.  Native kernel: ``rgs_histogram_kernel`` (``csrc/rgs_aux.cu``)."""
+    import ctypes
+
+    from ..ops import native
+    out = torch.zeros(grid.grid_size, dtype=torch.float32, device=xyz.device)
+    n = int(xyz.shape[0])
+    if n == 0:
+        return out
+    lo = (ctypes.c_double * 3)(*[float(v) for v in grid.range_low])
+    vs = (ctypes.c_double * 3)(*[float(v) for v in grid.voxel_size])
+    dims = (ctypes.c_int64 * 3)(*[int(v) for v in grid.grid_size])
+    w = None if weights is None else weights.detach().float().contiguous()
+    native.call("histogram", xyz.device, xyz.detach().float().contiguous(), w, n, lo, vs, dims, out, sig="ppippppp")
+    return out
 
 
 @dataclass

@@ -224,3 +224,14 @@ def test_ssim_tensor_core_path_matches_simt():
     assert (res[True][1] - d_ref).abs().max().item() <= 2e-3 * d_ref.abs().max().item()
     g_ref = res[False][2]
     assert (res[True][2] - g_ref).abs().max().item() <= 2e-3 * g_ref.abs().max().item()
+
+
+def test_aux_kernels_match_cpu():
+    """kNN initialiser, load histogram and frustum mask on the GPU against their CPU twins."""
+    from retinags_b200.ops.knn import knn3_dist2
+    from retinags_b200.parallel.partition import Grid3D, load_histogram
+    gen = torch.Generator().manual_seed(0)
+    pts = torch.cat([torch.randn(40000, 3, generator=gen), torch.rand(200, 3, generator=gen) * 30])
+    torch.testing.assert_close(knn3_dist2(pts.cuda()).cpu(), knn3_dist2(pts), atol=1e-9, rtol=1e-5)
+    grid = Grid3D.from_points(pts.numpy().astype("float64"), (64, 32, 1))
+    torch.testing.assert_close(load_histogram(pts.cuda(), grid).cpu(), load_histogram(pts, grid))

@@ -115,3 +115,12 @@ def test_interval_helpers():
     assert is_point_in_batch(10, 4, 13) and not is_point_in_batch(10, 4, 14)
     assert abs(expon_lr(0, 1.6e-4, 1.6e-6, max_steps=30000) - 1.6e-4) < 1e-12
     assert abs(expon_lr(30000, 1.6e-4, 1.6e-6, max_steps=30000) - 1.6e-6) < 1e-12
+
+
+def test_knn_matches_brute_force():
+    from retinags_b200.ops.knn import brute_force, knn3_dist2
+    g = torch.Generator().manual_seed(0)
+    for pts in (torch.rand(5000, 3, generator=g), torch.cat([torch.randn(3000, 3, generator=g) * 0.1, torch.rand(50, 3, generator=g) * 40]),
+                torch.rand(3, 3, generator=g), torch.rand(2000, 3, generator=g) * torch.tensor([1.0, 1.0, 0.0])):
+        a, b = knn3_dist2(pts), brute_force(pts)
+        torch.testing.assert_close(a, b, atol=1e-9, rtol=1e-4)

@@ -132,3 +132,6 @@ def test_autograd_function_interface():
     assert torch.equal(radii > 0, info["radii"] > 0)
     color.sum().backward()
     assert xyz.grad.abs().sum() > 0 and m2d.grad.abs().sum() > 0
+    vis = rasterize.GaussianRasterizer(st).markVisible(a["xyz"])
+    view = torch.cat([a["xyz"], torch.ones(a["xyz"].shape[0], 1)], 1) @ torch.tensor(cam.world_view_transform)
+    assert torch.equal(vis, view[:, 2] > 0.2)
