@@ -28,6 +28,7 @@ CUDA_SOURCES = [
     "rgs_p2p.cu",
     "rgs_border.cu",
     "rgs_aux.cu",
+    "rgs_surgery.cu",
     "rgs_ssim_tc.cu",
     "rgs_noalloc.cu",
 ]

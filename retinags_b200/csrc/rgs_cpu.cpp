@@ -13,6 +13,7 @@
 #include "rgs_api.h"
 #include "rgs_loss_math.h"
 #include "rgs_knn.h"
+#include "rgs_surgery.h"
 
 extern "C" {
 
@@ -436,6 +437,71 @@ int rgs_cpu_mark_visible(const float* xyz, int64_t n, const RgsCamera* cam, uint
         rgs_view_point(cam->view, xyz + 3 * i, t);
         out[i] = t[2] > RGS_NEAR_Z ? 1 : 0;
     }
+    return 0;
+}
+
+// CPU twins of rgs_surgery.cu (same entry points, same output order, same split samples)
+int rgs_cpu_densify_classify(const float* params, int64_t cap, int64_t n, const float* accum, const float* denom,
+                             const float* maxrad, const RgsDensifyCfg* cfg, uint8_t* codes, int32_t* block_counts,
+                             int64_t* totals, void*) {
+    for (int c = 0; c < 4; ++c) totals[c] = 0;
+    if (n <= 0) return 0;
+    const RgsConstBlock p = rgs_const_block_of(params, cap);
+    const int64_t nblocks = (n + RGS_SURGERY_BLOCK - 1) / RGS_SURGERY_BLOCK;
+    for (int64_t b = 0; b < nblocks; ++b) {
+        int cnt[4] = {0, 0, 0, 0};
+        const int64_t end = std::min<int64_t>(n, (b + 1) * RGS_SURGERY_BLOCK);
+        for (int64_t i = b * RGS_SURGERY_BLOCK; i < end; ++i) {
+            const uint32_t code = rgs_densify_code(*cfg, p.scale + 3 * i, p.opacity[i], accum[i], denom[i], maxrad[i]);
+            codes[i] = (uint8_t)code;
+            for (int c = 0; c < 4; ++c) cnt[c] += (code >> c) & 1u;
+        }
+        for (int c = 0; c < 4; ++c) {
+            block_counts[c * nblocks + b] = (int32_t)totals[c];
+            totals[c] += cnt[c];
+        }
+    }
+    return 0;
+}
+
+int rgs_cpu_densify_gather(const float* params, const float* m, const float* v, int64_t cap, int64_t n,
+                           const uint8_t* codes, const int32_t* block_offsets, const int64_t* totals, float* dparams,
+                           float* dm, float* dv, int64_t dcap, uint64_t seed, int* status, void*) {
+    if (n <= 0) return 0;
+    const int64_t base_of[4] = {0, totals[0], totals[0] + totals[1], totals[0] + totals[1] + totals[2]};
+    if (base_of[3] + totals[3] > dcap) { *status = 1; return 0; }
+    const RgsConstBlock sp = rgs_const_block_of(params, cap), sm = rgs_const_block_of(m, cap), sv = rgs_const_block_of(v, cap);
+    const RgsBlock dp = rgs_block_of(dparams, dcap), dmm = rgs_block_of(dm, dcap), dvv = rgs_block_of(dv, dcap);
+    const int64_t nblocks = (n + RGS_SURGERY_BLOCK - 1) / RGS_SURGERY_BLOCK;
+#pragma omp parallel for schedule(static)
+    for (int64_t b = 0; b < nblocks; ++b) {
+        int64_t run[4];
+        for (int c = 0; c < 4; ++c) run[c] = base_of[c] + block_offsets[c * nblocks + b];
+        const int64_t end = std::min<int64_t>(n, (b + 1) * RGS_SURGERY_BLOCK);
+        for (int64_t i = b * RGS_SURGERY_BLOCK; i < end; ++i)
+            for (int c = 0; c < 4; ++c)
+                if ((codes[i] >> c) & 1u) rgs_surgery_emit(sp, sm, sv, i, dp, dmm, dvv, run[c]++, c, seed);
+    }
+    return 0;
+}
+
+int rgs_cpu_records_pack(const float* params, const float* m, const float* v, int64_t cap, const int64_t* index,
+                         int64_t row0, int64_t n, float* out, void*) {
+    const float* src[3] = {params, m, v};
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < n; ++r) {
+        const int64_t i = index ? index[r] : row0 + r;
+        for (int c = 0; c < 177; ++c) out[r * 177 + c] = src[c / 59][rgs_record_offset(cap, i, c % 59)];
+    }
+    return 0;
+}
+
+int rgs_cpu_records_unpack(const float* rec, int64_t n, float* params, float* m, float* v, int64_t cap, int64_t start,
+                           void*) {
+    float* dst[3] = {params, m, v};
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < n; ++r)
+        for (int c = 0; c < 177; ++c) dst[c / 59][rgs_record_offset(cap, start + r, c % 59)] = rec[r * 177 + c];
     return 0;
 }
 

@@ -333,6 +333,16 @@ __global__ void __launch_bounds__(128, 8) rgs_geom_bwd_kernel(
         g.dpx = g0.x; g.dpy = g0.y; g.dca = g0.z; g.dcb = g0.w;
         g.dcc = g1.x; g.dopacity = g1.y; g.dr = g1.z; g.dg = g1.w;
         g.db = g2.x; g.ddepth = g2.y; g.pad0 = 0.f; g.pad1 = 0.f;
+        // A visible splat that no pixel blended (it lies behind saturated pixels) has exactly zero image-space
+        // gradients, hence exactly zero parameter gradients: only its visibility statistics change, and its
+        // gradient row stays untouched (which the optimiser exploits as well).
+        if (g0.x == 0.f && g0.y == 0.f && g0.z == 0.f && g0.w == 0.f && g1.x == 0.f && g1.y == 0.f && g1.z == 0.f &&
+            g1.w == 0.f && g2.x == 0.f) {
+            if (sg.g_mean2d) { sg.g_mean2d[2 * i] = 0.f; sg.g_mean2d[2 * i + 1] = 0.f; }
+            if (sg.stat_denom) sg.stat_denom[i] += 1.0f;
+            if (sg.stat_maxrad) sg.stat_maxrad[i] = fmaxf(sg.stat_maxrad[i], (float)(a >> 3));
+            continue;
+        }
         float p[3] = {sg.xyz[3 * i], sg.xyz[3 * i + 1], sg.xyz[3 * i + 2]};
         float s[3] = {sg.scale[3 * i], sg.scale[3 * i + 1], sg.scale[3 * i + 2]};
         float4 q4 = reinterpret_cast<const float4*>(sg.rot)[i];

@@ -7,12 +7,25 @@ screen-filling and world-oversized ones; new Gaussians start with zero Adam mome
 restart afterwards.  Differences: everything runs on the store's device (the reference samples the
 split offsets on the CPU, ``:707-708``), and the parameter/moment surgery is one gather per buffer
 instead of per-tensor optimizer rewrites (``:589-664``).
+
+Two implementations with the same decisions and the same output order (kept originals, clones, first
+split children, second split children):
+
+* :func:`densify_and_prune` with ``native=True`` (default): the classification, scan and compaction
+  kernels of ``csrc/rgs_surgery.cu`` (CPU twin in ``csrc/rgs_cpu.cpp``), split offsets from a
+  counter-based Philox generator keyed by ``(seed, row, child)``; parameters and moments are written once
+  into fresh buffers;
+* ``native=False``: the same rules in PyTorch operations (``torch.randn`` split offsets); it is the
+  oracle of the kernels and the fallback when the device cannot hold a second copy of the state.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
-from .gaussians import NAMES, GaussianStore
+from ..ops import native
+from .gaussians import NAMES, RECORD, GaussianStore, _round_cap
 
 
 def _rotation_matrices(q: torch.Tensor) -> torch.Tensor:
@@ -27,11 +40,17 @@ def _rotation_matrices(q: torch.Tensor) -> torch.Tensor:
 def densify_and_prune(store: GaussianStore, max_grad: float, min_opacity: float, extent: float,
                       max_screen_size: float | None, percent_dense: float = 0.01, max_size: int | None = None,
                       skip_prune: bool = False, skip_clone: bool = False, skip_split: bool = False,
-                      generator: torch.Generator | None = None, n_split: int = 2) -> dict:
+                      generator: torch.Generator | None = None, n_split: int = 2, native_path: bool | None = None,
+                      seed: int | None = None) -> dict:
     n0 = store.count
     info = dict(cloned=0, split=0, pruned=0)
     if n0 == 0:
         return info
+    if native_path is None:
+        native_path = n_split == 2 and _fits_twice(store)
+    if native_path:
+        return _densify_native(store, max_grad, min_opacity, extent, max_screen_size, percent_dense, max_size, skip_prune,
+                               skip_clone, skip_split, generator, seed)
     over = max_size is not None and n0 > max_size
     if not over:
         grads = store.grad_accum[:n0] / store.denom[:n0]
@@ -75,6 +94,47 @@ def densify_and_prune(store: GaussianStore, max_grad: float, min_opacity: float,
             store.keep(~prune)
     store.reset_stats()
     return info
+
+
+def _fits_twice(store: GaussianStore) -> bool:
+    """The compaction kernels write a second copy of parameters and moments before the old one is released."""
+    if store.device.type != "cuda":
+        return True
+    free, _ = torch.cuda.mem_get_info(store.device)
+    # the gradient buffer is released first, so that only two more buffers are needed
+    return free > 2.6 * RECORD * 4 * store.cap * 1.3
+
+
+def _densify_native(store: GaussianStore, max_grad, min_opacity, extent, max_screen_size, percent_dense, max_size, skip_prune,
+                    skip_clone, skip_split, generator, seed) -> dict:
+    n0, dev = store.count, store.device
+    if seed is None:
+        seed = int(torch.randint(0, 2 ** 62, (1,), generator=generator if generator is not None and
+                                 generator.device.type == "cpu" else None).item())
+    cfg = native.RgsDensifyCfg(float(max_grad), float(percent_dense * extent), float(min_opacity),
+                               float(max_screen_size) if max_screen_size else 0.0, float(0.1 * extent), int(skip_clone),
+                               int(skip_split), int(skip_prune), int(max_size is not None and n0 > max_size), seed)
+    nblocks = -(-n0 // native.SURGERY_BLOCK)
+    codes = torch.empty(n0, dtype=torch.uint8, device=dev)
+    offsets = torch.empty(4 * nblocks, dtype=torch.int32, device=dev)
+    totals = torch.zeros(4, dtype=torch.int64, device=dev)
+    native.call("densify_classify", dev, store.params, store.cap, n0, store.grad_accum, store.denom, store.max_radii, cfg,
+                codes, offsets, totals)
+    kept, cloned, child_a, child_b = (int(x) for x in totals.cpu())
+    n1 = kept + cloned + child_a + child_b
+    new_cap = _round_cap(max(n1, 4))
+    if new_cap < store.cap and n1 > 0.5 * store.cap:
+        new_cap = store.cap  # keep the capacity when the model did not shrink much: later growth needs no reallocation
+    store.grads = None  # gradients do not survive surgery; released first to bound the peak
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    new = [torch.zeros(RECORD * new_cap, dtype=torch.float32, device=dev) for _ in range(3)]
+    native.call("densify_gather", dev, store.params, store.exp_avg, store.exp_avg_sq, store.cap, n0, codes, offsets, totals,
+                new[0], new[1], new[2], new_cap, seed, status)
+    if int(status.item()) != 0:
+        raise RuntimeError("densify_gather: destination smaller than the new model")
+    store.adopt(new[0], new[1], new[2], new_cap, n1)
+    # both children of a split exist or neither; "pruned" counts the originals that disappeared without a split
+    return dict(cloned=cloned, split=child_a, pruned=n0 - kept - child_a)
 
 
 def reset_opacity(store: GaussianStore, ceiling: float = 0.01):

@@ -131,9 +131,14 @@ class GaussianStore:
         cols = [v[name] if index is None else v[name][index] for name in NAMES]
         return torch.cat(cols, dim=1)
 
-    def migration_records(self, index: torch.Tensor | None = None) -> torch.Tensor:
-        """(n,177) = [params, exp_avg, exp_avg_sq] rows."""
-        return torch.cat([self.records(w, index) for w in ("params", "exp_avg", "exp_avg_sq")], dim=1)
+    def migration_records(self, index: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+        """(n,177) = [params, exp_avg, exp_avg_sq] rows, packed by one kernel (``csrc/rgs_surgery.cu``)."""
+        n = self.count if index is None else int(index.numel())
+        rec = out if out is not None else torch.empty(n, 3 * RECORD, dtype=torch.float32, device=self.device)
+        if n:
+            idx = None if index is None else index.to(torch.int64).contiguous()
+            native.call("records_pack", self.device, self.params, self.exp_avg, self.exp_avg_sq, self.cap, idx, 0, n, rec)
+        return rec
 
     def load_records(self, rec: torch.Tensor, which: str = "params", start: int = 0):
         n = rec.shape[0]
@@ -149,10 +154,8 @@ class GaussianStore:
         if n == 0:
             return
         self.reserve(self.count + n)
-        rec = rec.to(self.device)
-        self.load_records(rec[:, 0:RECORD], "params", self.count)
-        self.load_records(rec[:, RECORD:2 * RECORD], "exp_avg", self.count)
-        self.load_records(rec[:, 2 * RECORD:3 * RECORD], "exp_avg_sq", self.count)
+        rec = rec.to(self.device, torch.float32).contiguous()
+        native.call("records_unpack", self.device, rec, n, self.params, self.exp_avg, self.exp_avg_sq, self.cap, self.count)
         for s in (self.grad_accum, self.denom, self.max_radii):
             s[self.count:self.count + n] = 0
         self.count += n
@@ -171,6 +174,18 @@ class GaussianStore:
         for s in (self.grad_accum, self.denom, self.max_radii):
             s[:n] = s[idx]
         self.count = n
+
+    def adopt(self, params: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, cap: int, count: int):
+        """Take over freshly written buffers of ``cap`` rows (the output of the compaction kernels): gradients and
+        statistics restart from zero."""
+        dev = self.device
+        self.params, self.exp_avg, self.exp_avg_sq = params, exp_avg, exp_avg_sq
+        self.cap, self.count = cap, count
+        self.grads = torch.zeros(RECORD * cap, dtype=torch.float32, device=dev)
+        self.grad_accum = torch.zeros(cap, dtype=torch.float32, device=dev)
+        self.denom = torch.zeros(cap, dtype=torch.float32, device=dev)
+        self.max_radii = torch.zeros(cap, dtype=torch.float32, device=dev)
+        self.touched = torch.zeros(cap, dtype=torch.uint8, device=dev)
 
     def append_new(self, g: dict):
         """Append freshly created Gaussians (zero moments, zero statistics)."""

@@ -39,6 +39,10 @@ SIGNATURES = {
     "composite_bwd": "ppipiiiipp",
     "ssim_fwd": "ppiiiiiippp",
     "ssim_bwd": "pppiiiiiiffpp",
+    "densify_classify": "piipppppppp",
+    "densify_gather": "pppiippppppiipp",
+    "records_pack": "pppipiipp",
+    "records_unpack": "pipppiip",
 }
 
 _CTYPE = {"p": ctypes.c_void_p, "i": ctypes.c_int64, "f": ctypes.c_double}
@@ -77,6 +81,17 @@ class RgsSegment(ctypes.Structure):
         "xyz", "sh", "scale", "rot", "opacity", "g_xyz", "g_sh", "g_scale", "g_rot", "g_opacity",
         "g_mean2d", "stat_grad", "stat_denom", "stat_maxrad", "touched")] + [("count", ctypes.c_int64)]
 
+
+class RgsDensifyCfg(ctypes.Structure):
+    """Mirror of ``struct RgsDensifyCfg`` (csrc/rgs_surgery.h)."""
+
+    _fields_ = [("max_grad", ctypes.c_float), ("dense_extent", ctypes.c_float), ("min_opacity", ctypes.c_float),
+                ("max_screen", ctypes.c_float), ("world_max", ctypes.c_float), ("skip_clone", ctypes.c_int),
+                ("skip_split", ctypes.c_int), ("skip_prune", ctypes.c_int), ("no_grow", ctypes.c_int),
+                ("seed", ctypes.c_uint64)]
+
+
+SURGERY_BLOCK = 1024
 
 CNT_VIS, CNT_INST, CNT_OVERFLOW, CNT_STATUS, CNT_WORDS = 0, 1, 2, 3, 8
 SPLAT_FLOATS = 12
@@ -138,7 +153,7 @@ def stream_ptr(device: torch.device):
 
 # kernels launched by one call of an entry point (the radix sort's count depends on the tile count)
 _KERNELS = {"project_slots": 1, "project_slots2": 2, "project_emit": 1, "blend_fwd": 1, "blend_bwd": 1, "geom_bwd": 1, "scatter_radii": 1, "adam": 1,
-            "composite_fwd": 1, "composite_bwd": 1, "ssim_fwd": 1, "ssim_bwd": 1}
+            "composite_fwd": 1, "composite_bwd": 1, "ssim_fwd": 1, "ssim_bwd": 1, "densify_classify": 2}
 _LAUNCHES = [0]
 
 

@@ -235,3 +235,24 @@ def test_aux_kernels_match_cpu():
     torch.testing.assert_close(knn3_dist2(pts.cuda()).cpu(), knn3_dist2(pts), atol=1e-9, rtol=1e-5)
     grid = Grid3D.from_points(pts.numpy().astype("float64"), (64, 32, 1))
     torch.testing.assert_close(load_histogram(pts.cuda(), grid).cpu(), load_histogram(pts, grid))
+
+
+def test_surgery_kernels_match_cpu():
+    """Densification (classify, scan, compaction with Philox split samples) and migration records: GPU against the CPU twin."""
+    from retinags_b200.models import densify
+    from test_store_cpu import _densify_store
+    for n, kw in ((7000, dict(extent=5.0, max_screen_size=20.0)), (2500, dict(extent=20.0, max_screen_size=None))):
+        extent = kw.pop("extent")
+        a, b = _densify_store(n, "cpu"), _densify_store(n, "cuda")
+        ia = densify.densify_and_prune(a, 0.0002, 0.005, extent, native_path=True, seed=9, **kw)
+        ib = densify.densify_and_prune(b, 0.0002, 0.005, extent, native_path=True, seed=9, **kw)
+        assert ia == ib and a.count == b.count
+        for which in ("params", "exp_avg", "exp_avg_sq"):
+            va, vb = a.views(which), b.views(which)
+            for nm in va:
+                torch.testing.assert_close(vb[nm].cpu(), va[nm], atol=2e-5, rtol=1e-5)
+        idx = torch.randperm(a.count)[:333]
+        torch.testing.assert_close(b.migration_records(idx.cuda()).cpu(), a.migration_records(idx), atol=2e-5, rtol=1e-5)
+        c = GaussianStore(8, "cuda")
+        c.append_migration(b.migration_records())
+        assert torch.equal(c.migration_records(), b.migration_records())
