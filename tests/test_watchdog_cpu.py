@@ -71,3 +71,19 @@ def test_rank_that_raises_stops_the_others(tmp_path):
     assert res[1] == "raised"
     assert res[0].startswith("peer failure") and "injected fault" in res[0]
     assert res[2].startswith("peer failure")
+
+
+def test_rank_leaving_between_steps_is_noticed_by_training_ranks():
+    """The scenario of the multi-GPU rank-loss test, on two gloo ranks: two real training steps, then the last rank leaves."""
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    port = 28100 + os.getpid() % 500
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   PYTHONPATH=root, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(root, "tests", "rank_loss_worker.py"), "--mode", "silent"],
+                                      env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert [p.returncode for p in procs] == [0, 0], "\n".join(o[-2000:] for o in outs)
+    assert "RANK_LOSS_DETECTED rank 0" in outs[0] and "no heartbeat" in outs[0]
