@@ -6,13 +6,24 @@ Each Gaussian moves, with its Adam moments, to the sub-model whose new box conta
 ``trainer4tree_partition.py:290-317``).  Records are produced one source sub-model at a time and in
 bounded chunks, so the peak extra memory is one chunk per peer rather than a full copy of the model
 (the reference warns about running out of memory here, ``trainer4tree_partition.py:681-682``).
-The per-pair counts travel as one all-reduce of an (M,M) matrix, the records as point-to-point
-messages; records that stay on the rank are appended directly.
+The per-pair counts travel as one all-reduce of an (M,M) matrix; records that stay on the rank are
+appended directly.  Records that change rank travel in one of two ways:
+
+* ``path="peer"`` (CUDA ranks of one node): the pack kernel (``csrc/rgs_surgery.cu``) gathers the rows from the
+  source's column groups and stores the 177-float records straight into the destination rank's inbox, a
+  peer-mapped region (``parallel/peer.py``); one source sub-model per round, so the inbox holds at most one
+  sub-model; the destination unpacks from its own memory after the round's barrier.  No NCCL call moves
+  Gaussian bytes.
+* ``path="dist"``: ``torch.distributed`` send/recv of packed chunks (gloo ranks, several nodes).
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
+
+from ..ops import native
 
 from ..models.gaussians import RECORD, GaussianStore
 
@@ -20,8 +31,11 @@ CHUNK_ROWS = 1 << 20
 
 
 def migrate(old: dict[int, GaussianStore], tree, lo, hi, model2rank, rank: int, world: int, device, sh_degree: int,
-            group=None) -> dict[int, GaussianStore]:
+            group=None, path: str = "auto") -> dict[int, GaussianStore]:
     M = len(model2rank)
+    device = torch.device(device)
+    if path == "auto":
+        path = "peer" if (device.type == "cuda" and world > 1 and os.environ.get("RGS_MIGRATE_PATH", "peer") == "peer") else "dist"
     local_new = [m for m in range(M) if model2rank[m] == rank]
     # destination of every resident Gaussian
     dest = {s: tree.label(st.xyz) if st.count else torch.zeros(0, dtype=torch.int64, device=device) for s, st in old.items()}
@@ -37,6 +51,9 @@ def migrate(old: dict[int, GaussianStore], tree, lo, hi, model2rank, rank: int, 
     for st in new.values():
         st.step = step
     old_rank_of = {s: r for s, r in enumerate(model2rank)}  # sub-model ids keep their rank (i % world)
+    if path == "peer" and world > 1:
+        _move_peer(old, new, dest, counts, model2rank, rank, world, device, group)
+        return new
     for s in range(M):
         for d in range(M):
             n = int(counts[s, d])
@@ -61,3 +78,54 @@ def migrate(old: dict[int, GaussianStore], tree, lo, hi, model2rank, rank: int, 
         if s in old:
             old[s].count = 0  # release the source as soon as it has been drained
     return new
+
+
+def _move_peer(old, new, dest, counts, model2rank, rank, world, device, group):
+    """One round per source sub-model: its owner packs the rows of every destination straight into the destination
+    rank's inbox (peer stores), everybody synchronises, destinations unpack from their own memory."""
+    from .peer import PeerRegion
+    M = len(model2rank)
+    row_bytes = 3 * RECORD * 4
+
+    def inbox_rows(s, r):  # rows that round s delivers to rank r from another rank
+        return sum(int(counts[s, d]) for d in range(M) if model2rank[d] == r and model2rank[s] != r)
+
+    need = max([inbox_rows(s, r) for s in range(M) for r in range(world)] + [1])
+    region = PeerRegion(need * row_bytes, device, group)
+    try:
+        for s in range(M):
+            rs = model2rank[s]
+            offset = {}
+            for r in range(world):
+                run = 0
+                for d in range(M):
+                    if model2rank[d] == r and rs != r:
+                        offset[d] = run
+                        run += int(counts[s, d])
+            if rs == rank and s in old:
+                st = old[s]
+                for d in range(M):
+                    n = int(counts[s, d])
+                    if n == 0:
+                        continue
+                    idx = (dest[s] == d).nonzero(as_tuple=True)[0].contiguous()
+                    rd = model2rank[d]
+                    if rd == rank:
+                        for c0 in range(0, n, CHUNK_ROWS):
+                            new[d].append_migration(st.migration_records(idx[c0:c0 + CHUNK_ROWS]))
+                    else:
+                        out = region.ptrs[rd] + offset[d] * row_bytes
+                        native.call("records_pack", device, st.params, st.exp_avg, st.exp_avg_sq, st.cap, idx, 0, n, out)
+            torch.cuda.synchronize(device)
+            dist.barrier(group)  # the round's records have landed
+            if rs != rank:
+                for d in range(M):
+                    n = int(counts[s, d])
+                    if n and model2rank[d] == rank:
+                        new[d].append_migration(region.view(offset[d] * row_bytes, (n, 3 * RECORD)))
+            if s in old:
+                old[s].count = 0
+            torch.cuda.synchronize(device)
+            dist.barrier(group)  # inbox free for the next round
+    finally:
+        region.close()

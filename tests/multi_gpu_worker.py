@@ -9,6 +9,42 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+def _check_migration(sess, rank, world, dev) -> bool:
+    """Repartition with the other split order: the peer-store path and the send/recv path build identical sub-models,
+    and no Gaussian is lost."""
+    from retinags_b200.models.gaussians import GaussianStore
+    from retinags_b200.parallel.migrate import migrate
+    from retinags_b200.parallel.partition import BvhTree
+
+    tree2 = BvhTree.build(sess.tree.grid, sess.bvh_depth, (1, 0))
+    lo, hi = tree2.leaf_boxes_world(open_border=True)
+
+    def clones():
+        out = {}
+        for m, st in sess.stores.items():
+            c = GaussianStore(max(st.count, 4), dev, st.max_sh_degree, st.box_lo, st.box_hi, m)
+            c.append_migration(st.migration_records())
+            c.step = st.step
+            out[m] = c
+        return out
+
+    before = torch.tensor([sum(st.count for st in sess.stores.values())], device=dev)
+    a = migrate(clones(), tree2, lo, hi, sess.model2rank, rank, world, dev, 3, None, path="peer")
+    b = migrate(clones(), tree2, lo, hi, sess.model2rank, rank, world, dev, 3, None, path="dist")
+    after = torch.tensor([sum(st.count for st in a.values())], device=dev)
+    moved = torch.tensor([sum(int((tree2.label(st.xyz) != m).sum()) for m, st in sess.stores.items())], device=dev)
+    for t in (before, after, moved):
+        dist.all_reduce(t)
+    same = all(a[m].count == b[m].count and torch.equal(a[m].migration_records(), b[m].migration_records()) for m in a)
+    inside = all(bool((tree2.label(st.xyz) == m).all()) for m, st in a.items() if st.count)
+    good = torch.tensor([int(same and inside)], device=dev)
+    dist.all_reduce(good, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(f"migration: {int(moved)} of {int(before)} Gaussians change sub-model; paths identical on every rank: "
+              f"{bool(good.item())}", flush=True)
+    return bool(good.item()) and int(before) == int(after) and int(moved) > 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--transport", default="peer")
@@ -50,6 +86,7 @@ def main():
         ref_losses = [single.step_e2e(it % 3)[0] for it in range(4)]
         print("losses", losses, ref_losses, flush=True)
         ok &= all(abs(x - y) < 5e-4 * max(1.0, abs(y)) for x, y in zip(losses, ref_losses))
+    ok &= _check_migration(sess, rank, world, dev)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.broadcast(flag, 0)
     dist.barrier()
