@@ -15,6 +15,9 @@
 #include "rgs_cuda_common.cuh"
 
 #include <stdlib.h>
+#include <string.h>
+
+#define RGS_BIN_WAIT_LIMIT (1u << 22)
 
 #define BS_THREADS 256
 #define BS_WARPS (BS_THREADS / 32)
@@ -149,45 +152,64 @@ __global__ void __launch_bounds__(256) rgs_cull_kernel(const __grid_constant__ R
 
 struct RgsSegs4 { RgsSegment s[4]; int n; };
 
-// Phase 2: full projection of the candidates (dense: every thread has work).
-__global__ void __launch_bounds__(256) rgs_project_cand_kernel(
+// Phase 2: full projection of the candidates (dense: every thread has work).  The 192-byte SH row of every
+// candidate is fetched by the bulk-copy engine into shared memory (one cp.async.bulk per thread, completing on an
+// mbarrier), so that the ~25 KB a block needs are in flight at once without occupying registers; the small columns
+// (position, scale, rotation, opacity) are ordinary loads issued before the wait.
+#define PC_THREADS 128
+#define PC_ROW 52  // floats per staged row: 48 + 4 of padding (conflict-free 128-bit reads, 16-byte aligned rows)
+
+__global__ void __launch_bounds__(PC_THREADS, 6) rgs_project_cand_kernel(
     const __grid_constant__ RgsCamera cam, const __grid_constant__ RgsSegs4 segs, const uint32_t* __restrict__ cand,
     uint32_t cap_cand, RgsSplat* __restrict__ splats, int32_t* __restrict__ vis_ids, uint32_t* __restrict__ aux,
     const uint32_t cap_vis, uint32_t* __restrict__ slot_depth, uint2* __restrict__ slot_rect, uint32_t* __restrict__ slot_cnt,
     uint32_t* __restrict__ counters, RgsSplatGrad* __restrict__ splat_grads) {
-    __shared__ uint32_t warp_vis[8];
+    __shared__ __align__(128) float s_sh[PC_THREADS * PC_ROW];
+    __shared__ unsigned long long bar;
+    __shared__ uint32_t warp_vis[PC_THREADS / 32];
     __shared__ uint32_t base_vis;
     __shared__ int drop;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     uint32_t n = counters[RGS_CNT_OVERFLOW] ? 0u : counters[RGS_CNT_CAND];
     if (n > cap_cand) n = cap_cand;
-    const uint32_t nblk = (n + 255) / 256;
-    for (uint32_t blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
-        const uint32_t c = blk * 256 + threadIdx.x;
+    const uint32_t nblk = (n + PC_THREADS - 1) / PC_THREADS;
+    if (threadIdx.x == 0) { rgs_mbar_init(&bar, 1); rgs_fence_mbar_init(); }
+    __syncthreads();
+    uint32_t round = 0;
+    bool failed = false;
+    for (uint32_t blk = blockIdx.x; blk < nblk; blk += gridDim.x, ++round) {
+        const uint32_t c = blk * PC_THREADS + threadIdx.x;
+        const uint32_t valid = n - blk * PC_THREADS < PC_THREADS ? n - blk * PC_THREADS : PC_THREADS;
         bool ok = false;
         RgsSplat sp;
         RgsRect rc;
         int radius = 0;
         unsigned clamped = 0;
         uint32_t gid = 0;
+        float p[3] = {0.f, 0.f, 0.f}, s[3] = {0.f, 0.f, 0.f}, q[4] = {1.f, 0.f, 0.f, 0.f}, o = 0.f;
+        rgs_fence_proxy_async();  // the rows read in the previous round may be overwritten now
+        if (threadIdx.x == 0) rgs_mbar_expect_tx(&bar, valid * 192u);
         if (c < n) {
             gid = cand[c];
             int64_t i = gid;
             int sidx = 0;
             while (sidx < segs.n - 1 && i >= segs.s[sidx].count) { i -= segs.s[sidx].count; ++sidx; }
             const RgsSegment& seg = segs.s[sidx];
-            float p[3] = {seg.xyz[3 * i], seg.xyz[3 * i + 1], seg.xyz[3 * i + 2]};
-            float s[3] = {seg.scale[3 * i], seg.scale[3 * i + 1], seg.scale[3 * i + 2]};
-            float4 q4 = reinterpret_cast<const float4*>(seg.rot)[i];
-            float q[4] = {q4.x, q4.y, q4.z, q4.w};
-            ok = rgs_project(cam, p, s, q, seg.opacity[i], seg.sh + 48 * i, sp, rc, radius, clamped);
+            rgs_bulk_g2s(&s_sh[threadIdx.x * PC_ROW], seg.sh + 48 * i, 192u, &bar);
+            p[0] = seg.xyz[3 * i]; p[1] = seg.xyz[3 * i + 1]; p[2] = seg.xyz[3 * i + 2];
+            s[0] = seg.scale[3 * i]; s[1] = seg.scale[3 * i + 1]; s[2] = seg.scale[3 * i + 2];
+            const float4 q4 = reinterpret_cast<const float4*>(seg.rot)[i];
+            q[0] = q4.x; q[1] = q4.y; q[2] = q4.z; q[3] = q4.w;
+            o = seg.opacity[i];
         }
+        if (!rgs_mbar_wait(&bar, round & 1u, RGS_BIN_WAIT_LIMIT)) failed = true;
+        if (c < n && !failed) ok = rgs_project(cam, p, s, q, o, &s_sh[threadIdx.x * PC_ROW], sp, rc, radius, clamped);
         const uint32_t vmask = __ballot_sync(0xffffffffu, ok);
         if (lane == 0) warp_vis[wid] = __popc(vmask);
         __syncthreads();
         if (threadIdx.x == 0) {
             uint32_t tv = 0;
-            for (int w = 0; w < 8; ++w) { uint32_t v = warp_vis[w]; warp_vis[w] = tv; tv += v; }
+            for (int w = 0; w < PC_THREADS / 32; ++w) { uint32_t v = warp_vis[w]; warp_vis[w] = tv; tv += v; }
             uint32_t bv = 0;
             int d = 0;
             if (tv) {
@@ -215,6 +237,9 @@ __global__ void __launch_bounds__(256) rgs_project_cand_kernel(
         }
         __syncthreads();
     }
+    // a wait that ran out: report through the status word; the copies of the round are not waited for again (the
+    // limit is far beyond any legitimate latency) and the block stops using the staged rows
+    if (failed && threadIdx.x == 0) atomicExch(&counters[RGS_CNT_STATUS], 1u);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -580,6 +605,157 @@ __global__ void rgs_bs_tile_ranges_kernel(const uint32_t* __restrict__ keys, con
 }
 
 // ---------------------------------------------------------------------------------------------
+// Grouping by tile without a second sort ("segmented counting").
+//
+// The depth-ordered splat list is cut into one contiguous piece per warp, balanced by instance count.  A warp
+// keeps one counter per tile in shared memory and walks its piece in depth order; all 32 lanes work on the tiles
+// of ONE splat at a time, so that no two lanes touch the same counter and the order of a tile's instances is the
+// depth order by construction.  Pass 1 counts (row w of the table = tile histogram of piece w), a column scan
+// turns the table into the number of earlier instances per (piece, tile), a scan of the tile totals yields the
+// tile ranges, and pass 2 repeats the walk with the counters preloaded with the final write positions and stores
+// each instance's slot straight to its place.  Against "emit (tile, slot) pairs, then a stable radix sort by tile"
+// this writes 4 bytes per instance once instead of moving 8 bytes per instance through 2 sort passes.
+// ---------------------------------------------------------------------------------------------
+#define SC_MAX_TILES 14336  // 56 KB of counters per warp
+
+__device__ __forceinline__ uint32_t sc_bound(const uint32_t* __restrict__ seg_excl, uint32_t nseg, uint32_t total,
+                                             uint32_t w, uint32_t W) {
+    if (w >= W) return nseg;
+    const uint32_t x = (uint32_t)(((unsigned long long)w * total) / W);
+    uint32_t lo = 0, hi = nseg;  // first segment whose exclusive prefix is >= x
+    while (lo < hi) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (seg_excl[mid] < x) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
+template <bool EMIT>
+__global__ void __launch_bounds__(32) rgs_sc_walk_kernel(const __grid_constant__ RgsCamera cam,
+                                                         const uint32_t* __restrict__ order,
+                                                         const uint2* __restrict__ slot_rect,
+                                                         const uint32_t* __restrict__ slot_cnt,
+                                                         const RgsSplat* __restrict__ splats,
+                                                         const uint32_t* __restrict__ counters, uint32_t cap_vis,
+                                                         const uint32_t* __restrict__ seg_excl, uint32_t* __restrict__ table,
+                                                         const uint32_t* __restrict__ tile_start,
+                                                         uint32_t* __restrict__ vals, uint32_t cap_inst, uint32_t num_tiles) {
+    extern __shared__ uint32_t sc_cnt[];
+    const int lane = threadIdx.x;
+    const uint32_t w = blockIdx.x, W = gridDim.x;
+    const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);
+    const uint32_t nseg = (n + EM_SEG - 1) / EM_SEG;
+    uint32_t* row = table + (size_t)w * num_tiles;
+    for (uint32_t t = lane; t < num_tiles; t += 32) sc_cnt[t] = EMIT ? tile_start[t] + row[t] : 0u;
+    __syncwarp();
+    const uint32_t total = counters[RGS_CNT_INST];
+    const uint32_t s0 = sc_bound(seg_excl, nseg, total, w, W), s1 = sc_bound(seg_excl, nseg, total, w + 1, W);
+    const uint32_t i0 = s0 * EM_SEG;
+    uint32_t i1 = s1 * EM_SEG;
+    if (i1 > n) i1 = n;
+    const int tiles_x = cam.tiles_x;
+    const bool exact = cam.tight_rect >= 2;
+    uint32_t nslot = 0;
+    uint2 nrect = make_uint2(0, 0);
+    if (i0 + lane < i1) {
+        nslot = order[i0 + lane];
+        nrect = slot_cnt[nslot] ? slot_rect[nslot] : make_uint2(0, 0);
+    }
+    for (uint32_t base = i0; base < i1; base += 32) {
+        const uint32_t cslot = nslot;
+        const uint2 crect = nrect;
+        nrect = make_uint2(0, 0);
+        if (base + 32 + lane < i1) {  // fetch the next 32 splats while this batch is walked
+            nslot = order[base + 32 + lane];
+            nrect = slot_cnt[nslot] ? slot_rect[nslot] : make_uint2(0, 0);
+        }
+        const int m = (int)(i1 - base < 32u ? i1 - base : 32u);
+        for (int j = 0; j < m; ++j) {
+            const uint32_t rx = __shfl_sync(0xffffffffu, crect.x, j), ry = __shfl_sync(0xffffffffu, crect.y, j);
+            const int x0 = rx & 0xffff, y0 = rx >> 16;
+            const uint32_t wd = (ry & 0xffffu) - (uint32_t)x0, c = wd * ((ry >> 16) - (uint32_t)y0);
+            if (c == 0) continue;
+            const uint32_t sl = __shfl_sync(0xffffffffu, cslot, j);
+            const float inv_w = 1.0f / (float)wd;
+            float4 q0 = make_float4(0.f, 0.f, 0.f, 0.f);
+            float2 q1 = make_float2(0.f, 0.f);
+            float bound = 0.f;
+            if (exact) {  // same test, same inputs as the count made by the projection kernel
+                q0 = reinterpret_cast<const float4*>(splats + sl)[0];
+                q1 = reinterpret_cast<const float2*>(splats + sl)[2];
+                bound = rgs_alpha_bound(q1.y);
+            }
+            for (uint32_t t = lane; t < c; t += 32) {
+                const uint32_t ty = (uint32_t)(((float)t + 0.5f) * inv_w), tx = t - ty * wd;
+                if (exact && !rgs_tile_hit(q0.x, q0.y, q0.z, q0.w, q1.x, bound, x0 + (int)tx, y0 + (int)ty, cam.W, cam.H))
+                    continue;
+                const uint32_t tile = (uint32_t)((y0 + (int)ty) * tiles_x + x0 + (int)tx);
+                const uint32_t pos = sc_cnt[tile];
+                sc_cnt[tile] = pos + 1u;
+                if (EMIT && pos < cap_inst) vals[pos] = sl;
+            }
+            __syncwarp();
+        }
+    }
+    if (!EMIT) {
+        __syncwarp();
+        for (uint32_t t = lane; t < num_tiles; t += 32) row[t] = sc_cnt[t];
+    }
+}
+
+// table[w][t] -> number of instances of tile t in pieces before w; tile_total[t] = instances of tile t
+__global__ void __launch_bounds__(128) rgs_sc_colscan_kernel(uint32_t* __restrict__ table, uint32_t W, uint32_t T,
+                                                             uint32_t* __restrict__ tile_total) {
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    uint32_t run = 0;
+    for (uint32_t w0 = 0; w0 < W; w0 += 8) {
+        uint32_t v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = w0 + k < W ? table[(size_t)(w0 + k) * T + t] : 0u;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (w0 + k < W) table[(size_t)(w0 + k) * T + t] = run;
+            run += v[k];
+        }
+    }
+    tile_total[t] = run;
+}
+
+// one CTA: tile_total -> tile_start (exclusive scan, in place) and ranges[t] = [start, start + total), clipped to cap_inst
+__global__ void __launch_bounds__(1024) rgs_sc_tilescan_kernel(uint32_t* __restrict__ tile_total, uint32_t T, uint32_t cap_inst,
+                                                               int2* __restrict__ ranges) {
+    __shared__ uint32_t warp_tot[32];
+    __shared__ uint32_t carry;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (uint32_t start = 0; start < T; start += 1024) {
+        const uint32_t i = start + threadIdx.x;
+        const uint32_t v = i < T ? tile_total[i] : 0u;
+        uint32_t incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += y;
+        }
+        if (lane == 31) warp_tot[wid] = incl;
+        __syncthreads();
+        uint32_t wbase = 0;
+        for (int k = 0; k < wid; ++k) wbase += warp_tot[k];
+        const uint32_t excl = carry + wbase + incl - v;
+        if (i < T) {
+            tile_total[i] = excl;
+            const uint32_t a = excl < cap_inst ? excl : cap_inst, b = excl + v < cap_inst ? excl + v : cap_inst;
+            ranges[i] = make_int2((int)a, (int)b);
+        }
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = excl + v;
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host
 // ---------------------------------------------------------------------------------------------
 // table sizes assume the smallest chunk any variant uses
@@ -670,17 +846,31 @@ int rgs_cuda_project_slots2(const RgsCamera* cam, const RgsSegment* segs, int64_
         }
         base += segs[k].count;
     }
-    const int64_t want = (cap_cand + 255) / 256;
+    const int64_t want = (cap_cand + PC_THREADS - 1) / PC_THREADS;
     const unsigned grid = (unsigned)(want < 1 ? 1 : (want > 148 * 8 ? 148 * 8 : want));
-    rgs_project_cand_kernel<<<grid, 256, 0, st>>>(*cam, s4, cand, (uint32_t)cap_cand, splats, vis_ids, aux, (uint32_t)cap_vis,
+    rgs_project_cand_kernel<<<grid, PC_THREADS, 0, st>>>(*cam, s4, cand, (uint32_t)cap_cand, splats, vis_ids, aux, (uint32_t)cap_vis,
                                                   slot_depth, reinterpret_cast<uint2*>(slot_rect), slot_cnt, cnt, splat_grads);
     return (int)cudaGetLastError();
+}
+
+// The counter table of the segmented counting holds (warps x tiles) words; warps per SM x tiles x 4 bytes never
+// exceeds the shared memory of an SM, which bounds the table for any image size.
+#define SC_TABLE_WORDS ((int64_t)148 * 227 * 256)
+
+// 1: group by tile with the segmented counting (default when the tile counters fit), 0: with the radix sort
+static int sc_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("RGS_TILE_GROUPING");
+        v = (e && !strcmp(e, "radix")) ? 0 : 1;
+    }
+    return v;
 }
 
 // words of uint32 scratch for capacities (cap_vis, cap_inst)
 int64_t rgs_cuda_bin_scratch_words(int64_t cap_vis, int64_t cap_inst) {
     const int64_t cap = cap_vis > cap_inst ? cap_vis : cap_inst;
-    return 256 * (int64_t)chunks_of(cap) + 256 + (cap_vis + EM_SEG - 1) / EM_SEG + 16;
+    return 256 * (int64_t)chunks_of(cap) + 256 + (cap_vis + EM_SEG - 1) / EM_SEG + 16 + SC_TABLE_WORDS + SC_MAX_TILES;
 }
 
 // Depth-order the visible slots, emit instances in that order, group them by tile.
@@ -708,6 +898,33 @@ int rgs_cuda_bin_instances(const RgsCamera* cam, const RgsSplat* splats, const u
     const unsigned egrid = nseg_cap < 148u * 8u ? (nseg_cap ? nseg_cap : 1u) : 148u * 8u;
     rgs_emit_count_kernel<<<egrid, 256, 0, st>>>(order, slot_cnt, cnt, (uint32_t)cap_vis, seg_sums);
     rgs_emit_scan_kernel<<<1, 1024, 0, st>>>(seg_sums, cnt, (uint32_t)cap_vis, (uint32_t)cap_inst);
+    if (sc_enabled() && num_tiles <= SC_MAX_TILES) {
+        // 3'. no pair emission, no second sort: count per (piece, tile), scan, store every slot at its final place
+        uint32_t* table = seg_sums + (cap_vis + EM_SEG - 1) / EM_SEG + 16;
+        uint32_t* tile_start = table + SC_TABLE_WORDS;
+        const size_t smem = (size_t)num_tiles * 4;
+        int per_sm = (int)((227 * 1024) / (smem + 1024));
+        per_sm = per_sm > 8 ? 8 : (per_sm < 1 ? 1 : per_sm);
+        const unsigned W = 148u * (unsigned)per_sm;
+        if ((int64_t)W * num_tiles > SC_TABLE_WORDS) return 13;
+        static bool attr_set = false;
+        if (!attr_set) {
+            RGS_CUDA_CHECK(cudaFuncSetAttribute(rgs_sc_walk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                SC_MAX_TILES * 4));
+            RGS_CUDA_CHECK(cudaFuncSetAttribute(rgs_sc_walk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                SC_MAX_TILES * 4));
+            attr_set = true;
+        }
+        const uint2* rects = reinterpret_cast<const uint2*>(slot_rect);
+        rgs_sc_walk_kernel<false><<<W, 32, smem, st>>>(*cam, order, rects, slot_cnt, splats, cnt, (uint32_t)cap_vis, seg_sums,
+                                                       table, tile_start, inst_vals, (uint32_t)cap_inst, (uint32_t)num_tiles);
+        rgs_sc_colscan_kernel<<<(unsigned)((num_tiles + 127) / 128), 128, 0, st>>>(table, W, (uint32_t)num_tiles, tile_start);
+        rgs_sc_tilescan_kernel<<<1, 1024, 0, st>>>(tile_start, (uint32_t)num_tiles, (uint32_t)cap_inst,
+                                                   reinterpret_cast<int2*>(ranges));
+        rgs_sc_walk_kernel<true><<<W, 32, smem, st>>>(*cam, order, rects, slot_cnt, splats, cnt, (uint32_t)cap_vis, seg_sums,
+                                                      table, tile_start, inst_vals, (uint32_t)cap_inst, (uint32_t)num_tiles);
+        return (int)cudaGetLastError();
+    }
     rgs_emit_kernel<<<egrid, 256, 0, st>>>(*cam, order, reinterpret_cast<const uint2*>(slot_rect), slot_cnt, splats, cnt,
                                            (uint32_t)cap_vis, seg_sums, inst_keys, inst_vals, (uint32_t)cap_inst);
     (void)tiles_x;

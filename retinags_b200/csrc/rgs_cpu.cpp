@@ -280,7 +280,7 @@ int rgs_cpu_scatter_radii(const int32_t* counters, const int32_t* vis_ids, const
 // `skip` (optional int32) != 0 turns the whole update into a no-op (overflow-guarded commit).
 int rgs_cpu_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t cap, const double* lrs,
                  double beta1, double beta2, double eps, int64_t step, int64_t zero_grad, const int32_t* skip,
-                 const uint8_t* touched, void*) {
+                 const uint8_t* touched, uint8_t* active, void*) {
     if (skip && skip[RGS_CNT_OVERFLOW]) return 0;
     const int widths[5] = {3, 48, 3, 4, 1};
     float bc1 = (float)(1.0 / (1.0 - std::pow(beta1, (double)step)));
@@ -301,12 +301,16 @@ int rgs_cpu_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t 
             }
             int64_t k = off + e;
             const bool t = touched ? touched[e / w] != 0 : true;
+            if (!t && touched && active && !active[e / w]) continue;  // never touched since the moments were zeroed
             if (!t && m[k] == 0.f && v[k] == 0.f) continue;  // zero gradient, zero moments: the update is exactly zero
             rgs_adam_elem(p[k], t ? g[k] : 0.f, m[k], v[k], lr, (float)beta1, (float)beta2, (float)eps, bc1, bc2s);
             if (zero_grad && t) g[k] = 0.f;
         }
         off += cap * w;
     }
+    if (touched && active)
+        for (int64_t r = 0; r < count; ++r)
+            if (touched[r]) active[r] = 1;
     return 0;
 }
 
@@ -409,6 +413,27 @@ int rgs_cpu_ssim_bwd(const float* img, const float* gt, const float* dmaps, int6
                 g_image[pid] = (float)w_l1 * sgn - (float)w_ssim * dssim;
             }
     return 0;
+}
+
+// CPU twins of the fused training path of rgs_loss.cu: the same four steps, run back to back.
+int rgs_cpu_composite_ssim_fwd(const float* const* partials, int64_t K, const float* bg, const float* gt, int64_t H,
+                               int64_t W, int64_t crow0, int64_t crow1, int64_t srow0, int64_t srow1, float* image,
+                               float* trans, float* dmaps, double* sums, void*) {
+    if (crow1 <= crow0) return 0;
+    const int64_t e0 = std::max<int64_t>(0, crow0 - 5), e1 = std::min<int64_t>(H, crow1 + 5);
+    int rc = rgs_cpu_composite_fwd(partials, K, bg, H, W, e0, e1, image, trans, nullptr);
+    if (rc) return rc;
+    return rgs_cpu_ssim_fwd(image, gt, H, W, crow0, crow1, srow0, srow1, dmaps, sums, nullptr);
+}
+
+int rgs_cpu_ssim_composite_bwd(const float* const* partials, float* const* grads, int64_t K, const float* bg,
+                               const float* img, const float* gt, const float* dmaps, int64_t H, int64_t W, int64_t row0,
+                               int64_t row1, int64_t vrow0, int64_t vrow1, double w_l1, double w_ssim, float* g_image,
+                               void*) {
+    if (row1 <= row0) return 0;
+    int rc = rgs_cpu_ssim_bwd(img, gt, dmaps, H, W, row0, row1, vrow0, vrow1, w_l1, w_ssim, g_image, nullptr);
+    if (rc) return rc;
+    return rgs_cpu_composite_bwd(partials, grads, K, bg, H, W, row0, row1, g_image, nullptr);
 }
 
 // CPU twins of rgs_aux.cu

@@ -190,6 +190,193 @@ __global__ void __launch_bounds__(256) rgs_ssim_bwd_kernel(const float* __restri
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Fused training path: two kernels instead of four.
+//   rgs_composite_ssim_fwd_kernel   folds the K partial slots of a 42x42 pixel patch (front to back) while it fills
+//                                   the shared-memory tile of the SSIM filter: the composited image is never read
+//                                   back from global memory; it is written once (tile interior) for the backward.
+//   rgs_ssim_composite_bwd_kernel   filters the derivative maps, forms d(loss)/d(image) in registers and writes
+//                                   d(loss)/d(partial_k) for every partial straight away (into peer-mapped gradient
+//                                   images when the partial came from another rank).
+// The arithmetic per pixel is the one of the four separate kernels above, in the same order.
+// ---------------------------------------------------------------------------------------------
+struct FusedFwdSmem {
+    float img[3][SH_][SH_ + 1];
+    float gt[SH_][SH_ + 1];
+    float hb[5][SH_][ST];
+    float red[3][8];
+};
+
+__global__ void __launch_bounds__(256) rgs_composite_ssim_fwd_kernel(
+    const __grid_constant__ RgsPartialPtrs parts, int K, float bg0, float bg1, float bg2, const float* __restrict__ gt,
+    int H, int W, int crow0, int crow1, int srow0, int srow1, float* __restrict__ image, float* __restrict__ trans,
+    float* __restrict__ dmaps, double* __restrict__ sums) {
+    extern __shared__ __align__(16) unsigned char fused_raw[];
+    FusedFwdSmem& sm = *reinterpret_cast<FusedFwdSmem*>(fused_raw);
+    float gw[11];
+    ssim_window(gw);
+    const int x0 = blockIdx.x * ST, y0 = crow0 + blockIdx.y * ST;
+    const size_t HW = (size_t)H * W;
+    for (int idx = threadIdx.x; idx < SH_ * SH_; idx += 256) {
+        const int r = idx / SH_, q = idx % SH_;
+        const int y = y0 + r - 5, x = x0 + q - 5;
+        float c0 = 0.f, c1 = 0.f, c2 = 0.f;
+        // rows beyond crow1 + 5 feed no output of this launch, and the partial slots need not hold them
+        if (y >= 0 && y < H && x >= 0 && x < W && y >= crow0 - 5 && y < crow1 + 5) {
+            const size_t pid = (size_t)y * W + x;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, t = 1.f;
+            for (int k = 0; k < K; ++k) {
+                const float4 v = reinterpret_cast<const float4*>(parts.p[k])[pid];
+                a0 += t * v.x; a1 += t * v.y; a2 += t * v.z;
+                t *= v.w;
+            }
+            c0 = a0 + bg0 * t; c1 = a1 + bg1 * t; c2 = a2 + bg2 * t;
+            if (r >= 5 && r < 5 + ST && q >= 5 && q < 5 + ST && y < crow1) {
+                image[pid] = c0; image[HW + pid] = c1; image[2 * HW + pid] = c2;
+                trans[pid] = t;
+            }
+        }
+        sm.img[0][r][q] = c0; sm.img[1][r][q] = c1; sm.img[2][r][q] = c2;
+    }
+    float l1 = 0.f, ss = 0.f, l2 = 0.f;
+    const int q = threadIdx.x & 31;
+    for (int c = 0; c < 3; ++c) {
+        const float* b = gt + (size_t)c * HW;
+        for (int idx = threadIdx.x; idx < SH_ * SH_; idx += 256) {
+            const int r = idx / SH_, qq = idx % SH_;
+            const int y = y0 + r - 5, x = x0 + qq - 5;
+            sm.gt[r][qq] = (y >= 0 && y < H && x >= 0 && x < W) ? b[(size_t)y * W + x] : 0.f;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < SH_ * ST; idx += 256) {
+            const int r = idx / ST, qq = idx % ST;
+            float m1 = 0, m2 = 0, e11 = 0, e22 = 0, e12 = 0;
+#pragma unroll
+            for (int k = 0; k < 11; ++k) {
+                const float p = sm.img[c][r][qq + k], v = sm.gt[r][qq + k], w = gw[k];
+                m1 += w * p; m2 += w * v; e11 += w * p * p; e22 += w * v * v; e12 += w * p * v;
+            }
+            sm.hb[0][r][qq] = m1; sm.hb[1][r][qq] = m2; sm.hb[2][r][qq] = e11; sm.hb[3][r][qq] = e22; sm.hb[4][r][qq] = e12;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = (threadIdx.x >> 5) + 8 * i;
+            const int y = y0 + r, x = x0 + q;
+            if (y < crow1 && y < H && x < W) {
+                float m[5] = {0, 0, 0, 0, 0};
+#pragma unroll
+                for (int k = 0; k < 11; ++k) {
+                    const float w = gw[k];
+#pragma unroll
+                    for (int j = 0; j < 5; ++j) m[j] += w * sm.hb[j][r + k][q];
+                }
+                float d[3];
+                const float sv = rgs_ssim_pixel(m[0], m[1], m[2], m[3], m[4], d);
+                const size_t pid = (size_t)c * HW + (size_t)y * W + x;
+                const size_t plane = (size_t)3 * HW;
+                dmaps[pid] = d[0]; dmaps[plane + pid] = d[1]; dmaps[2 * plane + pid] = d[2];
+                if (y >= srow0 && y < srow1) {
+                    const float diff = sm.img[c][r + 5][q + 5] - sm.gt[r + 5][q + 5];
+                    l1 += fabsf(diff); ss += sv; l2 += diff * diff;
+                }
+            }
+        }
+        __syncthreads();  // hb and the gt tile are reused by the next channel
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        l1 += __shfl_xor_sync(0xffffffffu, l1, d);
+        ss += __shfl_xor_sync(0xffffffffu, ss, d);
+        l2 += __shfl_xor_sync(0xffffffffu, l2, d);
+    }
+    if ((threadIdx.x & 31) == 0) { sm.red[0][threadIdx.x >> 5] = l1; sm.red[1][threadIdx.x >> 5] = ss; sm.red[2][threadIdx.x >> 5] = l2; }
+    __syncthreads();
+    if (threadIdx.x < 3) {
+        double t = 0;
+        for (int w = 0; w < 8; ++w) t += (double)sm.red[threadIdx.x][w];
+        atomicAdd(&sums[threadIdx.x], t);
+    }
+}
+
+__global__ void __launch_bounds__(256) rgs_ssim_composite_bwd_kernel(
+    const __grid_constant__ RgsPartialPtrs parts, const __grid_constant__ RgsGradPtrs grads, int K, float bg0, float bg1,
+    float bg2, const float* __restrict__ img, const float* __restrict__ gt, const float* __restrict__ dmaps, int H, int W,
+    int row0, int row1, int vrow0, int vrow1, float w_l1, float w_ssim, float* __restrict__ g_image) {
+    __shared__ float in[3][SH_][SH_ + 1];
+    __shared__ float hb[3][SH_][ST];
+    float gw[11];
+    ssim_window(gw);
+    const int x0 = blockIdx.x * ST, y0 = row0 + blockIdx.y * ST;
+    const size_t HW = (size_t)H * W, plane = 3 * HW;
+    const int q = threadIdx.x & 31;
+    float g[4][3];
+    for (int c = 0; c < 3; ++c) {
+        const float* dm = dmaps + (size_t)c * HW;
+        for (int idx = threadIdx.x; idx < SH_ * SH_; idx += 256) {
+            const int r = idx / SH_, qq = idx % SH_;
+            const int y = y0 + r - 5, x = x0 + qq - 5;
+            const bool ok = y >= vrow0 && y < vrow1 && x >= 0 && x < W;
+            const size_t o = (size_t)y * W + x;
+            in[0][r][qq] = ok ? dm[o] : 0.f;
+            in[1][r][qq] = ok ? dm[plane + o] : 0.f;
+            in[2][r][qq] = ok ? dm[2 * plane + o] : 0.f;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < SH_ * ST; idx += 256) {
+            const int r = idx / ST, qq = idx % ST;
+            float s0 = 0, s1 = 0, s2 = 0;
+#pragma unroll
+            for (int k = 0; k < 11; ++k) {
+                const float w = gw[k];
+                s0 += w * in[0][r][qq + k]; s1 += w * in[1][r][qq + k]; s2 += w * in[2][r][qq + k];
+            }
+            hb[0][r][qq] = s0; hb[1][r][qq] = s1; hb[2][r][qq] = s2;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = (threadIdx.x >> 5) + 8 * i;
+            const int y = y0 + r, x = x0 + q;
+            g[i][c] = 0.f;
+            if (y < row1 && y < H && x < W) {
+                float s0 = 0, s1 = 0, s2 = 0;
+#pragma unroll
+                for (int k = 0; k < 11; ++k) {
+                    const float w = gw[k];
+                    s0 += w * hb[0][r + k][q]; s1 += w * hb[1][r + k][q]; s2 += w * hb[2][r + k][q];
+                }
+                const size_t pid = (size_t)c * HW + (size_t)y * W + x;
+                const float p = img[pid], v = gt[pid];
+                const float dssim = s0 + 2.0f * p * s1 + v * s2;
+                const float diff = p - v;
+                const float sgn = diff > 0.f ? 1.f : (diff < 0.f ? -1.f : 0.f);
+                g[i][c] = w_l1 * sgn - w_ssim * dssim;
+                if (g_image) g_image[pid] = g[i][c];
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = (threadIdx.x >> 5) + 8 * i;
+        const int y = y0 + r, x = x0 + q;
+        if (!(y < row1 && y < H && x < W)) continue;
+        const size_t pid = (size_t)y * W + x;
+        const float g0 = g[i][0], g1 = g[i][1], g2 = g[i][2];
+        float tpre[RGS_MAX_PARTIALS];
+        float t = 1.f;
+        for (int k = 0; k < K; ++k) { tpre[k] = t; t *= parts.p[k][4 * pid + 3]; }
+        float s = bg0 * g0 + bg1 * g1 + bg2 * g2;
+        for (int k = K - 1; k >= 0; --k) {
+            const float4 v = reinterpret_cast<const float4*>(parts.p[k])[pid];
+            const float tp = tpre[k];
+            reinterpret_cast<float4*>(grads.p[k])[pid] = make_float4(tp * g0, tp * g1, tp * g2, tp * s);
+            s = v.x * g0 + v.y * g1 + v.z * g2 + v.w * s;
+        }
+    }
+}
+
 extern "C" {
 
 int rgs_cuda_composite_fwd(const float* const* partials, int64_t K, const float* bg, int64_t H, int64_t W,
@@ -241,6 +428,47 @@ int rgs_cuda_ssim_bwd(const float* img, const float* gt, const float* dmaps, int
     rgs_ssim_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(img, gt, dmaps, (int)H, (int)W, (int)row0, (int)row1,
                                                                 (int)vrow0, (int)vrow1, (float)w_l1, (float)w_ssim,
                                                                 g_image);
+    return (int)cudaGetLastError();
+}
+
+// Fused forward of the training path: composite rows [crow0-5, crow1+5) of the K partials on the fly, write the
+// composited image / transmittance on rows [crow0,crow1), the SSIM derivative maps there, and accumulate the loss
+// sums over rows [srow0,srow1).
+int rgs_cuda_composite_ssim_fwd(const float* const* partials, int64_t K, const float* bg, const float* gt, int64_t H,
+                                int64_t W, int64_t crow0, int64_t crow1, int64_t srow0, int64_t srow1, float* image,
+                                float* trans, float* dmaps, double* sums, void* stream) {
+    if (K < 0 || K > RGS_MAX_PARTIALS) return 12;
+    if (crow1 <= crow0) return 0;
+    RgsPartialPtrs pp;
+    for (int k = 0; k < K; ++k) pp.p[k] = partials[k];
+    static bool attr_set = false;
+    if (!attr_set) {
+        RGS_CUDA_CHECK(cudaFuncSetAttribute(rgs_composite_ssim_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)sizeof(FusedFwdSmem)));
+        attr_set = true;
+    }
+    dim3 grid((unsigned)((W + ST - 1) / ST), (unsigned)((crow1 - crow0 + ST - 1) / ST), 1);
+    rgs_composite_ssim_fwd_kernel<<<grid, 256, sizeof(FusedFwdSmem), (cudaStream_t)stream>>>(
+        pp, (int)K, bg[0], bg[1], bg[2], gt, (int)H, (int)W, (int)crow0, (int)crow1, (int)srow0, (int)srow1, image, trans,
+        dmaps, sums);
+    return (int)cudaGetLastError();
+}
+
+// Fused backward: d(loss)/d(image) on rows [row0,row1) from the derivative maps (valid on [vrow0,vrow1)) and, in the
+// same kernel, d(loss)/d(partial_k) into grads[k]; g_image (optional) receives d(loss)/d(image).
+int rgs_cuda_ssim_composite_bwd(const float* const* partials, float* const* grads, int64_t K, const float* bg,
+                                const float* img, const float* gt, const float* dmaps, int64_t H, int64_t W, int64_t row0,
+                                int64_t row1, int64_t vrow0, int64_t vrow1, double w_l1, double w_ssim, float* g_image,
+                                void* stream) {
+    if (K < 0 || K > RGS_MAX_PARTIALS) return 12;
+    if (row1 <= row0) return 0;
+    RgsPartialPtrs pp;
+    RgsGradPtrs gp;
+    for (int k = 0; k < K; ++k) { pp.p[k] = partials[k]; gp.p[k] = grads[k]; }
+    dim3 grid((unsigned)((W + ST - 1) / ST), (unsigned)((row1 - row0 + ST - 1) / ST), 1);
+    rgs_ssim_composite_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(pp, gp, (int)K, bg[0], bg[1], bg[2], img, gt, dmaps,
+                                                                         (int)H, (int)W, (int)row0, (int)row1, (int)vrow0,
+                                                                         (int)vrow1, (float)w_l1, (float)w_ssim, g_image);
     return (int)cudaGetLastError();
 }
 

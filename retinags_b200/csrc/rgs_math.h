@@ -226,6 +226,24 @@ RGS_HD void rgs_activate(int raw, const float* s_in, const float* q_in, float o_
     }
 }
 
+// The first 3*nc of the 48 SH coefficients of one Gaussian (`sh` is 16-byte aligned: rows of 192 bytes in a buffer
+// whose column group starts on a 16-byte boundary). Device code fetches them as 128-bit words, 12 requests instead of
+// 48, from global or shared memory alike.
+RGS_HD void rgs_sh_load(const float* sh, int nc, float* out) {
+#ifdef __CUDA_ARCH__
+    const float4* v = reinterpret_cast<const float4*>(sh);
+    RGS_UNROLL
+    for (int j = 0; j < 12; ++j) {
+        if (4 * j < 3 * nc) {
+            const float4 q = v[j];
+            out[4 * j] = q.x; out[4 * j + 1] = q.y; out[4 * j + 2] = q.z; out[4 * j + 3] = q.w;
+        }
+    }
+#else
+    for (int e = 0; e < 3 * nc; ++e) out[e] = sh[e];
+#endif
+}
+
 // Forward projection of one Gaussian. Returns false when it is culled (near plane, singular
 // covariance, empty tile rectangle). `sh` points at 16 RGB triples (coefficient-major).
 // `clamped` receives 3 bits (colour channel was clamped at 0), `radius` the 3-sigma pixel radius.
@@ -277,9 +295,11 @@ RGS_HD bool rgs_project(const RgsCamera& cam, const float* p, const float* s_in,
     rgs_sh_basis(cam.sh_degree, dx * inv, dy * inv, dz * inv, B);
     int nc = (cam.sh_degree + 1) * (cam.sh_degree + 1);
     float c0 = 0.5f, c1 = 0.5f, c2 = 0.5f;
+    float shv[48];
+    rgs_sh_load(sh, nc, shv);
     RGS_UNROLL
     for (int k = 0; k < 16; ++k)
-        if (k < nc) { c0 += B[k] * sh[3 * k]; c1 += B[k] * sh[3 * k + 1]; c2 += B[k] * sh[3 * k + 2]; }
+        if (k < nc) { c0 += B[k] * shv[3 * k]; c1 += B[k] * shv[3 * k + 1]; c2 += B[k] * shv[3 * k + 2]; }
     clamped = (c0 < 0.0f ? 1u : 0u) | (c1 < 0.0f ? 2u : 0u) | (c2 < 0.0f ? 4u : 0u);
     out.px = px; out.py = py;
     out.ca = e.c * det_inv; out.cb = -e.b * det_inv; out.cc = e.a * det_inv;
@@ -444,8 +464,8 @@ RGS_HD float rgs_project_bwd(const RgsCamera& cam, const float* p, const float* 
     rgs_sh_basis_grad(cam.sh_degree, ux, uy, uz, Bx, By, Bz);
     int nc = (cam.sh_degree + 1) * (cam.sh_degree + 1);
     float gux = 0.f, guy = 0.f, guz = 0.f;
-    RGS_UNROLL
     if (gc_out) { gc_out[0] = gc0; gc_out[1] = gc1; gc_out[2] = gc2; }
+    RGS_UNROLL
     for (int k = 0; k < 16; ++k) {
         if (basis_out) basis_out[k] = k < nc ? B[k] : 0.0f;
         if (k >= nc) continue;

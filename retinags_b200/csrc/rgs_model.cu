@@ -27,7 +27,8 @@ template <int W, int GRP>
 __device__ __forceinline__ void adam_vec(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
                                          float* __restrict__ v, int64_t e0, int64_t live, int64_t goff,
                                          const RgsLrTable& lrs, float beta1, float beta2, float eps, float bc1, float bc2s,
-                                         int zero_grad, const uint8_t* __restrict__ touched) {
+                                         int zero_grad, const uint8_t* __restrict__ touched,
+                                         const uint8_t* __restrict__ active) {
     const int64_t base = goff + e0;
     if (e0 + 3 < live) {
         // rows whose `touched` byte is 0 hold zero gradients: skip the gradient read and clear, and when the
@@ -38,6 +39,14 @@ __device__ __forceinline__ void adam_vec(float* __restrict__ p, float* __restric
             any = touched[r0] != 0;
             if (W < 4) { any = any || touched[(e0 + 1) / W] || touched[(e0 + 2) / W]; }
             if (r3 != r0) any = any || touched[r3];
+            // rows without the `active` mark have never received a gradient since their moments were zeroed: the
+            // moments are zero, the update is exactly zero, and not even the moments need to be read
+            if (!any && active) {
+                bool live_m = active[r0] != 0;
+                if (W < 4) { live_m = live_m || active[(e0 + 1) / W] || active[(e0 + 2) / W]; }
+                if (r3 != r0) live_m = live_m || active[r3];
+                if (!live_m) return;
+            }
         }
         float4 M = *reinterpret_cast<float4*>(m + base), V = *reinterpret_cast<float4*>(v + base);
         float4 G = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -58,6 +67,7 @@ __device__ __forceinline__ void adam_vec(float* __restrict__ p, float* __restric
         for (int k = 0; k < 4 && e0 + k < live; ++k) {
             const int col = (int)((e0 + k) % W);
             const bool t = touched ? touched[(e0 + k) / W] != 0 : true;
+            if (!t && touched && active && !active[(e0 + k) / W]) continue;
             if (!t && m[base + k] == 0.f && v[base + k] == 0.f) continue;
             rgs_adam_elem(p[base + k], t ? g[base + k] : 0.f, m[base + k], v[base + k], adam_lr(lrs, GRP, col), beta1, beta2,
                           eps, bc1, bc2s);
@@ -71,18 +81,26 @@ __global__ void __launch_bounds__(256) rgs_adam_kernel(float* __restrict__ p, fl
                                                        const __grid_constant__ RgsLrTable lrs, float beta1, float beta2,
                                                        float eps, float bc1, float bc2s, int zero_grad,
                                                        const uint32_t* __restrict__ skip,
-                                                       const uint8_t* __restrict__ touched) {
+                                                       const uint8_t* __restrict__ touched,
+                                                       uint8_t* __restrict__ active) {
     if (skip && skip[RGS_CNT_OVERFLOW]) return;
     // vector ranges of the five groups: xyz(3) sh(48) scale(3) rot(4) opacity(1)
     const int64_t n0 = (count * 3 + 3) / 4, n1 = count * 12, n2 = n0, n3 = count, n4 = (count + 3) / 4;
     const int64_t v1 = n0, v2 = v1 + n1, v3 = v2 + n2, v4 = v3 + n3, tv = v4 + n4;
     const int64_t o1 = cap * 3, o2 = o1 + cap * 48, o3 = o2 + cap * 3, o4 = o3 + cap * 4;
     for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < tv; t += (int64_t)gridDim.x * blockDim.x) {
-        if (t < v1) adam_vec<3, 0>(p, g, m, v, t * 4, count * 3, 0, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched);
-        else if (t < v2) adam_vec<48, 1>(p, g, m, v, (t - v1) * 4, count * 48, o1, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched);
-        else if (t < v3) adam_vec<3, 2>(p, g, m, v, (t - v2) * 4, count * 3, o2, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched);
-        else if (t < v4) adam_vec<4, 3>(p, g, m, v, (t - v3) * 4, count * 4, o3, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched);
-        else adam_vec<1, 4>(p, g, m, v, (t - v4) * 4, count, o4, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched);
+        if (t < v1) adam_vec<3, 0>(p, g, m, v, t * 4, count * 3, 0, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched, active);
+        else if (t < v2) adam_vec<48, 1>(p, g, m, v, (t - v1) * 4, count * 48, o1, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched, active);
+        else if (t < v3) adam_vec<3, 2>(p, g, m, v, (t - v2) * 4, count * 3, o2, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched, active);
+        else if (t < v4) adam_vec<4, 3>(p, g, m, v, (t - v3) * 4, count * 4, o3, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched, active);
+        else {
+            adam_vec<1, 4>(p, g, m, v, (t - v4) * 4, count, o4, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched, active);
+            // the opacity group visits every row exactly once: it carries the marks forward. No thread of this launch
+            // depends on a mark set here, because a touched row is processed whatever its mark says.
+            if (touched && active)
+                for (int64_t r = (t - v4) * 4; r < (t - v4) * 4 + 4 && r < count; ++r)
+                    if (touched[r]) active[r] = 1;
+        }
     }
 }
 
@@ -90,7 +108,7 @@ extern "C" {
 
 int rgs_cuda_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t cap, const double* lrs, double beta1,
                   double beta2, double eps, int64_t step, int64_t zero_grad, const int32_t* skip, const uint8_t* touched,
-                  void* stream) {
+                  uint8_t* active, void* stream) {
     if (count <= 0) return 0;
     if (cap % 4 != 0) return 13;
     RgsLrTable t;
@@ -102,7 +120,7 @@ int rgs_cuda_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t
     const unsigned blocks = (unsigned)(want > 148 * 64 ? 148 * 64 : want);
     rgs_adam_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, count, cap, t, (float)beta1, (float)beta2,
                                                              (float)eps, bc1, bc2s, (int)zero_grad,
-                                                             reinterpret_cast<const uint32_t*>(skip), touched);
+                                                             reinterpret_cast<const uint32_t*>(skip), touched, active);
     return (int)cudaGetLastError();
 }
 

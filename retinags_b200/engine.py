@@ -176,11 +176,8 @@ class StepEngine:
                 if b[1] <= b[0]:
                     sums.append(torch.zeros(3, dtype=torch.float64, device=self.device))
                     continue
-                e = (max(0, b[0] - 10), min(p.H, b[1] + 10))
                 gt = self._gt_rows(p.view, cam, (max(0, b[0] - 5), min(p.H, b[1] + 5)))
-                cl.composite(slots[p.view], bg, e[0], e[1])
-                sums.append(cl.loss(gt, self.lambda_dssim, b[0], b[1]).clone())
-                cl.backward(slots[p.view], gslots[p.view], bg, b[0], b[1])
+                sums.append(cl.fused_loss_backward(slots[p.view], gslots[p.view], gt, bg, self.lambda_dssim, b[0], b[1]).clone())
         with T("return_grads"):
             self.transport.return_grads(plans, gslots, local_grad)
         with T("render_backward"):

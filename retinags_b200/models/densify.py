@@ -132,7 +132,7 @@ def _densify_native(store: GaussianStore, max_grad, min_opacity, extent, max_scr
                 new[0], new[1], new[2], new_cap, seed, status)
     if int(status.item()) != 0:
         raise RuntimeError("densify_gather: destination smaller than the new model")
-    store.adopt(new[0], new[1], new[2], new_cap, n1)
+    store.adopt(new[0], new[1], new[2], new_cap, n1, with_moments=kept)
     # both children of a split exist or neither; "pruned" counts the originals that disappeared without a split
     return dict(cloned=cloned, split=child_a, pruned=n0 - kept - child_a)
 

@@ -46,13 +46,14 @@ class GaussianStore:
         self.params = self.grads = self.exp_avg = self.exp_avg_sq = None
         self.grad_accum = self.denom = self.max_radii = None
         self.touched = None  # uint8 per row: a gradient was written this step (rows with 0 hold zero gradients)
+        self.active = None   # uint8 per row: the Adam moments may be non-zero (rows with 0 hold zero moments)
         self._alloc(_round_cap(capacity))
 
     # -- storage --------------------------------------------------------------------------------
     def _alloc(self, cap: int):
         dev = self.device
         old = (self.params, self.grads, self.exp_avg, self.exp_avg_sq, self.cap, self.count)
-        old_stats = (self.grad_accum, self.denom, self.max_radii)
+        old_stats = (self.grad_accum, self.denom, self.max_radii, self.active)
         self.cap = cap
         self.params = torch.zeros(RECORD * cap, dtype=torch.float32, device=dev)
         self.grads = torch.zeros(RECORD * cap, dtype=torch.float32, device=dev)
@@ -63,6 +64,7 @@ class GaussianStore:
         self.max_radii = torch.zeros(cap, dtype=torch.float32, device=dev)
         # gradients do not survive a reallocation: the invariant "untouched rows are zero" restarts
         self.touched = torch.zeros(cap, dtype=torch.uint8, device=dev)
+        self.active = torch.zeros(cap, dtype=torch.uint8, device=dev)
         if old[0] is not None and old[5] > 0:
             n, ocap = old[5], old[4]
             for new_buf, old_buf in zip((self.params, None, self.exp_avg, self.exp_avg_sq), old[:4]):
@@ -70,7 +72,7 @@ class GaussianStore:
                     continue
                 for (_, nv), (_, ov) in zip(self._views(new_buf, cap, n), self._views(old_buf, ocap, n)):
                     nv.copy_(ov)
-            for nb, ob in zip((self.grad_accum, self.denom, self.max_radii), old_stats):
+            for nb, ob in zip((self.grad_accum, self.denom, self.max_radii, self.active), old_stats):
                 nb[:n].copy_(ob[:n])
 
     @staticmethod
@@ -97,6 +99,7 @@ class GaussianStore:
         for which in ("grads", "exp_avg", "exp_avg_sq"):
             getattr(self, which).zero_()
         self.touched.zero_()
+        self.active.zero_()
         self.reset_stats()
 
     def reset_stats(self):
@@ -158,6 +161,7 @@ class GaussianStore:
         native.call("records_unpack", self.device, rec, n, self.params, self.exp_avg, self.exp_avg_sq, self.cap, self.count)
         for s in (self.grad_accum, self.denom, self.max_radii):
             s[self.count:self.count + n] = 0
+        self.active[self.count:self.count + n] = 1  # the records carry moments
         self.count += n
 
     # -- surgery --------------------------------------------------------------------------------
@@ -171,13 +175,14 @@ class GaussianStore:
             full = dict(self._views(buf, self.cap, self.cap))
             for name in NAMES:
                 full[name][:n] = full[name][idx]
-        for s in (self.grad_accum, self.denom, self.max_radii):
+        for s in (self.grad_accum, self.denom, self.max_radii, self.active):
             s[:n] = s[idx]
         self.count = n
 
-    def adopt(self, params: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, cap: int, count: int):
+    def adopt(self, params: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, cap: int, count: int,
+              with_moments: int = 0):
         """Take over freshly written buffers of ``cap`` rows (the output of the compaction kernels): gradients and
-        statistics restart from zero."""
+        statistics restart from zero; the first ``with_moments`` rows carry Adam moments."""
         dev = self.device
         self.params, self.exp_avg, self.exp_avg_sq = params, exp_avg, exp_avg_sq
         self.cap, self.count = cap, count
@@ -186,6 +191,8 @@ class GaussianStore:
         self.denom = torch.zeros(cap, dtype=torch.float32, device=dev)
         self.max_radii = torch.zeros(cap, dtype=torch.float32, device=dev)
         self.touched = torch.zeros(cap, dtype=torch.uint8, device=dev)
+        self.active = torch.zeros(cap, dtype=torch.uint8, device=dev)
+        self.active[:with_moments] = 1
 
     def append_new(self, g: dict):
         """Append freshly created Gaussians (zero moments, zero statistics)."""
@@ -200,7 +207,7 @@ class GaussianStore:
             fullw = dict(self._views(getattr(self, which), self.cap, self.cap))
             for name in NAMES:
                 fullw[name][self.count:self.count + n] = 0
-        for s in (self.grad_accum, self.denom, self.max_radii):
+        for s in (self.grad_accum, self.denom, self.max_radii, self.active):
             s[self.count:self.count + n] = 0
         self.count += n
 
@@ -215,9 +222,15 @@ class GaussianStore:
         arr = (ctypes.c_double * 6)(*[float(x) for x in lrs])
         native.call("adam", self.device, self.params, self.grads, self.exp_avg, self.exp_avg_sq, self.count, self.cap, arr,
                     float(beta1), float(beta2), float(eps), self.step, 1 if zero_grad else 0, skip,
-                    self.touched if zero_grad else None)
+                    self.touched if zero_grad else None, self.active if zero_grad else None)
         if zero_grad:
             self.touched.zero_()
+        else:
+            self.active[:self.count] = 1  # dense update: every row may have moments now
+
+    def mark_active(self):
+        """Declare that Adam moments were written outside the optimiser kernel (e.g. loaded from a file)."""
+        self.active[:self.count] = 1
 
     def mark_touched(self, index: torch.Tensor | None = None):
         """Declare that gradient rows were written outside the render kernels (all rows when ``index`` is None)."""
@@ -279,3 +292,4 @@ class GaussianStore:
                 m["rot"].copy_(a); v["rot"].copy_(b)
             if "step" in entry:
                 self.step = int(float(entry["step"]))
+        self.mark_active()

@@ -87,6 +87,32 @@ class CompositeLoss:
                     weight * (1.0 - lambda_dssim) / npx, weight * lambda_dssim / npx, self.g_image)
         return self.sums
 
+    def fused_loss_backward(self, partials, grads, gt: torch.Tensor, bg, lambda_dssim: float = 0.2, row0: int = 0,
+                            row1: int | None = None, weight: float = 1.0):
+        """Training path in two launches: composite + loss statistics, then d(loss)/d(partial_k) for every partial.
+
+        Equivalent to ``composite`` on rows [row0-10, row1+10), ``loss`` and ``backward`` on rows [row0,row1); the
+        partial slots must hold rows [row0-10, row1+10) (clipped to the image).  Returns the loss sums.
+        """
+        H, W = self.H, self.W
+        row1 = H if row1 is None else row1
+        assert gt.is_contiguous() and gt.shape == (3, H, W)
+        if self.tensor_cores:  # the tensor-core statistics pass reads the composited image from memory
+            self.composite(partials, bg, max(0, row0 - 2 * HALO), min(H, row1 + 2 * HALO))
+            sums = self.loss(gt, lambda_dssim, row0, row1, weight)
+            self.backward(partials, grads, bg, row0, row1)
+            return sums
+        c0, c1 = max(0, row0 - HALO), min(H, row1 + HALO)
+        self.sums.zero_()
+        pp, gp, bgc = native.pointer_array(partials), native.pointer_array(grads), self._bg(bg)
+        native.call("composite_ssim_fwd", self.device, pp, len(partials), bgc, gt, H, W, c0, c1, row0, row1, self.image,
+                    self.trans, self.dmaps, self.sums, sig="pippiiiiiippppp")
+        npx = 3.0 * H * W
+        native.call("ssim_composite_bwd", self.device, pp, gp, len(partials), bgc, self.image, gt, self.dmaps, H, W, row0, row1,
+                    c0, c1, weight * (1.0 - lambda_dssim) / npx, weight * lambda_dssim / npx, self.g_image,
+                    sig="ppippppiiiiiiffpp")
+        return self.sums
+
     def stats(self, gt: torch.Tensor, row0: int = 0, row1: int | None = None):
         """Loss statistics only (no gradient): accumulated (sum|d|, sum ssim, sum d^2) over rows [row0,row1)."""
         H, W = self.H, self.W

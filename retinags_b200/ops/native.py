@@ -12,6 +12,7 @@ Counterpart in the reference: the pybind extension
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from pathlib import Path
 
@@ -34,7 +35,7 @@ SIGNATURES = {
     "blend_bwd": "pppppppppp",
     "geom_bwd": "ppipppppip",
     "scatter_radii": "pppiipp",
-    "adam": "ppppiipfffiippp",
+    "adam": "ppppiipfffiipppp",
     "composite_fwd": "pipiiiippp",
     "composite_bwd": "ppipiiiipp",
     "ssim_fwd": "ppiiiiiippp",
@@ -169,6 +170,8 @@ def _count_launches(name: str, args) -> int:
         return 3 * ((bits + 7) // 8) + 1
     if name == "bin_instances":
         tiles = max(int(args[17]), 1)
+        if tiles <= 14336 and os.environ.get("RGS_TILE_GROUPING", "") != "radix":
+            return 3 * 4 + 2 + 4  # depth sort, instance count + scan, segmented counting (count, 2 scans, emit)
         return 3 * 4 + 3 + 3 * max(1, (max(tiles - 1, 0).bit_length() + 7) // 8) + 1
     return _KERNELS.get(name, 1)
 

@@ -256,3 +256,33 @@ def test_surgery_kernels_match_cpu():
         c = GaussianStore(8, "cuda")
         c.append_migration(b.migration_records())
         assert torch.equal(c.migration_records(), b.migration_records())
+
+
+def test_fused_composite_loss_matches_separate_kernels():
+    """The two fused training kernels against the four separate ones on the GPU, and against the CPU twin."""
+    g = torch.Generator().manual_seed(5)
+    H, W, K = 150, 203, 3
+    parts = [torch.cat([torch.rand(H, W, 3, generator=g) * 0.4, torch.rand(H, W, 1, generator=g)], dim=2).contiguous()
+             for _ in range(K)]
+    gt = torch.rand(3, H, W, generator=g)
+    bg = (0.1, 0.2, 0.3)
+    for rows in ((0, H), (37, 101)):
+        out = {}
+        for dev, fused in (("cuda", False), ("cuda", True), ("cpu", True)):
+            cl = CompositeLoss(dev, H, W)
+            pp = [p.to(dev) for p in parts]
+            gg = [torch.zeros(H, W, 4, device=dev) for _ in range(K)]
+            if fused:
+                s = cl.fused_loss_backward(pp, gg, gt.to(dev), bg, 0.2, rows[0], rows[1]).clone()
+            else:
+                cl.composite(pp, bg, max(0, rows[0] - 10), min(H, rows[1] + 10))
+                s = cl.loss(gt.to(dev), 0.2, rows[0], rows[1]).clone()
+                cl.backward(pp, gg, bg, rows[0], rows[1])
+            out[(dev, fused)] = (s.cpu(), [x.cpu() for x in gg], cl.image[:, rows[0]:rows[1]].cpu())
+        ref = out[("cuda", False)]
+        for key in (("cuda", True), ("cpu", True)):
+            got = out[key]
+            torch.testing.assert_close(got[0], ref[0], rtol=1e-6, atol=1e-6)
+            torch.testing.assert_close(got[2], ref[2], rtol=1e-6, atol=1e-7)
+            for x, y in zip(got[1], ref[1]):
+                torch.testing.assert_close(x, y, rtol=1e-4, atol=1e-9)

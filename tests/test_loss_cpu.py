@@ -60,3 +60,27 @@ def test_row_bands_equal_whole_image():
     torch.testing.assert_close(s_total, s_whole, atol=1e-4, rtol=1e-6)
     for a, b in zip(g_band, g_whole):
         torch.testing.assert_close(a, b, atol=1e-9, rtol=1e-5)
+
+
+def test_fused_training_path_equals_separate_steps():
+    """composite + loss + backward in two calls == the four separate steps, on a row band of three partials."""
+    import torch
+    from retinags_b200.ops.loss import CompositeLoss
+    g = torch.Generator().manual_seed(5)
+    H, W, K = 70, 90, 3
+    parts = [torch.cat([torch.rand(H, W, 3, generator=g) * 0.4, torch.rand(H, W, 1, generator=g)], dim=2).contiguous()
+             for _ in range(K)]
+    gt = torch.rand(3, H, W, generator=g)
+    bg = (0.1, 0.2, 0.3)
+    for rows in ((0, H), (16, 48)):
+        a, b = CompositeLoss("cpu", H, W), CompositeLoss("cpu", H, W)
+        ga = [torch.zeros(H, W, 4) for _ in range(K)]
+        gb = [torch.zeros(H, W, 4) for _ in range(K)]
+        a.composite(parts, bg, max(0, rows[0] - 10), min(H, rows[1] + 10))
+        sa = a.loss(gt, 0.2, rows[0], rows[1]).clone()
+        a.backward(parts, ga, bg, rows[0], rows[1])
+        sb = b.fused_loss_backward(parts, gb, gt, bg, 0.2, rows[0], rows[1]).clone()
+        torch.testing.assert_close(sa, sb, rtol=1e-10, atol=1e-9)  # the sums are OpenMP reductions
+        for x, y in zip(ga, gb):
+            assert torch.equal(x, y)
+        assert float(sum(x.abs().sum() for x in gb)) > 0
