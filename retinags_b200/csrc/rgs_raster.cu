@@ -414,6 +414,7 @@ int rgs_cuda_project_emit(const RgsCamera* cam, const RgsSegment* seg, int64_t i
                           int64_t cap_inst, int32_t* counters, RgsSplatGrad* splat_grads, void* stream) {
     if (seg->count <= 0) return 0;
     if (cap_inst > 0xfffffff0ll || cap_vis > 0x7ffffff0ll) return 10;
+    if ((uintptr_t)seg->sh & 15u) return 14;  // SH rows are read as 128-bit words
     const unsigned blocks = (unsigned)((seg->count + 255) / 256);
     rgs_project_emit_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
         *cam, *seg, id_base, splats, vis_ids, aux, (uint32_t)cap_vis, keys, vals, (uint32_t)cap_inst,

@@ -170,7 +170,7 @@ def _count_launches(name: str, args) -> int:
         return 3 * ((bits + 7) // 8) + 1
     if name == "bin_instances":
         tiles = max(int(args[17]), 1)
-        if tiles <= 14336 and os.environ.get("RGS_TILE_GROUPING", "") != "radix":
+        if tiles <= 14336 and os.environ.get("RGS_TILE_GROUPING", "") == "count":
             return 3 * 4 + 2 + 4  # depth sort, instance count + scan, segmented counting (count, 2 scans, emit)
         return 3 * 4 + 3 + 3 * max(1, (max(tiles - 1, 0).bit_length() + 7) // 8) + 1
     return _KERNELS.get(name, 1)

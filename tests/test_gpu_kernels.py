@@ -286,3 +286,35 @@ def test_fused_composite_loss_matches_separate_kernels():
             torch.testing.assert_close(got[2], ref[2], rtol=1e-6, atol=1e-7)
             for x, y in zip(got[1], ref[1]):
                 torch.testing.assert_close(x, y, rtol=1e-4, atol=1e-9)
+
+
+def test_segmented_counting_grouping_matches_radix(tmp_path):
+    """The optional tile grouping without a second sort (RGS_TILE_GROUPING=count, read once per process) renders the same
+    image as the radix grouping, with both rectangle modes."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import sys, torch\n"
+        f"sys.path.insert(0, {os.path.join(root, 'tests')!r}); sys.path.insert(0, {root!r})\n"
+        "from retinags_b200.data import synthetic\n"
+        "from retinags_b200.ops import rasterize\n"
+        "g = synthetic.uniform_gaussians(60000, 4, sh_degree=3, log_scale_mean=-3.6)\n"
+        "cams = synthetic.ring_cameras(3, 3.0, 320, 208)\n"
+        "seg = rasterize.Segment(*(g[k].cuda().contiguous() for k in ('xyz', 'sh', 'scale', 'rot', 'opacity')))\n"
+        "outs = []\n"
+        "for mode in (1, 2):\n"
+        "    task = rasterize.RenderTask('cuda')\n"
+        "    outs.append((task.forward(rasterize.make_camera(cams[1], 3, tight_rect=mode), [seg], check=True).cpu(), task.n_inst))\n"
+        "torch.save(outs, sys.argv[1])\n")
+    res = {}
+    for mode in ("radix", "count"):
+        path = str(tmp_path / f"{mode}.pt")
+        env = dict(os.environ, RGS_TILE_GROUPING=mode)
+        proc = subprocess.run([sys.executable, "-c", code, path], env=env, capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+        res[mode] = torch.load(path)
+    for (a, na), (b, nb) in zip(res["radix"], res["count"]):
+        assert na == nb
+        assert torch.equal(a, b)
