@@ -38,6 +38,8 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--borrow-refresh", type=int, default=8,
                     help="steps between recomputations of the border-Gaussian selection (the rows are re-sent every step)")
+    ap.add_argument("--bvh-depth", type=int, default=None,
+                    help="2^depth sub-models (default: one per GPU); more sub-models than GPUs are spread round-robin")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--phases", action="store_true", help="also time the phases of a step (extra loop, after the timed one)")
     return ap.parse_args()
@@ -124,7 +126,7 @@ def run_own(args):
     sess = BenchSession(device=device, rank=rank, world=world, n_gaussians=args.gaussians, width=args.width,
                         height=args.height, batch=args.batch, n_views=(args.steps + args.warmup) * args.batch,
                         gt_gaussians=args.gt_gaussians, transport=args.transport, seed=args.seed,
-                        borrow_refresh=args.borrow_refresh)
+                        borrow_refresh=args.borrow_refresh, bvh_depth=args.bvh_depth)
     # ---- device-timed region ------------------------------------------------------------------
     sampler = ClockSampler(local_rank)
     if rank == 0:

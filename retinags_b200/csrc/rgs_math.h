@@ -325,10 +325,10 @@ RGS_HD float rgs_edge_min(float a, float b2, float c, float fixed, float lo, flo
     return a * fixed * fixed + b2 * fixed * t + c * t * t;
 }
 
-RGS_HD bool rgs_tile_hit(float px, float py, float ca, float cb, float cc, float bound, int tx, int ty, int W, int H) {
-    const float x0 = (float)(tx * RGS_TILE), y0 = (float)(ty * RGS_TILE);
-    const float x1 = fminf(x0 + (RGS_TILE - 1), (float)(W - 1)), y1 = fminf(y0 + (RGS_TILE - 1), (float)(H - 1));
-    // d = mean - pixel: ranges of dx, dy over the tile
+// Same test for an arbitrary rectangle of pixel centres [x0,x1] x [y0,y1].
+RGS_HD bool rgs_rect_hit(float px, float py, float ca, float cb, float cc, float bound, float x0, float y0, float x1,
+                         float y1) {
+    // d = mean - pixel: ranges of dx, dy over the rectangle
     const float dx_lo = px - x1, dx_hi = px - x0, dy_lo = py - y1, dy_hi = py - y0;
     if (dx_lo <= 0.0f && dx_hi >= 0.0f && dy_lo <= 0.0f && dy_hi >= 0.0f) return true;
     const float b2 = 2.0f * cb;
@@ -337,6 +337,12 @@ RGS_HD bool rgs_tile_hit(float px, float py, float ca, float cb, float cc, float
     m = fminf(m, rgs_edge_min(cc, b2, ca, dy_lo, dx_lo, dx_hi));
     m = fminf(m, rgs_edge_min(cc, b2, ca, dy_hi, dx_lo, dx_hi));
     return !(m > bound * 1.0005f + 0.001f);
+}
+
+RGS_HD bool rgs_tile_hit(float px, float py, float ca, float cb, float cc, float bound, int tx, int ty, int W, int H) {
+    const float x0 = (float)(tx * RGS_TILE), y0 = (float)(ty * RGS_TILE);
+    const float x1 = fminf(x0 + (RGS_TILE - 1), (float)(W - 1)), y1 = fminf(y0 + (RGS_TILE - 1), (float)(H - 1));
+    return rgs_rect_hit(px, py, ca, cb, cc, bound, x0, y0, x1, y1);
 }
 
 RGS_HD float rgs_alpha_bound(float opacity) { return 2.0f * logf(255.0f * opacity); }

