@@ -76,6 +76,35 @@ __device__ __forceinline__ void adam_vec(float* __restrict__ p, float* __restric
     }
 }
 
+// One 128-bit unit that lies inside a single row (SH and rotation groups, 13 of the 15 units of a row): the row and the
+// column are known to the caller, so that the flag test of a dead row costs two byte loads and no index arithmetic.
+template <int GRP>
+__device__ __forceinline__ void adam_row_vec(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
+                                             float* __restrict__ v, int64_t base, int64_t row, int col0,
+                                             const RgsLrTable& lrs, float beta1, float beta2, float eps, float bc1, float bc2s,
+                                             int zero_grad, const uint8_t* __restrict__ touched,
+                                             const uint8_t* __restrict__ active) {
+    bool any = true;
+    if (touched) {
+        any = touched[row] != 0;
+        if (!any && active && !active[row]) return;
+    }
+    float4 M = *reinterpret_cast<float4*>(m + base), V = *reinterpret_cast<float4*>(v + base);
+    float4 G = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (any) G = *reinterpret_cast<float4*>(g + base);
+    else if (M.x == 0.f && M.y == 0.f && M.z == 0.f && M.w == 0.f && V.x == 0.f && V.y == 0.f && V.z == 0.f && V.w == 0.f)
+        return;
+    float4 P = *reinterpret_cast<float4*>(p + base);
+    rgs_adam_elem(P.x, G.x, M.x, V.x, adam_lr(lrs, GRP, col0), beta1, beta2, eps, bc1, bc2s);
+    rgs_adam_elem(P.y, G.y, M.y, V.y, adam_lr(lrs, GRP, col0 + 1), beta1, beta2, eps, bc1, bc2s);
+    rgs_adam_elem(P.z, G.z, M.z, V.z, adam_lr(lrs, GRP, col0 + 2), beta1, beta2, eps, bc1, bc2s);
+    rgs_adam_elem(P.w, G.w, M.w, V.w, adam_lr(lrs, GRP, col0 + 3), beta1, beta2, eps, bc1, bc2s);
+    *reinterpret_cast<float4*>(p + base) = P;
+    *reinterpret_cast<float4*>(m + base) = M;
+    *reinterpret_cast<float4*>(v + base) = V;
+    if (zero_grad && any) *reinterpret_cast<float4*>(g + base) = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
 __global__ void __launch_bounds__(256) rgs_adam_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
                                                        float* __restrict__ v, int64_t count, int64_t cap,
                                                        const __grid_constant__ RgsLrTable lrs, float beta1, float beta2,
@@ -88,11 +117,20 @@ __global__ void __launch_bounds__(256) rgs_adam_kernel(float* __restrict__ p, fl
     const int64_t n0 = (count * 3 + 3) / 4, n1 = count * 12, n2 = n0, n3 = count, n4 = (count + 3) / 4;
     const int64_t v1 = n0, v2 = v1 + n1, v3 = v2 + n2, v4 = v3 + n3, tv = v4 + n4;
     const int64_t o1 = cap * 3, o2 = o1 + cap * 48, o3 = o2 + cap * 3, o4 = o3 + cap * 4;
+    const bool small = count < 300000000ll;
     for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < tv; t += (int64_t)gridDim.x * blockDim.x) {
         if (t < v1) adam_vec<3, 0>(p, g, m, v, t * 4, count * 3, 0, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched, active);
-        else if (t < v2) adam_vec<48, 1>(p, g, m, v, (t - v1) * 4, count * 48, o1, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched, active);
+        else if (t < v2) {
+            if (small) {  // 32-bit unit index: row = u / 12 is one multiply
+                const uint32_t u = (uint32_t)(t - v1), row = u / 12u, j = u - row * 12u;
+                adam_row_vec<1>(p, g, m, v, o1 + (int64_t)row * 48 + j * 4, row, (int)(j * 4), lrs, beta1, beta2, eps, bc1, bc2s,
+                                zero_grad, touched, active);
+            } else {
+                adam_vec<48, 1>(p, g, m, v, (t - v1) * 4, count * 48, o1, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched, active);
+            }
+        }
         else if (t < v3) adam_vec<3, 2>(p, g, m, v, (t - v2) * 4, count * 3, o2, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched, active);
-        else if (t < v4) adam_vec<4, 3>(p, g, m, v, (t - v3) * 4, count * 4, o3, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched, active);
+        else if (t < v4) adam_row_vec<3>(p, g, m, v, o3 + (t - v3) * 4, t - v3, 0, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched, active);
         else {
             adam_vec<1, 4>(p, g, m, v, (t - v4) * 4, count, o4, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad, touched, active);
             // the opacity group visits every row exactly once: it carries the marks forward. No thread of this launch

@@ -314,8 +314,25 @@ class Trainer:
         g = torch.Generator()
         g.manual_seed(seed)
         order = torch.randperm(len(self.train_dataset), generator=g).tolist()
-        groups = self.balancer.groups(self.train_rlt, order, self.args.MAX_LOAD, self.args.MAX_BATCH_SIZE) if self.rank == 0 else None
+        if getattr(self.args, "BALANCE_BATCHES", False) and self.world > 1:
+            cost = self._camera_costs()
+            groups = self.balancer.groups_balanced(self.train_rlt, order, cost, self.args.MAX_LOAD,
+                                                   self.args.MAX_BATCH_SIZE) if self.rank == 0 else None
+        else:
+            groups = self.balancer.groups(self.train_rlt, order, self.args.MAX_LOAD, self.args.MAX_BATCH_SIZE) if self.rank == 0 else None
         return self._bcast(groups)
+
+    def _camera_costs(self) -> np.ndarray:
+        """Estimated tile instances per (training camera, sub-model); recomputed when the model set changed."""
+        key = tuple(sorted((m, st.count) for m, st in self.stores.items()))
+        if getattr(self, "_cost_key", None) != key:
+            from .parallel.balancer import estimate_costs
+            cams = [self.train_dataset.empty_item(i) for i in range(len(self.train_dataset))]
+            cost = torch.from_numpy(estimate_costs(self.stores, cams, self.n_models)).to(self.device)
+            if self.world > 1:
+                dist.all_reduce(cost, group=self.group)
+            self._cost, self._cost_key = cost.cpu().numpy(), key
+        return self._cost
 
     def _fetch(self, dataset, ids):
         """Cameras of a batch; pixels are only needed by ranks that own rows (all of them with band ownership)."""

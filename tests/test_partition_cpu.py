@@ -124,3 +124,39 @@ def test_knn_matches_brute_force():
                 torch.rand(3, 3, generator=g), torch.rand(2000, 3, generator=g) * torch.tensor([1.0, 1.0, 0.0])):
         a, b = knn3_dist2(pts), brute_force(pts)
         torch.testing.assert_close(a, b, atol=1e-9, rtol=1e-4)
+
+
+def test_balanced_groups_keep_limits_and_lower_the_peak():
+    """Cost-aware batching uses every camera once, respects MAX_LOAD / MAX_BATCH_SIZE and is not worse than sequential
+    packing under the cost it was given."""
+    from retinags_b200.parallel.balancer import WorkloadBalancer
+    rng = np.random.default_rng(0)
+    n, M, W = 60, 8, 4
+    relation = np.where(rng.random((n, M)) < 0.85, 0, -1).astype(np.int32)
+    cost = rng.gamma(2.0, 1.0, size=(n, M)) * (relation >= 0)
+    b = WorkloadBalancer(W, [m % W for m in range(M)])
+    order = rng.permutation(n)
+    plain = b.groups(relation, order, 8, 4)
+    bal = b.groups_balanced(relation, order, cost, 8, 4, window=32)
+    assert sorted(c for g in bal for c in g) == list(range(n))
+    for g in bal:
+        assert 1 <= len(g) <= 4
+        load = sum(b.load_per_rank(relation[c]) for c in g)
+        assert (load <= 8).all() or len(g) == 1
+    assert b.imbalance(relation, bal, cost) < b.imbalance(relation, plain, cost)
+
+
+def test_cost_estimate_tracks_instance_counts():
+    """The geometric estimate of tile instances follows the rasteriser's own instance counter."""
+    from helpers import native_render
+    from retinags_b200.data import synthetic
+    from retinags_b200.models.gaussians import GaussianStore
+    from retinags_b200.parallel.balancer import estimate_costs
+    g = synthetic.uniform_gaussians(4000, 2, sh_degree=1, log_scale_mean=-3.2)
+    st = GaussianStore(4000, "cpu")
+    st.set_params(g)
+    cams = synthetic.ring_cameras(4, 2.5, 160, 112) + synthetic.ring_cameras(2, 6.0, 160, 112)
+    est = estimate_costs({0: st}, cams, 1, stride=1)[:, 0]
+    real = np.array([native_render(g, cam, 1, device="cpu")[1].n_inst for cam in cams], dtype=np.float64)
+    assert np.corrcoef(est, real)[0, 1] > 0.9
+    assert (est >= 0.8 * real).all() and (est <= 4.0 * real).all()
