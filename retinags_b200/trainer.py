@@ -532,6 +532,7 @@ class Trainer:
         """Rebalance: all-reduce the load histogram, rebuild the tree away from the old split planes, move
         every Gaussian (parameters + Adam moments, 177 floats) to the sub-model whose box now holds its
         centre (``trainer4tree_partition.py:220-317``)."""
+        self.logger.info("repartition at iteration %d: %s", self.iteration, {m: s.count for m, s in self.stores.items()})
         grid = self.tree.grid
         hist = torch.zeros(grid.grid_size, dtype=torch.float32, device=self.device)
         for st in self.stores.values():
