@@ -84,7 +84,10 @@ class StepEngine:
             if src.device == buf.device:
                 buf[:, rows[0]:rows[1]].copy_(src[:, rows[0]:rows[1]])
             else:
-                buf[:, rows[0]:rows[1]].copy_(src[:, rows[0]:rows[1]], non_blocking=True)
+                # one copy per colour plane: a band of a plane is contiguous on both sides, so the pinned source goes
+                # through the copy engine asynchronously (a strided band would be staged through pageable memory)
+                for c in range(3):
+                    buf[c, rows[0]:rows[1]].copy_(src[c, rows[0]:rows[1]], non_blocking=True)
         return buf
 
     # -- segments -------------------------------------------------------------------------------
