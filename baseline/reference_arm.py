@@ -247,6 +247,10 @@ def main(args):
     for d in glob.glob(os.path.join(model_dir, "rank_*")):
         shutil.rmtree(d, ignore_errors=True)
     depth = max(0, world.bit_length() - 1)
+    max_load = 2 * args.batch
+    if getattr(args, "bvh_depth", None) is not None and args.bvh_depth > depth:
+        depth = args.bvh_depth  # more sub-models than GPUs: every camera costs one render task per local sub-model
+        max_load = args.batch * max(1, (2 ** depth + world - 1) // world)
     env = dict(os.environ)
     env["PYTHONPATH"] = os.pathsep.join([SHIMS, REF, SRC, env.get("PYTHONPATH", "")])
     # allocator hint that torch's own out-of-memory message recommends; the reference's code is untouched
@@ -257,7 +261,7 @@ def main(args):
         env.pop(k, None)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
            "127.0.0.1", "--master-port", str(29800 + os.getpid() % 100), "main.py", "-s", data_dir, "-m", model_dir,
-           "--bvh_depth", str(depth), "--MAX_BATCH_SIZE", str(args.batch), "--MAX_LOAD", str(2 * args.batch), "-r", "1",
+           "--bvh_depth", str(depth), "--MAX_BATCH_SIZE", str(args.batch), "--MAX_LOAD", str(max_load), "-r", "1",
            "--ply_iteration", "1", "--ENABLE_TENSORBOARD", "--logdir", os.path.join(root, "tb"), "--epochs", "1",
            "--iterations", str(n_views), "--EVAL_INTERVAL_EPOCH", "100000", "--SAVE_INTERVAL_EPOCH", "100000",
            "--densify_from_iter", "100000000", "--log_level", "30", "--DATALOADER_FIX_SEED"]
