@@ -415,6 +415,13 @@ int rgs_cpu_ssim_bwd(const float* img, const float* gt, const float* dmaps, int6
     return 0;
 }
 
+// The CPU backward visits pixels in a fixed order and is deterministic as it is: the fixed-point variant is the same call.
+int rgs_cpu_blend_bwd_fixed(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
+                            const float* out, const int32_t* n_contrib, const float* grad_out, RgsSplatGrad* splat_grads,
+                            int32_t* counters, int64_t*, int64_t, void*) {
+    return rgs_cpu_blend_bwd(cam, ranges, vals, splats, out, n_contrib, grad_out, splat_grads, counters, nullptr);
+}
+
 // CPU twins of the fused training path of rgs_loss.cu: the same four steps, run back to back.
 int rgs_cpu_composite_ssim_fwd(const float* const* partials, int64_t K, const float* bg, const float* gt, int64_t H,
                                int64_t W, int64_t crow0, int64_t crow1, int64_t srow0, int64_t srow1, float* image,

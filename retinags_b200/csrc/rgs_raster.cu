@@ -107,14 +107,35 @@ struct BlendSmem {
 };
 
 // Issue the gather of one batch: every thread copies the 48-byte record of one sorted instance.
+#define RGS_STATUS_BAD_INDEX 16u  // a slot or range read from the binning buffers was out of bounds (flagged, clamped)
+
+// A slot index from the sorted instance list, checked against the number of visible splats: a bad index is reported
+// through the status word and replaced by slot 0, so that no copy ever leaves the splat buffer.
+__device__ __forceinline__ uint32_t checked_slot(uint32_t slot, uint32_t n_vis, uint32_t* counters) {
+    if (slot < n_vis) return slot;
+    atomicOr(&counters[RGS_CNT_STATUS], RGS_STATUS_BAD_INDEX);
+    return 0u;
+}
+
+// Tile range clipped to [0, n_inst]; an inverted or out-of-range record is reported and treated as empty.
+__device__ __forceinline__ int2 checked_range(int2 r, uint32_t* counters) {
+    if (counters[RGS_CNT_OVERFLOW]) return make_int2(0, 0);
+    const uint32_t n_inst = counters[RGS_CNT_INST];
+    if (r.x < 0 || r.y < r.x || (uint32_t)r.y > n_inst) {
+        atomicOr(&counters[RGS_CNT_STATUS], RGS_STATUS_BAD_INDEX);
+        return make_int2(0, 0);
+    }
+    return r;
+}
+
 __device__ __forceinline__ void blend_issue(BlendSmem& sm, int stage, const RgsSplat* __restrict__ splats,
                                             const uint32_t* __restrict__ vals, int first, int count, bool reverse,
-                                            int range_end) {
+                                            int range_end, uint32_t n_vis, uint32_t* counters) {
     const int t = threadIdx.x;
     if (t == 0) rgs_mbar_expect_tx(&sm.bar[stage], (uint32_t)count * (uint32_t)sizeof(RgsSplat));
     if (t < count) {
         const int idx = reverse ? (range_end - 1 - first - t) : (first + t);
-        const uint32_t slot = vals[idx];
+        const uint32_t slot = checked_slot(vals[idx], n_vis, counters);
         rgs_bulk_g2s(&sm.buf[stage][t], splats + slot, (uint32_t)sizeof(RgsSplat), &sm.bar[stage]);
     }
 }
@@ -138,8 +159,8 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
     const int px = blockIdx.x * RGS_TILE + lx, py = blockIdx.y * RGS_TILE + ly;
     const bool inside = px < cam.W && py < cam.H;
     const int tile = blockIdx.y * cam.tiles_x + blockIdx.x;
-    int2 range = ranges[tile];
-    if (counters[RGS_CNT_OVERFLOW]) range = make_int2(0, 0);
+    const int2 range = checked_range(ranges[tile], counters);
+    const uint32_t n_vis = counters[RGS_CNT_VIS];
     const int total = range.y - range.x;
     const int rounds = (total + BLEND_BATCH - 1) / BLEND_BATCH;
     if (tid == 0) { rgs_mbar_init(&sm.bar[0], 1); rgs_mbar_init(&sm.bar[1], 1); rgs_fence_mbar_init(); }
@@ -156,7 +177,7 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
     rgs_pixel_init(st);
     st.done = !inside;
 
-    if (rounds > 0) blend_issue(sm, 0, splats, vals, range.x, min(BLEND_BATCH, total), false, range.y);
+    if (rounds > 0) blend_issue(sm, 0, splats, vals, range.x, min(BLEND_BATCH, total), false, range.y, n_vis, counters);
     int pending = rounds > 0 ? 0 : -1;  // stage with a copy in flight that has not been waited for
     bool failed = false;
     for (int b = 0; b < rounds; ++b) {
@@ -165,7 +186,7 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
         if (b + 1 < rounds) {
             rgs_fence_proxy_async();
             blend_issue(sm, stage ^ 1, splats, vals, range.x + (b + 1) * BLEND_BATCH,
-                        min(BLEND_BATCH, total - (b + 1) * BLEND_BATCH), false, range.y);
+                        min(BLEND_BATCH, total - (b + 1) * BLEND_BATCH), false, range.y, n_vis, counters);
         }
         if (!rgs_mbar_wait(&sm.bar[stage], (b >> 1) & 1, RGS_WAIT_LIMIT)) failed = true;
         pending = (b + 1 < rounds) ? (stage ^ 1) : -1;
@@ -200,7 +221,7 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
             break;
         }
     }
-    if (failed && tid == 0) atomicExch(&counters[RGS_CNT_STATUS], 1u);
+    if (failed && tid == 0) atomicOr(&counters[RGS_CNT_STATUS], 1u);
     if (inside) {
         const int64_t pid = (int64_t)py * cam.W + px;
         const float4 val = make_float4(st.C[0], st.C[1], st.C[2], st.T);
@@ -224,10 +245,16 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// FIXED: the cross-warp / cross-tile accumulation goes through 64-bit fixed-point integers (scale 2^40) instead of
+// float atomics. Integer addition is associative, so the result no longer depends on the order in which tiles and
+// warps arrive: two runs give identical bits, which separates a race from rounding when gradients disagree.
+#define RGS_FIXED_SCALE 1099511627776.0  // 2^40: resolution 9e-13, range +-8.4e6
+template <bool FIXED>
 __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
     const __grid_constant__ RgsCamera cam, const int2* __restrict__ ranges, const uint32_t* __restrict__ vals,
     const RgsSplat* __restrict__ splats, const float4* __restrict__ out, const int32_t* __restrict__ n_contrib,
-    const float4* __restrict__ grad_out, RgsSplatGrad* __restrict__ splat_grads, uint32_t* __restrict__ counters) {
+    const float4* __restrict__ grad_out, RgsSplatGrad* __restrict__ splat_grads, uint32_t* __restrict__ counters,
+    unsigned long long* __restrict__ fixed_acc) {
     __shared__ __align__(128) BlendSmem sm;
     __shared__ uint32_t sm_slot[2][BLEND_BATCH];
     const int tid = threadIdx.x, lane = tid & 31;
@@ -235,8 +262,8 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
     const int px = blockIdx.x * RGS_TILE + lx, py = blockIdx.y * RGS_TILE + ly;
     const bool inside = px < cam.W && py < cam.H;
     const int tile = blockIdx.y * cam.tiles_x + blockIdx.x;
-    int2 range = ranges[tile];
-    if (counters[RGS_CNT_OVERFLOW]) range = make_int2(0, 0);
+    const int2 range = checked_range(ranges[tile], counters);
+    const uint32_t n_vis = counters[RGS_CNT_VIS];
     const int64_t pid = (int64_t)py * cam.W + px;
     const int last = inside ? n_contrib[pid] : 0;
     // only the first max(last) instances of the tile contributed to any pixel
@@ -269,7 +296,7 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
         const int cnt = min(BLEND_BATCH, total - b * BLEND_BATCH);
         if (tid == 0) rgs_mbar_expect_tx(&sm.bar[stage], (uint32_t)cnt * (uint32_t)sizeof(RgsSplat));
         if (tid < cnt) {
-            const uint32_t slot = vals[range_end - 1 - b * BLEND_BATCH - tid];
+            const uint32_t slot = checked_slot(vals[range_end - 1 - b * BLEND_BATCH - tid], n_vis, counters);
             sm_slot[stage][tid] = slot;
             rgs_bulk_g2s(&sm.buf[stage][tid], splats + slot, (uint32_t)sizeof(RgsSplat), &sm.bar[stage]);
         }
@@ -340,15 +367,36 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
                 w1 += __shfl_xor_sync(0xffffffffu, w1, 1);
                 v8 = warp_sum(v8);
                 // value index held by this lane: bit 16 -> +4, bit 8 -> +2, bit 4 -> +1
-                float* dst = reinterpret_cast<float*>(splat_grads + sm_slot[stage][j]);
-                if ((lane & 3) == 0) atomicAdd(dst + (((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)), w1);
-                if (lane == 0) atomicAdd(dst + 8, v8);
+                const int which = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                if (FIXED) {
+                    unsigned long long* dst = fixed_acc + (size_t)sm_slot[stage][j] * 9;
+                    if ((lane & 3) == 0) atomicAdd(dst + which, (unsigned long long)__double2ll_rn((double)w1 * RGS_FIXED_SCALE));
+                    if (lane == 0) atomicAdd(dst + 8, (unsigned long long)__double2ll_rn((double)v8 * RGS_FIXED_SCALE));
+                } else {
+                    float* dst = reinterpret_cast<float*>(splat_grads + sm_slot[stage][j]);
+                    if ((lane & 3) == 0) atomicAdd(dst + which, w1);
+                    if (lane == 0) atomicAdd(dst + 8, v8);
+                }
             }
           }
         }
         __syncthreads();  // frees this stage for the copy issued two rounds later
     }
-    if (failed && tid == 0) atomicExch(&counters[RGS_CNT_STATUS], 2u);
+    if (failed && tid == 0) atomicOr(&counters[RGS_CNT_STATUS], 2u);
+}
+
+__global__ void __launch_bounds__(256) rgs_fixed_fold_kernel(long long* __restrict__ fixed_acc, int64_t cap_vis,
+                                                             const uint32_t* __restrict__ counters,
+                                                             RgsSplatGrad* __restrict__ splat_grads) {
+    int64_t n = counters[RGS_CNT_OVERFLOW] ? 0 : (int64_t)counters[RGS_CNT_VIS];
+    if (n > cap_vis) n = cap_vis;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n * 9; e += (int64_t)gridDim.x * blockDim.x) {
+        const long long v = fixed_acc[e];
+        if (v == 0) continue;
+        fixed_acc[e] = 0;
+        const int64_t slot = e / 9;
+        reinterpret_cast<float*>(splat_grads + slot)[e - slot * 9] += (float)((double)v / RGS_FIXED_SCALE);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -367,6 +415,10 @@ __global__ void __launch_bounds__(128, 8) rgs_geom_bwd_kernel(
         int sidx = 0;
         while (sidx < segs.n - 1 && i >= segs.s[sidx].count) { i -= segs.s[sidx].count; ++sidx; }
         const RgsSegment& sg = segs.s[sidx];
+        if (i < 0 || i >= sg.count) {  // a corrupt id would address another buffer: report and skip
+            atomicOr(const_cast<uint32_t*>(&counters[RGS_CNT_STATUS]), RGS_STATUS_BAD_INDEX);
+            continue;
+        }
         const uint32_t a = aux[slot];
         const float4* gsrc = reinterpret_cast<const float4*>(splat_grads + slot);
         float4 g0 = gsrc[0], g1 = gsrc[1], g2 = gsrc[2];
@@ -494,9 +546,27 @@ int rgs_cuda_blend_bwd(const RgsCamera* cam, const int32_t* ranges, const uint32
                        const float* out, const int32_t* n_contrib, const float* grad_out, RgsSplatGrad* splat_grads,
                        int32_t* counters, void* stream) {
     dim3 grid(cam->tiles_x, cam->tiles_y);
-    rgs_blend_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
+    rgs_blend_bwd_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(
         *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
-        reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters));
+        reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters), nullptr);
+    return (int)cudaGetLastError();
+}
+
+// Debug variant with order-independent accumulation. fixed_acc: 9 int64 words per slot (cap_vis slots), all zero on
+// entry; they are folded into splat_grads (added to what it holds) and zeroed again before the call returns control
+// to the stream.
+int rgs_cuda_blend_bwd_fixed(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
+                             const float* out, const int32_t* n_contrib, const float* grad_out, RgsSplatGrad* splat_grads,
+                             int32_t* counters, int64_t* fixed_acc, int64_t cap_vis, void* stream) {
+    dim3 grid(cam->tiles_x, cam->tiles_y);
+    rgs_blend_bwd_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
+        reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters),
+        reinterpret_cast<unsigned long long*>(fixed_acc));
+    const int64_t want = (cap_vis * 9 + 255) / 256;
+    const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > 148 * 32 ? 148 * 32 : want));
+    rgs_fixed_fold_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<long long*>(fixed_acc), cap_vis,
+                                                                   reinterpret_cast<const uint32_t*>(counters), splat_grads);
     return (int)cudaGetLastError();
 }
 

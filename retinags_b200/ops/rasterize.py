@@ -15,6 +15,7 @@ activated means/scales/rotations/opacities/SHs in, premultiplied colour, depth a
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 from dataclasses import dataclass
 
@@ -200,6 +201,9 @@ class RenderTask:
         self.out = self.depth = self.n_contrib = self.splat_grads = None
         self.total_count = 0
         self.timer = None  # optional utils.profiler.PhaseTimer for per-kernel-group timing
+        # debug mode: accumulate the blend backward through 64-bit fixed point so that two runs give identical bits
+        self.deterministic = os.environ.get("RGS_DETERMINISTIC", "0") == "1"
+        self._fixed_acc = None
 
     def _phase(self, name: str):
         import contextlib
@@ -320,7 +324,12 @@ class RenderTask:
         c = self._host_counters.tolist()
         info = dict(n_vis=c[CNT_VIS], n_inst=c[CNT_INST] & 0xFFFFFFFF, overflow=bool(c[CNT_OVERFLOW]), status=c[CNT_STATUS])
         if info["status"]:
-            raise RuntimeError(f"rasteriser wait expired (status {info['status']})")
+            what = []
+            if info["status"] & 3:
+                what.append("a bounded wait on a bulk copy ran out")
+            if info["status"] & 16:
+                what.append("an index read from the binning buffers was out of bounds (clamped)")
+            raise RuntimeError(f"rasteriser status {info['status']}: " + "; ".join(what or ["unknown"]))
         if info["overflow"] or info["n_inst"] > 0.8 * self.cap_inst:
             self._grow_inst(int(info["n_inst"] * 1.5) + 1024)
         return info
@@ -331,8 +340,15 @@ class RenderTask:
         cam = self.cam
         assert grad_out.is_contiguous() and grad_out.shape == (cam.H, cam.W, 4)
         with self._phase("bwd.blend"):
-            native.call("blend_bwd", self.device, cam, self.ranges, self.vals, self.splats, self.last_out, self.n_contrib,
-                        grad_out, self.splat_grads, self.counters)
+            if self.deterministic:
+                if self._fixed_acc is None or self._fixed_acc.numel() < 9 * self.cap_vis:
+                    self._fixed_acc = torch.zeros(9 * self.cap_vis, dtype=torch.int64, device=self.device)
+                native.call("blend_bwd_fixed", self.device, cam, self.ranges, self.vals, self.splats, self.last_out,
+                            self.n_contrib, grad_out, self.splat_grads, self.counters, self._fixed_acc, self.cap_vis,
+                            sig="ppppppppppip")
+            else:
+                native.call("blend_bwd", self.device, cam, self.ranges, self.vals, self.splats, self.last_out, self.n_contrib,
+                            grad_out, self.splat_grads, self.counters)
         structs = (RgsSegment * len(segments))(*[s.struct(True) for s in segments])
         with self._phase("bwd.geometry"):
             native.call("geom_bwd", self.device, cam, structs, len(segments), self.counters, self.splats, self.vis_ids,
