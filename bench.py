@@ -42,6 +42,7 @@ def parse_args():
                     help="2^depth sub-models (default: one per GPU); more sub-models than GPUs are spread round-robin")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--phases", action="store_true", help="also time the phases of a step (extra loop, after the timed one)")
+    ap.add_argument("--trace", default="", help="with --phases: write a Chrome trace of the phase loop to <path>.rank<r>.json")
     return ap.parse_args()
 
 
@@ -177,9 +178,12 @@ def run_own(args):
     if args.phases:
         sess.engine.timer.enabled = True
         sess.engine.timer.reset()
+        sess.engine.timer.trace = bool(args.trace)
         for i in range(args.steps):
             sess.step(args.warmup + i)
         phases = sess.engine.timer.table(args.steps)
+        if args.trace:
+            sess.engine.timer.export_chrome_trace(f"{args.trace}.rank{rank}.json", rank)
         sess.engine.timer.enabled = False
     if rank == 0:
         value = args.steps * args.batch / (ms / 1e3)

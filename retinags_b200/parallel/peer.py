@@ -38,8 +38,15 @@ class _DevBuf:
                                          "strides": None}
 
 
+GUARD_BYTES = 256           # canary zone in front of and behind the usable bytes of a region
+CANARY = 0x5A5AC3C3          # pattern of the canary words (int32)
+
+
 class PeerRegion:
-    """Symmetric region: the same byte size on every rank, mapped everywhere."""
+    """Symmetric region: the same byte size on every rank, mapped everywhere.
+
+    The usable bytes sit between two guard zones filled with a canary pattern; ``verify_canaries`` tells whether a
+    kernel (of this rank or of a peer: the region is mapped everywhere) stored outside the region's bounds."""
 
     def __init__(self, nbytes: int, device: torch.device, group=None):
         self.device, self.group = device, group
@@ -57,19 +64,21 @@ class PeerRegion:
         self._lib = lib
         with torch.cuda.device(device):
             p = ctypes.c_void_p()
-            rc = lib.rgs_cuda_ipc_alloc(self.nbytes, ctypes.byref(p))
+            rc = lib.rgs_cuda_ipc_alloc(self.nbytes + 2 * GUARD_BYTES, ctypes.byref(p))
             if rc:
                 raise RuntimeError(f"cudaMalloc of the exchange region failed ({rc})")
-            self.local_ptr = int(p.value)
+            self._alloc_ptr = int(p.value)
+            self.local_ptr = self._alloc_ptr + GUARD_BYTES
             handle = ctypes.create_string_buffer(64)
             if self.world > 1:
-                rc = lib.rgs_cuda_ipc_get_handle(self.local_ptr, handle)
+                rc = lib.rgs_cuda_ipc_get_handle(self._alloc_ptr, handle)
                 if rc:
                     raise RuntimeError(f"cudaIpcGetMemHandle failed ({rc})")
             handles = [None] * self.world
             if self.world > 1:
                 dist.all_gather_object(handles, bytes(handle.raw), group=group)
             self.ptrs = []
+            self._peer_bases: dict[int, int] = {}
             for r in range(self.world):
                 if r == self.rank:
                     self.ptrs.append(self.local_ptr)
@@ -78,8 +87,13 @@ class PeerRegion:
                     rc = lib.rgs_cuda_ipc_open(handles[r], ctypes.byref(q))
                     if rc:
                         raise RuntimeError(f"cudaIpcOpenMemHandle for rank {r} failed ({rc})")
-                    self.ptrs.append(int(q.value))
-        self.local = torch.as_tensor(_DevBuf(self.local_ptr, self.nbytes), device=device)
+                    self._peer_bases[r] = int(q.value)
+                    self.ptrs.append(int(q.value) + GUARD_BYTES)
+        self._whole = torch.as_tensor(_DevBuf(self._alloc_ptr, self.nbytes + 2 * GUARD_BYTES), device=device)
+        self._guards = (self._whole[:GUARD_BYTES].view(torch.int32), self._whole[GUARD_BYTES + self.nbytes:].view(torch.int32))
+        for gz in self._guards:
+            gz.fill_(CANARY)
+        self.local = self._whole[GUARD_BYTES:GUARD_BYTES + self.nbytes]
         if self.world > 1:
             dist.barrier(group)
 
@@ -90,6 +104,10 @@ class PeerRegion:
         nbytes = n * torch.empty(0, dtype=dtype).element_size()
         return self.local[offset:offset + nbytes].view(dtype).view(*shape)
 
+    def verify_canaries(self) -> bool:
+        """True when both guard zones still hold the pattern (synchronises the device)."""
+        return all(bool((gz == CANARY).all()) for gz in self._guards)
+
     def close(self):
         if getattr(self, "ptrs", None) is None:
             return
@@ -97,11 +115,11 @@ class PeerRegion:
             torch.cuda.synchronize(self.device)
             if self.world > 1:
                 dist.barrier(self.group)
-            for r, p in enumerate(self.ptrs):
+            for r in range(self.world):
                 if r != self.rank:
-                    self._lib.rgs_cuda_ipc_close(p)
-            self.local = None
-            self._lib.rgs_cuda_ipc_free(self.local_ptr)
+                    self._lib.rgs_cuda_ipc_close(self._peer_bases[r])
+            self.local = self._whole = self._guards = None
+            self._lib.rgs_cuda_ipc_free(self._alloc_ptr)
         self.ptrs = None
 
 
@@ -174,6 +192,8 @@ class PeerTransport:
         st = int(self.status[0].item())
         if st:
             raise RuntimeError(f"peer wait expired: no signal from rank {st & 0xff} within the cycle budget")
+        if self.region is not None and not self.region.verify_canaries():
+            raise RuntimeError("a kernel stored outside the bounds of this rank's exchange region (canary overwritten)")
 
     # -- transport interface ------------------------------------------------------------------------
     def push_plan(self, plan: ViewPlan, model: int):

@@ -340,3 +340,16 @@ def test_deterministic_backward_mode_gives_identical_bits():
     assert torch.equal(runs[0], runs[1])
     assert (runs[0] - runs[2]).norm().item() <= 1e-4 * runs[2].norm().item()
     assert float(runs[0].abs().sum()) > 0
+
+
+def test_peer_region_canaries_detect_an_out_of_bounds_store():
+    """The guard zones around an exchange region: intact after normal use, flagged after a store one byte past the end
+    (the store stays inside the allocation, nothing faults)."""
+    from retinags_b200.parallel.peer import GUARD_BYTES, PeerRegion
+    region = PeerRegion(4096, torch.device("cuda", 0))
+    region.view(0, (1024,)).fill_(3.0)
+    region.view(4096 - 16, (4,)).fill_(7.0)
+    assert region.verify_canaries()
+    region._whole[GUARD_BYTES + region.nbytes] = 1  # what an off-by-one peer store would hit
+    assert not region.verify_canaries()
+    region.close()

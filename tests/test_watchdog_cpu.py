@@ -87,3 +87,24 @@ def test_rank_leaving_between_steps_is_noticed_by_training_ranks():
     outs = [p.communicate(timeout=300)[0] for p in procs]
     assert [p.returncode for p in procs] == [0, 0], "\n".join(o[-2000:] for o in outs)
     assert "RANK_LOSS_DETECTED rank 0" in outs[0] and "no heartbeat" in outs[0]
+
+
+def test_phase_timer_writes_a_chrome_trace(tmp_path):
+    import json
+    from retinags_b200.utils.profiler import PhaseTimer
+    t = PhaseTimer("cpu", enabled=True)
+    t.trace = True
+    for _ in range(2):
+        with t.phase("step"):
+            with t.phase("forward"):
+                time.sleep(0.002)
+            with t.phase("backward"):
+                time.sleep(0.001)
+    path = str(tmp_path / "trace.json")
+    t.export_chrome_trace(path, rank=3)
+    ev = [e for e in json.load(open(path))["traceEvents"] if e["ph"] == "X"]
+    assert [e["name"] for e in ev].count("forward") == 2 and all(e["pid"] == 3 for e in ev)
+    step = [e for e in ev if e["name"] == "step"][0]
+    fwd = [e for e in ev if e["name"] == "forward"][0]
+    assert step["ts"] <= fwd["ts"] and fwd["ts"] + fwd["dur"] <= step["ts"] + step["dur"] + 1.0
+    assert t.table(2)["forward"] >= 2.0
