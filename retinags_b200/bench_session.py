@@ -20,7 +20,7 @@ from .engine import StepEngine
 from .models.gaussians import GaussianStore
 from .ops import native
 from .ops.rasterize import RenderTask, Segment, make_camera
-from .parallel.compositing import LocalTransport, TorchDistTransport, band_rows
+from .parallel.compositing import LocalTransport, TorchDistTransport
 from .parallel.partition import BvhTree, Grid3D, assign_models, load_histogram
 
 CHUNK = 4_000_000

@@ -4,7 +4,6 @@ from __future__ import annotations
 import datetime
 import logging
 import os
-import sys
 import time
 import traceback
 

@@ -6,7 +6,6 @@ underscore-prefixed fields) for every attribute, booleans become ``store_true``.
 """
 from __future__ import annotations
 
-import argparse
 from argparse import ArgumentParser, Namespace
 
 

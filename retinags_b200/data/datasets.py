@@ -12,7 +12,6 @@ import torch
 from torch.utils.data import Dataset
 
 from .cameras import Camera
-from .readers import CameraInfo
 
 
 def target_resolution(orig_w: int, orig_h: int, resolution, resolution_scale: float = 1.0) -> tuple[int, int]:

@@ -11,10 +11,9 @@ a ``CameraInfo`` only records the path; pixels are loaded lazily by the dataset
 from __future__ import annotations
 
 import json
-import math
 import os
 import struct
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from pathlib import Path
 
 import numpy as np

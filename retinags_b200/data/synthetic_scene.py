@@ -7,7 +7,6 @@ initial points handed to the trainer (sampled from the target's centres with the
 """
 from __future__ import annotations
 
-import numpy as np
 import torch
 
 from ..ops.rasterize import RenderTask, Segment, make_camera

@@ -18,7 +18,7 @@ from .data.cameras import Camera
 from .models.gaussians import GaussianStore
 from .ops.loss import CompositeLoss
 from .ops.rasterize import RenderTask, Segment, make_camera
-from .parallel.compositing import LocalTransport, ViewPlan, band_rows, extended
+from .parallel.compositing import LocalTransport, ViewPlan, band_rows
 from .utils.profiler import PhaseTimer
 
 

@@ -20,8 +20,6 @@ split children, second split children):
 """
 from __future__ import annotations
 
-import ctypes
-
 import torch
 
 from ..ops import native

@@ -14,7 +14,6 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from pathlib import Path
 
 import torch
 

@@ -16,10 +16,8 @@ from __future__ import annotations
 
 import ctypes
 import os
-import math
 from dataclasses import dataclass
 
-import numpy as np
 import torch
 
 from ..data.cameras import Camera

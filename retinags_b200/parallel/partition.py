@@ -14,7 +14,6 @@ median-of-load split with margin and jitter ``:228-263``, BFS build ``:334-360``
 """
 from __future__ import annotations
 
-import math
 import pickle
 from dataclasses import dataclass, field
 

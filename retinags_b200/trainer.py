@@ -24,7 +24,6 @@ from __future__ import annotations
 import glob
 import json
 import logging
-import math
 import os
 import shutil
 import time
@@ -38,7 +37,7 @@ from .data.cameras import Camera
 from .data.datasets import CameraListDataset, DatasetRepeater
 from .engine import StepEngine
 from .models import densify, ply_io
-from .models.gaussians import NAMES, GaussianStore
+from .models.gaussians import GaussianStore
 from .ops.knn import knn3_dist2
 from .parallel.balancer import WorkloadBalancer
 from .parallel.border import BorderExchange
