@@ -33,8 +33,8 @@ def setup_distributed(device_kind: str):
 def main(argv=None) -> int:
     parser, lp, op, pp = build_parser()
     args = parser.parse_args(argv)
-    if getattr(args, "detect_anomaly", False):
-        torch.autograd.set_detect_anomaly(True)
+    # --detect_anomaly: the step engine checks loss sums and gradients for non-finite values after every backward
+    # (retinags_b200/engine.py); no autograd graph exists on the training path
     seed_everything(0)
     rank, world, _ = setup_distributed(args.device)
     if world > 2 ** args.bvh_depth:

@@ -155,7 +155,10 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
     int32_t* __restrict__ n_contrib, uint32_t* __restrict__ counters, const __grid_constant__ RgsPushPlan push) {
     __shared__ __align__(128) BlendSmem sm;
     const int tid = threadIdx.x;
-    const int lx = tid & 15, ly = tid >> 4;
+    // a warp owns a compact 8x4 block of the tile (2 x 4 blocks per tile): the smaller the extent of the warp's
+    // pixels, the more splats the warp-level test rejects
+    const int bx = (tid >> 5) & 1, by = tid >> 6;
+    const int lx = bx * 8 + (tid & 7), ly = by * 4 + ((tid >> 3) & 3);
     const int px = blockIdx.x * RGS_TILE + lx, py = blockIdx.y * RGS_TILE + ly;
     const bool inside = px < cam.W && py < cam.H;
     const int tile = blockIdx.y * cam.tiles_x + blockIdx.x;
@@ -168,9 +171,9 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
 
     const float pixx = (float)px, pixy = (float)py;
     const int lane = tid & 31;
-    // pixel-centre rectangle of this warp: 16 columns x 2 rows of the tile, clipped to the image
-    const float strip_x0 = (float)(blockIdx.x * RGS_TILE), strip_y0 = (float)(blockIdx.y * RGS_TILE + 2 * (tid >> 5));
-    const float strip_x1 = fminf(strip_x0 + (RGS_TILE - 1), (float)(cam.W - 1)), strip_y1 = fminf(strip_y0 + 1.0f, (float)(cam.H - 1));
+    // pixel-centre rectangle of this warp's 8x4 block, clipped to the image
+    const float strip_x0 = (float)(blockIdx.x * RGS_TILE + bx * 8), strip_y0 = (float)(blockIdx.y * RGS_TILE + by * 4);
+    const float strip_x1 = fminf(strip_x0 + 7.0f, (float)(cam.W - 1)), strip_y1 = fminf(strip_y0 + 3.0f, (float)(cam.H - 1));
     RgsPixelRay ray;
     rgs_pixel_ray(cam, pixx, pixy, ray);
     RgsPixelState st;
@@ -191,7 +194,7 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
         if (!rgs_mbar_wait(&sm.bar[stage], (b >> 1) & 1, RGS_WAIT_LIMIT)) failed = true;
         pending = (b + 1 < rounds) ? (stage ^ 1) : -1;
         if (!failed) {
-            // Warp-level culling: the 32 lanes test 32 splats of the batch against the warp's 16x2 pixel strip (exact
+            // Warp-level culling: the 32 lanes test 32 splats of the batch against the warp's 8x4 pixel block (exact
             // minimum of the quadratic form over the strip, the rule of rgs_tile_hit), then all lanes walk only the
             // splats that can reach the strip, in order. A skipped splat fails the per-pixel test at every pixel of the
             // strip, so no output bit changes.
@@ -258,7 +261,8 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
     __shared__ __align__(128) BlendSmem sm;
     __shared__ uint32_t sm_slot[2][BLEND_BATCH];
     const int tid = threadIdx.x, lane = tid & 31;
-    const int lx = tid & 15, ly = tid >> 4;
+    const int bx = (tid >> 5) & 1, by = tid >> 6;  // 8x4 block per warp, as in the forward
+    const int lx = bx * 8 + (tid & 7), ly = by * 4 + ((tid >> 3) & 3);
     const int px = blockIdx.x * RGS_TILE + lx, py = blockIdx.y * RGS_TILE + ly;
     const bool inside = px < cam.W && py < cam.H;
     const int tile = blockIdx.y * cam.tiles_x + blockIdx.x;
@@ -306,8 +310,8 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
     int warp_last = last;
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) warp_last = max(warp_last, __shfl_xor_sync(0xffffffffu, warp_last, d));
-    const float strip_x0 = (float)(blockIdx.x * RGS_TILE), strip_y0 = (float)(blockIdx.y * RGS_TILE + 2 * (tid >> 5));
-    const float strip_x1 = fminf(strip_x0 + (RGS_TILE - 1), (float)(cam.W - 1)), strip_y1 = fminf(strip_y0 + 1.0f, (float)(cam.H - 1));
+    const float strip_x0 = (float)(blockIdx.x * RGS_TILE + bx * 8), strip_y0 = (float)(blockIdx.y * RGS_TILE + by * 4);
+    const float strip_x1 = fminf(strip_x0 + 7.0f, (float)(cam.W - 1)), strip_y1 = fminf(strip_y0 + 3.0f, (float)(cam.H - 1));
     for (int b = 0; b < rounds; ++b) {
         const int stage = b & 1;
         const int cnt = min(BLEND_BATCH, total - b * BLEND_BATCH);

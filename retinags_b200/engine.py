@@ -44,6 +44,11 @@ class StepEngine:
         self.tight_rect = tight_rect
         self.borrow = borrow  # optional BorderExchange (parallel/border.py)
         self.timer = PhaseTimer(self.device, enabled=False)
+        # debug aids (the reference has ``pipe.debug``: a device sync after every launch plus a dump of the rasteriser
+        # inputs when it throws, and ``--detect_anomaly`` for NaN hunting; its trainer never switches the former on)
+        self.debug = False            # synchronise and read every task's status word after each phase of a step
+        self.detect_anomaly = False   # after the backward: non-finite loss sums or gradients raise, naming the sub-model
+        self.dump_dir = "."
         self._tasks: dict = {}
         self._grads: dict = {}
         self._closs: dict = {}
@@ -181,6 +186,8 @@ class StepEngine:
                     continue
                 gt = self._gt_rows(p.view, cam, (max(0, b[0] - 5), min(p.H, b[1] + 5)))
                 sums.append(cl.fused_loss_backward(slots[p.view], gslots[p.view], gt, bg, self.lambda_dssim, b[0], b[1]).clone())
+        if self.debug:
+            self._debug_check("forward+loss", cams)
         with T("return_grads"):
             self.transport.return_grads(plans, gslots, local_grad)
         with T("render_backward"):
@@ -188,12 +195,51 @@ class StepEngine:
                 for m, r in zip(p.models, p.ranks):
                     if r == self.rank:
                         self._task(p.view, m).backward(local_grad[p.view][m], self._segments(m, True))
+        if self.debug:
+            self._debug_check("backward", cams)
+        if self.detect_anomaly:
+            self._anomaly_check(sums)
         if self.borrow is not None:
             with T("border_return"):
                 self.borrow.return_grads(self.stores)
         if optimizer_step:
             self.optimizer_step(lrs, plans)
         return StepResult(sums=sums, plans=plans)
+
+    # -- debug aids -------------------------------------------------------------------------------
+    def _debug_check(self, phase: str, cams):
+        """Synchronise, read the status words of all render tasks; on an error write the inputs of the step to
+        ``snapshot_<phase>.dump`` (cameras and parameters of the local sub-models) and re-raise."""
+        try:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            for task in self._tasks.values():
+                if task.cam is not None:
+                    task._record_counters()
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            for task in self._tasks.values():
+                if task.cam is not None:
+                    task.poll()
+            if hasattr(self.transport, "check"):
+                self.transport.check()
+        except Exception:
+            import os
+            path = os.path.join(self.dump_dir, f"snapshot_{phase.replace('+', '_')}.dump")
+            torch.save({"phase": phase, "cameras": [c.pack() for c in cams],
+                        "models": {m: st.records().cpu() for m, st in self.stores.items()}}, path)
+            raise
+
+    def _anomaly_check(self, sums):
+        for i, s in enumerate(sums):
+            if not bool(torch.isfinite(s).all()):
+                raise FloatingPointError(f"non-finite loss sums for view {i} of the batch: {s.tolist()}")
+        for m, st in self.stores.items():
+            g = st.views("grads")
+            for name, t in g.items():
+                if t.numel() and not bool(torch.isfinite(t).all()):
+                    bad = int((~torch.isfinite(t)).any(dim=1).nonzero()[0])
+                    raise FloatingPointError(f"non-finite gradient in sub-model {m}, group '{name}', first at Gaussian {bad}")
 
     def optimizer_step(self, lrs, plans=None):
         with self.timer.phase("adam"):

@@ -275,6 +275,9 @@ class Trainer:
                 self.border = BorderExchange(lo, hi, self.model2rank, self.rank, self.world, self.device, self.group, interval)
         self.engine = StepEngine(self.stores, self.model2rank, self.device, tr, self.opt.lambda_dssim, self.background,
                                  borrow=self.border)
+        self.engine.debug = bool(getattr(self.pipe, "debug", False))
+        self.engine.detect_anomaly = bool(getattr(self.args, "detect_anomaly", False))
+        self.engine.dump_dir = self.model_path
         self.balancer = WorkloadBalancer(self.world, self.model2rank)
 
     def _relation(self, dataset: CameraListDataset, cache_name: str) -> np.ndarray:

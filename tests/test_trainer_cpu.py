@@ -78,3 +78,28 @@ def test_repartition_keeps_every_gaussian(tmp_path):
         assert bool(((p > torch.tensor(lo[m], dtype=torch.float32)) & (p <= torch.tensor(hi[m], dtype=torch.float32))).all())
     counts = [s.count for s in tr.stores.values()]
     assert min(counts) > 0.6 * max(counts)
+
+
+def test_anomaly_check_names_the_submodel_and_debug_mode_polls():
+    """--detect_anomaly / pipe.debug: a NaN parameter is reported with sub-model and group; debug mode checks status words."""
+    import pytest
+    from retinags_b200.bench_session import BenchSession
+    sess = BenchSession("cpu", 0, 1, 4000, 96, 64, batch=1, n_views=2, gt_gaussians=2000, seed=1, sh_degree=1, grid=(32, 32, 1),
+                        bvh_depth=1, scene_kind="uniform")
+    eng = sess.engine
+    eng.debug = True
+    eng.detect_anomaly = True
+    sess.step(0)  # a healthy step passes both checks
+    # the rasteriser itself is robust against NaN parameters (such Gaussians are culled); a NaN target is not survivable
+    sess.cams[1].image[:, 10:20, 10:20] = float("nan")
+    with pytest.raises(FloatingPointError) as err:
+        sess.step(1)
+    assert "non-finite loss sums" in str(err.value)
+    victim = sorted(sess.stores)[1]
+    st = sess.stores[victim]
+    for other in sess.stores.values():
+        other.zero_grad()  # the failed step left its NaN gradients behind
+    st.views("grads")["scale"][3, 1] = float("inf")
+    with pytest.raises(FloatingPointError) as err:
+        eng._anomaly_check([])
+    assert f"sub-model {victim}" in str(err.value) and "'scale'" in str(err.value) and "Gaussian 3" in str(err.value)
