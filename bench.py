@@ -184,6 +184,9 @@ def run_own(args):
         if args.trace:
             sess.engine.timer.export_chrome_trace(f"{args.trace}.rank{rank}.json", rank)
         sess.engine.timer.enabled = False
+    # share of this rank's Gaussians that have received a gradient so far (Adam streams only those rows)
+    total_rows = sum(st.count for st in sess.stores.values())
+    live_rows = round(sum(int(st.active[:st.count].sum()) for st in sess.stores.values()) / max(total_rows, 1), 4)
     if rank == 0:
         value = args.steps * args.batch / (ms / 1e3)
         out = {
@@ -197,8 +200,9 @@ def run_own(args):
                        "parallelism": f"spatial-mp{world}", "transport": sess.transport_name,
                        "border_selection_refresh_steps": sess.borrow_refresh if sess.n_models > 1 else None,
                        "l2": "inputs larger than L2 (parameter blocks of >= 1.8 GB per GPU are streamed every step)",
-                       "visible_splats_per_view": sess.last_info.get("n_vis"),
-                       "instances_per_view": sess.last_info.get("n_inst"), "overflow_in_timed_region": overflow},
+                       "visible_splats_per_step_rank0": sess.last_info.get("n_vis"),
+                       "tile_instances_per_step_rank0": sess.last_info.get("n_inst"),
+                       "rows_with_adam_moments_rank0": live_rows, "overflow_in_timed_region": overflow},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "phases_ms_per_step_max_over_ranks": phases,
         }
         print(json.dumps(out), flush=True)
