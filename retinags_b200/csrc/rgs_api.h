@@ -43,6 +43,7 @@ struct RgsSegment {
 #define RGS_CNT_OVERFLOW 2  // set to 1 when CNT_INST exceeded the capacity (instances were dropped)
 #define RGS_CNT_STATUS 3    // error/status word of bounded waits (0 = ok)
 #define RGS_CNT_CAND 4      // candidates that survived the conservative cull (two-phase projection)
+#define RGS_CNT_INST2 5     // instances of the second depth slab (two-slab binning)
 #define RGS_CNT_WORDS 8
 
 // lr table of the fused Adam: columns of the 59-float record grouped by learning rate

@@ -607,12 +607,15 @@ __global__ void rgs_bs_tile_ranges_kernel(const uint32_t* __restrict__ keys, con
 
 // Tile ranges by binary search in the sorted tile keys: one thread per tile, ~2 log2(n) probes, instead of a pass
 // over all keys (340 MB per view at 85 M instances).
+// `which`: counter word holding the number of sorted keys; `base` is added to the indices written (the keys of a
+// depth slab start `base` elements into the instance buffers).
 __global__ void __launch_bounds__(128) rgs_bs_tile_ranges_search_kernel(const uint32_t* __restrict__ keys,
                                                                         const uint32_t* __restrict__ counters, uint32_t cap,
-                                                                        int2* __restrict__ ranges, uint32_t num_tiles) {
+                                                                        int2* __restrict__ ranges, uint32_t num_tiles,
+                                                                        int which, uint32_t base) {
     const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= num_tiles) return;
-    const uint32_t n = bs_count(counters, RGS_CNT_INST, cap);
+    const uint32_t n = bs_count(counters, which, cap);
     uint32_t lo = 0, hi = n;  // first index with key >= t
     while (lo < hi) {
         const uint32_t mid = lo + ((hi - lo) >> 1);
@@ -624,7 +627,220 @@ __global__ void __launch_bounds__(128) rgs_bs_tile_ranges_search_kernel(const ui
         const uint32_t mid = lo + ((hi - lo) >> 1);
         if (keys[mid] <= t) lo = mid + 1; else hi = mid;
     }
-    ranges[t] = lo > first ? make_int2((int)first, (int)lo) : make_int2(0, 0);
+    ranges[t] = lo > first ? make_int2((int)(base + first), (int)(base + lo)) : make_int2(0, 0);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Two-slab binning. In a dense scene most tiles are saturated (every pixel below the transmittance threshold) after
+// the nearest splats, yet the single-pass pipeline emits and sorts the instances of all splats. Here the depth-ordered
+// splats are cut in two slabs: the instances of the near slab are emitted, sorted and blended first; the blend marks
+// the tiles in which every pixel is done, and the far slab emits instances only for the other tiles. The count of
+// such tiles inside a splat's rectangle is four reads of a summed-area table, so splats over saturated regions cost
+// a few loads and no instance. Nothing that could change a pixel is skipped: the output is bit-identical.
+// ---------------------------------------------------------------------------------------------
+// segments [s0,s1) of EM_SEG depth-ordered splats that belong to `slab` (0 = near, 1 = far); frac256/256 of the
+// splats (rounded down to whole segments) form the near slab
+__device__ __forceinline__ void slab_segments(uint32_t n, uint32_t frac256, int slab, uint32_t& s0, uint32_t& s1) {
+    const uint32_t nseg = (n + EM_SEG - 1) / EM_SEG;
+    uint32_t split = (uint32_t)(((unsigned long long)n * frac256) >> 8) / EM_SEG;
+    if (split > nseg) split = nseg;
+    s0 = slab == 0 ? 0u : split;
+    s1 = slab == 0 ? split : nseg;
+}
+
+__global__ void __launch_bounds__(256) rgs_slab_count_kernel(const uint32_t* __restrict__ order,
+                                                             const uint32_t* __restrict__ slot_cnt,
+                                                             const uint32_t* __restrict__ counters, uint32_t cap_vis,
+                                                             uint32_t frac256, int slab, uint32_t* __restrict__ seg_sums) {
+    __shared__ uint32_t red[8];
+    const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);
+    uint32_t s0, s1;
+    slab_segments(n, frac256, slab, s0, s1);
+    for (uint32_t s = s0 + blockIdx.x; s < s1; s += gridDim.x) {
+        uint32_t sum = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t i = s * EM_SEG + k * 256 + threadIdx.x;
+            if (i < n) sum += slot_cnt[order[i]];
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t t = 0;
+            for (int w = 0; w < 8; ++w) t += red[w];
+            seg_sums[s] = t;
+        }
+        __syncthreads();
+    }
+}
+
+// one CTA: exclusive scan of seg_sums[s0..s1) in place (relative to the slab's first instance); the slab's total goes
+// to counters[which], exceeding region_cap raises the overflow flag
+__global__ void __launch_bounds__(1024) rgs_slab_scan_kernel(uint32_t* __restrict__ seg_sums, uint32_t* __restrict__ counters,
+                                                             uint32_t cap_vis, uint32_t frac256, int slab, int which,
+                                                             uint32_t region_cap) {
+    __shared__ uint32_t warp_tot[32];
+    __shared__ unsigned long long carry_s;
+    const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);
+    uint32_t s0, s1;
+    slab_segments(n, frac256, slab, s0, s1);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry_s = 0;
+    __syncthreads();
+    for (uint32_t start = s0; start < s1; start += 1024) {
+        const uint32_t i = start + threadIdx.x;
+        const uint32_t v = i < s1 ? seg_sums[i] : 0u;
+        uint32_t incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += t;
+        }
+        if (lane == 31) warp_tot[wid] = incl;
+        __syncthreads();
+        uint32_t wbase = 0;
+        for (int w = 0; w < wid; ++w) wbase += warp_tot[w];
+        const unsigned long long excl = carry_s + wbase + incl - v;
+        if (i < s1) seg_sums[i] = excl > 0xffffffffull ? 0xffffffffu : (uint32_t)excl;
+        __syncthreads();
+        if (threadIdx.x == 1023) carry_s = excl + v;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const unsigned long long tot = carry_s;
+        counters[which] = tot > 0xffffffffull ? 0xffffffffu : (uint32_t)tot;
+        if (tot > (unsigned long long)region_cap) atomicExch(&counters[RGS_CNT_OVERFLOW], 1u);
+    }
+}
+
+// Emission of one slab. tile_keys / vals point at the slab's region; with tile_done only tiles that are not marked
+// are written (slot_cnt holds exactly that count for the slab's splats).
+__global__ void __launch_bounds__(256) rgs_slab_emit_kernel(const __grid_constant__ RgsCamera cam,
+                                                            const uint32_t* __restrict__ order,
+                                                            const uint2* __restrict__ slot_rect,
+                                                            const uint32_t* __restrict__ slot_cnt,
+                                                            const uint32_t* __restrict__ counters, uint32_t cap_vis,
+                                                            uint32_t frac256, int slab, const uint32_t* __restrict__ seg_excl,
+                                                            uint32_t* __restrict__ tile_keys, uint32_t* __restrict__ vals,
+                                                            uint32_t region_cap, const uint8_t* __restrict__ tile_done) {
+    __shared__ uint32_t warp_tot[8];
+    __shared__ uint32_t s_slot[EM_SEG], s_base[EM_SEG];
+    __shared__ uint2 s_rect[EM_SEG];
+    const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);  // 0 after an overflow: nothing is written
+    uint32_t s0, s1;
+    slab_segments(n, frac256, slab, s0, s1);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int tiles_x = cam.tiles_x;
+    for (uint32_t s = s0 + blockIdx.x; s < s1; s += gridDim.x) {
+        uint32_t slot[4], cnt[4];
+        uint2 rect[4];
+        uint32_t mine = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t i = s * EM_SEG + threadIdx.x * 4 + k;
+            if (i < n) { slot[k] = order[i]; rect[k] = slot_rect[slot[k]]; cnt[k] = slot_cnt[slot[k]]; }
+            else { slot[k] = 0; rect[k] = make_uint2(0, 0); cnt[k] = 0; }
+            mine += cnt[k];
+        }
+        uint32_t incl = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += t;
+        }
+        if (lane == 31) warp_tot[wid] = incl;
+        __syncthreads();
+        uint32_t wbase = 0;
+        for (int w = 0; w < wid; ++w) wbase += warp_tot[w];
+        uint32_t base = seg_excl[s] + wbase + incl - mine;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int e = threadIdx.x * 4 + k;
+            s_slot[e] = slot[k]; s_base[e] = base;
+            s_rect[e] = cnt[k] ? rect[k] : make_uint2(0, 0);
+            base += cnt[k];
+        }
+        __syncthreads();
+        for (int j = 0; j < EM_SEG / 8; ++j) {
+            const int e = wid * (EM_SEG / 8) + j;
+            const uint2 r = s_rect[e];
+            const uint32_t c = rect_count(r);
+            if (c == 0) continue;
+            const int x0 = r.x & 0xffff, y0 = r.x >> 16, w = (int)(r.y & 0xffff) - x0;
+            const uint32_t sl = s_slot[e];
+            uint32_t o = s_base[e];
+            if (!tile_done) {
+                for (uint32_t t = lane; t < c; t += 32) {
+                    const uint32_t ty = t / (uint32_t)w, tx = t - ty * (uint32_t)w;
+                    if (o + t < region_cap) { tile_keys[o + t] = (uint32_t)((y0 + (int)ty) * tiles_x + x0 + (int)tx); vals[o + t] = sl; }
+                }
+                continue;
+            }
+            for (uint32_t t0 = 0; t0 < c; t0 += 32) {
+                const uint32_t t = t0 + lane;
+                bool hit = false;
+                uint32_t key = 0;
+                if (t < c) {
+                    const uint32_t ty = t / (uint32_t)w, tx = t - ty * (uint32_t)w;
+                    key = (uint32_t)((y0 + (int)ty) * tiles_x + x0 + (int)tx);
+                    hit = tile_done[key] == 0;
+                }
+                const uint32_t m = __ballot_sync(0xffffffffu, hit);
+                if (hit) {
+                    const uint32_t dst = o + __popc(m & ((1u << lane) - 1u));
+                    if (dst < region_cap) { tile_keys[dst] = key; vals[dst] = sl; }
+                }
+                o += __popc(m);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// Summed-area table of the tiles that are NOT done: sat[(y+1)*(tiles_x+1) + (x+1)] = number of such tiles in
+// [0,x] x [0,y]. One CTA: rows first, then columns.
+__global__ void __launch_bounds__(1024) rgs_slab_sat_kernel(const uint8_t* __restrict__ tile_done, int tiles_x, int tiles_y,
+                                                            uint32_t* __restrict__ sat) {
+    const int pitch = tiles_x + 1;
+    for (int x = threadIdx.x; x <= tiles_x; x += blockDim.x) sat[x] = 0u;
+    for (int y = threadIdx.x; y < tiles_y; y += blockDim.x) {
+        uint32_t run = 0;
+        sat[(y + 1) * pitch] = 0u;
+        for (int x = 0; x < tiles_x; ++x) {
+            run += tile_done[y * tiles_x + x] ? 0u : 1u;
+            sat[(y + 1) * pitch + x + 1] = run;
+        }
+    }
+    __syncthreads();
+    for (int x = threadIdx.x; x < tiles_x; x += blockDim.x) {
+        uint32_t run = 0;
+        for (int y = 0; y < tiles_y; ++y) {
+            run += sat[(y + 1) * pitch + x + 1];
+            sat[(y + 1) * pitch + x + 1] = run;
+        }
+    }
+}
+
+// slot_cnt of every splat of the far slab = number of not-done tiles in its rectangle
+__global__ void __launch_bounds__(256) rgs_slab_filtered_count_kernel(const uint32_t* __restrict__ order,
+                                                                      const uint2* __restrict__ slot_rect,
+                                                                      const uint32_t* __restrict__ counters, uint32_t cap_vis,
+                                                                      uint32_t frac256, const uint32_t* __restrict__ sat,
+                                                                      int tiles_x, uint32_t* __restrict__ slot_cnt) {
+    const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);
+    uint32_t s0, s1;
+    slab_segments(n, frac256, 1, s0, s1);
+    const int pitch = tiles_x + 1;
+    for (uint32_t i = s0 * EM_SEG + blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const uint32_t slot = order[i];
+        const uint2 r = slot_rect[slot];
+        const int x0 = r.x & 0xffff, y0 = r.x >> 16, x1 = r.y & 0xffff, y1 = r.y >> 16;
+        uint32_t c = 0;
+        if (x1 > x0 && y1 > y0) c = sat[y1 * pitch + x1] - sat[y0 * pitch + x1] - sat[y1 * pitch + x0] + sat[y0 * pitch + x0];
+        slot_cnt[slot] = c;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -808,7 +1024,7 @@ static void bs_pass(const uint32_t* kin, const uint32_t* vin, uint32_t* kout, ui
     const uint32_t nch = (cap + chunk - 1) / chunk;
     const unsigned grid = nch < 1u ? 1u : (nch < 148u * 8u ? nch : 148u * 8u);
     // which == CNT_INST is the tile sort: its upper digit repeats inside a warp, everything else is close to random
-    const int aggregate = (which == RGS_CNT_INST && shift >= 8) ? 1 : 0;
+    const int aggregate = ((which == RGS_CNT_INST || which == RGS_CNT_INST2) && shift >= 8) ? 1 : 0;
     rgs_bs_hist_kernel<ITEMS><<<grid, BS_THREADS, 0, st>>>(kin, cnt, which, cap, shift, hist, nchunks_cap, aggregate);
     rgs_bs_scan_kernel<<<256, 256, 0, st>>>(hist, totals, cnt, which, cap, nchunks_cap, chunk);
     rgs_bs_scatter_kernel<ITEMS><<<grid, BS_THREADS, 0, st>>>(kin, vin, kout, vout, cnt, which, cap, shift, hist, totals,
@@ -970,12 +1186,70 @@ int rgs_cuda_bin_instances(const RgsCamera* cam, const RgsSplat* splats, const u
     const bool in_tmp = (tv != inst_vals);
     if (!in_tmp) {  // nothing to copy back: find the ranges without reading every key
         rgs_bs_tile_ranges_search_kernel<<<(unsigned)((num_tiles + 127) / 128), 128, 0, st>>>(
-            tk, cnt, (uint32_t)cap_inst, reinterpret_cast<int2*>(ranges), (uint32_t)num_tiles);
+            tk, cnt, (uint32_t)cap_inst, reinterpret_cast<int2*>(ranges), (uint32_t)num_tiles, RGS_CNT_INST, 0u);
         return (int)cudaGetLastError();
     }
     RGS_CUDA_CHECK(cudaMemsetAsync(ranges, 0, (size_t)num_tiles * 8, st));
     rgs_bs_tile_ranges_kernel<<<148 * 8, 256, 0, st>>>(tk, cnt, (uint32_t)cap_inst, reinterpret_cast<int2*>(ranges),
                                                        (uint32_t)num_tiles, in_tmp ? tv : nullptr, in_tmp ? inst_vals : nullptr);
+    return (int)cudaGetLastError();
+}
+
+// Two-slab binning, one call per slab (see the comment above rgs_slab_count_kernel).
+//   slab 0: depth sort of all visible slots, then emission + tile sort of the near slab (frac256/256 of the splats)
+//           into the first region_cap elements of the instance buffers; count -> counters[RGS_CNT_INST].
+//   slab 1: tile_done (one byte per tile, written by the blend of slab 0) -> summed-area table -> filtered counts,
+//           emission + tile sort of the far slab into the region starting at region_off; count -> counters[RGS_CNT_INST2];
+//           ranges hold absolute indices into inst_vals.
+// sat: (tiles_x + 1) * (tiles_y + 1) words. Only tile grids of at most 65536 tiles and tight_rect < 2.
+int rgs_cuda_bin_slab(const RgsCamera* cam, const uint32_t* slot_depth, const uint32_t* slot_rect, uint32_t* slot_cnt,
+                      int64_t cap_vis, uint32_t* vis_ka, uint32_t* vis_va, uint32_t* vis_kb, uint32_t* vis_vb,
+                      uint32_t* inst_keys, uint32_t* inst_vals, uint32_t* inst_keys_tmp, uint32_t* inst_vals_tmp,
+                      int64_t region_off, int64_t region_cap, int32_t* counters, int64_t num_tiles, int32_t* ranges,
+                      uint32_t* scratch, int64_t scratch_cap_inst, int64_t slab, int64_t frac256, const uint8_t* tile_done,
+                      uint32_t* sat, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (num_tiles > 65536 || cam->tight_rect >= 2 || slab < 0 || slab > 1) return 15;
+    if (region_off + region_cap > 0xfffffe00ll || frac256 < 0 || frac256 > 256) return 10;
+    uint32_t* cnt = reinterpret_cast<uint32_t*>(counters);
+    const int64_t cap = cap_vis > scratch_cap_inst ? cap_vis : scratch_cap_inst;
+    uint32_t* hist = scratch;
+    uint32_t* totals = scratch + 256 * (size_t)chunks_of(cap);
+    uint32_t* seg_sums = totals + 256;
+    uint32_t* order = vis_va;  // where four ping-pong passes leave the sorted values
+    if (slab == 0) {
+        uint32_t *dk, *ord;
+        bs_sort(slot_depth, vis_ka, vis_va, vis_kb, vis_vb, cnt, RGS_CNT_VIS, (uint32_t)cap_vis, 4, hist, totals, 1, st, &dk, &ord);
+        if (ord != order) return 16;
+    }
+    const int which = slab == 0 ? RGS_CNT_INST : RGS_CNT_INST2;
+    const uint2* rects = reinterpret_cast<const uint2*>(slot_rect);
+    const uint32_t nseg_cap = (uint32_t)((cap_vis + EM_SEG - 1) / EM_SEG);
+    const unsigned egrid = nseg_cap < 148u * 8u ? (nseg_cap ? nseg_cap : 1u) : 148u * 8u;
+    if (slab == 1) {
+        rgs_slab_sat_kernel<<<1, 1024, 0, st>>>(tile_done, cam->tiles_x, cam->tiles_y, sat);
+        rgs_slab_filtered_count_kernel<<<148 * 8, 256, 0, st>>>(order, rects, cnt, (uint32_t)cap_vis, (uint32_t)frac256, sat,
+                                                               cam->tiles_x, slot_cnt);
+    }
+    rgs_slab_count_kernel<<<egrid, 256, 0, st>>>(order, slot_cnt, cnt, (uint32_t)cap_vis, (uint32_t)frac256, (int)slab, seg_sums);
+    rgs_slab_scan_kernel<<<1, 1024, 0, st>>>(seg_sums, cnt, (uint32_t)cap_vis, (uint32_t)frac256, (int)slab, which,
+                                             (uint32_t)region_cap);
+    uint32_t* rk = inst_keys + region_off;
+    uint32_t* rv = inst_vals + region_off;
+    rgs_slab_emit_kernel<<<egrid, 256, 0, st>>>(*cam, order, rects, slot_cnt, cnt, (uint32_t)cap_vis, (uint32_t)frac256,
+                                                (int)slab, seg_sums, rk, rv, (uint32_t)region_cap,
+                                                slab == 1 ? tile_done : nullptr);
+    int tile_bits = 0;
+    while ((1ll << tile_bits) < num_tiles) ++tile_bits;
+    const int npass = tile_bits <= 8 ? 1 : 2;
+    uint32_t *tk, *tv;
+    bs_sort(rk, rk, rv, inst_keys_tmp + region_off, inst_vals_tmp + region_off, cnt, which, (uint32_t)region_cap, npass, hist,
+            totals, 0, st, &tk, &tv);
+    if (tv != rv) {  // a single pass leaves the result in the second buffer
+        RGS_CUDA_CHECK(cudaMemcpyAsync(rv, tv, (size_t)region_cap * 4, cudaMemcpyDeviceToDevice, st));
+    }
+    rgs_bs_tile_ranges_search_kernel<<<(unsigned)((num_tiles + 127) / 128), 128, 0, st>>>(
+        tk, cnt, (uint32_t)region_cap, reinterpret_cast<int2*>(ranges), (uint32_t)num_tiles, which, (uint32_t)region_off);
     return (int)cudaGetLastError();
 }
 

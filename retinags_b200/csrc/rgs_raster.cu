@@ -118,15 +118,27 @@ __device__ __forceinline__ uint32_t checked_slot(uint32_t slot, uint32_t n_vis, 
 }
 
 // Tile range clipped to [0, n_inst]; an inverted or out-of-range record is reported and treated as empty.
-__device__ __forceinline__ int2 checked_range(int2 r, uint32_t* counters) {
+__device__ __forceinline__ int2 checked_range(int2 r, uint32_t* counters, int which = RGS_CNT_INST, uint32_t base = 0u) {
     if (counters[RGS_CNT_OVERFLOW]) return make_int2(0, 0);
-    const uint32_t n_inst = counters[RGS_CNT_INST];
-    if (r.x < 0 || r.y < r.x || (uint32_t)r.y > n_inst) {
+    if (r.x == 0 && r.y == 0) return r;  // empty
+    const uint32_t end = base + counters[which];
+    if (r.x < 0 || r.y < r.x || (uint32_t)r.x < base || (uint32_t)r.y > end) {
         atomicOr(&counters[RGS_CNT_STATUS], RGS_STATUS_BAD_INDEX);
         return make_int2(0, 0);
     }
     return r;
 }
+
+// Two-slab rendering (see rgs_binning.cu): how a blend launch relates to the slabs.
+#define RGS_SLAB_SINGLE 0  // one list per tile, the whole render
+#define RGS_SLAB_NEAR 1    // first of two launches: leaves the pixel state in the output buffers, marks finished tiles
+#define RGS_SLAB_FAR 2     // second launch: resumes from that state with the far slab's list
+struct RgsSlabArgs {
+    const int2* ranges_b;   // per-tile ranges of the far slab (absolute indices into vals), null without slabs
+    uint8_t* tile_done;     // one byte per tile: every pixel of the tile is finished after the near slab
+    uint32_t base_b;        // first element of the far slab's region in vals
+    int mode;
+};
 
 __device__ __forceinline__ void blend_issue(BlendSmem& sm, int stage, const RgsSplat* __restrict__ splats,
                                             const uint32_t* __restrict__ vals, int first, int count, bool reverse,
@@ -152,7 +164,8 @@ struct RgsPushPlan {
 __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
     const __grid_constant__ RgsCamera cam, const int2* __restrict__ ranges, const uint32_t* __restrict__ vals,
     const RgsSplat* __restrict__ splats, float4* __restrict__ out, float* __restrict__ depth,
-    int32_t* __restrict__ n_contrib, uint32_t* __restrict__ counters, const __grid_constant__ RgsPushPlan push) {
+    int32_t* __restrict__ n_contrib, uint32_t* __restrict__ counters, const __grid_constant__ RgsPushPlan push,
+    const __grid_constant__ RgsSlabArgs slab) {
     __shared__ __align__(128) BlendSmem sm;
     const int tid = threadIdx.x;
     // a warp owns a compact 8x4 block of the tile (2 x 4 blocks per tile): the smaller the extent of the warp's
@@ -162,7 +175,11 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
     const int px = blockIdx.x * RGS_TILE + lx, py = blockIdx.y * RGS_TILE + ly;
     const bool inside = px < cam.W && py < cam.H;
     const int tile = blockIdx.y * cam.tiles_x + blockIdx.x;
-    const int2 range = checked_range(ranges[tile], counters);
+    const int2 range_a = checked_range(ranges[tile], counters);
+    const int2 range = slab.mode == RGS_SLAB_FAR ? checked_range(slab.ranges_b[tile], counters, RGS_CNT_INST2, slab.base_b)
+                                                 : range_a;
+    // position of this launch's first instance in the tile's whole (near + far) list
+    const int first_contrib = slab.mode == RGS_SLAB_FAR ? range_a.y - range_a.x : 0;
     const uint32_t n_vis = counters[RGS_CNT_VIS];
     const int total = range.y - range.x;
     const int rounds = (total + BLEND_BATCH - 1) / BLEND_BATCH;
@@ -179,6 +196,15 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
     RgsPixelState st;
     rgs_pixel_init(st);
     st.done = !inside;
+    if (slab.mode == RGS_SLAB_FAR && inside) {  // resume where the near slab stopped
+        const int64_t pid = (int64_t)py * cam.W + px;
+        const float4 o = out[pid];
+        st.C[0] = o.x; st.C[1] = o.y; st.C[2] = o.z; st.T = o.w;
+        if (depth) st.D = depth[pid];
+        const uint32_t nc = (uint32_t)n_contrib[pid];
+        st.last = (int)(nc & 0x7fffffffu);
+        st.done = (int)(nc >> 31);
+    }
 
     if (rounds > 0) blend_issue(sm, 0, splats, vals, range.x, min(BLEND_BATCH, total), false, range.y, n_vis, counters);
     int pending = rounds > 0 ? 0 : -1;  // stage with a copy in flight that has not been waited for
@@ -211,7 +237,7 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
                     const int j = g0 + __ffs(m) - 1;
                     m &= m - 1;
                     if (!st.done) {
-                        st.contributor = b * BLEND_BATCH + j;
+                        st.contributor = first_contrib + b * BLEND_BATCH + j;
                         rgs_blend_fwd_step(cam, ray, pixx, pixy, sm.buf[stage][j], st);
                     }
                 }
@@ -225,12 +251,18 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
         }
     }
     if (failed && tid == 0) atomicOr(&counters[RGS_CNT_STATUS], 1u);
+    if (slab.mode == RGS_SLAB_NEAR) {
+        // a tile whose every pixel is finished needs no instance of the far slab
+        const int all_done = __syncthreads_and(st.done);
+        if (tid == 0) slab.tile_done[tile] = all_done ? 1 : 0;
+    }
     if (inside) {
         const int64_t pid = (int64_t)py * cam.W + px;
         const float4 val = make_float4(st.C[0], st.C[1], st.C[2], st.T);
         out[pid] = val;
         if (depth) depth[pid] = st.D;
-        n_contrib[pid] = st.last;
+        // between the two launches the finished flag travels in the top bit
+        n_contrib[pid] = slab.mode == RGS_SLAB_NEAR ? (int32_t)((uint32_t)st.last | ((uint32_t)(st.done ? 1 : 0) << 31)) : st.last;
         // epilogue push: the finished pixel goes straight into the slot of every rank that composites
         // this row (plain stores; the destination may be another GPU's memory mapped over NVLink)
         for (int o = 0; o < push.n; ++o)
@@ -257,7 +289,7 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
     const __grid_constant__ RgsCamera cam, const int2* __restrict__ ranges, const uint32_t* __restrict__ vals,
     const RgsSplat* __restrict__ splats, const float4* __restrict__ out, const int32_t* __restrict__ n_contrib,
     const float4* __restrict__ grad_out, RgsSplatGrad* __restrict__ splat_grads, uint32_t* __restrict__ counters,
-    unsigned long long* __restrict__ fixed_acc) {
+    unsigned long long* __restrict__ fixed_acc, const __grid_constant__ RgsSlabArgs slab) {
     __shared__ __align__(128) BlendSmem sm;
     __shared__ uint32_t sm_slot[2][BLEND_BATCH];
     const int tid = threadIdx.x, lane = tid & 31;
@@ -266,7 +298,11 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
     const int px = blockIdx.x * RGS_TILE + lx, py = blockIdx.y * RGS_TILE + ly;
     const bool inside = px < cam.W && py < cam.H;
     const int tile = blockIdx.y * cam.tiles_x + blockIdx.x;
+    // the tile's list is the near slab's range followed by the far slab's (empty without slabs)
     const int2 range = checked_range(ranges[tile], counters);
+    const int2 range_b = slab.ranges_b ? checked_range(slab.ranges_b[tile], counters, RGS_CNT_INST2, slab.base_b)
+                                       : make_int2(0, 0);
+    const int len_a = range.y - range.x, len_b = range_b.y - range_b.x;
     const uint32_t n_vis = counters[RGS_CNT_VIS];
     const int64_t pid = (int64_t)py * cam.W + px;
     const int last = inside ? n_contrib[pid] : 0;
@@ -281,8 +317,7 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
         if (lane == 0) atomicMax(&sm_max_last, m);
     }
     __syncthreads();
-    const int total = min(sm_max_last, range.y - range.x);
-    const int range_end = range.x + total;  // replay [range.x, range_end) back to front
+    const int total = min(sm_max_last, len_a + len_b);  // replay positions [0, total) of the list back to front
     const int rounds = (total + BLEND_BATCH - 1) / BLEND_BATCH;
 
     const float pixx = (float)px, pixy = (float)py;
@@ -300,7 +335,9 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
         const int cnt = min(BLEND_BATCH, total - b * BLEND_BATCH);
         if (tid == 0) rgs_mbar_expect_tx(&sm.bar[stage], (uint32_t)cnt * (uint32_t)sizeof(RgsSplat));
         if (tid < cnt) {
-            const uint32_t slot = checked_slot(vals[range_end - 1 - b * BLEND_BATCH - tid], n_vis, counters);
+            const int v = total - 1 - b * BLEND_BATCH - tid;  // position in the concatenated list
+            const int idx = v < len_a ? range.x + v : range_b.x + (v - len_a);
+            const uint32_t slot = checked_slot(vals[idx], n_vis, counters);
             sm_slot[stage][tid] = slot;
             rgs_bulk_g2s(&sm.buf[stage][tid], splats + slot, (uint32_t)sizeof(RgsSplat), &sm.bar[stage]);
         }
@@ -526,7 +563,7 @@ int rgs_cuda_blend_fwd(const RgsCamera* cam, const int32_t* ranges, const uint32
     push.n = 0;
     rgs_blend_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
         *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<float4*>(out), depth, n_contrib,
-        reinterpret_cast<uint32_t*>(counters), push);
+        reinterpret_cast<uint32_t*>(counters), push, RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE});
     return (int)cudaGetLastError();
 }
 
@@ -542,7 +579,25 @@ int rgs_cuda_blend_fwd_push(const RgsCamera* cam, const int32_t* ranges, const u
     for (int o = 0; o < n_dst; ++o) { push.row0[o] = row0[o]; push.row1[o] = row1[o]; push.dst[o] = reinterpret_cast<float4*>(dst[o]); }
     rgs_blend_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
         *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<float4*>(out), depth, n_contrib,
-        reinterpret_cast<uint32_t*>(counters), push);
+        reinterpret_cast<uint32_t*>(counters), push, RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE});
+    return (int)cudaGetLastError();
+}
+
+// One launch of the two-slab forward. mode 1 (near slab): ranges_a is walked, tile_done is written, no push.
+// mode 2 (far slab): resumes from out / depth / n_contrib, walks ranges_b (indices from base_b on), pushes.
+int rgs_cuda_blend_fwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const int32_t* ranges_b, const uint32_t* vals,
+                            const RgsSplat* splats, float* out, float* depth, int32_t* n_contrib, int32_t* counters,
+                            uint8_t* tile_done, int64_t base_b, int64_t mode, int64_t n_dst, const int32_t* row0,
+                            const int32_t* row1, float* const* dst, void* stream) {
+    if (n_dst < 0 || n_dst > RGS_MAX_PUSH || (mode != RGS_SLAB_NEAR && mode != RGS_SLAB_FAR)) return 15;
+    dim3 grid(cam->tiles_x, cam->tiles_y);
+    RgsPushPlan push;
+    push.n = mode == RGS_SLAB_FAR ? (int)n_dst : 0;
+    for (int o = 0; o < push.n; ++o) { push.row0[o] = row0[o]; push.row1[o] = row1[o]; push.dst[o] = reinterpret_cast<float4*>(dst[o]); }
+    rgs_blend_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
+        *cam, reinterpret_cast<const int2*>(ranges_a), vals, splats, reinterpret_cast<float4*>(out), depth, n_contrib,
+        reinterpret_cast<uint32_t*>(counters), push,
+        RgsSlabArgs{reinterpret_cast<const int2*>(ranges_b), tile_done, (uint32_t)base_b, (int)mode});
     return (int)cudaGetLastError();
 }
 
@@ -552,7 +607,33 @@ int rgs_cuda_blend_bwd(const RgsCamera* cam, const int32_t* ranges, const uint32
     dim3 grid(cam->tiles_x, cam->tiles_y);
     rgs_blend_bwd_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(
         *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
-        reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters), nullptr);
+        reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters), nullptr,
+        RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE});
+    return (int)cudaGetLastError();
+}
+
+// Backward of a two-slab render: the list of a tile is ranges_a followed by ranges_b. fixed_acc (nullable) selects the
+// order-independent accumulation (see rgs_cuda_blend_bwd_fixed).
+int rgs_cuda_blend_bwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const int32_t* ranges_b, int64_t base_b,
+                            const uint32_t* vals, const RgsSplat* splats, const float* out, const int32_t* n_contrib,
+                            const float* grad_out, RgsSplatGrad* splat_grads, int32_t* counters, int64_t* fixed_acc,
+                            int64_t cap_vis, void* stream) {
+    dim3 grid(cam->tiles_x, cam->tiles_y);
+    const RgsSlabArgs slab{reinterpret_cast<const int2*>(ranges_b), nullptr, (uint32_t)base_b, RGS_SLAB_SINGLE};
+    if (!fixed_acc) {
+        rgs_blend_bwd_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(
+            *cam, reinterpret_cast<const int2*>(ranges_a), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
+            reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters), nullptr, slab);
+        return (int)cudaGetLastError();
+    }
+    rgs_blend_bwd_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        *cam, reinterpret_cast<const int2*>(ranges_a), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
+        reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters),
+        reinterpret_cast<unsigned long long*>(fixed_acc), slab);
+    const int64_t want = (cap_vis * 9 + 255) / 256;
+    const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > 148 * 32 ? 148 * 32 : want));
+    rgs_fixed_fold_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<long long*>(fixed_acc), cap_vis,
+                                                                   reinterpret_cast<const uint32_t*>(counters), splat_grads);
     return (int)cudaGetLastError();
 }
 
@@ -566,7 +647,7 @@ int rgs_cuda_blend_bwd_fixed(const RgsCamera* cam, const int32_t* ranges, const 
     rgs_blend_bwd_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(
         *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
         reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters),
-        reinterpret_cast<unsigned long long*>(fixed_acc));
+        reinterpret_cast<unsigned long long*>(fixed_acc), RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE});
     const int64_t want = (cap_vis * 9 + 255) / 256;
     const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > 148 * 32 ? 148 * 32 : want));
     rgs_fixed_fold_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<long long*>(fixed_acc), cap_vis,

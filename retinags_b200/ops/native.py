@@ -94,6 +94,7 @@ class RgsDensifyCfg(ctypes.Structure):
 SURGERY_BLOCK = 1024
 
 CNT_VIS, CNT_INST, CNT_OVERFLOW, CNT_STATUS, CNT_WORDS = 0, 1, 2, 3, 8
+CNT_INST2 = 5  # instances of the far slab (two-slab binning)
 SPLAT_FLOATS = 12
 
 
@@ -153,7 +154,7 @@ def stream_ptr(device: torch.device):
 
 # kernels launched by one call of an entry point (the radix sort's count depends on the tile count)
 _KERNELS = {"project_slots": 1, "project_slots2": 2, "project_emit": 1, "blend_fwd": 1, "blend_bwd": 1, "geom_bwd": 1, "scatter_radii": 1, "adam": 1,
-            "composite_fwd": 1, "composite_bwd": 1, "ssim_fwd": 1, "ssim_bwd": 1, "densify_classify": 2}
+            "composite_fwd": 1, "composite_bwd": 1, "ssim_fwd": 1, "ssim_bwd": 1, "densify_classify": 2, "bin_slab": 14, "blend_fwd_slab": 1, "blend_bwd_slab": 1}
 _LAUNCHES = [0]
 
 

@@ -22,7 +22,7 @@ import torch
 
 from ..data.cameras import Camera
 from . import native
-from .native import CNT_INST, CNT_OVERFLOW, CNT_STATUS, CNT_VIS, CNT_WORDS, RgsCamera, RgsSegment
+from .native import CNT_INST, CNT_INST2, CNT_OVERFLOW, CNT_STATUS, CNT_VIS, CNT_WORDS, RgsCamera, RgsSegment
 
 TILE = 16
 INF = float("inf")
@@ -199,6 +199,14 @@ class RenderTask:
         self.out = self.depth = self.n_contrib = self.splat_grads = None
         self.total_count = 0
         self.timer = None  # optional utils.profiler.PhaseTimer for per-kernel-group timing
+        # Two-slab forward (CUDA, depth-first binning): bin and blend the nearest splats first, then emit instances of
+        # the rest only for tiles that are not saturated yet. Bit-identical output, fewer instances in dense scenes.
+        self.slabs = os.environ.get("RGS_SLABS", "0") == "1"
+        self.slab_frac256 = int(os.environ.get("RGS_SLAB_FRACTION", "32"))   # share of the splats in the near slab, /256
+        self._split = 0.4            # share of the instance buffers given to the near slab (adapted from the counters)
+        self._slab_active = False    # the last forward used two slabs (the backward walks two lists)
+        self._base_b = 0
+        self.ranges_b = self.tile_done = self.sat = None
         # debug mode: accumulate the blend backward through 64-bit fixed point so that two runs give identical bits
         self.deterministic = os.environ.get("RGS_DETERMINISTIC", "0") == "1"
         self._fixed_acc = None
@@ -223,6 +231,9 @@ class RenderTask:
             self.hw = (H, W)
             tiles = ((H + TILE - 1) // TILE) * ((W + TILE - 1) // TILE)
             self.ranges = torch.zeros(tiles, 2, dtype=torch.int32, device=dev)
+            self.ranges_b = torch.zeros(tiles, 2, dtype=torch.int32, device=dev)
+            self.tile_done = torch.zeros(tiles, dtype=torch.uint8, device=dev)
+            self.sat = torch.zeros(((H + TILE - 1) // TILE + 1) * ((W + TILE - 1) // TILE + 1), dtype=torch.int32, device=dev)
             self.out = torch.empty(H, W, 4, dtype=torch.float32, device=dev)
             self.n_contrib = torch.empty(H, W, dtype=torch.int32, device=dev)
             self.depth = None
@@ -275,6 +286,23 @@ class RenderTask:
                     native.call("project_slots2", self.device, cam, structs, len(segments), bs.vis[3], self.cap_vis,
                                 self.splats, self.vis_ids, self.aux, self.cap_vis, bs.slot_depth, bs.slot_rect,
                                 bs.slot_cnt, self.counters, self.splat_grads)
+                tiles = cam.tiles_x * cam.tiles_y
+                self._slab_active = (self.slabs and self.device.type == "cuda" and cam.tight_rect < 2 and 64 <= tiles <= 65536)
+                if self._slab_active:
+                    self._forward_slabs(cam, bs, dst, want_depth, push)
+                    self.last_out = dst
+                    if not check:
+                        self._record_counters()
+                        return dst
+                    cnt = self.counters.tolist()
+                    if cnt[CNT_STATUS]:
+                        raise RuntimeError(f"rasteriser status {cnt[CNT_STATUS]}")
+                    self._adapt_split(cnt[CNT_INST] & 0xFFFFFFFF, cnt[CNT_INST2] & 0xFFFFFFFF)
+                    if not cnt[CNT_OVERFLOW]:
+                        self.n_vis, self.n_inst = cnt[CNT_VIS], cnt[CNT_INST] + cnt[CNT_INST2]
+                        return dst
+                    self._grow_inst(int(((cnt[CNT_INST] & 0xFFFFFFFF) + (cnt[CNT_INST2] & 0xFFFFFFFF)) * 1.25) + 1024)
+                    continue
                 with self._phase("fwd.binning"):
                     native.call("bin_instances", self.device, cam, self.splats, bs.slot_depth, bs.slot_rect, bs.slot_cnt,
                                 self.cap_vis, bs.vis[0],
@@ -302,6 +330,43 @@ class RenderTask:
             need = cnt[CNT_INST] & 0xFFFFFFFF
             self._grow_inst(int(need * 1.25) + 1024)
 
+    _SIG_BIN_SLAB = "pppp" + "i" + "pppp" + "pppp" + "ii" + "p" + "i" + "p" + "p" + "iii" + "pp" + "p"
+    _SIG_FWD_SLAB = "pppppppppp" + "iii" + "ppp" + "p"
+    _SIG_BWD_SLAB = "ppp" + "i" + "pppppppp" + "i" + "p"
+
+    def _forward_slabs(self, cam: RgsCamera, bs: BinScratch, dst: torch.Tensor, want_depth: bool, push):
+        tiles = cam.tiles_x * cam.tiles_y
+        cap_a = max(1024, int(self.cap_inst * self._split) // 4 * 4)
+        cap_a = min(cap_a, self.cap_inst - 1024)
+        cap_b = self.cap_inst - cap_a
+        self._base_b = cap_a
+        depth = self.depth if want_depth else None
+
+        def bin_slab(slab, off, cap, ranges):
+            native.call("bin_slab", self.device, cam, bs.slot_depth, bs.slot_rect, bs.slot_cnt, self.cap_vis, bs.vis[0], bs.vis[1],
+                        bs.vis[2], bs.vis[3], bs.inst_keys, self.vals, bs.inst_keys_tmp, bs.inst_vals_tmp, off, cap, self.counters,
+                        tiles, ranges, bs.words, self.cap_inst, slab, self.slab_frac256, self.tile_done if slab else None,
+                        self.sat if slab else None, sig=self._SIG_BIN_SLAB)
+
+        def blend(mode):
+            p = push if (mode == 2 and push is not None) else (0, None, None, None)
+            native.call("blend_fwd_slab", self.device, cam, self.ranges, self.ranges_b, self.vals, self.splats, dst, depth,
+                        self.n_contrib, self.counters, self.tile_done, cap_a, mode, p[0], p[1], p[2], p[3], sig=self._SIG_FWD_SLAB)
+
+        with self._phase("fwd.binning"):
+            bin_slab(0, 0, cap_a, self.ranges)
+        with self._phase("fwd.blend"):
+            blend(1)
+        with self._phase("fwd.binning"):
+            bin_slab(1, cap_a, cap_b, self.ranges_b)
+        with self._phase("fwd.blend"):
+            blend(2)
+
+    def _adapt_split(self, n_a: int, n_b: int):
+        """Share of the instance buffers for the near slab, from the counts of the last render (with head room)."""
+        if n_a + n_b > 0:
+            self._split = min(0.9, max(0.05, (1.15 * n_a + 4096) / max(self.cap_inst, 1)))
+
     def _record_counters(self):
         if self.device.type == "cuda":
             self._host_counters.copy_(self.counters, non_blocking=True)
@@ -320,7 +385,10 @@ class RenderTask:
             self._event.synchronize()
             self._event = None
         c = self._host_counters.tolist()
-        info = dict(n_vis=c[CNT_VIS], n_inst=c[CNT_INST] & 0xFFFFFFFF, overflow=bool(c[CNT_OVERFLOW]), status=c[CNT_STATUS])
+        n_b = (c[CNT_INST2] & 0xFFFFFFFF) if self._slab_active else 0
+        info = dict(n_vis=c[CNT_VIS], n_inst=(c[CNT_INST] & 0xFFFFFFFF) + n_b, overflow=bool(c[CNT_OVERFLOW]), status=c[CNT_STATUS])
+        if self._slab_active:
+            self._adapt_split(c[CNT_INST] & 0xFFFFFFFF, n_b)
         if info["status"]:
             what = []
             if info["status"] & 3:
@@ -338,7 +406,16 @@ class RenderTask:
         cam = self.cam
         assert grad_out.is_contiguous() and grad_out.shape == (cam.H, cam.W, 4)
         with self._phase("bwd.blend"):
-            if self.deterministic:
+            if self._slab_active:
+                fixed = None
+                if self.deterministic:
+                    if self._fixed_acc is None or self._fixed_acc.numel() < 9 * self.cap_vis:
+                        self._fixed_acc = torch.zeros(9 * self.cap_vis, dtype=torch.int64, device=self.device)
+                    fixed = self._fixed_acc
+                native.call("blend_bwd_slab", self.device, cam, self.ranges, self.ranges_b, self._base_b, self.vals, self.splats,
+                            self.last_out, self.n_contrib, grad_out, self.splat_grads, self.counters, fixed, self.cap_vis,
+                            sig=self._SIG_BWD_SLAB)
+            elif self.deterministic:
                 if self._fixed_acc is None or self._fixed_acc.numel() < 9 * self.cap_vis:
                     self._fixed_acc = torch.zeros(9 * self.cap_vis, dtype=torch.int64, device=self.device)
                 native.call("blend_bwd_fixed", self.device, cam, self.ranges, self.vals, self.splats, self.last_out,

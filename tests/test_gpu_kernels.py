@@ -353,3 +353,33 @@ def test_peer_region_canaries_detect_an_out_of_bounds_store():
     region._whole[GUARD_BYTES + region.nbytes] = 1  # what an off-by-one peer store would hit
     assert not region.verify_canaries()
     region.close()
+
+
+def test_two_slab_forward_is_bit_identical_and_emits_fewer_instances():
+    """Near slab first, far slab only for unsaturated tiles: same image, same contributor indices, same gradients (with
+    the order-independent accumulation: bit for bit), fewer tile instances in a dense opaque scene."""
+    g = synthetic.uniform_gaussians(150000, 5, sh_degree=3, log_scale_mean=-3.0)
+    g["opacity"] = g["opacity"] + 4.0
+    cams = synthetic.ring_cameras(3, 3.0, 320, 208)
+    grad = torch.randn(208, 320, 4, generator=torch.Generator().manual_seed(2)).cuda().contiguous()
+    res = {}
+    for slabs in (False, True):
+        seg = rasterize.Segment(*(g[k].cuda().contiguous() for k in ("xyz", "sh", "scale", "rot", "opacity")))
+        task = rasterize.RenderTask("cuda")
+        task.slabs = slabs
+        task.deterministic = True
+        out = task.forward(rasterize.make_camera(cams[1], 3), [seg], want_depth=True, check=True).clone()
+        n = seg.count
+        for name, w in (("g_xyz", 3), ("g_sh", 48), ("g_scale", 3), ("g_rot", 4), ("g_opacity", 1)):
+            setattr(seg, name, torch.zeros(n, w, device="cuda"))
+        task.backward(grad, [seg])
+        task._record_counters()
+        torch.cuda.synchronize()
+        assert task.poll()["status"] == 0
+        res[slabs] = (out, task.n_contrib.clone(), task.depth.clone(), task.n_inst,
+                      torch.cat([seg.g_xyz, seg.g_sh, seg.g_scale, seg.g_rot, seg.g_opacity], dim=1))
+    a, b = res[False], res[True]
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+    assert torch.equal(a[4], b[4])
+    assert b[3] < a[3], (a[3], b[3])
+    assert (a[0][..., 3] < 1e-3).float().mean() > 0.3  # the scene does saturate
