@@ -191,9 +191,13 @@ class RenderTask:
         self.hw = (0, 0)
         self.cam: RgsCamera | None = None
         self.counters = torch.zeros(CNT_WORDS, dtype=torch.int32, device=self.device)
+        # overflow flag and status word of every forward since the last poll (the counters restart with each forward)
+        self._sticky = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self._host_sticky = torch.zeros(2, dtype=torch.int32)
         self._host_counters = torch.zeros(CNT_WORDS, dtype=torch.int32)
         if self.device.type == "cuda":
             self._host_counters = self._host_counters.pin_memory()
+            self._host_sticky = self._host_sticky.pin_memory()
         self._event = None
         self.splats = self.vis_ids = self.aux = self.keys = self.vals = self.ranges = None
         self.out = self.depth = self.n_contrib = self.splat_grads = None
@@ -204,6 +208,7 @@ class RenderTask:
         self.slabs = os.environ.get("RGS_SLABS", "0") == "1"
         self.slab_frac256 = int(os.environ.get("RGS_SLAB_FRACTION", "32"))   # share of the splats in the near slab, /256
         self._split = 0.4            # share of the instance buffers given to the near slab (adapted from the counters)
+        self._max_a = self._max_b = 0
         self._slab_active = False    # the last forward used two slabs (the backward walks two lists)
         self._base_b = 0
         self.ranges_b = self.tile_done = self.sat = None
@@ -261,7 +266,7 @@ class RenderTask:
         self.cam = cam
         self.total_count = sum(s.count for s in segments)
         self._ensure(self.total_count, H, W, want_depth)
-        while True:
+        for attempt in range(12):
             dst = self.out if out is None else out
             self.counters.zero_()
             base = 0
@@ -329,6 +334,7 @@ class RenderTask:
                 return dst
             need = cnt[CNT_INST] & 0xFFFFFFFF
             self._grow_inst(int(need * 1.25) + 1024)
+        raise RuntimeError("the instance buffers still overflow after 12 attempts to grow them")
 
     _SIG_BIN_SLAB = "pppp" + "i" + "pppp" + "pppp" + "ii" + "p" + "i" + "p" + "p" + "iii" + "pp" + "p"
     _SIG_FWD_SLAB = "pppppppppp" + "iii" + "ppp" + "p"
@@ -363,16 +369,21 @@ class RenderTask:
             blend(2)
 
     def _adapt_split(self, n_a: int, n_b: int):
-        """Share of the instance buffers for the near slab, from the counts of the last render (with head room)."""
-        if n_a + n_b > 0:
-            self._split = min(0.9, max(0.05, (1.15 * n_a + 4096) / max(self.cap_inst, 1)))
+        """Share of the instance buffers for the near slab: proportional to the largest counts seen, so that both
+        regions keep the same relative head room."""
+        self._max_a, self._max_b = max(self._max_a, n_a), max(self._max_b, n_b)
+        if self._max_a + self._max_b > 0:
+            self._split = min(0.9, max(0.05, (self._max_a + 2048.0) / (self._max_a + self._max_b + 4096.0)))
 
     def _record_counters(self):
+        torch.bitwise_or(self._sticky, self.counters[CNT_OVERFLOW:CNT_STATUS + 1], out=self._sticky)
         if self.device.type == "cuda":
+            self._host_sticky.copy_(self._sticky, non_blocking=True)
             self._host_counters.copy_(self.counters, non_blocking=True)
             self._event = torch.cuda.Event()
             self._event.record(torch.cuda.current_stream(self.device))
         else:
+            self._host_sticky.copy_(self._sticky)
             self._host_counters.copy_(self.counters)
 
     def poll(self) -> dict:
@@ -385,8 +396,12 @@ class RenderTask:
             self._event.synchronize()
             self._event = None
         c = self._host_counters.tolist()
+        sticky = self._host_sticky.tolist()
+        self._sticky.zero_()
         n_b = (c[CNT_INST2] & 0xFFFFFFFF) if self._slab_active else 0
-        info = dict(n_vis=c[CNT_VIS], n_inst=(c[CNT_INST] & 0xFFFFFFFF) + n_b, overflow=bool(c[CNT_OVERFLOW]), status=c[CNT_STATUS])
+        # `overflow` / `status` cover every forward since the previous poll, the counts are those of the last one
+        info = dict(n_vis=c[CNT_VIS], n_inst=(c[CNT_INST] & 0xFFFFFFFF) + n_b, overflow=bool(c[CNT_OVERFLOW] or sticky[0]),
+                    status=c[CNT_STATUS] | sticky[1])
         if self._slab_active:
             self._adapt_split(c[CNT_INST] & 0xFFFFFFFF, n_b)
         if info["status"]:
@@ -396,8 +411,9 @@ class RenderTask:
             if info["status"] & 16:
                 what.append("an index read from the binning buffers was out of bounds (clamped)")
             raise RuntimeError(f"rasteriser status {info['status']}: " + "; ".join(what or ["unknown"]))
-        if info["overflow"] or info["n_inst"] > 0.8 * self.cap_inst:
-            self._grow_inst(int(info["n_inst"] * 1.5) + 1024)
+        need = (self._max_a + self._max_b) if self._slab_active else info["n_inst"]
+        if info["overflow"] or need > 0.6 * self.cap_inst:
+            self._grow_inst(max(int(need * 2.0) + 1024, self.cap_inst if info["overflow"] else 0))
         return info
 
     # -- backward -----------------------------------------------------------------------------
