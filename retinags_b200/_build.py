@@ -18,7 +18,7 @@ ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
 LIB = ROOT / "lib"
 
-CPU_SOURCES = ["rgs_cpu.cpp", "rgs_host.cpp"]
+CPU_SOURCES = ["rgs_cpu.cpp"]
 CUDA_SOURCES = [
     "rgs_raster.cu",
     "rgs_sort.cu",
