@@ -382,7 +382,9 @@ def test_two_slab_forward_is_bit_identical_and_emits_fewer_instances():
         res[slabs] = (out, task.n_contrib.clone(), task.depth.clone(), task.n_inst,
                       torch.cat([seg.g_xyz, seg.g_sh, seg.g_scale, seg.g_rot, seg.g_opacity], dim=1))
     a, b = res[False], res[True]
-    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
-    assert torch.equal(a[4], b[4])
-    assert b[3] < a[3], (a[3], b[3])
-    assert (a[0][..., 3] < 1e-3).float().mean() > 0.3  # the scene does saturate
+    assert (a[0][..., 3] < 1e-3).float().mean() > 0.3, "the scene does not saturate"
+    assert torch.equal(a[0], b[0]), f"image differs at {int((a[0] != b[0]).any(-1).sum())} pixels"
+    assert torch.equal(a[1], b[1]), f"contributor index differs at {int((a[1] != b[1]).sum())} pixels"
+    assert torch.equal(a[2], b[2]), f"depth differs at {int((a[2] != b[2]).sum())} pixels"
+    assert b[3] < a[3], f"instances: single pass {a[3]}, two slabs {b[3]}"
+    assert torch.equal(a[4], b[4]), f"gradients differ in {int((a[4] != b[4]).any(1).sum())} rows"
