@@ -207,8 +207,7 @@ class RenderTask:
         # the rest only for tiles that are not saturated yet. Bit-identical output, fewer instances in dense scenes.
         self.slabs = os.environ.get("RGS_SLABS", "0") == "1"
         self.slab_frac256 = int(os.environ.get("RGS_SLAB_FRACTION", "32"))   # share of the splats in the near slab, /256
-        self._split = 0.4            # share of the instance buffers given to the near slab (adapted from the counters)
-        self._max_a = self._max_b = 0
+        self._need_a = self._need_b = 0   # largest instance counts of the near / far slab seen so far
         self._slab_active = False    # the last forward used two slabs (the backward walks two lists)
         self._base_b = 0
         self.ranges_b = self.tile_done = self.sat = None
@@ -302,11 +301,10 @@ class RenderTask:
                     cnt = self.counters.tolist()
                     if cnt[CNT_STATUS]:
                         raise RuntimeError(f"rasteriser status {cnt[CNT_STATUS]}")
-                    self._adapt_split(cnt[CNT_INST] & 0xFFFFFFFF, cnt[CNT_INST2] & 0xFFFFFFFF)
+                    self._note_slab_counts(cnt[CNT_INST] & 0xFFFFFFFF, cnt[CNT_INST2] & 0xFFFFFFFF)
                     if not cnt[CNT_OVERFLOW]:
                         self.n_vis, self.n_inst = cnt[CNT_VIS], cnt[CNT_INST] + cnt[CNT_INST2]
                         return dst
-                    self._grow_inst(int(((cnt[CNT_INST] & 0xFFFFFFFF) + (cnt[CNT_INST2] & 0xFFFFFFFF)) * 1.25) + 1024)
                     continue
                 with self._phase("fwd.binning"):
                     native.call("bin_instances", self.device, cam, self.splats, bs.slot_depth, bs.slot_rect, bs.slot_cnt,
@@ -342,8 +340,10 @@ class RenderTask:
 
     def _forward_slabs(self, cam: RgsCamera, bs: BinScratch, dst: torch.Tensor, want_depth: bool, push):
         tiles = cam.tiles_x * cam.tiles_y
-        cap_a = max(1024, int(self.cap_inst * self._split) // 4 * 4)
-        cap_a = min(cap_a, self.cap_inst - 1024)
+        # the near slab gets what it needed so far plus 30 %, the far slab the rest (_note_slab_counts keeps the total
+        # large enough for both); before any count is known the buffers are split 40 : 60
+        want_a = int(1.3 * self._need_a) + 4096 if self._need_a else int(0.4 * self.cap_inst)
+        cap_a = max(1024, min(want_a, self.cap_inst - 1024)) // 4 * 4
         cap_b = self.cap_inst - cap_a
         self._base_b = cap_a
         depth = self.depth if want_depth else None
@@ -368,12 +368,14 @@ class RenderTask:
         with self._phase("fwd.blend"):
             blend(2)
 
-    def _adapt_split(self, n_a: int, n_b: int):
-        """Share of the instance buffers for the near slab: proportional to the largest counts seen, so that both
-        regions keep the same relative head room."""
-        self._max_a, self._max_b = max(self._max_a, n_a), max(self._max_b, n_b)
-        if self._max_a + self._max_b > 0:
-            self._split = min(0.9, max(0.05, (self._max_a + 2048.0) / (self._max_a + self._max_b + 4096.0)))
+    def _note_slab_counts(self, n_a: int, n_b: int):
+        """Remember the largest instance counts of both slabs and make the buffers hold 1.3x of each. The needs only grow
+        and the buffers never shrink, so a render that overflowed fits after at most two more attempts (the far slab's
+        count is only known once the near slab fitted)."""
+        self._need_a, self._need_b = max(self._need_a, n_a), max(self._need_b, n_b)
+        want = int(1.3 * self._need_a) + int(1.3 * self._need_b) + 16384
+        if want > self.cap_inst:
+            self._grow_inst(int(1.5 * (self._need_a + self._need_b)) + 16384)
 
     def _record_counters(self):
         torch.bitwise_or(self._sticky, self.counters[CNT_OVERFLOW:CNT_STATUS + 1], out=self._sticky)
@@ -402,8 +404,6 @@ class RenderTask:
         # `overflow` / `status` cover every forward since the previous poll, the counts are those of the last one
         info = dict(n_vis=c[CNT_VIS], n_inst=(c[CNT_INST] & 0xFFFFFFFF) + n_b, overflow=bool(c[CNT_OVERFLOW] or sticky[0]),
                     status=c[CNT_STATUS] | sticky[1])
-        if self._slab_active:
-            self._adapt_split(c[CNT_INST] & 0xFFFFFFFF, n_b)
         if info["status"]:
             what = []
             if info["status"] & 3:
@@ -411,9 +411,10 @@ class RenderTask:
             if info["status"] & 16:
                 what.append("an index read from the binning buffers was out of bounds (clamped)")
             raise RuntimeError(f"rasteriser status {info['status']}: " + "; ".join(what or ["unknown"]))
-        need = (self._max_a + self._max_b) if self._slab_active else info["n_inst"]
-        if info["overflow"] or need > 0.6 * self.cap_inst:
-            self._grow_inst(max(int(need * 2.0) + 1024, self.cap_inst if info["overflow"] else 0))
+        if self._slab_active:
+            self._note_slab_counts(c[CNT_INST] & 0xFFFFFFFF, n_b)
+        elif info["overflow"] or info["n_inst"] > 0.6 * self.cap_inst:
+            self._grow_inst(max(int(info["n_inst"] * 2.0) + 1024, self.cap_inst if info["overflow"] else 0))
         return info
 
     # -- backward -----------------------------------------------------------------------------
