@@ -142,6 +142,91 @@ __global__ void __launch_bounds__(256) rgs_adam_kernel(float* __restrict__ p, fl
     }
 }
 
+// Row-block variant: a warp looks at the marks of 32 consecutive rows first (one byte pair per lane, one ballot) and
+// then works only on the rows that are live, two rows per pass (15 units of a row on 15 lanes of a half-warp:
+// 12 float4 of SH, the rotation, position, scale + opacity). A block of rows without a live row costs a few
+// instructions instead of fifteen unit tests per row, which is what bounds rgs_adam_kernel when few rows are live
+// (62.9 M rows, 0.2 % live: 3.9 ms of flag tests). Same arithmetic per element, same results.
+__device__ __forceinline__ void adam_scalar(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
+                                            float* __restrict__ v, int64_t idx, bool touched_row, float lr, float beta1,
+                                            float beta2, float eps, float bc1, float bc2s, int zero_grad) {
+    float M = m[idx], V = v[idx];
+    if (!touched_row && M == 0.f && V == 0.f) return;
+    float P = p[idx];
+    rgs_adam_elem(P, touched_row ? g[idx] : 0.f, M, V, lr, beta1, beta2, eps, bc1, bc2s);
+    p[idx] = P; m[idx] = M; v[idx] = V;
+    if (zero_grad && touched_row) g[idx] = 0.f;
+}
+
+template <int GRP>
+__device__ __forceinline__ void adam_quad(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
+                                          float* __restrict__ v, int64_t base, int col0, bool touched_row,
+                                          const RgsLrTable& lrs, float beta1, float beta2, float eps, float bc1, float bc2s,
+                                          int zero_grad) {
+    float4 M = *reinterpret_cast<float4*>(m + base), V = *reinterpret_cast<float4*>(v + base);
+    float4 G = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (touched_row) G = *reinterpret_cast<float4*>(g + base);
+    else if (M.x == 0.f && M.y == 0.f && M.z == 0.f && M.w == 0.f && V.x == 0.f && V.y == 0.f && V.z == 0.f && V.w == 0.f)
+        return;
+    float4 P = *reinterpret_cast<float4*>(p + base);
+    rgs_adam_elem(P.x, G.x, M.x, V.x, adam_lr(lrs, GRP, col0), beta1, beta2, eps, bc1, bc2s);
+    rgs_adam_elem(P.y, G.y, M.y, V.y, adam_lr(lrs, GRP, col0 + 1), beta1, beta2, eps, bc1, bc2s);
+    rgs_adam_elem(P.z, G.z, M.z, V.z, adam_lr(lrs, GRP, col0 + 2), beta1, beta2, eps, bc1, bc2s);
+    rgs_adam_elem(P.w, G.w, M.w, V.w, adam_lr(lrs, GRP, col0 + 3), beta1, beta2, eps, bc1, bc2s);
+    *reinterpret_cast<float4*>(p + base) = P;
+    *reinterpret_cast<float4*>(m + base) = M;
+    *reinterpret_cast<float4*>(v + base) = V;
+    if (zero_grad && touched_row) *reinterpret_cast<float4*>(g + base) = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+__global__ void __launch_bounds__(256) rgs_adam_rows_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
+                                                            float* __restrict__ v, int64_t count, int64_t cap,
+                                                            const __grid_constant__ RgsLrTable lrs, float beta1, float beta2,
+                                                            float eps, float bc1, float bc2s, int zero_grad,
+                                                            const uint32_t* __restrict__ skip,
+                                                            const uint8_t* __restrict__ touched, uint8_t* __restrict__ active) {
+    if (skip && skip[RGS_CNT_OVERFLOW]) return;
+    const int64_t o1 = cap * 3, o2 = o1 + cap * 48, o3 = o2 + cap * 3, o4 = o3 + cap * 4;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int64_t nblk = (count + 31) / 32;
+    for (int64_t blk = warp; blk < nblk; blk += nwarps) {
+        const int64_t r = blk * 32 + lane;
+        bool t = false, live = false;
+        if (r < count) {
+            t = touched ? touched[r] != 0 : true;
+            live = t || !touched || !active || active[r] != 0;  // without marks every row counts as live
+            if (t && touched && active) active[r] = 1;          // read again by no lane of this launch
+        }
+        uint32_t mask = __ballot_sync(0xffffffffu, live);
+        const uint32_t tmask = __ballot_sync(0xffffffffu, t);
+        const int half = lane >> 4, u = lane & 15;
+        while (mask) {
+            const int j0 = __ffs(mask) - 1;
+            mask &= mask - 1;
+            int j1 = -1;
+            if (mask) { j1 = __ffs(mask) - 1; mask &= mask - 1; }
+            const int jr = half ? j1 : j0;
+            if (jr < 0 || u >= 15) continue;
+            const int64_t row = blk * 32 + jr;
+            const bool tr = (tmask >> jr) & 1u;
+            if (u < 12) {
+                adam_quad<1>(p, g, m, v, o1 + row * 48 + u * 4, u * 4, tr, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad);
+            } else if (u == 12) {
+                adam_quad<3>(p, g, m, v, o3 + row * 4, 0, tr, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad);
+            } else if (u == 13) {
+                for (int c = 0; c < 3; ++c)
+                    adam_scalar(p, g, m, v, row * 3 + c, tr, lrs.lr[RGS_LR_XYZ], beta1, beta2, eps, bc1, bc2s, zero_grad);
+            } else {
+                for (int c = 0; c < 3; ++c)
+                    adam_scalar(p, g, m, v, o2 + row * 3 + c, tr, lrs.lr[RGS_LR_SCALE], beta1, beta2, eps, bc1, bc2s, zero_grad);
+                adam_scalar(p, g, m, v, o4 + row, tr, lrs.lr[RGS_LR_OPACITY], beta1, beta2, eps, bc1, bc2s, zero_grad);
+            }
+        }
+    }
+}
+
 extern "C" {
 
 int rgs_cuda_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t cap, const double* lrs, double beta1,
@@ -159,6 +244,24 @@ int rgs_cuda_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t
     rgs_adam_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, count, cap, t, (float)beta1, (float)beta2,
                                                              (float)eps, bc1, bc2s, (int)zero_grad,
                                                              reinterpret_cast<const uint32_t*>(skip), touched, active);
+    return (int)cudaGetLastError();
+}
+
+// Same contract as rgs_cuda_adam, row-block kernel (see rgs_adam_rows_kernel).
+int rgs_cuda_adam_rows(float* p, float* g, float* m, float* v, int64_t count, int64_t cap, const double* lrs, double beta1,
+                       double beta2, double eps, int64_t step, int64_t zero_grad, const int32_t* skip, const uint8_t* touched,
+                       uint8_t* active, void* stream) {
+    if (count <= 0) return 0;
+    if (cap % 4 != 0) return 13;
+    RgsLrTable t;
+    for (int k = 0; k < 6; ++k) t.lr[k] = (float)lrs[k];
+    const float bc1 = (float)(1.0 / (1.0 - pow(beta1, (double)step)));
+    const float bc2s = (float)(1.0 / sqrt(1.0 - pow(beta2, (double)step)));
+    const int64_t want = ((count + 31) / 32 + 7) / 8;  // 8 warps per block, one 32-row block per warp and pass
+    const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > 148 * 64 ? 148 * 64 : want));
+    rgs_adam_rows_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, count, cap, t, (float)beta1, (float)beta2,
+                                                                  (float)eps, bc1, bc2s, (int)zero_grad,
+                                                                  reinterpret_cast<const uint32_t*>(skip), touched, active);
     return (int)cudaGetLastError();
 }
 

@@ -17,6 +17,7 @@ and 177 floats ``[params, exp_avg, exp_avg_sq]`` (``:849-870``).
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -45,6 +46,9 @@ class GaussianStore:
         self.step = 0
         self.params = self.grads = self.exp_avg = self.exp_avg_sq = None
         self.grad_accum = self.denom = self.max_radii = None
+        # "units": one thread per 128-bit unit (default); "rows": a warp per 32 rows that skips dead rows after one
+        # ballot (csrc/rgs_model.cu: rgs_adam_rows_kernel; written for models in which few rows are live)
+        self.adam_variant = os.environ.get("RGS_ADAM", "units")
         self.touched = None  # uint8 per row: a gradient was written this step (rows with 0 hold zero gradients)
         self.active = None   # uint8 per row: the Adam moments may be non-zero (rows with 0 hold zero moments)
         self._alloc(_round_cap(capacity))
@@ -220,7 +224,7 @@ class GaussianStore:
             return
         import ctypes
         arr = (ctypes.c_double * 6)(*[float(x) for x in lrs])
-        native.call("adam", self.device, self.params, self.grads, self.exp_avg, self.exp_avg_sq, self.count, self.cap, arr,
+        native.call("adam_rows" if self.adam_variant == "rows" else "adam", self.device, self.params, self.grads, self.exp_avg, self.exp_avg_sq, self.count, self.cap, arr,
                     float(beta1), float(beta2), float(eps), self.step, 1 if zero_grad else 0, skip,
                     self.touched if zero_grad else None, self.active if zero_grad else None)
         if zero_grad:

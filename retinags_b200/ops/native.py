@@ -35,6 +35,7 @@ SIGNATURES = {
     "geom_bwd": "ppipppppip",
     "scatter_radii": "pppiipp",
     "adam": "ppppiipfffiipppp",
+    "adam_rows": "ppppiipfffiipppp",
     "composite_fwd": "pipiiiippp",
     "composite_bwd": "ppipiiiipp",
     "ssim_fwd": "ppiiiiiippp",
