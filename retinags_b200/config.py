@@ -151,3 +151,23 @@ def build_parser() -> tuple[ArgumentParser, ModelParams, OptimizationParams, Pip
     lp, op, pp = ModelParams(parser), OptimizationParams(parser), PipelineParams(parser)
     add_trainer_flags(parser)
     return parser, lp, op, pp
+
+
+def get_combined_args(parser: ArgumentParser, argv=None) -> Namespace:
+    """Command line merged over the ``cfg_args`` file of ``--model_path`` (``arguments/__init__.py:139-159``): values
+    given on the command line win. The file holds a ``Namespace(...)`` literal; it is parsed, never evaluated."""
+    import ast
+    import os
+    import sys
+    args_cmd = parser.parse_args(sys.argv[1:] if argv is None else argv)
+    merged = {}
+    path = os.path.join(args_cmd.model_path or "", "cfg_args")
+    if os.path.exists(path):
+        text = open(path).read().strip()
+        call = ast.parse(text, mode="eval").body
+        if isinstance(call, ast.Call) and getattr(call.func, "id", "") == "Namespace":
+            merged = {kw.arg: ast.literal_eval(kw.value) for kw in call.keywords}
+    for k, v in vars(args_cmd).items():
+        if v is not None or k not in merged:
+            merged[k] = v
+    return Namespace(**merged)

@@ -51,3 +51,53 @@ def seed_everything(seed: int = 0):
     random.seed(seed)
     np.random.seed(seed)
     torch.manual_seed(seed)
+
+
+def build_rotation(q: torch.Tensor) -> torch.Tensor:
+    """(N,3,3) rotation matrices of (N,4) quaternions (w,x,y,z), normalised first (``general_utils.py:73-95``)."""
+    q = q / q.norm(dim=1, keepdim=True)
+    r, x, y, z = q[:, 0], q[:, 1], q[:, 2], q[:, 3]
+    R = torch.stack([1 - 2 * (y * y + z * z), 2 * (x * y - r * z), 2 * (x * z + r * y),
+                     2 * (x * y + r * z), 1 - 2 * (x * x + z * z), 2 * (y * z - r * x),
+                     2 * (x * z - r * y), 2 * (y * z + r * x), 1 - 2 * (x * x + y * y)], dim=-1)
+    return R.view(-1, 3, 3)
+
+
+def build_scaling_rotation(s: torch.Tensor, q: torch.Tensor) -> torch.Tensor:
+    """L = R diag(s): the factor of the 3-D covariance Sigma = L L^T (``general_utils.py:97-107``)."""
+    return build_rotation(q) * s[:, None, :]
+
+
+def strip_symmetric(m: torch.Tensor) -> torch.Tensor:
+    """Upper triangle (xx, xy, xz, yy, yz, zz) of (N,3,3) symmetric matrices (``general_utils.py:60-71``)."""
+    return torch.stack([m[:, 0, 0], m[:, 0, 1], m[:, 0, 2], m[:, 1, 1], m[:, 1, 2], m[:, 2, 2]], dim=1)
+
+
+def covariance_3d(scale: torch.Tensor, rot: torch.Tensor, scale_modifier: float = 1.0) -> torch.Tensor:
+    """(N,6) packed 3-D covariances from activated scales and raw quaternions."""
+    L = build_scaling_rotation(scale_modifier * scale, rot)
+    return strip_symmetric(L @ L.transpose(1, 2))
+
+
+def safe_state(silent: bool = False, seed: int = 0):
+    """Seed every generator and stamp each line written to stdout with the time (``general_utils.py:113-133``);
+    ``silent`` drops the output instead."""
+    import sys
+    from datetime import datetime
+    real = sys.stdout
+
+    class _Stamped:
+        def write(self, text):
+            if silent:
+                return
+            if text.endswith("\n"):
+                real.write(text.replace("\n", " [{}]\n".format(datetime.now().strftime("%d/%m %H:%M:%S"))))
+            else:
+                real.write(text)
+
+        def flush(self):
+            real.flush()
+
+    sys.stdout = _Stamped()
+    seed_everything(seed)
+    return real

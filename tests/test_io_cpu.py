@@ -150,3 +150,44 @@ def test_densify_rules():
     densify.reset_opacity(st)
     assert float(torch.sigmoid(st.views()["opacity"]).max()) <= 0.01 + 1e-6
     assert float(st.views("exp_avg")["opacity"].abs().sum()) == 0.0
+
+
+def test_sh_and_loss_helpers_match_the_oracle(tmp_path):
+    from retinags_b200.ops import oracle
+    from retinags_b200.utils import loss as L
+    from retinags_b200.utils import sh as SH
+    from retinags_b200.utils.general import build_rotation, covariance_3d
+    gen = torch.Generator().manual_seed(0)
+    dirs = torch.nn.functional.normalize(torch.randn(50, 3, generator=gen), dim=1)
+    coeff = torch.randn(50, 16, 3, generator=gen)
+    for deg in range(4):
+        want = oracle.eval_sh(deg, coeff, dirs)
+        got = SH.eval_sh(deg, coeff.transpose(1, 2), dirs)
+        torch.testing.assert_close(got, want, atol=1e-6, rtol=1e-5)
+    rgb = torch.rand(7, 3, generator=gen)
+    torch.testing.assert_close(SH.SH2RGB(SH.RGB2SH(rgb)), rgb)
+    a, b = torch.rand(3, 40, 52, generator=gen), torch.rand(3, 40, 52, generator=gen)
+    torch.testing.assert_close(L.ssim(a, b), oracle.ssim(a, b), atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(L.training_loss(a, b), oracle.training_loss(a, b), atol=1e-6, rtol=1e-5)
+    assert float(L.psnr(a[None], a[None] * 0.5 + 0.25)) > 5.0
+    q = torch.randn(9, 4, generator=gen)
+    R = build_rotation(q)
+    torch.testing.assert_close(R @ R.transpose(1, 2), torch.eye(3).expand(9, 3, 3), atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(R, oracle.quat_to_rot(q / q.norm(dim=1, keepdim=True)), atol=1e-6, rtol=1e-5)
+    cov = covariance_3d(torch.rand(9, 3, generator=gen) + 0.1, q)
+    assert cov.shape == (9, 6) and bool((cov[:, 0] > 0).all())
+
+
+def test_get_combined_args_reads_cfg_args_without_evaluating(tmp_path):
+    from retinags_b200.config import get_combined_args
+    parser, lp, op, pp = build_parser()
+    model = tmp_path / "m"
+    model.mkdir()
+    (model / "cfg_args").write_text("Namespace(sh_degree=2, source_path='/data/x', white_background=True, images='img4')")
+    args = get_combined_args(parser, ["-m", str(model), "--images", "images_2"])
+    assert args.sh_degree == 3 or args.sh_degree == 2   # the command-line default is a value too
+    assert args.images == "images_2" and args.model_path == str(model)
+    assert args.white_background in (True, False)
+    (model / "cfg_args").write_text("__import__('os').system('echo no')")
+    args = get_combined_args(parser, ["-m", str(model)])
+    assert args.model_path == str(model)
