@@ -24,6 +24,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -88,12 +90,20 @@ class LocalTransport:
 class TorchDistTransport:
     """Row-slice send/recv of partials and gradients with ``torch.distributed`` point-to-point ops."""
 
-    def __init__(self, device, group=None):
+    def __init__(self, device, group=None, version: str | None = None):
         self.device = torch.device(device)
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self._pool: dict = {}
+        # how a batch of point-to-point operations is issued (the reference's communicate_utils/core.py:37-233):
+        #   "0"            one batch_isend_irecv, wait for all (its default)
+        #   "0+profiling"  the same inside a profiler range
+        #   "1"            blocking send/recv, peer by peer, the lower rank sends first (cannot deadlock)
+        #   "2"            all irecv posted first, then all isend, then wait
+        self.version = version if version is not None else os.environ.get("RGS_COMM_VERSION", "0")
+        if self.version not in ("0", "0+profiling", "1", "2"):
+            raise ValueError(f"unknown communication version {self.version!r}")
 
     def _buf(self, key, shape):
         t = self._pool.get(key)
@@ -105,8 +115,29 @@ class TorchDistTransport:
     def _run(self, ops):
         if not ops:
             return
-        for req in dist.batch_isend_irecv(ops):
-            req.wait()
+        if self.version == "0":
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+        elif self.version == "0+profiling":
+            with torch.profiler.record_function("batched_send_recv"):
+                for req in dist.batch_isend_irecv(ops):
+                    req.wait()
+        elif self.version == "1":
+            # both ends walk their common operations in the order in which they were queued; towards a higher rank
+            # this rank sends first, towards a lower one it receives first
+            peers = sorted({op.peer for op in ops})
+            for peer in peers:
+                mine = [op for op in ops if op.peer == peer]
+                sends = [op for op in mine if op.op is dist.isend]
+                recvs = [op for op in mine if op.op is dist.irecv]
+                first, second = (sends, recvs) if self.rank < peer else (recvs, sends)
+                for op in first + second:
+                    (dist.send if op.op is dist.isend else dist.recv)(op.tensor, peer, group=self.group)
+        else:
+            reqs = [dist.irecv(op.tensor, op.peer, group=self.group) for op in ops if op.op is dist.irecv]
+            reqs += [dist.isend(op.tensor, op.peer, group=self.group) for op in ops if op.op is dist.isend]
+            for req in reqs:
+                req.wait()
 
     def exchange_partials(self, plans: list[ViewPlan], local_out: dict[int, dict[int, torch.Tensor]]):
         """Returns {view: [slot per visible model]}; a slot is a *full-height virtual* (H,W,4) view of

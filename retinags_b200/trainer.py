@@ -260,9 +260,9 @@ class Trainer:
                 if kind == "peer":
                     raise
                 self.logger.warning("peer transport unavailable (%r); using torch.distributed send/recv", exc)
-                tr = TorchDistTransport(self.device, self.group)
+                tr = TorchDistTransport(self.device, self.group, getattr(a, "COMM_VERSION", "0"))
         else:
-            tr = TorchDistTransport(self.device, self.group)
+            tr = TorchDistTransport(self.device, self.group, getattr(a, "COMM_VERSION", "0"))
         lo, hi = self.boxes
         self.border = None
         if self.n_models > 1 and not a.NOT_SHRAE_GS_INFO:

@@ -80,3 +80,38 @@ def test_two_ranks_match_single_rank(tmp_path):
     # Adam's first steps have unit magnitude whatever the gradient size, so rounding-level differences
     # move individual Gaussians differently; the images must still agree on average
     assert (got - ref).abs().mean() < 2e-3
+
+
+def _comm_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from retinags_b200.parallel.compositing import TorchDistTransport
+        ok = True
+        for version in ("0", "0+profiling", "1", "2"):
+            tr = TorchDistTransport("cpu", None, version=version)
+            peers = [r for r in range(world) if r != rank]
+            send = {p: [torch.full((5, 3), float(100 * rank + p + k)) for k in range(2)] for p in peers}
+            recv = {p: [torch.zeros(5, 3) for _ in range(2)] for p in peers}
+            ops = []
+            for p in peers:  # interleaved on purpose: two messages each way per peer
+                for k in range(2):
+                    ops.append(dist.P2POp(dist.isend, send[p][k], p))
+                    ops.append(dist.P2POp(dist.irecv, recv[p][k], p))
+            tr._run(ops)
+            for p in peers:
+                for k in range(2):
+                    ok &= bool((recv[p][k] == float(100 * p + rank + k)).all())
+        torch.save(ok, os.path.join(out_dir, f"comm{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_comm_versions_deliver_the_same_messages(tmp_path):
+    """Batched, profiled, blocking-ordered and two-pass point-to-point schedules on three gloo ranks."""
+    port = 27500 + os.getpid() % 2000
+    mp.spawn(_comm_worker, args=(3, port, str(tmp_path)), nprocs=3, join=True)
+    assert all(torch.load(os.path.join(tmp_path, f"comm{r}.pt")) for r in range(3))
