@@ -140,6 +140,7 @@ def add_trainer_flags(parser: ArgumentParser):
     p.add_argument("--synthetic", default="", help="name of a seeded synthetic scene instead of -s (see data/synthetic.py)")
     p.add_argument("--WATCHDOG_TIMEOUT", type=float, default=120.0,
                    help="seconds without a heartbeat after which a peer counts as failed (0 disables the watchdog)")
+    p.add_argument("--LPIPS_WEIGHTS", default="", help="directory with vgg16.pth and lpips_vgg.pth; without it LPIPS is NaN")
     p.add_argument("--COMM_VERSION", default="0", choices=["0", "0+profiling", "1", "2"],
                    help="schedule of the torch.distributed transport: batched, batched inside a profiler range, blocking "
                         "in rank order, two-pass isend/irecv")

@@ -476,8 +476,12 @@ class Trainer:
         n_tr = len(self.train_dataset)
         splits = (("train", DatasetRepeater(self.train_dataset, n_tr // max(a.EVAL_PSNR_INTERVAL, 1), False, a.EVAL_PSNR_INTERVAL),
                    self.train_rlt, a.EVAL_PSNR_INTERVAL), ("test", self.test_dataset, self.test_rlt, 1))
+        if not hasattr(self, "_lpips"):
+            from .utils.lpips import load_lpips
+            self._lpips = load_lpips(getattr(a, "LPIPS_WEIGHTS", ""), self.device)
         for name, ds, rlt, stride in splits:
             stat = torch.zeros(4, dtype=torch.float64, device=self.device)  # samples, l1, psnr, ssim
+            lp_sum, lp_n = 0.0, 0
             for b0 in range(0, len(ds), max(a.MAX_BATCH_SIZE, 1)):
                 idx = list(range(b0, min(len(ds), b0 + a.MAX_BATCH_SIZE)))
                 cams = [ds[i] for i in idx]
@@ -495,6 +499,17 @@ class Trainer:
                     l1, ssim, mse = (sums / npx).tolist()
                     stat += torch.tensor([1.0, l1, psnr_from_mse(mse), ssim], dtype=torch.float64, device=self.device)
                     self.logger.info("%s, image %s, psnr %f, ssim %f, l1 %f", name, cam.image_name, psnr_from_mse(mse), ssim, l1)
+                    if self._lpips is not None:
+                        # the perceptual metric needs whole images: the row bands are summed into one on every rank
+                        full = torch.zeros(3, cam.height, cam.width, device=self.device)
+                        full[:, r0:r1] = out["image"][:, r0:r1]
+                        gt_full = torch.zeros_like(full)
+                        gt_full[:, r0:r1] = gt[:, r0:r1]
+                        if self.world > 1:
+                            dist.all_reduce(full, group=self.group)
+                            dist.all_reduce(gt_full, group=self.group)
+                        lp_sum += float(self._lpips(full.clamp(0, 1), gt_full))
+                        lp_n += 1
                     if a.SAVE_EVAL_IMAGE:
                         self._save_rows(out, cam, name)
                     if a.SAVE_EVAL_SUB_IMAGE:
@@ -503,9 +518,10 @@ class Trainer:
                                      part[..., :3].permute(2, 0, 1))
             n, l1, ps, ss = stat.tolist()
             n = max(n, 1.0)
-            results[name] = dict(samples=n, l1=l1 / n, psnr=ps / n, ssim=ss / n, lpips=float("nan"))
+            lp = lp_sum / lp_n if lp_n else float("nan")
+            results[name] = dict(samples=n, l1=l1 / n, psnr=ps / n, ssim=ss / n, lpips=lp)
             if self.rank == 0:
-                msg = f"\n[ITER {self.iteration}] Evaluating {name}: samples {n} L1 {l1 / n} PSNR {ps / n} SSIM {ss / n} LPIPS nan"
+                msg = f"\n[ITER {self.iteration}] Evaluating {name}: samples {n} L1 {l1 / n} PSNR {ps / n} SSIM {ss / n} LPIPS {lp}"
                 print(msg, flush=True)
                 self.logger.info(msg)
                 if self.tb:

@@ -191,3 +191,22 @@ def test_get_combined_args_reads_cfg_args_without_evaluating(tmp_path):
     (model / "cfg_args").write_text("__import__('os').system('echo no')")
     args = get_combined_args(parser, ["-m", str(model)])
     assert args.model_path == str(model)
+
+
+def test_lpips_module_with_local_weight_files(tmp_path):
+    """The perceptual metric: zero for identical images, positive otherwise, weights read from local files only."""
+    from retinags_b200.utils.lpips import LPIPS, load_lpips
+    assert load_lpips(str(tmp_path)) is None  # no files -> the evaluation reports NaN
+    torch.manual_seed(0)
+    ref = LPIPS()
+    for p in ref.parameters():
+        p.copy_(torch.rand_like(p) * 0.1)
+    torch.save({"features." + k: v for k, v in ref.features.state_dict().items()}, str(tmp_path / "vgg16.pth"))
+    torch.save({f"lin{k}.model.1.weight": lin.weight for k, lin in enumerate(ref.lins)}, str(tmp_path / "lpips_vgg.pth"))
+    net = load_lpips(str(tmp_path))
+    assert net is not None
+    a, b = torch.rand(3, 48, 64), torch.rand(3, 48, 64)
+    assert float(net(a, a)) == 0.0
+    d = float(net(a, b))
+    assert d > 0 and abs(d - float(ref(a, b))) < 1e-6
+    assert net(torch.stack([a, b]), torch.stack([b, b])).shape == (2,)
