@@ -15,6 +15,7 @@
 #include <stdint.h>
 #include "rgs_api.h"
 #include "rgs_cuda_common.cuh"
+#include "rgs_border.h"
 
 struct RgsColumns { float* xyz; float* sh; float* scale; float* rot; float* opacity; };
 struct RgsConstColumns { const float* xyz; const float* sh; const float* scale; const float* rot; const float* opacity; };
@@ -91,6 +92,20 @@ __global__ void __launch_bounds__(256) rgs_border_grad_add_kernel(const float* _
     }
 }
 
+// one destination bit mask per Gaussian (see rgs_border.h); boxes: M x 6 floats in device memory
+__global__ void __launch_bounds__(256) rgs_border_mask_kernel(const float* __restrict__ xyz, const float* __restrict__ scale,
+                                                              int64_t n, const float* __restrict__ boxes, int M, int self,
+                                                              float margin, int64_t* __restrict__ masks) {
+    __shared__ float sb[6 * RGS_MAX_BORDER_MODELS];
+    for (int k = threadIdx.x; k < 6 * M; k += blockDim.x) sb[k] = boxes[k];
+    __syncthreads();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float p[3] = {xyz[3 * i], xyz[3 * i + 1], xyz[3 * i + 2]};
+        const float s[3] = {scale[3 * i], scale[3 * i + 1], scale[3 * i + 2]};
+        masks[i] = rgs_border_mask(p, s, sb, M, self, margin);
+    }
+}
+
 static inline unsigned border_grid(int64_t n) {
     const int64_t want = (n * 15 + 255) / 256;
     return (unsigned)(want < 1 ? 1 : (want > 148 * 16 ? 148 * 16 : want));
@@ -105,6 +120,17 @@ int rgs_cuda_border_pack(const float* const* src, const int64_t* idx, int64_t n,
     RgsConstColumns s{src[0], src[1], src[2], src[3], src[4]};
     RgsColumns d{dst[0], dst[1], dst[2], dst[3], dst[4]};
     rgs_border_pack_kernel<<<border_grid(n), 256, 0, (cudaStream_t)stream>>>(s, idx, n, d, dst_row0);
+    return (int)cudaGetLastError();
+}
+
+// masks[i]: bit d set when Gaussian i of sub-model `self` is lent to sub-model d (M <= 63 sub-models).
+int rgs_cuda_border_mask(const float* xyz, const float* scale, int64_t n, const float* boxes, int64_t M, int64_t self,
+                         double margin, int64_t* masks, void* stream) {
+    if (M < 1 || M > RGS_MAX_BORDER_MODELS || self < 0 || self >= M) return 17;
+    if (n <= 0) return 0;
+    const int64_t want = (n + 255) / 256;
+    const unsigned blocks = (unsigned)(want > 148 * 32 ? 148 * 32 : want);
+    rgs_border_mask_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(xyz, scale, n, boxes, (int)M, (int)self, (float)margin, masks);
     return (int)cudaGetLastError();
 }
 

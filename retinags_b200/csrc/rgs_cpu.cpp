@@ -14,6 +14,7 @@
 #include "rgs_loss_math.h"
 #include "rgs_knn.h"
 #include "rgs_surgery.h"
+#include "rgs_border.h"
 
 extern "C" {
 
@@ -448,6 +449,15 @@ int rgs_cpu_ssim_composite_bwd(const float* const* partials, float* const* grads
     int rc = rgs_cpu_ssim_bwd(img, gt, dmaps, H, W, row0, row1, vrow0, vrow1, w_l1, w_ssim, g_image, nullptr);
     if (rc) return rc;
     return rgs_cpu_composite_bwd(partials, grads, K, bg, H, W, row0, row1, g_image, nullptr);
+}
+
+// CPU twin of rgs_border_mask_kernel
+int rgs_cpu_border_mask(const float* xyz, const float* scale, int64_t n, const float* boxes, int64_t M, int64_t self,
+                        double margin, int64_t* masks, void*) {
+    if (M < 1 || M > RGS_MAX_BORDER_MODELS || self < 0 || self >= M) return 17;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) masks[i] = rgs_border_mask(xyz + 3 * i, scale + 3 * i, boxes, (int)M, (int)self, (float)margin);
+    return 0;
 }
 
 // CPU twins of rgs_aux.cu

@@ -16,13 +16,58 @@ every step because parameters change.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
 from ..models.gaussians import NAMES, RECORD, WIDTHS, GaussianStore
+from ..ops import native
 from ..ops.rasterize import Segment
 
 GRAD_COLS = RECORD + 1  # 59 parameter gradients + the screen-gradient statistic
+
+
+def select_border(store: GaussianStore, m: int, lo: torch.Tensor, hi: torch.Tensor, margin: float = 0.0,
+                  native_mask: bool | None = None) -> dict[int, torch.Tensor]:
+    """Indices (ascending) of the Gaussians of sub-model ``m`` that are lent to every other sub-model d: the box
+    centre +- 3 exp(max log-scale) (1 + margin) leaves the box of m and overlaps the box of d. ``lo``/``hi``: (M,3).
+
+    ``native_mask``: one pass of the mask kernel (``csrc/rgs_border.cu``, ``rgs_border.h``) instead of boolean-mask
+    gathers per destination; default: on for CPU stores, on CUDA only with ``RGS_BORDER_SELECT=native``."""
+    M = int(lo.shape[0])
+    out: dict[int, torch.Tensor] = {}
+    if store.count == 0 or M < 2:
+        return out
+    v = store.views()
+    if native_mask is None:
+        native_mask = (store.device.type == "cpu" or os.environ.get("RGS_BORDER_SELECT", "torch") == "native") and M <= 63
+    if native_mask:
+        boxes = torch.cat([lo, hi], dim=1).to(store.device, torch.float32).contiguous()
+        masks = torch.empty(store.count, dtype=torch.int64, device=store.device)
+        native.call("border_mask", store.device, v["xyz"], v["scale"], store.count, boxes, M, m, float(margin), masks,
+                    sig="ppipiifpp")
+        cand = masks.nonzero(as_tuple=True)[0]
+        if cand.numel():
+            cm = masks[cand]
+            for d in range(M):
+                if d != m:
+                    idx = cand[((cm >> d) & 1).bool()]
+                    if idx.numel():
+                        out[d] = idx.contiguous()
+        return out
+    ext = 3.0 * torch.exp(v["scale"]).max(dim=1, keepdim=True).values * (1.0 + margin)
+    blo, bhi = v["xyz"] - ext, v["xyz"] + ext
+    cand = ((blo <= lo[m]) | (bhi > hi[m])).any(dim=1).nonzero(as_tuple=True)[0]
+    if cand.numel() == 0:
+        return out
+    clo, chi = blo[cand], bhi[cand]
+    for d in range(M):
+        if d != m:
+            idx = cand[((chi > lo[d]) & (clo <= hi[d])).all(dim=1)]
+            if idx.numel():
+                out[d] = idx.contiguous()
+    return out
 
 
 class BorderExchange:
@@ -57,22 +102,9 @@ class BorderExchange:
         for m, st in stores.items():
             if st.count == 0:
                 continue
-            v = st.views()
-            ext = 3.0 * torch.exp(v["scale"]).max(dim=1, keepdim=True).values
-            lo, hi = v["xyz"] - ext, v["xyz"] + ext
-            crossing = ((lo <= self.lo[m]) | (hi > self.hi[m])).any(dim=1)
-            cand = crossing.nonzero(as_tuple=True)[0]
-            if cand.numel() == 0:
-                continue
-            clo, chi = lo[cand], hi[cand]
-            for d in range(self.M):
-                if d == m:
-                    continue
-                hit = ((chi > self.lo[d]) & (clo <= self.hi[d])).all(dim=1)
-                idx = cand[hit]
-                if idx.numel():
-                    self._index[(m, d)] = idx
-                    counts[m, d] = idx.numel()
+            for d, idx in select_border(st, m, self.lo, self.hi).items():
+                self._index[(m, d)] = idx
+                counts[m, d] = idx.numel()
         if self.world > 1:
             dist.all_reduce(counts, group=self.group)
         self._counts = counts.cpu()

@@ -26,6 +26,7 @@ import torch.distributed as dist
 from ..models.gaussians import NAMES, WIDTHS, GaussianStore
 from ..ops import native
 from ..ops.rasterize import Segment
+from .border import select_border
 from .peer import PeerRegion
 
 ROW_FLOATS = 59
@@ -84,20 +85,9 @@ class PeerBorderExchange:
         for m, st in stores.items():
             if st.count == 0:
                 continue
-            v = st.views()
-            ext = 3.0 * torch.exp(v["scale"]).max(dim=1, keepdim=True).values * (1.0 + self.margin)
-            lo, hi = v["xyz"] - ext, v["xyz"] + ext
-            cand = ((lo <= self.lo[m]) | (hi > self.hi[m])).any(dim=1).nonzero(as_tuple=True)[0]
-            if cand.numel() == 0:
-                continue
-            clo, chi = lo[cand], hi[cand]
-            for d in range(self.M):
-                if d == m:
-                    continue
-                idx = cand[((chi > self.lo[d]) & (clo <= self.hi[d])).all(dim=1)]
-                if idx.numel():
-                    self._index[(m, d)] = idx.contiguous()
-                    counts[m, d] = idx.numel()
+            for d, idx in select_border(st, m, self.lo, self.hi, self.margin).items():
+                self._index[(m, d)] = idx
+                counts[m, d] = idx.numel()
         if self.world > 1:
             dist.all_reduce(counts, group=self.group)
         self._counts = counts.cpu()

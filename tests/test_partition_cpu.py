@@ -160,3 +160,28 @@ def test_cost_estimate_tracks_instance_counts():
     real = np.array([native_render(g, cam, 1, device="cpu")[1].n_inst for cam in cams], dtype=np.float64)
     assert np.corrcoef(est, real)[0, 1] > 0.9
     assert (est >= 0.8 * real).all() and (est <= 4.0 * real).all()
+
+
+def test_border_mask_kernel_matches_boolean_mask_selection():
+    """One pass of the native selection (a destination bit mask per Gaussian) == per-destination boolean-mask gathers."""
+    import torch
+    from retinags_b200.data import synthetic
+    from retinags_b200.models.gaussians import GaussianStore
+    from retinags_b200.parallel.border import select_border
+    g = synthetic.uniform_gaussians(6000, 3, sh_degree=1, log_scale_mean=-2.0)
+    inf = float("inf")
+    lo = torch.tensor([[-inf, -inf, -inf], [0.0, -inf, -inf], [-inf, 0.0, -inf], [0.0, 0.0, -inf]])
+    hi = torch.tensor([[0.0, 0.0, inf], [inf, 0.0, inf], [0.0, inf, inf], [inf, inf, inf]])
+    total = 0
+    for m in range(4):
+        inside = ((g["xyz"] > lo[m]) & (g["xyz"] <= hi[m])).all(dim=1)
+        st = GaussianStore(int(inside.sum()), "cpu", 1, lo[m].tolist(), hi[m].tolist(), m)
+        st.set_params({k: v[inside] for k, v in g.items()})
+        for margin in (0.0, 0.05):
+            a = select_border(st, m, lo, hi, margin, native_mask=True)
+            b = select_border(st, m, lo, hi, margin, native_mask=False)
+            assert sorted(a) == sorted(b)
+            for d in a:
+                assert torch.equal(a[d], b[d])
+                total += int(a[d].numel())
+    assert total > 100
