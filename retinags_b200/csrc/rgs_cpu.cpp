@@ -423,6 +423,134 @@ int rgs_cpu_ssim_bwd(const float* img, const float* gt, const float* dmaps, int6
     return 0;
 }
 
+// ---------------------------------------------------------------------------------------------
+// CPU twins of the two-slab forward (rgs_cuda_bin_slab, rgs_cuda_blend_fwd_slab, rgs_cuda_blend_bwd_slab): the same
+// contract (regions of the instance buffers, counter words, absolute ranges, state carried in out / depth /
+// n_contrib with the finished flag in the top bit, tile_done bytes), written as plain loops. They let the host-side
+// logic around the slabs (capacities, regrow, mode switching) run in tests without a GPU.
+// ---------------------------------------------------------------------------------------------
+int rgs_cpu_bin_slab(const RgsCamera* cam, const uint32_t* slot_depth, const uint32_t* slot_rect, uint32_t* slot_cnt,
+                     int64_t cap_vis, uint32_t*, uint32_t* vis_va, uint32_t*, uint32_t*, uint32_t* inst_keys,
+                     uint32_t* inst_vals, uint32_t*, uint32_t*, int64_t region_off, int64_t region_cap, int32_t* counters,
+                     int64_t num_tiles, int32_t* ranges, uint32_t*, int64_t, int64_t slab, int64_t frac256,
+                     const uint8_t* tile_done, uint32_t*, void*) {
+    if (num_tiles > 65536 || cam->tight_rect >= 2 || slab < 0 || slab > 1) return 15;
+    const int which = slab == 0 ? RGS_CNT_INST : RGS_CNT_INST2;
+    std::memset(ranges, 0, num_tiles * 8);
+    counters[which] = 0;
+    if (counters[RGS_CNT_OVERFLOW]) return 0;
+    const int64_t n = std::min<int64_t>(counters[RGS_CNT_VIS], cap_vis);
+    uint32_t* order = vis_va;  // the sorted slot order lives where the CUDA sort leaves it
+    if (slab == 0) {
+        std::iota(order, order + n, 0u);
+        std::stable_sort(order, order + n, [&](uint32_t a, uint32_t b) { return slot_depth[a] < slot_depth[b]; });
+    }
+    const int64_t seg = 1024, nseg = (n + seg - 1) / seg;
+    int64_t split = std::min<int64_t>(nseg, ((n * frac256) >> 8) / seg);
+    const int64_t i0 = (slab == 0 ? 0 : split) * seg, i1 = std::min<int64_t>(n, (slab == 0 ? split : nseg) * seg);
+    const int tiles_x = cam->tiles_x;
+    std::vector<std::pair<uint32_t, uint32_t>> inst;
+    for (int64_t i = i0; i < i1; ++i) {
+        const uint32_t s = order[i], lo = slot_rect[2 * s], hi = slot_rect[2 * s + 1];
+        uint32_t c = 0;
+        for (uint32_t y = lo >> 16; y < (hi >> 16); ++y)
+            for (uint32_t x = lo & 0xffff; x < (hi & 0xffff); ++x) {
+                const uint32_t t = y * (uint32_t)tiles_x + x;
+                if (slab == 1 && tile_done[t]) continue;
+                if (slab == 0 && slot_cnt[s] == 0) continue;
+                inst.emplace_back(t, s);
+                ++c;
+            }
+        if (slab == 1) slot_cnt[s] = c;
+    }
+    counters[which] = (int32_t)std::min<size_t>(inst.size(), 0x7fffffff);
+    if ((int64_t)inst.size() > region_cap) { counters[RGS_CNT_OVERFLOW] = 1; return 0; }
+    std::stable_sort(inst.begin(), inst.end(),
+                     [](const std::pair<uint32_t, uint32_t>& a, const std::pair<uint32_t, uint32_t>& b) { return a.first < b.first; });
+    const int64_t m = (int64_t)inst.size();
+    for (int64_t i = 0; i < m; ++i) {
+        inst_keys[region_off + i] = inst[i].first; inst_vals[region_off + i] = inst[i].second;
+        const uint32_t t = inst[i].first;
+        if (i == 0 || inst[i - 1].first != t) ranges[2 * t] = (int32_t)(region_off + i);
+        if (i == m - 1 || inst[i + 1].first != t) ranges[2 * t + 1] = (int32_t)(region_off + i + 1);
+    }
+    return 0;
+}
+
+int rgs_cpu_blend_fwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const int32_t* ranges_b, const uint32_t* vals,
+                           const RgsSplat* splats, float* out, float* depth, int32_t* n_contrib, int32_t* counters,
+                           uint8_t* tile_done, int64_t, int64_t mode, int64_t n_dst, const int32_t* row0, const int32_t* row1,
+                           float* const* dst, void*) {
+    if (mode != 1 && mode != 2) return 15;
+    const int W = cam->W, H = cam->H;
+    const bool blank = counters[RGS_CNT_OVERFLOW] != 0;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int tile = 0; tile < cam->tiles_x * cam->tiles_y; ++tile) {
+        const int tx = tile % cam->tiles_x, ty = tile / cam->tiles_x;
+        const int len_a = blank ? 0 : ranges_a[2 * tile + 1] - ranges_a[2 * tile];
+        const int r0 = blank ? 0 : (mode == 1 ? ranges_a[2 * tile] : ranges_b[2 * tile]);
+        const int r1 = blank ? 0 : (mode == 1 ? ranges_a[2 * tile + 1] : ranges_b[2 * tile + 1]);
+        bool all_done = true;
+        for (int ly = 0; ly < RGS_TILE; ++ly)
+            for (int lx = 0; lx < RGS_TILE; ++lx) {
+                const int x = tx * RGS_TILE + lx, y = ty * RGS_TILE + ly;
+                if (x >= W || y >= H) continue;
+                const int64_t pid = (int64_t)y * W + x;
+                RgsPixelRay ray; rgs_pixel_ray(*cam, (float)x, (float)y, ray);
+                RgsPixelState st; rgs_pixel_init(st);
+                if (mode == 2) {
+                    st.C[0] = out[4 * pid]; st.C[1] = out[4 * pid + 1]; st.C[2] = out[4 * pid + 2]; st.T = out[4 * pid + 3];
+                    if (depth) st.D = depth[pid];
+                    const uint32_t nc = (uint32_t)n_contrib[pid];
+                    st.last = (int)(nc & 0x7fffffffu); st.done = (int)(nc >> 31);
+                }
+                for (int i = r0; i < r1 && !st.done; ++i) {
+                    st.contributor = (mode == 2 ? len_a : 0) + (i - r0);
+                    rgs_blend_fwd_step(*cam, ray, (float)x, (float)y, splats[vals[i]], st);
+                }
+                out[4 * pid] = st.C[0]; out[4 * pid + 1] = st.C[1]; out[4 * pid + 2] = st.C[2]; out[4 * pid + 3] = st.T;
+                if (depth) depth[pid] = st.D;
+                n_contrib[pid] = mode == 1 ? (int32_t)((uint32_t)st.last | ((uint32_t)(st.done ? 1 : 0) << 31)) : st.last;
+                all_done = all_done && st.done;
+            }
+        if (mode == 1) tile_done[tile] = all_done ? 1 : 0;
+    }
+    if (mode == 2)
+        for (int64_t o = 0; o < n_dst; ++o)
+            if (row1[o] > row0[o])
+                std::memcpy(dst[o], out + (int64_t)row0[o] * W * 4, (size_t)(row1[o] - row0[o]) * W * 16);
+    return 0;
+}
+
+int rgs_cpu_blend_bwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const int32_t* ranges_b, int64_t,
+                           const uint32_t* vals, const RgsSplat* splats, const float* out, const int32_t* n_contrib,
+                           const float* grad_out, RgsSplatGrad* splat_grads, int32_t* counters, int64_t*, int64_t, void*) {
+    const int W = cam->W, H = cam->H;
+    if (counters[RGS_CNT_OVERFLOW]) return 0;
+    for (int tile = 0; tile < cam->tiles_x * cam->tiles_y; ++tile) {
+        const int tx = tile % cam->tiles_x, ty = tile / cam->tiles_x;
+        const int a0 = ranges_a[2 * tile], len_a = ranges_a[2 * tile + 1] - a0, b0 = ranges_b[2 * tile];
+        for (int ly = 0; ly < RGS_TILE; ++ly)
+            for (int lx = 0; lx < RGS_TILE; ++lx) {
+                const int x = tx * RGS_TILE + lx, y = ty * RGS_TILE + ly;
+                if (x >= W || y >= H) continue;
+                const int64_t pid = (int64_t)y * W + x;
+                RgsPixelRay ray; rgs_pixel_ray(*cam, (float)x, (float)y, ray);
+                RgsPixelBwd st;
+                rgs_pixel_bwd_init(st, out[4 * pid + 3], grad_out + 4 * pid, grad_out[4 * pid + 3]);
+                for (int v = n_contrib[pid] - 1; v >= 0; --v) {  // position in the list "near range, then far range"
+                    const uint32_t slot = vals[v < len_a ? a0 + v : b0 + (v - len_a)];
+                    RgsSplatGrad g;
+                    if (!rgs_blend_bwd_step(*cam, ray, (float)x, (float)y, splats[slot], st, g)) continue;
+                    float* d = reinterpret_cast<float*>(&splat_grads[slot]);
+                    const float* src = reinterpret_cast<const float*>(&g);
+                    for (int k = 0; k < 10; ++k) d[k] += src[k];
+                }
+            }
+    }
+    return 0;
+}
+
 // The CPU backward visits pixels in a fixed order and is deterministic as it is: the fixed-point variant is the same call.
 int rgs_cpu_blend_bwd_fixed(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
                             const float* out, const int32_t* n_contrib, const float* grad_out, RgsSplatGrad* splat_grads,

@@ -208,6 +208,7 @@ class RenderTask:
         self.slabs = os.environ.get("RGS_SLABS", "0") == "1"
         self.slab_frac256 = int(os.environ.get("RGS_SLAB_FRACTION", "32"))   # share of the splats in the near slab, /256
         self._need_a = self._need_b = 0   # largest instance counts of the near / far slab seen so far
+        self._need_known = False
         self._slab_active = False    # the last forward used two slabs (the backward walks two lists)
         self._base_b = 0
         self.ranges_b = self.tile_done = self.sat = None
@@ -291,7 +292,7 @@ class RenderTask:
                                 self.splats, self.vis_ids, self.aux, self.cap_vis, bs.slot_depth, bs.slot_rect,
                                 bs.slot_cnt, self.counters, self.splat_grads)
                 tiles = cam.tiles_x * cam.tiles_y
-                self._slab_active = (self.slabs and self.device.type == "cuda" and cam.tight_rect < 2 and 64 <= tiles <= 65536)
+                self._slab_active = self.slabs and cam.tight_rect < 2 and 8 <= tiles <= 65536
                 if self._slab_active:
                     self._forward_slabs(cam, bs, dst, want_depth, push)
                     self.last_out = dst
@@ -342,7 +343,7 @@ class RenderTask:
         tiles = cam.tiles_x * cam.tiles_y
         # the near slab gets what it needed so far plus 30 %, the far slab the rest (_note_slab_counts keeps the total
         # large enough for both); before any count is known the buffers are split 40 : 60
-        want_a = int(1.3 * self._need_a) + 4096 if self._need_a else int(0.4 * self.cap_inst)
+        want_a = int(1.3 * self._need_a) + 4096 if self._need_known else int(0.4 * self.cap_inst)
         cap_a = max(1024, min(want_a, self.cap_inst - 1024)) // 4 * 4
         cap_b = self.cap_inst - cap_a
         self._base_b = cap_a
@@ -373,7 +374,8 @@ class RenderTask:
         and the buffers never shrink, so a render that overflowed fits after at most two more attempts (the far slab's
         count is only known once the near slab fitted)."""
         self._need_a, self._need_b = max(self._need_a, n_a), max(self._need_b, n_b)
-        want = int(1.3 * self._need_a) + int(1.3 * self._need_b) + 16384
+        self._need_known = True
+        want = int(1.3 * self._need_a) + int(1.3 * self._need_b) + 16384  # regions of 1.3x + 4096 and 1.3x + 12288
         if want > self.cap_inst:
             self._grow_inst(int(1.5 * (self._need_a + self._need_b)) + 16384)
 

@@ -135,3 +135,109 @@ def test_autograd_function_interface():
     vis = rasterize.GaussianRasterizer(st).markVisible(a["xyz"])
     view = torch.cat([a["xyz"], torch.ones(a["xyz"].shape[0], 1)], 1) @ torch.tensor(cam.world_view_transform)
     assert torch.equal(vis, view[:, 2] > 0.2)
+
+
+def _slab_render(g, cam, slabs, frac=32, inst_per_gaussian=4.0, min_inst=1 << 16, check=True):
+    import torch
+    from retinags_b200.ops import rasterize
+    seg = rasterize.Segment(*(g[k].contiguous() for k in ("xyz", "sh", "scale", "rot", "opacity")))
+    task = rasterize.RenderTask("cpu", inst_per_gaussian=inst_per_gaussian, min_inst=min_inst)
+    task.slabs, task.slab_frac256 = slabs, frac
+    c = rasterize.make_camera(cam, 3)
+    if check:
+        out = task.forward(c, [seg], want_depth=True, check=True).clone()
+    else:  # the training pattern: unchecked forwards, capacities adapted by poll() between steps
+        for _ in range(6):
+            out = task.forward(c, [seg], want_depth=True).clone()
+            if not task.poll()["overflow"]:
+                break
+        else:
+            raise AssertionError("capacities did not settle")
+        task.n_inst = task.poll()["n_inst"]
+    n = seg.count
+    for name, w in (("g_xyz", 3), ("g_sh", 48), ("g_scale", 3), ("g_rot", 4), ("g_opacity", 1)):
+        setattr(seg, name, torch.zeros(n, w))
+    grad = torch.randn(cam.height, cam.width, 4, generator=torch.Generator().manual_seed(2))
+    task.backward(grad, [seg])
+    grads = torch.cat([seg.g_xyz, seg.g_sh, seg.g_scale, seg.g_rot, seg.g_opacity], dim=1)
+    return out, task.n_contrib.clone(), task.depth.clone(), task.n_inst, grads
+
+
+def test_two_slab_forward_equals_single_pass_on_cpu():
+    """Near slab first, far slab only for unsaturated tiles (CPU twins of the slab entry points): identical image, depth,
+    contributor indices and gradients, fewer instances; also with buffers that start far too small, with unchecked
+    forwards whose capacities poll() adapts, and with extreme slab fractions."""
+    import torch
+    from retinags_b200.data import synthetic
+    g = synthetic.uniform_gaussians(30000, 5, sh_degree=3, log_scale_mean=-2.6)
+    g["opacity"] = g["opacity"] + 4.0
+    cam = synthetic.ring_cameras(3, 3.0, 160, 112)[1]
+    ref = _slab_render(g, cam, False)
+    assert (ref[0][..., 3] < 1e-3).float().mean() > 0.3  # the scene saturates
+    cases = [dict(frac=32), dict(frac=12), dict(frac=200), dict(frac=0), dict(frac=256),
+             dict(frac=32, inst_per_gaussian=0.01, min_inst=1024), dict(frac=12, inst_per_gaussian=0.01, min_inst=1024),
+             dict(frac=32, inst_per_gaussian=0.01, min_inst=1024, check=False)]
+    for kw in cases:
+        got = _slab_render(g, cam, True, **kw)
+        assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1]) and torch.equal(got[2], ref[2]), kw
+        assert torch.equal(got[4], ref[4]), kw
+        assert got[3] <= ref[3], kw
+    assert _slab_render(g, cam, True, frac=64)[3] < 0.8 * ref[3]
+
+
+def test_two_slab_capacities_follow_changing_views():
+    """One task, several cameras in turn, unchecked forwards: whenever poll() reports an overflow the render is repeated
+    (as the trainer's warm-up does); every settled render equals the single-pass render."""
+    import torch
+    from retinags_b200.data import synthetic
+    from retinags_b200.ops import rasterize
+    g = synthetic.uniform_gaussians(30000, 7, sh_degree=3, log_scale_mean=-2.6)
+    g["opacity"] = g["opacity"] + 4.0
+    cams = synthetic.ring_cameras(4, 3.0, 160, 112) + synthetic.ring_cameras(2, 1.2, 160, 112)
+    seg = rasterize.Segment(*(g[k].contiguous() for k in ("xyz", "sh", "scale", "rot", "opacity")))
+    slab = rasterize.RenderTask("cpu", inst_per_gaussian=0.01, min_inst=1024)
+    slab.slabs, slab.slab_frac256 = True, 48
+    single = rasterize.RenderTask("cpu")
+    renders = 0
+    for cam in cams:
+        c = rasterize.make_camera(cam, 3)
+        ref = single.forward(c, [seg], check=True).clone()
+        for _ in range(5):
+            out = slab.forward(c, [seg]).clone()
+            renders += 1
+            if not slab.poll()["overflow"]:
+                break
+        else:
+            raise AssertionError("capacities did not settle")
+        assert torch.equal(out, ref)
+        assert torch.equal(slab.n_contrib, single.n_contrib)
+    assert renders <= len(cams) + 6
+
+
+def test_training_steps_are_identical_with_two_slabs(monkeypatch):
+    """Whole training steps (two local sub-models, compositing, loss, backward, Adam) with and without the two-slab
+    forward: identical loss sums and parameters."""
+    import torch
+    from retinags_b200.bench_session import BenchSession
+
+    def run(slabs):
+        monkeypatch.setenv("RGS_SLABS", "1" if slabs else "0")
+        monkeypatch.setenv("RGS_SLAB_FRACTION", "64")
+        sess = BenchSession("cpu", 0, 1, 30000, 160, 112, batch=2, n_views=4, gt_gaussians=3000, seed=3, sh_degree=2,
+                            grid=(32, 32, 1), bvh_depth=1, scene_kind="uniform")
+        for st in sess.stores.values():
+            st.views()["opacity"].add_(3.0)  # opaque enough for tiles to saturate
+        sums = []
+        for it in range(3):
+            res = sess.engine.train_step(*sess._batch(it), sess.sh_degree, sess.lrs)
+            sess.settle()
+            sums.append(torch.stack(res.sums).clone())
+        active = any(t._slab_active for t in sess.engine._tasks.values())
+        return sums, torch.cat([st.records() for st in sess.stores.values()]), active
+
+    a, pa, used_a = run(False)
+    b, pb, used_b = run(True)
+    assert used_b and not used_a
+    for x, y in zip(a, b):
+        torch.testing.assert_close(x, y, rtol=1e-11, atol=1e-8)  # the loss sums are OpenMP reductions
+    assert torch.equal(pa, pb)
