@@ -18,10 +18,12 @@ def _session(rank, world, bvh_depth, group=None, transport="nccl"):
                         seed=3, sh_degree=1, grid=(64, 64, 1), bvh_depth=bvh_depth, scene_kind="uniform", group=group)
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, slabs=False):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    os.environ["RGS_SLABS"] = "1" if slabs else "0"
+    os.environ["RGS_SLAB_FRACTION"] = "96"
     torch.set_num_threads(2)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -45,10 +47,12 @@ def _worker(rank, world, port, out_dir):
 
 
 @pytest.mark.timeout(600)
-def test_two_ranks_match_single_rank(tmp_path):
+@pytest.mark.parametrize("slabs", [False, True])
+def test_two_ranks_match_single_rank(tmp_path, slabs):
+    """``slabs``: the ranks render with the two-slab forward (CPU twins), the single-rank reference without."""
     sys.path.insert(0, ROOT)
-    port = 29500 + os.getpid() % 2000
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    port = 29500 + os.getpid() % 2000 + (1000 if slabs else 0)
+    mp.spawn(_worker, args=(2, port, str(tmp_path), slabs), nprocs=2, join=True)
     res = [torch.load(os.path.join(tmp_path, f"rank{r}.pt"), weights_only=False) for r in range(2)]
     assert sum(sum(r["counts"].values()) for r in res) == N_GAUSS
     assert res[0]["borrowed"] > 0
