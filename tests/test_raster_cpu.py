@@ -241,3 +241,45 @@ def test_training_steps_are_identical_with_two_slabs(monkeypatch):
     for x, y in zip(a, b):
         torch.testing.assert_close(x, y, rtol=1e-11, atol=1e-8)  # the loss sums are OpenMP reductions
     assert torch.equal(pa, pb)
+
+
+def test_gradients_against_finite_differences():
+    """Central differences of a scalar function of the native render, for the parameters with the largest analytic
+    gradient of every group (raw parameters, so the activation chain rules are included)."""
+    deg = 2
+    g, cams = small_scene(n=120, seed=9, width=48, height=32)
+    cam = cams[0]
+    gen = torch.Generator().manual_seed(4)
+    weight = torch.randn(cam.height, cam.width, 4, generator=gen)
+
+    def value(params):
+        out, _, _, _ = native_render(params, cam, deg)
+        return float((out.double() * weight.double()).sum())
+
+    out, task, seg, c = native_render(g, cam, deg)
+    n = seg.count
+    for name, w in (("g_xyz", 3), ("g_sh", 48), ("g_scale", 3), ("g_rot", 4), ("g_opacity", 1)):
+        setattr(seg, name, torch.zeros(n, w))
+    task.backward(weight.contiguous(), [seg])
+    checked = 0
+    for name, key, steps in (("g_xyz", "xyz", (2e-4, 1e-3, 5e-3)), ("g_scale", "scale", (1e-3, 5e-3, 2e-2)),
+                             ("g_rot", "rot", (1e-3, 5e-3, 2e-2)), ("g_opacity", "opacity", (2e-3, 1e-2, 5e-2)),
+                             ("g_sh", "sh", (2e-3, 1e-2, 5e-2))):
+        analytic = getattr(seg, name)
+        flat = analytic.abs().flatten()
+        for idx in flat.topk(3).indices.tolist():
+            i, j = divmod(idx, analytic.shape[1])
+            an = float(analytic[i, j])
+            errs = []
+            for eps in steps:
+                plus = {k: v.clone() for k, v in g.items()}
+                minus = {k: v.clone() for k, v in g.items()}
+                plus[key][i, j] += eps
+                minus[key][i, j] -= eps
+                fd = (value(plus) - value(minus)) / (2 * eps)
+                errs.append(abs(fd - an) / max(abs(an), abs(fd), 1e-9))
+            # The render has jumps (alpha threshold 1/255, integer radius, stop rule): a jump inside [-eps, eps] spoils that
+            # difference quotient by jump / (2 eps), so one of three step sizes has to agree, not all of them.
+            assert min(errs) < 0.06, (name, i, j, an, errs)
+            checked += 1
+    assert checked == 15
