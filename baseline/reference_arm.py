@@ -31,7 +31,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 REF = os.path.join(HERE, "_ref")
 SRC = os.path.join(REF, "reference_src")
 SHIMS = os.path.join(REF, "shims")
-UPSTREAM = "/root/reference"
+# checkout of the reference to copy from when baseline/_ref/reference_src does not exist yet
+UPSTREAM = os.environ.get("RGS_REFERENCE_SRC", os.path.join(os.path.dirname(REF), "..", "..", "reference"))
 
 PLYFILE_SHIM = '''"""Minimal stand-in for the ``plyfile`` package (binary little-endian vertex elements only)."""
 import numpy as np
@@ -136,7 +137,7 @@ def available() -> str | None:
     """None when the reference arm can run, else the reason (one line)."""
     ext = glob.glob(os.path.join(REF, "diff_gaussian_rasterization_half_gaussian", "_C*.so"))
     if not ext:
-        return "reference CUDA extension not built under baseline/_ref (see DESIGN.md: reference install)"
+        return "reference CUDA extension not built under baseline/_ref (build it with TORCH_CUDA_ARCH_LIST=10.0 pip install --target baseline/_ref)"
     if not os.path.isdir(UPSTREAM) and not os.path.isdir(SRC):
         return "reference sources not present"
     return None
