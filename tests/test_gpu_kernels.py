@@ -1,4 +1,6 @@
 """sm_100a kernels against the native CPU backend / PyTorch references (needs a B200)."""
+import os
+
 import pytest
 import torch
 
@@ -9,6 +11,8 @@ from retinags_b200.ops import native, rasterize
 from retinags_b200.ops.loss import CompositeLoss
 
 pytestmark = pytest.mark.gpu
+# kernels behind an opt-in switch whose latest version has not run on a GPU: their tests are opt-in as well
+EXPERIMENTAL = os.environ.get("RGS_TEST_EXPERIMENTAL", "0") == "1"
 
 
 def _scene(n=40000, w=320, h=208, deg=3, seed=4):
@@ -169,8 +173,8 @@ def test_adam_matches_cpu():
     assert float(stores["cuda"].grads.abs().sum()) == 0.0
 
 
-@pytest.mark.skip(reason="the row-block Adam kernel (RGS_ADAM=rows) was written after the last GPU run of this build; "
-                         "parked until it has run on a GPU")
+@pytest.mark.skipif(not EXPERIMENTAL, reason="the row-block Adam kernel (RGS_ADAM=rows) has not run on a GPU yet; its test "
+                    "only runs with RGS_TEST_EXPERIMENTAL=1")
 def test_adam_row_block_variant_matches_unit_variant():
     """Both work distributions of the fused Adam give the same bits: sparse marks, dense marks, a tail that is not a
     multiple of 32 rows."""
@@ -385,8 +389,8 @@ def test_peer_region_canaries_detect_an_out_of_bounds_store():
     region.close()
 
 
-@pytest.mark.skip(reason="the two-slab forward is opt-in (RGS_SLABS=1); its buffer policy was rewritten after the last "
-                         "GPU run and has not run on a GPU since, so the test stays parked until it has")
+@pytest.mark.skipif(not EXPERIMENTAL, reason="the two-slab forward is opt-in (RGS_SLABS=1); its buffer policy was rewritten "
+                    "after its last GPU run, so its GPU test only runs with RGS_TEST_EXPERIMENTAL=1 until it has run again")
 def test_two_slab_forward_matches_single_pass_and_emits_fewer_instances():
     """Near slab first, far slab only for unsaturated tiles: same image, contributor indices and gradients as the single
     pass, fewer tile instances in a dense opaque scene."""
