@@ -210,3 +210,27 @@ def test_lpips_module_with_local_weight_files(tmp_path):
     d = float(net(a, b))
     assert d > 0 and abs(d - float(ref(a, b))) < 1e-6
     assert net(torch.stack([a, b]), torch.stack([b, b])).shape == (2,)
+
+
+def test_scannetpp_and_mill19_layouts(tmp_path):
+    """Dataset sniffing in the reference's order: a COLMAP model with ``train_test_lists.json`` is ScanNet++, one with a
+    ``test/`` folder is Mill-19 (test pictures live there, training pictures in ``train/``)."""
+    import json
+    cams = synthetic.ring_cameras(8, 3.0, 80, 60)
+    sn = tmp_path / "scannetpp"
+    _write_colmap_bin(str(sn), cams, 80, 60)
+    (sn / "train_test_lists.json").write_text(json.dumps({"train": [f"img_{i:03d}.png" for i in range(6)],
+                                                          "test": ["img_006.png", "img_007.png"]}))
+    sc = readers.read_scene(str(sn), eval_split=False)
+    assert sc.kind == "ScanNet++" and len(sc.train_cameras) == 6 and len(sc.test_cameras) == 2
+    assert sc.test_cameras[0].image_name == "img_006"
+    ml = tmp_path / "mill19"
+    _write_colmap_bin(str(ml), cams, 80, 60)
+    os.makedirs(ml / "test")
+    os.makedirs(ml / "train")
+    for i in range(8):
+        (ml / ("test" if i % 4 == 0 else "train") / f"img_{i:03d}.png").write_bytes(b"")
+    sc = readers.read_scene(str(ml))
+    assert sc.kind == "Mill19" and len(sc.test_cameras) == 2 and len(sc.train_cameras) == 6
+    assert sc.test_cameras[1].image_path.endswith(os.path.join("test", "img_004.png"))
+    assert sc.train_cameras[0].image_path.endswith(os.path.join("train", "img_001.png"))
