@@ -359,7 +359,13 @@ class Trainer:
                 cams = self._fetch(self.train_dataset, ids)
                 bs = len(cams)
                 t0 = time.perf_counter()
-                res = self.engine.train_step(cams, self.train_rlt[list(ids)], sh_deg, lrs, optimizer_step=False)
+                bg = None
+                if o.random_background:
+                    # a random background colour per step (the reference draws it in its blender when the option is
+                    # set, result_aggregator.py:256); seeded by the iteration so that every rank composites with the same
+                    gen = torch.Generator().manual_seed(1_000_003 + self.iteration)
+                    bg = tuple(torch.rand(3, generator=gen).tolist())
+                res = self.engine.train_step(cams, self.train_rlt[list(ids)], sh_deg, lrs, optimizer_step=False, background=bg)
                 # after a densification the reference's rebuilt optimiser holds no gradients, so that step
                 # updates nothing (trainer4tree_partition.py:657-666); same here
                 if not self._densify_and_reset(self.iteration, bs):
