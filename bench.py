@@ -187,6 +187,13 @@ def run_own(args):
     # share of this rank's Gaussians that have received a gradient so far (Adam streams only those rows)
     total_rows = sum(st.count for st in sess.stores.values())
     live_rows = round(sum(int(st.active[:st.count].sum()) for st in sess.stores.values()) / max(total_rows, 1), 4)
+    roofline = None
+    if phases and rank == 0:
+        from retinags_b200.bench_session import phase_roofline
+        peaks = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+        hbm = json.load(open(peaks)).get("hbm_gbs") if os.path.exists(peaks) else None
+        roofline = phase_roofline(phases, args.batch, total_rows, sess.last_info.get("n_vis") or 0, sess.last_info.get("n_inst") or 0,
+                                  int(live_rows * total_rows), args.height, args.width, sess.n_models, hbm)
     if rank == 0:
         value = args.steps * args.batch / (ms / 1e3)
         out = {
@@ -204,6 +211,7 @@ def run_own(args):
                        "tile_instances_per_step_rank0": sess.last_info.get("n_inst"),
                        "rows_with_adam_moments_rank0": live_rows, "overflow_in_timed_region": overflow},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "phases_ms_per_step_max_over_ranks": phases,
+            "roofline_rank0_of_measured": roofline,
         }
         print(json.dumps(out), flush=True)
     if world > 1:

@@ -233,3 +233,32 @@ class BenchSession:
 
     def launch_count(self) -> int:
         return native.launch_count() - self._launch_base
+
+
+def phase_roofline(phases: dict, views_per_step: int, n_gaussians: int, n_vis: int, n_inst: int, live_rows: int, height: int,
+                   width: int, partials: int, hbm_gbs: float | None) -> dict:
+    """Algorithmic bytes per step of the memory-bound phases and what they make of the measured phase times.
+
+    ``phases``: ms per step and phase (``PhaseTimer.table``); ``n_vis`` / ``n_inst``: visible splats and tile instances
+    of one step on this rank; ``live_rows``: rows the Adam kernel updates; ``partials``: partial images per view. The
+    byte counts are what the kernels must move at least (each operand once): cull 24 B per Gaussian and view, projection
+    236 B in + 110 B out per visible splat, depth sort 4 passes and tile sort 2 passes of 8-byte pairs (read + write +
+    4 B histogram read), emission 8 B per instance, compositing + loss ~32 B per pixel and partial + 160 B per pixel,
+    Adam 1416 B per live row + 2 mark bytes per row. The blend kernels are instruction-bound and have no entry.
+    Fractions are of the measured copy bandwidth (``hbm_gbs``) when it is known.
+    """
+    model = {
+        "fwd.project": views_per_step * 24.0 * n_gaussians + 346.0 * n_vis,
+        "fwd.binning": 104.0 * n_vis + 48.0 * n_inst,
+        "composite_loss": views_per_step * float(height) * width * (32.0 * partials + 160.0),
+        "adam": 1416.0 * live_rows + 2.0 * n_gaussians,
+    }
+    out = {}
+    for name, nbytes in model.items():
+        ms = phases.get(name)
+        if not ms:
+            continue
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": round(ms, 3), "algorithmic_gb": round(nbytes / 1e9, 3), "gb_per_s": round(gbs, 1),
+                     "frac_of_measured_hbm": round(gbs / hbm_gbs, 3) if hbm_gbs else None}
+    return out
