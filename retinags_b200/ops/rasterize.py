@@ -207,6 +207,7 @@ class RenderTask:
         # the rest only for tiles that are not saturated yet. Bit-identical output, fewer instances in dense scenes.
         self.slabs = os.environ.get("RGS_SLABS", "0") == "1"
         self.slab_frac256 = int(os.environ.get("RGS_SLAB_FRACTION", "32"))   # share of the splats in the near slab, /256
+        self._pending_cap = 0             # capacity that poll() asked for; applied by the next forward
         self._need_a = self._need_b = 0   # largest instance counts of the near / far slab seen so far
         self._need_known = False
         self._slab_active = False    # the last forward used two slabs (the backward walks two lists)
@@ -267,6 +268,9 @@ class RenderTask:
         self.total_count = sum(s.count for s in segments)
         self._ensure(self.total_count, H, W, want_depth)
         for attempt in range(12):
+            if self._pending_cap > self.cap_inst:  # asked for by poll() or by the previous attempt
+                self._grow_inst(self._pending_cap)
+            self._pending_cap = 0
             dst = self.out if out is None else out
             self.counters.zero_()
             base = 0
@@ -377,7 +381,7 @@ class RenderTask:
         self._need_known = True
         want = int(1.3 * self._need_a) + int(1.3 * self._need_b) + 16384  # regions of 1.3x + 4096 and 1.3x + 12288
         if want > self.cap_inst:
-            self._grow_inst(int(1.5 * (self._need_a + self._need_b)) + 16384)
+            self._pending_cap = int(1.5 * (self._need_a + self._need_b)) + 16384  # applied by the next forward attempt
 
     def _record_counters(self):
         torch.bitwise_or(self._sticky, self.counters[CNT_OVERFLOW:CNT_STATUS + 1], out=self._sticky)
@@ -416,7 +420,8 @@ class RenderTask:
         if self._slab_active:
             self._note_slab_counts(c[CNT_INST] & 0xFFFFFFFF, n_b)
         elif info["overflow"] or info["n_inst"] > 0.6 * self.cap_inst:
-            self._grow_inst(max(int(info["n_inst"] * 2.0) + 1024, self.cap_inst if info["overflow"] else 0))
+            # applied by the next forward: the lists of the last render stay valid for a backward that is still to come
+            self._pending_cap = max(int(info["n_inst"] * 2.0) + 1024, self.cap_inst if info["overflow"] else 0)
         return info
 
     # -- backward -----------------------------------------------------------------------------
