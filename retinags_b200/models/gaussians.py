@@ -33,6 +33,56 @@ def _round_cap(n: int) -> int:
     return max(4, (int(n) + 3) // 4 * 4)
 
 
+_ADAM_ROWS_OK: dict[str, bool] = {}
+
+
+def adam_rows_agrees(device) -> bool:
+    """One-off check per device: the row-block Adam kernel and the per-unit kernel, run on the same small store with
+    sparse marks, dense marks and a ragged tail, must leave every buffer identical bit for bit. The result is cached;
+    a disagreement (or any error) selects the per-unit kernel and is reported once."""
+    key = str(device)
+    if key in _ADAM_ROWS_OK:
+        return _ADAM_ROWS_OK[key]
+    _ADAM_ROWS_OK[key] = False  # also guards against re-entry while the check runs
+    try:
+        gen = torch.Generator().manual_seed(1234)
+        n = 1001
+        stores = []
+        for variant in ("units", "rows"):
+            st = GaussianStore(n, device)
+            st.adam_variant = variant
+            st.count = n
+            stores.append(st)
+        init = torch.randn(stores[0].params.shape, generator=gen)
+        for st in stores:
+            st.params.copy_(init)
+        lrs = (1.6e-4, 2.5e-3, 1.25e-4, 5e-3, 1e-3, 5e-2)
+        for step in range(4):
+            grads = torch.randn(stores[0].grads.shape, generator=gen) * 1e-3
+            rows = torch.arange(0, n, 7 if step < 2 else 1)
+            for st in stores:
+                st.grads.copy_(grads)
+                keep = torch.zeros(st.cap, dtype=torch.bool, device=st.device)
+                keep[rows.to(st.device)] = True
+                for view in dict(GaussianStore._views(st.grads, st.cap, st.cap)).values():
+                    view[~keep] = 0
+                st.mark_touched(rows.to(st.device))
+                st.adam_step(lrs)
+        for st in stores:  # and one dense step without marks
+            st.grads.copy_(grads)
+            st.adam_step(lrs, zero_grad=False)
+        a, b = stores
+        same = all(torch.equal(getattr(a, w), getattr(b, w)) for w in ("params", "grads", "exp_avg", "exp_avg_sq", "active"))
+        _ADAM_ROWS_OK[key] = bool(same)
+        if not same:
+            import warnings
+            warnings.warn("the row-block Adam kernel disagrees with the per-unit kernel on this device; using the latter")
+    except Exception as exc:  # keep training on the validated kernel
+        import warnings
+        warnings.warn(f"the check of the row-block Adam kernel failed ({exc!r}); using the per-unit kernel")
+    return _ADAM_ROWS_OK[key]
+
+
 class GaussianStore:
     def __init__(self, capacity: int, device, sh_degree: int = 3, box_lo=None, box_hi=None, model_id: int = 0):
         self.device = torch.device(device)
@@ -46,9 +96,10 @@ class GaussianStore:
         self.step = 0
         self.params = self.grads = self.exp_avg = self.exp_avg_sq = None
         self.grad_accum = self.denom = self.max_radii = None
-        # "units": one thread per 128-bit unit (default); "rows": a warp per 32 rows that skips dead rows after one
-        # ballot (csrc/rgs_model.cu: rgs_adam_rows_kernel; written for models in which few rows are live)
-        self.adam_variant = os.environ.get("RGS_ADAM", "units")
+        # "units": one thread per 128-bit unit; "rows": a warp per 32 rows that skips dead rows after one ballot
+        # (csrc/rgs_model.cu: rgs_adam_rows_kernel, much cheaper when few rows are live); "auto": "rows" on CUDA devices
+        # on which a one-off comparison of the two kernels agreed bit for bit, "units" otherwise
+        self.adam_variant = os.environ.get("RGS_ADAM", "auto")
         self.touched = None  # uint8 per row: a gradient was written this step (rows with 0 hold zero gradients)
         self.active = None   # uint8 per row: the Adam moments may be non-zero (rows with 0 hold zero moments)
         self._alloc(_round_cap(capacity))
@@ -224,7 +275,10 @@ class GaussianStore:
             return
         import ctypes
         arr = (ctypes.c_double * 6)(*[float(x) for x in lrs])
-        native.call("adam_rows" if self.adam_variant == "rows" else "adam", self.device, self.params, self.grads, self.exp_avg, self.exp_avg_sq, self.count, self.cap, arr,
+        variant = self.adam_variant
+        if variant == "auto":
+            variant = "rows" if (self.device.type == "cuda" and adam_rows_agrees(self.device)) else "units"
+        native.call("adam_rows" if variant == "rows" else "adam", self.device, self.params, self.grads, self.exp_avg, self.exp_avg_sq, self.count, self.cap, arr,
                     float(beta1), float(beta2), float(eps), self.step, 1 if zero_grad else 0, skip,
                     self.touched if zero_grad else None, self.active if zero_grad else None)
         if zero_grad:
