@@ -345,9 +345,10 @@ class RenderTask:
 
     def _forward_slabs(self, cam: RgsCamera, bs: BinScratch, dst: torch.Tensor, want_depth: bool, push):
         tiles = cam.tiles_x * cam.tiles_y
-        # the near slab gets what it needed so far plus 30 %, the far slab the rest (_note_slab_counts keeps the total
-        # large enough for both); before any count is known the buffers are split 40 : 60
-        want_a = int(1.3 * self._need_a) + 4096 if self._need_known else int(0.4 * self.cap_inst)
+        # The buffers are shared in proportion to the largest needs seen so far, so that both slabs keep the same head
+        # room (_note_slab_counts keeps the total at 1.3x of their sum or more); before any count is known: 40 : 60.
+        share = (self._need_a + 2048.0) / (self._need_a + self._need_b + 4096.0) if self._need_known else 0.4
+        want_a = int(self.cap_inst * min(0.95, max(0.05, share)))
         cap_a = max(1024, min(want_a, self.cap_inst - 1024)) // 4 * 4
         cap_b = self.cap_inst - cap_a
         self._base_b = cap_a
@@ -379,9 +380,9 @@ class RenderTask:
         count is only known once the near slab fitted)."""
         self._need_a, self._need_b = max(self._need_a, n_a), max(self._need_b, n_b)
         self._need_known = True
-        want = int(1.3 * self._need_a) + int(1.3 * self._need_b) + 16384  # regions of 1.3x + 4096 and 1.3x + 12288
+        want = int(1.4 * (self._need_a + self._need_b)) + 65536
         if want > self.cap_inst:
-            self._pending_cap = int(1.5 * (self._need_a + self._need_b)) + 16384  # applied by the next forward attempt
+            self._pending_cap = int(2.0 * (self._need_a + self._need_b)) + 65536  # applied by the next forward attempt
 
     def _record_counters(self):
         torch.bitwise_or(self._sticky, self.counters[CNT_OVERFLOW:CNT_STATUS + 1], out=self._sticky)
