@@ -39,6 +39,9 @@ def parse_args():
                     help="steps between recomputations of the border-Gaussian selection (the rows are re-sent every step)")
     ap.add_argument("--bvh-depth", type=int, default=None,
                     help="2^depth sub-models (default: one per GPU); more sub-models than GPUs are spread round-robin")
+    ap.add_argument("--slabs", type=int, default=None, metavar="N",
+                    help="two-slab forward with the nearest N/256 of the splats in the first slab (same as RGS_SLABS=1 "
+                         "RGS_SLAB_FRACTION=N); experimental")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--phases", action="store_true", help="also time the phases of a step (extra loop, after the timed one)")
     ap.add_argument("--trace", default="", help="with --phases: write a Chrome trace of the phase loop to <path>.rank<r>.json")
@@ -112,6 +115,8 @@ def run_own(args):
 
     from retinags_b200.bench_session import BenchSession
 
+    if args.slabs is not None:
+        os.environ["RGS_SLABS"], os.environ["RGS_SLAB_FRACTION"] = "1", str(args.slabs)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -209,7 +214,8 @@ def run_own(args):
                        "l2": "inputs larger than L2 (parameter blocks of >= 1.8 GB per GPU are streamed every step)",
                        "visible_splats_per_step_rank0": sess.last_info.get("n_vis"),
                        "tile_instances_per_step_rank0": sess.last_info.get("n_inst"),
-                       "rows_with_adam_moments_rank0": live_rows, "overflow_in_timed_region": overflow},
+                       "rows_with_adam_moments_rank0": live_rows, "overflow_in_timed_region": overflow,
+                       "two_slab_forward": os.environ.get("RGS_SLABS", "0") == "1"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "phases_ms_per_step_max_over_ranks": phases,
             "roofline_rank0_of_measured": roofline,
         }
