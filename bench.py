@@ -44,6 +44,8 @@ def parse_args():
                          "RGS_SLAB_FRACTION=N); experimental")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--phases", action="store_true", help="also time the phases of a step (extra loop, after the timed one)")
+    ap.add_argument("--task-times", default="", help="with --phases: write the per-(camera, sub-model) render times of every "
+                    "rank to <path>.rank<r>.json")
     ap.add_argument("--trace", default="", help="with --phases: write a Chrome trace of the phase loop to <path>.rank<r>.json")
     return ap.parse_args()
 
@@ -183,8 +185,17 @@ def run_own(args):
         sess.engine.timer.enabled = True
         sess.engine.timer.reset()
         sess.engine.timer.trace = bool(args.trace)
+        sess.engine.task_detail = bool(args.task_times)
         for i in range(args.steps):
             sess.step(args.warmup + i)
+        if args.task_times:  # per-rank tables: read before the max-over-ranks reduction
+            tot = sess.engine.timer.collect()
+            per_rank = {k: (v if k.startswith("task.") else v / args.steps) for k, v in tot.items()}  # a task occurs once
+            with open(f"{args.task_times}.rank{rank}.json", "w") as f:
+                json.dump({"rank": rank, "world": world, "models": sorted(sess.stores), "ms_per_step": per_rank,
+                           "relation": [[int(x) for x in row] for row in sess.relation.tolist()]}, f)
+            for k in [k for k in tot if k.startswith("task.")]:  # the names differ from rank to rank: keep them out
+                del sess.engine.timer.totals[k]                   # of the reduction over ranks
         phases = sess.engine.timer.table(args.steps)
         if args.trace:
             sess.engine.timer.export_chrome_trace(f"{args.trace}.rank{rank}.json", rank)

@@ -73,7 +73,7 @@ def build_cpu(force: bool = False) -> Path:
     sources = [CSRC / s for s in CPU_SOURCES if (CSRC / s).exists()]
     if force or _stale(target, sources):
         tmp = target.with_suffix(f".tmp{os.getpid()}.so")
-        _run(["g++", "-O2", "-std=c++17", "-fopenmp", "-shared", "-fPIC", "-I", str(CSRC), "-o", str(tmp)]
+        _run(["g++", "-O2", "-std=c++17", "-ffp-contract=off", "-fopenmp", "-shared", "-fPIC", "-I", str(CSRC), "-o", str(tmp)]
              + [str(s) for s in sources])
         os.replace(tmp, target)
         target.with_suffix(".sha1").write_text(_digest(sources + _headers()))

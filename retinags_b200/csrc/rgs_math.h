@@ -618,9 +618,23 @@ RGS_HD bool rgs_blend_bwd_step(const RgsCamera& cam, const RgsPixelRay& ray, flo
 RGS_HD void rgs_adam_elem(float& p, float g, float& m, float& v, float lr, float beta1, float beta2, float eps,
                           float inv_bc1, float inv_bc2_sqrt) {
     // torch.optim.Adam: m = b1 m + (1-b1) g ; v = b2 v + (1-b2) g^2 ;
-    // p -= lr / bc1 * m / (sqrt(v)/sqrt(bc2) + eps); the two bias corrections arrive as reciprocals
-    m = beta1 * m + (1.0f - beta1) * g;
-    v = beta2 * v + (1.0f - beta2) * g * g;
-    const float denom = sqrtf(v) * inv_bc2_sqrt + eps;
-    p -= (lr * inv_bc1) * (m / denom);
+    // p -= lr / bc1 * m / (sqrt(v)/sqrt(bc2) + eps); the two bias corrections arrive as reciprocals.
+    // Every product and sum is rounded on its own: left to the compiler, a*b + c*d is contracted into a fused
+    // multiply-add around either product, and the choice differs between the kernels this function is inlined
+    // into (and from the host build), so that two work distributions of the same update disagreed in the last bit.
+#ifdef __CUDA_ARCH__
+    m = __fadd_rn(__fmul_rn(beta1, m), __fmul_rn(1.0f - beta1, g));
+    v = __fadd_rn(__fmul_rn(beta2, v), __fmul_rn(__fmul_rn(1.0f - beta2, g), g));
+    const float denom = __fadd_rn(__fmul_rn(__fsqrt_rn(v), inv_bc2_sqrt), eps);
+    p = __fsub_rn(p, __fmul_rn(__fmul_rn(lr, inv_bc1), __fdiv_rn(m, denom)));
+#else
+    const float a = beta1 * m, b = (1.0f - beta1) * g;
+    m = a + b;
+    const float c = beta2 * v, d = ((1.0f - beta2) * g) * g;
+    v = c + d;
+    const float e = sqrtf(v) * inv_bc2_sqrt;
+    const float denom = e + eps;
+    const float step = (lr * inv_bc1) * (m / denom);
+    p = p - step;
+#endif
 }

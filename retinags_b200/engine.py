@@ -10,6 +10,7 @@ blocking exchange phases reduced to two and no host synchronisation inside a ste
 """
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass, field
 
 import torch
@@ -44,6 +45,7 @@ class StepEngine:
         self.tight_rect = tight_rect
         self.borrow = borrow  # optional BorderExchange (parallel/border.py)
         self.timer = PhaseTimer(self.device, enabled=False)
+        self.task_detail = False
         # debug aids (the reference has ``pipe.debug``: a device sync after every launch plus a dump of the rasteriser
         # inputs when it throws, and ``--detect_anomaly`` for NaN hunting; its trainer never switches the former on)
         self.debug = False            # synchronise and read every task's status word after each phase of a step
@@ -53,6 +55,13 @@ class StepEngine:
         self._grads: dict = {}
         self._closs: dict = {}
         self._gt: dict = {}
+
+    def _task_phase(self, kind: str, cam: Camera, mid: int):
+        """With ``task_detail`` the phase timer also keeps one entry per (camera, sub-model) render:
+        ``task.<fwd|bwd>:<camera uid>:<sub-model>`` -- the cost matrix behind the load-balance decisions."""
+        if self.task_detail and self.timer.enabled:
+            return self.timer.phase(f"task.{kind}:{cam.uid}:{mid}")
+        return contextlib.nullcontext()
 
     # -- pools ----------------------------------------------------------------------------------
     def _task(self, view: int, mid: int) -> RenderTask:
@@ -128,8 +137,9 @@ class StepEngine:
                 c = make_camera(cam, sh_degree, st.box_lo, st.box_hi, raw_params=True, tight_rect=self.tight_rect)
                 task = self._task(p.view, m)
                 push = self.transport.push_plan(p, m) if hasattr(self.transport, "push_plan") else None
-                local_out[p.view][m] = task.forward(c, self._segments(m, False), want_depth=want_depth, check=check,
-                                                    push=push)
+                with self._task_phase("fwd", cam, m):
+                    local_out[p.view][m] = task.forward(c, self._segments(m, False), want_depth=want_depth, check=check,
+                                                        push=push)
         return local_out
 
     def render(self, cams: list[Camera], relations, sh_degree: int, background=None):
@@ -191,10 +201,11 @@ class StepEngine:
         with T("return_grads"):
             self.transport.return_grads(plans, gslots, local_grad)
         with T("render_backward"):
-            for p in plans:
+            for p, cam in zip(plans, cams):
                 for m, r in zip(p.models, p.ranks):
                     if r == self.rank:
-                        self._task(p.view, m).backward(local_grad[p.view][m], self._segments(m, True))
+                        with self._task_phase("bwd", cam, m):
+                            self._task(p.view, m).backward(local_grad[p.view][m], self._segments(m, True))
         if self.debug:
             self._debug_check("backward", cams)
         if self.detect_anomaly:

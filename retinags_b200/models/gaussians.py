@@ -72,15 +72,35 @@ def adam_rows_agrees(device) -> bool:
             st.grads.copy_(grads)
             st.adam_step(lrs, zero_grad=False)
         a, b = stores
-        same = all(torch.equal(getattr(a, w), getattr(b, w)) for w in ("params", "grads", "exp_avg", "exp_avg_sq", "active"))
-        _ADAM_ROWS_OK[key] = bool(same)
-        if not same:
+        diff = first_store_difference(a, b)
+        _ADAM_ROWS_OK[key] = diff is None
+        if diff is not None:
             import warnings
-            warnings.warn("the row-block Adam kernel disagrees with the per-unit kernel on this device; using the latter")
+            warnings.warn("the row-block Adam kernel disagrees with the per-unit kernel on this device; using the latter "
+                          f"(first difference: {diff})")
     except Exception as exc:  # keep training on the validated kernel
         import warnings
         warnings.warn(f"the check of the row-block Adam kernel failed ({exc!r}); using the per-unit kernel")
     return _ADAM_ROWS_OK[key]
+
+
+def first_store_difference(a: "GaussianStore", b: "GaussianStore") -> str | None:
+    """Where two stores of equal shape first differ bit for bit: buffer, column group, row, column and the two bit
+    patterns; ``None`` when parameters, gradients, both moments and the ``active`` marks are identical."""
+    for which in ("params", "grads", "exp_avg", "exp_avg_sq"):
+        va, vb = a.views(which), b.views(which)
+        for name in NAMES:
+            xa, xb = va[name].contiguous().view(torch.int32), vb[name].contiguous().view(torch.int32)
+            ne = (xa != xb)
+            if bool(ne.any()):
+                row, col = [int(x) for x in ne.nonzero()[0]]
+                return (f"{which}.{name} row {row} column {col}: {int(xa[row, col]) & 0xFFFFFFFF:#010x} vs "
+                        f"{int(xb[row, col]) & 0xFFFFFFFF:#010x} ({int(ne.sum())} of {ne.numel()} words differ)")
+    ne = a.active[:a.count] != b.active[:b.count]
+    if bool(ne.any()):
+        row = int(ne.nonzero()[0])
+        return f"active row {row}: {int(a.active[row])} vs {int(b.active[row])}"
+    return None
 
 
 class GaussianStore:
