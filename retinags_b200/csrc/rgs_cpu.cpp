@@ -278,12 +278,21 @@ int rgs_cpu_scatter_radii(const int32_t* counters, const int32_t* vis_ids, const
 
 // Fused Adam over the grouped parameter block. The block holds five groups of `cap` rows each:
 // xyz(3) sh(48) scale(3) rot(4) opacity(1); only the first `count` rows of each group are live.
-// `skip` (optional int32) != 0 turns the whole update into a no-op (overflow-guarded commit).
+// `skip` (optional counter block) with a non-zero overflow word drops the update and clears the step's gradients.
 int rgs_cpu_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t cap, const double* lrs,
                  double beta1, double beta2, double eps, int64_t step, int64_t zero_grad, const int32_t* skip,
                  const uint8_t* touched, uint8_t* active, void*) {
-    if (skip && skip[RGS_CNT_OVERFLOW]) return 0;
     const int widths[5] = {3, 48, 3, 4, 1};
+    if (skip && skip[RGS_CNT_OVERFLOW]) {  // dropped step: no update, but the gradients that were written are cleared
+        int64_t goff = 0;
+        for (int grp = 0; grp < 5 && zero_grad; ++grp) {
+            const int w = widths[grp];
+            for (int64_t e = 0; e < count * w; ++e)
+                if (!touched || touched[e / w]) g[goff + e] = 0.f;
+            goff += cap * w;
+        }
+        return 0;
+    }
     float bc1 = (float)(1.0 / (1.0 - std::pow(beta1, (double)step)));
     float bc2s = (float)(1.0 / std::sqrt(1.0 - std::pow(beta2, (double)step)));
     int64_t off = 0;

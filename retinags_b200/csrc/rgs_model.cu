@@ -105,6 +105,20 @@ __device__ __forceinline__ void adam_row_vec(float* __restrict__ p, float* __res
     if (zero_grad && any) *reinterpret_cast<float4*>(g + base) = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
+// A step whose forward overflowed its instance buffers rendered garbage: its update is dropped on every rank. The
+// gradients that were written must still be cleared, or the invariant "rows without the touched mark hold zero
+// gradients" would break when the host clears the marks.
+__device__ __forceinline__ void adam_drop_gradients(float* __restrict__ g, int64_t count, int64_t cap,
+                                                    const uint8_t* __restrict__ touched) {
+    const int64_t off[5] = {0, cap * 3, cap * 51, cap * 54, cap * 58};
+    const int wid[5] = {3, 48, 3, 4, 1};
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < count; r += (int64_t)gridDim.x * blockDim.x) {
+        if (touched && !touched[r]) continue;
+        for (int grp = 0; grp < 5; ++grp)
+            for (int c = 0; c < wid[grp]; ++c) g[off[grp] + r * wid[grp] + c] = 0.f;
+    }
+}
+
 __global__ void __launch_bounds__(256) rgs_adam_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
                                                        float* __restrict__ v, int64_t count, int64_t cap,
                                                        const __grid_constant__ RgsLrTable lrs, float beta1, float beta2,
@@ -112,7 +126,10 @@ __global__ void __launch_bounds__(256) rgs_adam_kernel(float* __restrict__ p, fl
                                                        const uint32_t* __restrict__ skip,
                                                        const uint8_t* __restrict__ touched,
                                                        uint8_t* __restrict__ active) {
-    if (skip && skip[RGS_CNT_OVERFLOW]) return;
+    if (skip && skip[RGS_CNT_OVERFLOW]) {
+        if (zero_grad) adam_drop_gradients(g, count, cap, touched);
+        return;
+    }
     // vector ranges of the five groups: xyz(3) sh(48) scale(3) rot(4) opacity(1)
     const int64_t n0 = (count * 3 + 3) / 4, n1 = count * 12, n2 = n0, n3 = count, n4 = (count + 3) / 4;
     const int64_t v1 = n0, v2 = v1 + n1, v3 = v2 + n2, v4 = v3 + n3, tv = v4 + n4;
@@ -185,7 +202,10 @@ __global__ void __launch_bounds__(256) rgs_adam_rows_kernel(float* __restrict__ 
                                                             float eps, float bc1, float bc2s, int zero_grad,
                                                             const uint32_t* __restrict__ skip,
                                                             const uint8_t* __restrict__ touched, uint8_t* __restrict__ active) {
-    if (skip && skip[RGS_CNT_OVERFLOW]) return;
+    if (skip && skip[RGS_CNT_OVERFLOW]) {
+        if (zero_grad) adam_drop_gradients(g, count, cap, touched);
+        return;
+    }
     const int64_t o1 = cap * 3, o2 = o1 + cap * 48, o3 = o2 + cap * 3, o4 = o3 + cap * 4;
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;

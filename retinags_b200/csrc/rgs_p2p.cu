@@ -17,30 +17,46 @@
 #include "rgs_api.h"
 #include "rgs_cuda_common.cuh"
 
-struct RgsPeerFlagPtrs { uint32_t* p[16]; };
+// Layout of a rank's flag array (RGS_P2P_FLAG_WORDS 32-bit words): [0,32) the epoch word of every rank,
+// [32,64) and [64,96) two banks of one payload word per rank. A signal of epoch e stores the sender's payload into
+// bank e & 1 before it releases the epoch word; a peer is never more than one signal ahead of a waiting rank, so the
+// bank a wait reads is not overwritten under it. The payload carries the sender's "this step overflowed" word: every
+// rank leaves the wait with the OR over all ranks and drops the optimiser update together.
+#define RGS_P2P_MAX_WORLD 32
+#define RGS_P2P_FLAG_WORDS 96
+
+struct RgsPeerFlagPtrs { uint32_t* p[RGS_P2P_MAX_WORLD]; };
 
 __global__ void rgs_p2p_signal_kernel(const __grid_constant__ RgsPeerFlagPtrs flags, int world, int my_rank,
-                                      uint32_t epoch) {
+                                      uint32_t epoch, const uint32_t* __restrict__ payload_src) {
     const int o = threadIdx.x;
     if (o < world) {
+        if (payload_src) flags.p[o][RGS_P2P_MAX_WORLD * (1 + (epoch & 1u)) + my_rank] = *payload_src;
         __threadfence_system();
         rgs_st_release_sys(flags.p[o] + my_rank, epoch);
     }
 }
 
 __global__ void rgs_p2p_wait_kernel(const uint32_t* __restrict__ my_flags, int world, uint32_t epoch,
-                                    long long budget_cycles, uint32_t* __restrict__ status) {
+                                    long long budget_cycles, uint32_t* __restrict__ status,
+                                    uint32_t* __restrict__ payload_out) {
     const int r = threadIdx.x;
     if (r >= world) return;
     const long long t0 = clock64();
+    bool arrived = true;
     while (true) {
         const uint32_t v = rgs_ld_acquire_sys(my_flags + r);
         if ((int32_t)(v - epoch) >= 0) break;
         if (clock64() - t0 > budget_cycles) {
             atomicExch(status, 0x100u | (uint32_t)r);  // gave up waiting for rank r
+            arrived = false;
             break;
         }
         __nanosleep(200);
+    }
+    if (arrived && payload_out) {
+        const uint32_t pv = *reinterpret_cast<const volatile uint32_t*>(my_flags + RGS_P2P_MAX_WORLD * (1 + (epoch & 1u)) + r);
+        if (pv) atomicOr(payload_out, pv);
     }
     __threadfence_system();
 }
@@ -77,22 +93,28 @@ int rgs_cuda_ipc_open(const char* in64, void** out) {
 
 int rgs_cuda_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
 
-// flag_ptrs: `world` device pointers (host array): the flag array of every rank as mapped here.
-int rgs_cuda_p2p_signal(uint32_t* const* flag_ptrs, int64_t world, int64_t my_rank, int64_t epoch, void* stream) {
-    if (world < 1 || world > 16) return 14;
+// flag_ptrs: `world` device pointers (host array): the flag array of every rank as mapped here. payload_src
+// (optional, device): one word that travels with the signal (see the layout above).
+int rgs_cuda_p2p_signal(uint32_t* const* flag_ptrs, int64_t world, int64_t my_rank, int64_t epoch,
+                        const uint32_t* payload_src, void* stream) {
+    if (world < 1 || world > RGS_P2P_MAX_WORLD) return 14;
     RgsPeerFlagPtrs f;
     for (int i = 0; i < world; ++i) f.p[i] = flag_ptrs[i];
-    rgs_p2p_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, (int)world, (int)my_rank, (uint32_t)epoch);
+    rgs_p2p_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, (int)world, (int)my_rank, (uint32_t)epoch, payload_src);
     return (int)cudaGetLastError();
 }
 
+// payload_out (optional, device): receives the OR of the payload words of all ranks whose signal arrived.
 int rgs_cuda_p2p_wait(const uint32_t* my_flags, int64_t world, int64_t epoch, int64_t budget_cycles, int32_t* status,
-                      void* stream) {
-    if (world < 1 || world > 16) return 14;
+                      uint32_t* payload_out, void* stream) {
+    if (world < 1 || world > RGS_P2P_MAX_WORLD) return 14;
     rgs_p2p_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(my_flags, (int)world, (uint32_t)epoch,
                                                            (long long)budget_cycles,
-                                                           reinterpret_cast<uint32_t*>(status));
+                                                           reinterpret_cast<uint32_t*>(status), payload_out);
     return (int)cudaGetLastError();
 }
+
+int64_t rgs_cuda_p2p_flag_bytes() { return RGS_P2P_FLAG_WORDS * 4; }
+int64_t rgs_cuda_p2p_max_world() { return RGS_P2P_MAX_WORLD; }
 
 }  // extern "C"

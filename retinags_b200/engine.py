@@ -18,6 +18,7 @@ import torch
 from .data.cameras import Camera
 from .models.gaussians import GaussianStore
 from .ops.loss import CompositeLoss
+from .ops.native import CNT_OVERFLOW, CNT_WORDS
 from .ops.rasterize import RenderTask, Segment, make_camera
 from .parallel.compositing import LocalTransport, ViewPlan, band_rows
 from .utils.profiler import PhaseTimer
@@ -51,6 +52,14 @@ class StepEngine:
         self.debug = False            # synchronise and read every task's status word after each phase of a step
         self.detect_anomaly = False   # after the backward: non-finite loss sums or gradients raise, naming the sub-model
         self.dump_dir = "."
+        # Overflow guard: OR of the overflow words of this step's forwards, on every rank the OR over all ranks by the
+        # time the optimiser runs (the peer transport carries the word with its signals, the torch.distributed transport
+        # all-reduces it). A step in which any render ran out of instance capacity composited garbage: the fused Adam
+        # kernels see the word and drop the update -- on every rank, without a host synchronisation.
+        self._skip = torch.zeros(CNT_WORDS, dtype=torch.int32, device=self.device)
+        if hasattr(self.transport, "attach_skip"):
+            self.transport.attach_skip(self._skip)
+        self.dropped_steps = 0
         self._tasks: dict = {}
         self._grads: dict = {}
         self._closs: dict = {}
@@ -178,6 +187,7 @@ class StepEngine:
                 self.borrow.refresh(self.stores, need_grads=True)
         with T("render_forward"):
             local_out = self.render_partials(cams, plans, sh_degree)
+            self._collect_overflow(plans)
         with T("exchange_partials"):
             slots = self.transport.exchange_partials(plans, local_out)
         if hasattr(self.transport, "local_grad_images"):
@@ -252,10 +262,51 @@ class StepEngine:
                     bad = int((~torch.isfinite(t)).any(dim=1).nonzero()[0])
                     raise FloatingPointError(f"non-finite gradient in sub-model {m}, group '{name}', first at Gaussian {bad}")
 
+    def _collect_overflow(self, plans):
+        """Fold the overflow words of this step's forwards into the step's skip word (see ``__init__``)."""
+        cnts = [self._tasks[(p.view, m)].counters for p in plans for m, r in zip(p.models, p.ranks) if r == self.rank]
+        flags = self._skip[CNT_OVERFLOW:CNT_OVERFLOW + 2]  # overflow and status word; the counts are not flags
+        if cnts:
+            torch.amax(torch.stack([c[CNT_OVERFLOW:CNT_OVERFLOW + 2] for c in cnts]), dim=0, out=flags)
+        else:
+            flags.zero_()
+        if hasattr(self.transport, "reduce_skip"):
+            self.transport.reduce_skip(self._skip)
+
     def optimizer_step(self, lrs, plans=None):
         with self.timer.phase("adam"):
             for m, st in self.stores.items():
-                st.adam_step(lrs)
+                st.adam_step(lrs, skip=self._skip)
+        self._record_step_status()
+
+    def _record_step_status(self):
+        """Queue copies of the skip word and of the transport's wait status to the host (read by ``poll_async``)."""
+        if self.device.type == "cuda":
+            if not hasattr(self, "_host_skip"):
+                self._host_skip = torch.zeros(CNT_WORDS, dtype=torch.int32).pin_memory()
+            self._host_skip.copy_(self._skip, non_blocking=True)
+            self._skip_event = torch.cuda.Event()
+            self._skip_event.record(torch.cuda.current_stream(self.device))
+            if hasattr(self.transport, "record_status"):
+                self.transport.record_status()
+
+    def poll_async(self) -> dict | None:
+        """Look at the counters of the last step whose copies have reached the host, without waiting for the device:
+        grows instance buffers that overflowed or came close (applied by the next forward), raises when a bounded wait of
+        the transport gave up, and tells whether that step's optimiser update was dropped. ``None`` while the copies
+        are still in flight (the step is then looked at by a later call)."""
+        if self.device.type != "cuda":
+            return self.poll()
+        ev = getattr(self, "_skip_event", None)
+        if ev is None or not ev.query():
+            return None
+        self._skip_event = None
+        info = self.poll()
+        info["dropped"] = bool(self._host_skip[CNT_OVERFLOW])
+        self.dropped_steps += int(info["dropped"])
+        if hasattr(self.transport, "check"):
+            self.transport.check(block=False)
+        return info
 
     def poll(self) -> dict:
         """After a host synchronisation: read the counters of all tasks (grows buffers when needed)."""

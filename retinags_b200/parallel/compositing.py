@@ -188,5 +188,9 @@ class TorchDistTransport:
                     ops.append(dist.P2POp(dist.isend, slots[p.view][k][b[0]:b[1]], r, self.group))
         self._run(ops)
 
+    def reduce_skip(self, skip: torch.Tensor):
+        """Every rank leaves with the maximum over ranks of the step's overflow word (queued on the stream)."""
+        dist.all_reduce(skip, op=dist.ReduceOp.MAX, group=self.group)
+
     def barrier(self):
         dist.barrier(self.group)

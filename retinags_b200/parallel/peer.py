@@ -62,33 +62,41 @@ class PeerRegion:
             f = getattr(lib, fn)
             f.argtypes, f.restype = args, ctypes.c_int
         self._lib = lib
+        # Every step that can fail on one rank only (allocation, export, mapping a peer's handle) is followed by an
+        # exchange of the outcome, so that all ranks raise together instead of one raising while the others wait in the
+        # next collective.
+        self._alloc_ptr = 0
+        self._peer_bases: dict[int, int] = {}
+        err = ""
+        handle = ctypes.create_string_buffer(64)
         with torch.cuda.device(device):
             p = ctypes.c_void_p()
             rc = lib.rgs_cuda_ipc_alloc(self.nbytes + 2 * GUARD_BYTES, ctypes.byref(p))
             if rc:
-                raise RuntimeError(f"cudaMalloc of the exchange region failed ({rc})")
-            self._alloc_ptr = int(p.value)
-            self.local_ptr = self._alloc_ptr + GUARD_BYTES
-            handle = ctypes.create_string_buffer(64)
-            if self.world > 1:
-                rc = lib.rgs_cuda_ipc_get_handle(self._alloc_ptr, handle)
-                if rc:
-                    raise RuntimeError(f"cudaIpcGetMemHandle failed ({rc})")
-            handles = [None] * self.world
-            if self.world > 1:
-                dist.all_gather_object(handles, bytes(handle.raw), group=group)
-            self.ptrs = []
-            self._peer_bases: dict[int, int] = {}
+                err = f"cudaMalloc of the exchange region failed ({rc})"
+            else:
+                self._alloc_ptr = int(p.value)
+                if self.world > 1:
+                    rc = lib.rgs_cuda_ipc_get_handle(self._alloc_ptr, handle)
+                    if rc:
+                        err = f"cudaIpcGetMemHandle failed ({rc})"
+        handles = self._agree(err, bytes(handle.raw))
+        self.local_ptr = self._alloc_ptr + GUARD_BYTES
+        self.ptrs = []
+        err = ""
+        with torch.cuda.device(device):
             for r in range(self.world):
                 if r == self.rank:
                     self.ptrs.append(self.local_ptr)
-                else:
-                    q = ctypes.c_void_p()
-                    rc = lib.rgs_cuda_ipc_open(handles[r], ctypes.byref(q))
-                    if rc:
-                        raise RuntimeError(f"cudaIpcOpenMemHandle for rank {r} failed ({rc})")
-                    self._peer_bases[r] = int(q.value)
-                    self.ptrs.append(int(q.value) + GUARD_BYTES)
+                    continue
+                q = ctypes.c_void_p()
+                rc = lib.rgs_cuda_ipc_open(handles[r], ctypes.byref(q))
+                if rc:
+                    err = f"cudaIpcOpenMemHandle for rank {r} failed ({rc})"
+                    break
+                self._peer_bases[r] = int(q.value)
+                self.ptrs.append(int(q.value) + GUARD_BYTES)
+        self._agree(err, None)
         self._whole = torch.as_tensor(_DevBuf(self._alloc_ptr, self.nbytes + 2 * GUARD_BYTES), device=device)
         self._guards = (self._whole[:GUARD_BYTES].view(torch.int32), self._whole[GUARD_BYTES + self.nbytes:].view(torch.int32))
         for gz in self._guards:
@@ -96,6 +104,26 @@ class PeerRegion:
         self.local = self._whole[GUARD_BYTES:GUARD_BYTES + self.nbytes]
         if self.world > 1:
             dist.barrier(group)
+
+    def _agree(self, err: str, payload):
+        """All ranks exchange (error text, payload); when any rank failed, every rank releases what it holds and raises."""
+        if self.world > 1:
+            got = [None] * self.world
+            dist.all_gather_object(got, (err, payload), group=self.group)
+        else:
+            got = [(err, payload)]
+        failed = [(r, e) for r, (e, _) in enumerate(got) if e]
+        if failed:
+            with torch.cuda.device(self.device):
+                for base in self._peer_bases.values():
+                    self._lib.rgs_cuda_ipc_close(base)
+                self._peer_bases.clear()
+                if self._alloc_ptr:
+                    self._lib.rgs_cuda_ipc_free(self._alloc_ptr)
+                    self._alloc_ptr = 0
+            self.ptrs = None
+            raise RuntimeError("peer-mapped exchange region unavailable: " + "; ".join(f"rank {r}: {e}" for r, e in failed))
+        return [pl for _, pl in got]
 
     def view(self, offset: int, shape, dtype=torch.float32) -> torch.Tensor:
         n = 1
@@ -126,39 +154,54 @@ class PeerRegion:
 class PeerTransport:
     """Compositing transport in which kernels store straight into the consumer's memory."""
 
-    FLAG_BYTES = 256
-
     def __init__(self, device, group=None, max_views: int = 4, region: PeerRegion | None = None):
         self.device = torch.device(device)
         self.group = group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        lib = native.lib("cuda")
+        for fn in ("rgs_cuda_p2p_flag_bytes", "rgs_cuda_p2p_max_world"):
+            getattr(lib, fn).restype = ctypes.c_int64
+        self.FLAG_BYTES = (int(lib.rgs_cuda_p2p_flag_bytes()) + 255) // 256 * 256
+        if self.world > int(lib.rgs_cuda_p2p_max_world()):
+            raise RuntimeError(f"the peer transport handles at most {int(lib.rgs_cuda_p2p_max_world())} ranks "
+                               f"(world size {self.world}); use the torch.distributed transport")
         self.max_views = max_views
         self.region = region
         self.epoch = 0
         self.layout = None
         self.status = torch.zeros(native.CNT_WORDS, dtype=torch.int32, device=self.device)
+        self._host_status = torch.zeros(native.CNT_WORDS, dtype=torch.int32).pin_memory()
+        self._status_event = None
+        self.skip_word = None  # optional device counter block: its overflow word travels with every signal (attach_skip)
+        # Map a small region right away: a rank whose peers are not reachable through CUDA IPC (another node, a
+        # container without shared IPC namespace) fails here, on every rank together, and the caller can fall back to
+        # the torch.distributed transport before any step has run.
+        if region is None and self.world > 1:
+            PeerRegion(4096, self.device, self.group).close()
+
+    def attach_skip(self, counters: torch.Tensor):
+        """``counters``: device int32 block (layout of the rasteriser's counters). Its overflow word is sent with every
+        signal and every wait ORs the words of all ranks into it, so that all ranks drop the same optimiser step."""
+        self.skip_word = counters
 
     # -- layout -----------------------------------------------------------------------------------
-    def _ensure(self, H: int, W: int, n_models: int, local_models: list[int], n_views: int):
-        key = (H, W, n_models, tuple(local_models), max(n_views, self.max_views))
-        if self.layout is not None and self.layout["key"] == key:
+    def _ensure(self, slot_bytes: int, grad_bytes: int, n_models: int, max_local: int, n_views: int):
+        V = max(n_views, self.max_views)
+        L = self.layout
+        if L is not None and L["n_models"] == n_models and L["max_local"] == max_local and L["V"] >= V and \
+                L["slot_bytes"] >= slot_bytes and L["grad_bytes"] >= grad_bytes:
             return
+        if L is not None:  # sizes only grow: a batch of smaller images reuses the region
+            slot_bytes, grad_bytes, V = max(slot_bytes, L["slot_bytes"]), max(grad_bytes, L["grad_bytes"]), max(V, L["V"])
         if self.region is not None:
             self.region.close()
-        V = key[4]
-        bands = band_rows(H, self.world)
-        ext = [extended(b, H) for b in bands]
-        max_ext = max(e[1] - e[0] for e in ext)
-        slot_bytes = max_ext * W * 16
-        grad_bytes = H * W * 16
-        max_local = -(-n_models // self.world)
         off_slots = self.FLAG_BYTES
         off_grads = off_slots + V * n_models * slot_bytes
         total = off_grads + V * max_local * grad_bytes
         self.region = PeerRegion(total, self.device, self.group)
-        self.layout = dict(key=key, V=V, bands=bands, ext=ext, slot_bytes=slot_bytes, grad_bytes=grad_bytes,
-                           off_slots=off_slots, off_grads=off_grads, n_models=n_models, H=H, W=W)
+        self.layout = dict(V=V, slot_bytes=slot_bytes, grad_bytes=grad_bytes, off_slots=off_slots, off_grads=off_grads,
+                           n_models=n_models, max_local=max_local)
         self.flags = self.region.view(0, (self.FLAG_BYTES // 4,), torch.int32)
         self._flag_ptrs = (ctypes.c_void_p * self.world)(*self.region.ptrs)
         self.epoch = 0
@@ -169,30 +212,56 @@ class PeerTransport:
 
     def _grad_off(self, view: int, model: int) -> int:
         L = self.layout
-        return L["off_grads"] + (view * (-(-L["n_models"] // self.world)) + model // self.world) * L["grad_bytes"]
+        return L["off_grads"] + (view * L["max_local"] + self._local_index[model]) * L["grad_bytes"]
+
+    @staticmethod
+    def _plan_ext(plan: ViewPlan):
+        return [extended(b, plan.H) for b in plan.bands]
 
     def prepare(self, plans: list[ViewPlan], n_models: int, model2rank: list[int]):
-        p0 = plans[0]
-        local = [m for m in range(n_models) if model2rank[m] == self.rank]
-        self._ensure(p0.H, p0.W, n_models, local, len(plans))
+        """Size the exchange region for this batch. Views may differ in size (scenes with several intrinsics): slots
+        and gradient images are sized for the largest view, every view is laid out with its own width and bands."""
+        per_rank: dict[int, int] = {}
+        self._local_index = {}
+        for m in range(n_models):  # position of a sub-model among the sub-models of its rank
+            self._local_index[m] = per_rank.get(model2rank[m], 0)
+            per_rank[model2rank[m]] = self._local_index[m] + 1
+        slot_bytes = max(max(e[1] - e[0] for e in self._plan_ext(p)) * p.W * 16 for p in plans)
+        grad_bytes = max(p.H * p.W * 16 for p in plans)
+        self._ensure(slot_bytes, grad_bytes, n_models, max(per_rank.values()), len(plans))
 
     # -- signalling -------------------------------------------------------------------------------
     def _signal_wait(self):
         self.epoch += 1
-        native.call("p2p_signal", self.device, self._flag_ptrs, self.world, self.rank, self.epoch, sig="piiip")
-        native.call("p2p_wait", self.device, self.flags, self.world, self.epoch, WAIT_BUDGET_CYCLES, self.status,
-                    sig="piiipp")
+        pay = None if self.skip_word is None else self.skip_word[native.CNT_OVERFLOW:]
+        native.call("p2p_signal", self.device, self._flag_ptrs, self.world, self.rank, self.epoch, pay, sig="piiipp")
+        native.call("p2p_wait", self.device, self.flags, self.world, self.epoch, WAIT_BUDGET_CYCLES, self.status, pay,
+                    sig="piiippp")
 
     def barrier(self):
         if self.layout is not None:
             self._signal_wait()
 
-    def check(self):
-        """Host check of the wait status (call after a synchronise)."""
-        st = int(self.status[0].item())
+    def record_status(self):
+        """Queue a copy of the wait status to pinned host memory (no synchronisation); ``check(block=False)`` reads it
+        once the copy has completed."""
+        self._host_status.copy_(self.status, non_blocking=True)
+        self._status_event = torch.cuda.Event()
+        self._status_event.record(torch.cuda.current_stream(self.device))
+
+    def check(self, block: bool = True):
+        """Host check of the wait status and of the canaries. ``block``: synchronise and read the device words;
+        otherwise only look at the last recorded copy, and only if it has arrived."""
+        if block:
+            st = int(self.status[0].item())
+        else:
+            if self._status_event is None or not self._status_event.query():
+                return
+            self._status_event = None
+            st = int(self._host_status[0])
         if st:
             raise RuntimeError(f"peer wait expired: no signal from rank {st & 0xff} within the cycle budget")
-        if self.region is not None and not self.region.verify_canaries():
+        if block and self.region is not None and not self.region.verify_canaries():
             raise RuntimeError("a kernel stored outside the bounds of this rank's exchange region (canary overwritten)")
 
     # -- transport interface ------------------------------------------------------------------------
@@ -200,9 +269,10 @@ class PeerTransport:
         """Rows and slot addresses for the blend epilogue of (view, model)."""
         L = self.layout
         rows0, rows1, dst = [], [], []
-        for o in range(self.world):
-            e = L["ext"][o]
+        for o, e in enumerate(self._plan_ext(plan)):
             if e[1] > e[0]:
+                if (e[1] - e[0]) * plan.W * 16 > L["slot_bytes"]:
+                    raise RuntimeError("a view needs more rows per slot than the exchange region was sized for")
                 rows0.append(e[0]); rows1.append(e[1])
                 dst.append(self.region.ptrs[o] + self._slot_off(plan.view, model))
         n = len(dst)
@@ -213,16 +283,14 @@ class PeerTransport:
         """The pushes already happened inside the blend kernels; order them and hand out the slots as
         full-height virtual base addresses."""
         self._signal_wait()
-        L = self.layout
-        e = L["ext"][self.rank]
         out = {}
         for p in plans:
+            e = self._plan_ext(p)[self.rank]
             out[p.view] = [self.region.ptrs[self.rank] + self._slot_off(p.view, m) - e[0] * p.W * 16 for m in p.models]
         return out
 
     def local_grad_images(self, plans) -> dict:
         """Gradient images of this rank's renders, inside the exchange region (peer-writable)."""
-        L = self.layout
         out = {}
         for p in plans:
             out[p.view] = {m: self.region.view(self._grad_off(p.view, m), (p.H, p.W, 4))

@@ -47,8 +47,11 @@ class PeerBorderExchange:
         self.margin = margin if self.refresh_interval > 1 else 0.0
         self.enabled = True
         self.local = [m for m in range(self.M) if self.model2rank[m] == rank]
-        self.slot_of = {m: m // world for m in range(self.M)}  # position of a model among its rank's models
-        self.max_local = -(-self.M // world)
+        self.slot_of, per_rank = {}, {}  # position of a model among its rank's models (any assignment)
+        for m in range(self.M):
+            self.slot_of[m] = per_rank.get(self.model2rank[m], 0)
+            per_rank[self.model2rank[m]] = self.slot_of[m] + 1
+        self.max_local = max(per_rank.values())
         self._step = 0
         self._index: dict[tuple[int, int], torch.Tensor] = {}
         self._counts = None
