@@ -21,31 +21,37 @@ _PLY_TYPES = {
 }
 
 
+def _parse_header(f, path: str):
+    """(format, elements) of an open PLY file; the file position is left at the first byte of the data."""
+    if f.readline().strip() != b"ply":
+        raise ValueError(f"{path}: not a PLY file")
+    fmt, elements, cur = None, [], None
+    while True:
+        line = f.readline()
+        if not line:
+            raise ValueError(f"{path}: truncated header")
+        tok = line.decode("ascii", "replace").split()
+        if not tok:
+            continue
+        if tok[0] == "format":
+            fmt = tok[1]
+        elif tok[0] == "element":
+            cur = {"name": tok[1], "count": int(tok[2]), "props": []}
+            elements.append(cur)
+        elif tok[0] == "property":
+            if tok[1] == "list":
+                cur["props"].append(("list", tok[2], tok[3], tok[4]))
+            else:
+                cur["props"].append((tok[2], _PLY_TYPES[tok[1]]))
+        elif tok[0] == "end_header":
+            break
+    return fmt, elements
+
+
 def read_ply_vertices(path: str) -> np.ndarray:
     """Structured array of the ``vertex`` element of a PLY file (binary little/big endian or ascii)."""
     with open(path, "rb") as f:
-        if f.readline().strip() != b"ply":
-            raise ValueError(f"{path}: not a PLY file")
-        fmt, elements, cur = None, [], None
-        while True:
-            line = f.readline()
-            if not line:
-                raise ValueError(f"{path}: truncated header")
-            tok = line.decode("ascii", "replace").split()
-            if not tok:
-                continue
-            if tok[0] == "format":
-                fmt = tok[1]
-            elif tok[0] == "element":
-                cur = {"name": tok[1], "count": int(tok[2]), "props": []}
-                elements.append(cur)
-            elif tok[0] == "property":
-                if tok[1] == "list":
-                    cur["props"].append(("list", tok[2], tok[3], tok[4]))
-                else:
-                    cur["props"].append((tok[2], _PLY_TYPES[tok[1]]))
-            elif tok[0] == "end_header":
-                break
+        fmt, elements = _parse_header(f, path)
         endian = "<" if fmt in ("binary_little_endian", "ascii") else ">"
         for el in elements:
             if any(p[0] == "list" for p in el["props"]):
@@ -63,6 +69,42 @@ def read_ply_vertices(path: str) -> np.ndarray:
             if el["name"] == "vertex":
                 return arr
     raise ValueError(f"{path}: no vertex element")
+
+
+class PlyVertexStream:
+    """The ``vertex`` element of a binary PLY file read piecewise through a memory map: a model of hundreds of
+    millions of Gaussians (54 GB at 217 M) is walked in chunks of a few hundred MB instead of being parsed into host
+    memory at once (the reference parses the whole file on rank 0, ``scene/gaussian_nn_module.py:134-174``).
+    Only a leading vertex element of fixed-size properties is supported, which is what every Gaussian model file is."""
+
+    def __init__(self, path: str):
+        self.path = path
+        with open(path, "rb") as f:
+            fmt, elements = _parse_header(f, path)
+            self.offset = f.tell()
+        if fmt not in ("binary_little_endian", "binary_big_endian"):
+            raise ValueError(f"{path}: streaming needs a binary PLY file")
+        el = elements[0] if elements else None
+        if el is None or el["name"] != "vertex" or any(p[0] == "list" for p in el["props"]):
+            raise ValueError(f"{path}: the first element must be a vertex element of scalar properties")
+        endian = "<" if fmt == "binary_little_endian" else ">"
+        self.dtype = np.dtype([(n, endian + t) for n, t in el["props"]])
+        self.count = el["count"]
+        self.names = self.dtype.names
+
+    def memmap(self) -> np.ndarray:
+        if self.count == 0:
+            return np.zeros(0, dtype=self.dtype)
+        return np.memmap(self.path, dtype=self.dtype, mode="r", offset=self.offset, shape=(self.count,))
+
+    def chunks(self, rows: int = 2_000_000, start: int = 0, step: int = 1):
+        """Yields (first row, structured array copy) for chunk ``start``, ``start + step``, ... of ``rows`` rows."""
+        mm = self.memmap()
+        nchunks = (self.count + rows - 1) // rows
+        for k in range(start, nchunks, step):
+            a = k * rows
+            yield a, np.array(mm[a:min(self.count, a + rows)])  # one copy into host memory, then the pages can go
+        del mm
 
 
 def write_ply_vertices(path: str, names: list[str], data: np.ndarray, types: list[str] | None = None):
@@ -85,8 +127,8 @@ def gaussian_attribute_names(sh_degree: int = 3) -> list[str]:
             + ["opacity"] + [f"scale_{i}" for i in range(3)] + [f"rot_{i}" for i in range(4)])
 
 
-def save_gaussians(path: str, g: dict, sh_degree: int = 3):
-    """``g``: xyz (P,3), sh (P,48) coefficient-major, scale (P,3), rot (P,4), opacity (P,1) raw values."""
+def _gaussian_rows(g: dict, sh_degree: int) -> np.ndarray:
+    """(n, 62 at SH-3) float32 rows in file order from a dict of raw parameter tensors."""
     P = g["xyz"].shape[0]
     nc = (sh_degree + 1) ** 2
     sh = g["sh"].detach().cpu().float().view(P, 16, 3)
@@ -94,12 +136,54 @@ def save_gaussians(path: str, g: dict, sh_degree: int = 3):
     f_rest = sh[:, 1:nc].transpose(1, 2).reshape(P, -1)  # channel-major
     cols = [g["xyz"].detach().cpu().float(), torch.zeros(P, 3), f_dc, f_rest, g["opacity"].detach().cpu().float().view(P, 1),
             g["scale"].detach().cpu().float(), g["rot"].detach().cpu().float()]
-    write_ply_vertices(path, gaussian_attribute_names(sh_degree), torch.cat(cols, dim=1).numpy())
+    return torch.cat(cols, dim=1).numpy()
 
 
-def load_gaussians(path: str, max_sh_degree: int = 3) -> dict:
-    """Inverse of :func:`save_gaussians`; accepts any property order and lower SH degrees."""
-    v = read_ply_vertices(path)
+def _gaussian_header(count: int, sh_degree: int) -> bytes:
+    names = gaussian_attribute_names(sh_degree)
+    return ("ply\nformat binary_little_endian 1.0\n" + f"element vertex {count}\n" +
+            "".join(f"property float {n}\n" for n in names) + "end_header\n").encode("ascii")
+
+
+def save_gaussians(path: str, g: dict, sh_degree: int = 3, chunk: int = 2_000_000):
+    """``g``: xyz (P,3), sh (P,48) coefficient-major, scale (P,3), rot (P,4), opacity (P,1) raw values. The rows are
+    converted and written ``chunk`` at a time, so that the host never holds a second copy of a large sub-model."""
+    P = int(g["xyz"].shape[0])
+    with open(path, "wb") as f:
+        f.write(_gaussian_header(P, sh_degree))
+        for a in range(0, P, chunk):
+            part = {k: v[a:a + chunk] for k, v in g.items()}
+            f.write(np.ascontiguousarray(_gaussian_rows(part, sh_degree), dtype="<f4").tobytes())
+
+
+def merge_gaussian_files(out_path: str, files: list[str], sh_degree: int = 3, block_rows: int = 1_000_000) -> int:
+    """Concatenate Gaussian model files into one (``scene/gaussian_nn_module.py:58-132``: the whole-model merge)
+    without loading them: files in this writer's layout are copied as bytes block by block, others are converted
+    chunk by chunk. Returns the number of Gaussians written."""
+    streams = [PlyVertexStream(f) for f in files]
+    total = sum(st.count for st in streams)
+    target = np.dtype([(n, "<f4") for n in gaussian_attribute_names(sh_degree)])
+    with open(out_path, "wb") as out:
+        out.write(_gaussian_header(total, sh_degree))
+        for st in streams:
+            if st.dtype == target:
+                with open(st.path, "rb") as src:
+                    src.seek(st.offset)
+                    left = st.count * target.itemsize
+                    while left > 0:
+                        buf = src.read(min(left, block_rows * target.itemsize))
+                        if not buf:
+                            raise ValueError(f"{st.path}: truncated vertex data")
+                        out.write(buf)
+                        left -= len(buf)
+            else:
+                for _, v in st.chunks(block_rows):
+                    out.write(np.ascontiguousarray(_gaussian_rows(gaussians_from_vertices(v, sh_degree), sh_degree), dtype="<f4").tobytes())
+    return total
+
+
+def gaussians_from_vertices(v: np.ndarray, max_sh_degree: int = 3) -> dict:
+    """Parameter tensors of a structured vertex array (any property order, any SH degree up to 3)."""
     names = v.dtype.names
     P = v.shape[0]
 
@@ -119,6 +203,17 @@ def load_gaussians(path: str, max_sh_degree: int = 3) -> dict:
     rot = torch.stack([col(n) for n in sorted((n for n in names if n.startswith("rot")), key=lambda s: int(s.split("_")[-1]))], 1)
     return dict(xyz=xyz.contiguous(), sh=sh.view(P, 48).contiguous(), scale=scale.contiguous(), rot=rot.contiguous(),
                 opacity=col("opacity").view(P, 1).contiguous())
+
+
+def load_gaussians(path: str, max_sh_degree: int = 3) -> dict:
+    """Inverse of :func:`save_gaussians`; accepts any property order and lower SH degrees."""
+    return gaussians_from_vertices(read_ply_vertices(path), max_sh_degree)
+
+
+def iter_gaussians(path: str, max_sh_degree: int = 3, rows: int = 2_000_000, start: int = 0, step: int = 1):
+    """Yields (first row, parameter dict) for chunks ``start``, ``start + step``, ... of a model file (memory-mapped)."""
+    for a, v in PlyVertexStream(path).chunks(rows, start, step):
+        yield a, gaussians_from_vertices(v, max_sh_degree)
 
 
 def fetch_point_cloud(path: str, sample_rate: int = 1, seed: int = 0):

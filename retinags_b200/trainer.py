@@ -194,21 +194,7 @@ class Trainer:
                 self.stores[m] = st
         elif self.load_iteration > 0:
             ply = os.path.join(self.model_root, "point_cloud", f"iteration_{self.load_iteration}", "point_cloud.ply")
-            g = ply_io.load_gaussians(ply, self.sh_degree) if self.rank == 0 or not a.NOT_SHRAE_GS_INFO else None
-            if g is None:
-                g = ply_io.load_gaussians(ply, self.sh_degree)
-            xyz = g["xyz"]
-            ext = 3.0 * float(torch.exp(g["scale"]).max())
-            grid = Grid3D((xyz.min(0).values - ext).numpy(), (xyz.max(0).values + ext).numpy(), self.SCENE_GRID_SIZE)
-            grid.accumulate(xyz.numpy())
-            self.tree = BvhTree.build(grid, self.bvh_depth, self.SPLIT_ORDERS, rng=rng)
-            lo, hi = self._stores_from_tree()
-            ids = self.tree.label(xyz)
-            for m in self.local_ids:
-                sel = (ids == m).nonzero(as_tuple=True)[0]
-                st = GaussianStore(max(int(sel.numel()), 4), self.device, self.sh_degree, lo[m], hi[m], m)
-                st.set_params({k: v[sel] for k, v in g.items()})
-                self.stores[m] = st
+            self._load_whole_model(ply, rng)
         else:
             pts, col = self.scene.points, self.scene.colors
             if pts is None:
@@ -229,6 +215,66 @@ class Trainer:
             st.active_sh_degree = active
         self.logger.info("sub-models %s on rank %d: %s", self.local_ids, self.rank, {m: s.count for m, s in self.stores.items()})
 
+    LOAD_CHUNK_ROWS = 2_000_000
+
+    def _load_whole_model(self, ply: str, rng):
+        """Start from one whole-model file of any size. The file is memory-mapped and walked in chunks, never parsed
+        as a whole (the reference parses it into host memory on rank 0 and scatters it with point-to-point messages,
+        ``gaussian_utils.py:128-171``, ``gaussian_nn_module.py:134-261``):
+
+        1. every rank scans a 1/world share of the chunks for the bounds (positions +- 3 max scale) and, after the
+           bounds are agreed, for the load histogram; both are all-reduced; rank 0 builds the tree and broadcasts it;
+        2. every rank walks all chunks once and keeps the Gaussians of its own sub-models.
+
+        No rank holds more than one chunk besides its own sub-models. With ``--NOT_SHRAE_GS_INFO`` a sub-model keeps
+        every Gaussian whose 3-sigma extent reaches its box instead of only those whose centre lies in it, because no
+        border Gaussians are exchanged afterwards (``gaussian_utils.py:177-193``, ``gaussian_nn_module.py:1028-1036``)."""
+        a = self.args
+        rows = self.LOAD_CHUNK_ROWS
+        stream = ply_io.PlyVertexStream(ply)
+        lo = torch.full((3,), float("inf"), dtype=torch.float64)
+        hi = torch.full((3,), float("-inf"), dtype=torch.float64)
+        smax = torch.zeros(1, dtype=torch.float64)
+        for _, v in stream.chunks(rows, self.rank, self.world):
+            xyz = torch.from_numpy(np.stack([v["x"], v["y"], v["z"]], 1).astype(np.float64))
+            sc = np.stack([v[n] for n in stream.names if n.startswith("scale_")], 1).astype(np.float64)
+            lo, hi = torch.minimum(lo, xyz.min(0).values), torch.maximum(hi, xyz.max(0).values)
+            smax = torch.maximum(smax, torch.from_numpy(np.exp(sc.max(keepdims=True)).reshape(1)))
+        if self.world > 1:
+            pack = torch.cat([-lo, hi, smax]).to(self.device)  # one MAX reduction for all three
+            dist.all_reduce(pack, op=dist.ReduceOp.MAX, group=self.group)
+            pack = pack.cpu()
+            lo, hi, smax = -pack[:3], pack[3:6], pack[6:]
+        ext = 3.0 * float(smax)
+        grid = Grid3D((lo - ext).numpy(), (hi + ext).numpy(), self.SCENE_GRID_SIZE)
+        for _, v in stream.chunks(rows, self.rank, self.world):
+            grid.accumulate(np.stack([v["x"], v["y"], v["z"]], 1).astype(np.float32))
+        if self.world > 1:
+            load = torch.from_numpy(np.ascontiguousarray(grid.load)).to(self.device)
+            dist.all_reduce(load, group=self.group)
+            grid.load = load.cpu().numpy()
+        self.tree = self._bcast(BvhTree.build(grid, self.bvh_depth, self.SPLIT_ORDERS, rng=rng) if self.rank == 0 else None)
+        blo, bhi = self._stores_from_tree()
+        for m in self.local_ids:
+            self.stores[m] = GaussianStore(max(stream.count // max(self.n_models, 1), 4), self.device, self.sh_degree,
+                                           blo[m], bhi[m], m)
+        keep_reach = bool(a.NOT_SHRAE_GS_INFO)
+        for _, g in ply_io.iter_gaussians(ply, self.sh_degree, rows):
+            if keep_reach:
+                r = 3.0 * torch.exp(g["scale"]).max(dim=1, keepdim=True).values
+                for m in self.local_ids:
+                    mlo = torch.as_tensor(blo[m], dtype=torch.float32)
+                    mhi = torch.as_tensor(bhi[m], dtype=torch.float32)
+                    sel = ((g["xyz"] + r >= mlo) & (g["xyz"] - r <= mhi)).all(dim=1).nonzero(as_tuple=True)[0]
+                    if sel.numel():
+                        self.stores[m].append_new({k: v[sel].to(self.device) for k, v in g.items()})
+            else:
+                ids = self.tree.label(g["xyz"])
+                for m in self.local_ids:
+                    sel = (ids == m).nonzero(as_tuple=True)[0]
+                    if sel.numel():
+                        self.stores[m].append_new({k: v[sel].to(self.device) for k, v in g.items()})
+
     def _create_from_points(self, pts: torch.Tensor, rgb: torch.Tensor, lo, hi, mid: int) -> GaussianStore:
         """3DGS initialisation per sub-model (``scene/gaussian_nn_module.py:403-427``): SH DC from the point
         colours, isotropic scale from the mean distance to the 3 nearest neighbours *inside the sub-model*."""
@@ -246,6 +292,14 @@ class Trainer:
         opacity = inverse_sigmoid(self.mdp.opacity_init * torch.ones(n, 1, device=self.device))
         st.set_params(dict(xyz=p, sh=sh.view(n, 48), scale=scale, rot=rot, opacity=opacity))
         return st
+
+    def _close_engine(self):
+        """Release the peer-mapped regions of the current engine (collective with the peer transport)."""
+        if getattr(self, "border", None) is not None and hasattr(self.border, "close"):
+            self.border.close()
+        eng = getattr(self, "engine", None)
+        if eng is not None and hasattr(eng.transport, "close"):
+            eng.transport.close()
 
     def _build_engine(self):
         a = self.args
@@ -280,19 +334,28 @@ class Trainer:
         self.engine.dump_dir = self.model_path
         self.balancer = WorkloadBalancer(self.world, self.model2rank)
 
-    def _relation(self, dataset: CameraListDataset, cache_name: str) -> np.ndarray:
-        path = os.path.join(self.model_root, "rank_0", cache_name)
-        if self.args.USE_RELATION_CACHE and os.path.exists(path):
-            rel = torch.load(path, weights_only=False)
-            rel = rel.numpy() if isinstance(rel, torch.Tensor) else np.asarray(rel)
-            if rel.shape == (len(dataset), self.n_models):
-                return rel.astype(np.int32)
+    def _relation(self, dataset: CameraListDataset, cache_name: str, use_cache: bool = True) -> np.ndarray:
+        """Camera -> sub-model relation (visibility and front-to-back position) of a dataset. Rank 0 alone decides
+        whether the cached file is used and every rank takes part in the one broadcast, so that all ranks follow the
+        same collective path; the file is written after the broadcast. After a repartition the tree has changed while
+        the shape of the matrix has not: the callers pass ``use_cache=False`` there (the reference recomputes as well,
+        ``trainer4tree_partition.py:308-314``)."""
         rel = None
         if self.rank == 0:
-            cams = [dataset.empty_item(i) for i in range(len(dataset))]
-            rel = self.tree.relation(cams, self.args.Z_NEAR, self.args.Z_FAR) if cams else np.zeros((0, self.n_models), np.int32)
-            torch.save(torch.from_numpy(rel), os.path.join(self.model_path, cache_name))
-        return self._bcast(rel)
+            path = os.path.join(self.model_root, "rank_0", cache_name)
+            if use_cache and self.args.USE_RELATION_CACHE and os.path.exists(path):
+                cached = torch.load(path, weights_only=False)
+                cached = cached.numpy() if isinstance(cached, torch.Tensor) else np.asarray(cached)
+                if cached.shape == (len(dataset), self.n_models):
+                    rel = cached.astype(np.int32)
+            if rel is None:
+                cams = [dataset.empty_item(i) for i in range(len(dataset))]
+                rel = self.tree.relation(cams, self.args.Z_NEAR, self.args.Z_FAR) if cams else \
+                    np.zeros((0, self.n_models), np.int32)
+        rel = self._bcast(rel)
+        if self.rank == 0:
+            torch.save(torch.from_numpy(np.ascontiguousarray(rel)), os.path.join(self.model_path, cache_name))
+        return rel
 
     # ------------------------------------------------------------------------------------------------
     # schedules
@@ -381,9 +444,12 @@ class Trainer:
                     if self.rank == 0 and not a.quiet and time.time() - t_last > 5:
                         print(f"[iter {self.iteration}] loss {ema:.6f} points {sum(s.count for s in self.stores.values())}", flush=True)
                         t_last = time.time()
-                    info = self.engine.poll()
-                    if info["overflow"]:
-                        self.logger.warning("instance buffers overflowed at iteration %d; grown for the next step", self.iteration)
+                # every step, without waiting for the device: the counters of the newest step whose copies have arrived
+                # (buffers grow before the next forward; a step that overflowed was dropped by the optimiser on all ranks)
+                info = self.engine.poll_async()
+                if info is not None and info.get("dropped"):
+                    self.logger.warning("a render of the step before iteration %d ran out of instance capacity: its update "
+                                        "was dropped on every rank, the buffers have been grown", self.iteration + bs)
                 self.iteration += bs
             last = epoch == epochs - 1
             if (epoch % a.SAVE_INTERVAL_EPOCH == 0 and epoch != 0) or last:
@@ -458,16 +524,15 @@ class Trainer:
         return out
 
     def save_whole_model(self, iteration: int):
-        """Merge every rank's sub-model files into one vanilla-3DGS ``point_cloud.ply`` (rank 0, in host memory;
-        ``scene/gaussian_nn_module.py:58-132``)."""
+        """Merge every rank's sub-model files into one vanilla-3DGS ``point_cloud.ply`` (rank 0;
+        ``scene/gaussian_nn_module.py:58-132``). The files are concatenated block by block, never loaded."""
         files = sorted(glob.glob(os.path.join(self.model_root, "rank_*", "point_cloud", f"iteration_{iteration}", "point_cloud_*.ply")))
-        parts = [ply_io.load_gaussians(f, self.sh_degree) for f in files]
-        if not parts:
+        if not files:
             return
-        g = {k: torch.cat([p[k] for p in parts]) for k in parts[0]}
         out = os.path.join(self.model_root, "point_cloud", f"iteration_{iteration}")
         os.makedirs(out, exist_ok=True)
-        ply_io.save_gaussians(os.path.join(out, "point_cloud.ply"), g, self.sh_degree)
+        n = ply_io.merge_gaussian_files(os.path.join(out, "point_cloud.ply"), files, self.sh_degree)
+        self.logger.info("merged %d sub-model files (%d Gaussians) into %s", len(files), n, out)
 
     # ------------------------------------------------------------------------------------------------
     # evaluation
@@ -575,6 +640,7 @@ class Trainer:
                               self.group)
         for st in self.stores.values():
             st.active_sh_degree = min(self.sh_degree, self.iteration // 1000)
+        self._close_engine()  # the old exchange regions are unmapped before new ones are created
         self._build_engine()
-        self.train_rlt = self._relation(self.train_dataset, "trainset_relation.pt")
-        self.test_rlt = self._relation(self.test_dataset, "testset_relation.pt")
+        self.train_rlt = self._relation(self.train_dataset, "trainset_relation.pt", use_cache=False)
+        self.test_rlt = self._relation(self.test_dataset, "testset_relation.pt", use_cache=False)

@@ -103,3 +103,41 @@ def test_anomaly_check_names_the_submodel_and_debug_mode_polls():
     with pytest.raises(FloatingPointError) as err:
         eng._anomaly_check([])
     assert f"sub-model {victim}" in str(err.value) and "'scale'" in str(err.value) and "Gaussian 3" in str(err.value)
+
+
+def test_whole_model_is_streamed_in_chunks_and_not_share_keeps_reaching_gaussians(tmp_path, monkeypatch):
+    """The whole-model loader walks the file in chunks (here 300 rows) and ends with the same sub-models as labelling
+    everything at once; with --NOT_SHRAE_GS_INFO a sub-model also keeps the Gaussians of its neighbours whose 3-sigma
+    extent reaches into its box (nothing is borrowed later), and only those."""
+    g = {k: v for k, v in __import__("retinags_b200.data.synthetic", fromlist=["x"]).uniform_gaussians(2500, 7, sh_degree=3).items()}
+    it = 40
+    os.makedirs(tmp_path / "point_cloud" / f"iteration_{it}")
+    whole = str(tmp_path / "point_cloud" / f"iteration_{it}" / "point_cloud.ply")
+    ply_io.save_gaussians(whole, g, 3, chunk=700)
+    assert ply_io.PlyVertexStream(whole).count == 2500
+    torch.testing.assert_close(ply_io.load_gaussians(whole)["sh"], g["sh"])
+    monkeypatch.setattr(Trainer, "LOAD_CHUNK_ROWS", 300)
+    tr, scene = _trainer(tmp_path, ["--epochs", "1", "--bvh_depth", "2"])
+    assert tr.iteration == it and tr.n_models == 4 and sum(s.count for s in tr.stores.values()) == 2500
+    ids = tr.tree.label(g["xyz"])
+    for m, st in tr.stores.items():
+        want = g["xyz"][ids == m]
+        torch.testing.assert_close(st.xyz[torch.argsort(st.xyz[:, 0])], want[torch.argsort(want[:, 0])])
+    assert tr.border is not None
+    tr2, _ = _trainer(tmp_path, ["--epochs", "1", "--bvh_depth", "2", "--NOT_SHRAE_GS_INFO"], scene)
+    assert tr2.border is None
+    lo, hi = tr2.boxes
+    r = 3.0 * torch.exp(g["scale"]).max(dim=1, keepdim=True).values
+    total = 0
+    for m, st in tr2.stores.items():
+        reach = ((g["xyz"] + r >= torch.tensor(lo[m], dtype=torch.float32)) &
+                 (g["xyz"] - r <= torch.tensor(hi[m], dtype=torch.float32))).all(dim=1)
+        assert st.count == int(reach.sum()) and st.count >= int((ids == m).sum())
+        total += st.count
+    assert total > 2500  # border Gaussians live in more than one sub-model
+    # the merge concatenates bytes and equals the parts in order
+    parts = [str(tmp_path / f"part_{k}.ply") for k in range(2)]
+    ply_io.save_gaussians(parts[0], {k: v[:1000] for k, v in g.items()}, 3)
+    ply_io.save_gaussians(parts[1], {k: v[1000:] for k, v in g.items()}, 3)
+    assert ply_io.merge_gaussian_files(str(tmp_path / "merged.ply"), parts, 3, block_rows=256) == 2500
+    assert open(tmp_path / "merged.ply", "rb").read() == open(whole, "rb").read()
