@@ -193,9 +193,10 @@ int rgs_cpu_blend_fwd_push(const RgsCamera* cam, const int32_t* ranges, const ui
 }
 
 // grad_out: (H,W,4) = dL/dC (rgb), dL/dT. splat_grads[n_vis] must be zeroed by the caller.
-int rgs_cpu_blend_bwd(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
-                      const float* out, const int32_t* n_contrib, const float* grad_out, RgsSplatGrad* splat_grads,
-                      int32_t* counters, void*) {
+// grad_depth (optional, H*W): gradient of the depth output
+int rgs_cpu_blend_bwd_depth(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
+                            const float* out, const int32_t* n_contrib, const float* grad_out, const float* grad_depth,
+                            RgsSplatGrad* splat_grads, int32_t* counters, void*) {
     (void)counters;
     const int W = cam->W, H = cam->H;
     // serial over tiles: the accumulation order is then fixed, which makes this path the
@@ -211,10 +212,12 @@ int rgs_cpu_blend_bwd(const RgsCamera* cam, const int32_t* ranges, const uint32_
                 RgsPixelRay ray; rgs_pixel_ray(*cam, (float)x, (float)y, ray);
                 RgsPixelBwd st;
                 rgs_pixel_bwd_init(st, out[4 * pid + 3], grad_out + 4 * pid, grad_out[4 * pid + 3]);
+                RgsPixelBwdDepth dep = {0.f, 0.f, grad_depth ? grad_depth[pid] : 0.f};
                 for (int i = r0 + n_contrib[pid] - 1; i >= r0; --i) {
                     RgsSplatGrad g;
                     uint32_t slot = vals[i];
-                    if (!rgs_blend_bwd_step(*cam, ray, (float)x, (float)y, splats[slot], st, g)) continue;
+                    if (!rgs_blend_bwd_step(*cam, ray, (float)x, (float)y, splats[slot], st, g, grad_depth ? &dep : nullptr))
+                        continue;
                     float* dst = reinterpret_cast<float*>(&splat_grads[slot]);
                     const float* src = reinterpret_cast<const float*>(&g);
                     for (int k = 0; k < 10; ++k) dst[k] += src[k];
@@ -222,6 +225,12 @@ int rgs_cpu_blend_bwd(const RgsCamera* cam, const int32_t* ranges, const uint32_
             }
     }
     return 0;
+}
+
+int rgs_cpu_blend_bwd(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
+                      const float* out, const int32_t* n_contrib, const float* grad_out, RgsSplatGrad* splat_grads,
+                      int32_t* counters, void*) {
+    return rgs_cpu_blend_bwd_depth(cam, ranges, vals, splats, out, n_contrib, grad_out, nullptr, splat_grads, counters, nullptr);
 }
 
 static inline const RgsSegment* find_segment(const RgsSegment* segs, int nseg, int64_t id, int64_t& local) {

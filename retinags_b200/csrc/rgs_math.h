@@ -408,7 +408,8 @@ RGS_HD float rgs_project_bwd(const RgsCamera& cam, const float* p, const float* 
     float dty = e.clamp_y ? 0.0f : -cam.focal_y * tz2 * dJ12;
     float dtz = -cam.focal_x * tz2 * dJ00 - cam.focal_y * tz2 * dJ11 + 2.f * cam.focal_x * e.txc * tz3 * dJ02 +
                 2.f * cam.focal_y * e.tyc * tz3 * dJ12;
-    // t = Wrot p + trans
+    // t = Wrot p + trans; the splat's depth is t_z itself (gradient of the depth output, zero in training)
+    dtz += g.ddepth;
     for (int j = 0; j < 3; ++j) gp[j] += v[4 * j + 0] * dtx + v[4 * j + 1] * dty + v[4 * j + 2] * dtz;
 
     // ---- Sigma = L L^T, L = R diag(s*mod)
@@ -578,10 +579,20 @@ RGS_HD void rgs_pixel_bwd_init(RgsPixelBwd& st, float T_final, const float* gC, 
     st.gC[0] = gC[0]; st.gC[1] = gC[1]; st.gC[2] = gC[2]; st.gT = gT;
 }
 
+// Extra backward state of a pixel when the depth output D = sum depth_i alpha_i T_i carries a gradient
+// (the reference's dL/ddepth path, cuda_rasterizer_hgs/backward.cu:391-403,584). Training never sets it.
+struct RgsPixelBwdDepth {
+    float acc;      // depth accumulated behind the current splat
+    float last_d;   // depth of the splat visited before (the one behind)
+    float gD;       // dL/dD of this pixel
+};
+
 // One (pixel, splat) step of the backward. Returns false when the pair did not contribute;
 // otherwise fills `g` with this pixel's contribution to the splat's image-space gradients.
+// `dep` (optional): also propagate the gradient of the depth output.
 RGS_HD bool rgs_blend_bwd_step(const RgsCamera& cam, const RgsPixelRay& ray, float pixx, float pixy,
-                               const RgsSplat& sp, RgsPixelBwd& st, RgsSplatGrad& g) {
+                               const RgsSplat& sp, RgsPixelBwd& st, RgsSplatGrad& g,
+                               RgsPixelBwdDepth* dep = nullptr) {
     float alpha, G, dx, dy;
     if (!rgs_alpha(cam, ray, pixx, pixy, sp, alpha, G, dx, dy)) return false;
     st.T = st.T / (1.0f - alpha);
@@ -594,6 +605,13 @@ RGS_HD bool rgs_blend_bwd_step(const RgsCamera& cam, const RgsPixelRay& ray, flo
         st.last_c[ch] = col[ch];
         dL_dalpha += (col[ch] - st.acc[ch]) * st.gC[ch];
         gcol[ch] = wgt * st.gC[ch];
+    }
+    float g_depth = 0.0f;
+    if (dep) {  // same recurrence as a colour channel, with the splat's view depth as its "colour"
+        dep->acc = st.last_alpha * dep->last_d + (1.0f - st.last_alpha) * dep->acc;
+        dep->last_d = sp.depth;
+        dL_dalpha += (sp.depth - dep->acc) * dep->gD;
+        g_depth = wgt * dep->gD;
     }
     dL_dalpha *= st.T;
     st.last_alpha = alpha;
@@ -608,7 +626,7 @@ RGS_HD bool rgs_blend_bwd_step(const RgsCamera& cam, const RgsPixelRay& ray, flo
     g.dcb = -gdx * dy * dL_dG;
     g.dcc = -0.5f * gdy * dy * dL_dG;
     g.dopacity = G * dL_dalpha;
-    g.ddepth = 0.0f; g.pad0 = 0.0f; g.pad1 = 0.0f;
+    g.ddepth = g_depth; g.pad0 = 0.0f; g.pad1 = 0.0f;
     return true;
 }
 

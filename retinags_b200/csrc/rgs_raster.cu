@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(256) rgs_project_emit_kernel(
 // blend forward
 // ---------------------------------------------------------------------------------------------
 #define BLEND_BATCH 256
-#define RGS_MAX_PUSH 16
+#define RGS_MAX_PUSH 32
 #define RGS_WAIT_LIMIT (1u << 22)
 
 struct BlendSmem {
@@ -284,12 +284,14 @@ __device__ __forceinline__ float warp_sum(float v) {
 // float atomics. Integer addition is associative, so the result no longer depends on the order in which tiles and
 // warps arrive: two runs give identical bits, which separates a race from rounding when gradients disagree.
 #define RGS_FIXED_SCALE 1099511627776.0  // 2^40: resolution 9e-13, range +-8.4e6
-template <bool FIXED>
+// DEPTH: the depth output carries a gradient (grad_depth, one float per pixel); a tenth value per splat is reduced.
+template <bool FIXED, bool DEPTH = false>
 __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
     const __grid_constant__ RgsCamera cam, const int2* __restrict__ ranges, const uint32_t* __restrict__ vals,
     const RgsSplat* __restrict__ splats, const float4* __restrict__ out, const int32_t* __restrict__ n_contrib,
     const float4* __restrict__ grad_out, RgsSplatGrad* __restrict__ splat_grads, uint32_t* __restrict__ counters,
-    unsigned long long* __restrict__ fixed_acc, const __grid_constant__ RgsSlabArgs slab) {
+    unsigned long long* __restrict__ fixed_acc, const __grid_constant__ RgsSlabArgs slab,
+    const float* __restrict__ grad_depth = nullptr) {
     __shared__ __align__(128) BlendSmem sm;
     __shared__ uint32_t sm_slot[2][BLEND_BATCH];
     const int tid = threadIdx.x, lane = tid & 31;
@@ -330,6 +332,7 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
         float gC[3] = {g.x, g.y, g.z};
         rgs_pixel_bwd_init(st, o.w, gC, g.w);
     }
+    RgsPixelBwdDepth dep = {0.f, 0.f, (DEPTH && inside) ? grad_depth[pid] : 0.f};
     auto issue = [&](int b) {
         const int stage = b & 1;
         const int cnt = min(BLEND_BATCH, total - b * BLEND_BATCH);
@@ -371,7 +374,7 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
                 const int contributor = total - (b * BLEND_BATCH + j);  // 1-based index of this instance in the tile list
                 RgsSplatGrad g;
                 bool hit = false;
-                if (contributor <= last) hit = rgs_blend_bwd_step(cam, ray, pixx, pixy, sm.buf[stage][j], st, g);
+                if (contributor <= last) hit = rgs_blend_bwd_step(cam, ray, pixx, pixy, sm.buf[stage][j], st, g, DEPTH ? &dep : nullptr);
                 if (!__any_sync(0xffffffffu, hit)) continue;
                 // Reduce 8 of the 9 values with a transposing butterfly: at every step a lane keeps half of its values
                 // and hands the other half to its partner, so the 8 sums cost 4+2+1+1+1 = 9 shuffles instead of 40;
@@ -407,6 +410,8 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
                 w1 += __shfl_xor_sync(0xffffffffu, w1, 2);
                 w1 += __shfl_xor_sync(0xffffffffu, w1, 1);
                 v8 = warp_sum(v8);
+                float v9 = 0.f;
+                if (DEPTH) v9 = warp_sum(hit ? g.ddepth : 0.f);
                 // value index held by this lane: bit 16 -> +4, bit 8 -> +2, bit 4 -> +1
                 const int which = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
                 if (FIXED) {
@@ -417,6 +422,7 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
                     float* dst = reinterpret_cast<float*>(splat_grads + sm_slot[stage][j]);
                     if ((lane & 3) == 0) atomicAdd(dst + which, w1);
                     if (lane == 0) atomicAdd(dst + 8, v8);
+                    if (DEPTH && lane == 1) atomicAdd(dst + 9, v9);
                 }
             }
           }
@@ -471,7 +477,7 @@ __global__ void __launch_bounds__(128, 8) rgs_geom_bwd_kernel(
         // gradients, hence exactly zero parameter gradients: only its visibility statistics change, and its
         // gradient row stays untouched (which the optimiser exploits as well).
         if (g0.x == 0.f && g0.y == 0.f && g0.z == 0.f && g0.w == 0.f && g1.x == 0.f && g1.y == 0.f && g1.z == 0.f &&
-            g1.w == 0.f && g2.x == 0.f) {
+            g1.w == 0.f && g2.x == 0.f && g2.y == 0.f) {
             if (sg.g_mean2d) { sg.g_mean2d[2 * i] = 0.f; sg.g_mean2d[2 * i + 1] = 0.f; }
             if (sg.stat_denom) sg.stat_denom[i] += 1.0f;
             if (sg.stat_maxrad) sg.stat_maxrad[i] = fmaxf(sg.stat_maxrad[i], (float)(a >> 3));
@@ -609,6 +615,19 @@ int rgs_cuda_blend_bwd(const RgsCamera* cam, const int32_t* ranges, const uint32
         *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
         reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters), nullptr,
         RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE});
+    return (int)cudaGetLastError();
+}
+
+// Backward with a gradient on the depth output as well (grad_depth: H*W floats): the path of the autograd interface.
+int rgs_cuda_blend_bwd_depth(const RgsCamera* cam, const int32_t* ranges, const uint32_t* vals, const RgsSplat* splats,
+                             const float* out, const int32_t* n_contrib, const float* grad_out, const float* grad_depth,
+                             RgsSplatGrad* splat_grads, int32_t* counters, void* stream) {
+    dim3 grid(cam->tiles_x, cam->tiles_y);
+    if (!grad_depth) return rgs_cuda_blend_bwd(cam, ranges, vals, splats, out, n_contrib, grad_out, splat_grads, counters, stream);
+    rgs_blend_bwd_kernel<false, true><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
+        reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters), nullptr,
+        RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE}, grad_depth);
     return (int)cudaGetLastError();
 }
 

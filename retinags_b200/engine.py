@@ -151,15 +151,19 @@ class StepEngine:
                                                         push=push)
         return local_out
 
-    def render(self, cams: list[Camera], relations, sh_degree: int, background=None):
+    def render(self, cams: list[Camera], relations, sh_degree: int, background=None, want_depth: bool = False):
         """Eval-time render: returns per view the composited (3,H,W) image rows this rank owns
-        (``image``, ``rows``) -- with world size 1 that is the whole image."""
+        (``image``, ``rows``) -- with world size 1 that is the whole image.
+
+        ``want_depth`` adds the composited depth ``sum_k T_<k D_k`` and ``alpha = 1 - T_total`` on the same rows
+        (``result_aggregator.py:244-259`` of the reference). The depth partials travel as a second 4-channel
+        image (D_k, 0, 0, T_k) through the same ordered "over": its first channel composites to exactly that sum."""
         bg = self.background if background is None else background
         plans = self.plan(cams, relations)
         self._prepare_transport(plans)
         if self.borrow is not None:
             self.borrow.refresh(self.stores, need_grads=False)
-        local_out = self.render_partials(cams, plans, sh_degree, check=True)
+        local_out = self.render_partials(cams, plans, sh_degree, want_depth=want_depth, check=True)
         slots = self.transport.exchange_partials(plans, local_out)
         out = []
         for p in plans:
@@ -169,6 +173,25 @@ class StepEngine:
                 cl.composite(slots[p.view], bg, max(0, b[0] - 5), min(p.H, b[1] + 5))
             out.append(dict(image=cl.image, trans=cl.trans, rows=b, partials=local_out[p.view], plan=p))
         self.transport.barrier()  # slots may be overwritten by the next render only after everyone composited
+        if want_depth:
+            dparts = {}
+            for p in plans:
+                dparts[p.view] = {}
+                for m, part in local_out[p.view].items():
+                    d4 = torch.zeros_like(part)
+                    d4[..., 0] = self._tasks[(p.view, m)].depth
+                    d4[..., 3] = part[..., 3]
+                    dparts[p.view][m] = d4
+            move = getattr(self.transport, "exchange_images", self.transport.exchange_partials)
+            dslots = move(plans, dparts)
+            for p, o in zip(plans, out):
+                b = p.bands[self.rank]
+                dimg = torch.zeros(3, p.H, p.W, dtype=torch.float32, device=self.device)
+                dtr = torch.ones(p.H, p.W, dtype=torch.float32, device=self.device)
+                if b[1] > b[0]:
+                    self._loss(p.view, p.H, p.W).composite(dslots[p.view], (0.0, 0.0, 0.0), b[0], b[1], image=dimg, trans=dtr)
+                o["depth"], o["alpha"] = dimg[0], 1.0 - dtr
+            self.transport.barrier()
         return out
 
     def _prepare_transport(self, plans):

@@ -58,15 +58,18 @@ class CompositeLoss:
     def _bg(bg):
         return (ctypes.c_float * 3)(*[float(v) for v in bg])
 
-    def composite(self, partials: list[torch.Tensor], bg, row0: int = 0, row1: int | None = None):
-        """Composite rows [row0,row1) of the ordered partials into ``self.image`` / ``self.trans``."""
+    def composite(self, partials: list[torch.Tensor], bg, row0: int = 0, row1: int | None = None, image=None, trans=None):
+        """Composite rows [row0,row1) of the ordered partials into ``self.image`` / ``self.trans`` (or into the
+        (3,H,W) / (H,W) buffers given)."""
         row1 = self.H if row1 is None else row1
         for p in partials:  # tensors, or raw (virtual full-height) base addresses
             assert isinstance(p, int) or (p.is_contiguous() and p.shape[-1] == 4)
+        image = self.image if image is None else image
+        trans = self.trans if trans is None else trans
         ptrs = native.pointer_array(partials)
         native.call("composite_fwd", self.device, ptrs, len(partials), self._bg(bg), self.H, self.W, row0, row1,
-                    self.image, self.trans)
-        return self.image, self.trans
+                    image, trans)
+        return image, trans
 
     def loss(self, gt: torch.Tensor, lambda_dssim: float = 0.2, row0: int = 0, row1: int | None = None,
              weight: float = 1.0):

@@ -32,6 +32,7 @@ SIGNATURES = {
     "blend_fwd": "ppppppppp",
     "blend_fwd_push": "ppppppppipppp",
     "blend_bwd": "pppppppppp",
+    "blend_bwd_depth": "ppppppppppp",
     "geom_bwd": "ppipppppip",
     "scatter_radii": "pppiipp",
     "adam": "ppppiipfffiipppp",

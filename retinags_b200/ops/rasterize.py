@@ -426,12 +426,19 @@ class RenderTask:
         return info
 
     # -- backward -----------------------------------------------------------------------------
-    def backward(self, grad_out: torch.Tensor, segments: list[Segment]):
-        """Accumulate parameter gradients of the last forward. ``grad_out`` is (H,W,4): dL/dC, dL/dT."""
+    def backward(self, grad_out: torch.Tensor, segments: list[Segment], grad_depth: torch.Tensor | None = None):
+        """Accumulate parameter gradients of the last forward. ``grad_out`` is (H,W,4): dL/dC, dL/dT; ``grad_depth``
+        (optional, (H,W)) is the gradient of the depth output (a single-pass render only)."""
         cam = self.cam
         assert grad_out.is_contiguous() and grad_out.shape == (cam.H, cam.W, 4)
         with self._phase("bwd.blend"):
-            if self._slab_active:
+            if grad_depth is not None:
+                if self._slab_active or self.deterministic:
+                    raise NotImplementedError("a depth gradient needs the single-pass, float-accumulating backward")
+                assert grad_depth.is_contiguous() and grad_depth.shape == (cam.H, cam.W) and grad_depth.dtype == torch.float32
+                native.call("blend_bwd_depth", self.device, cam, self.ranges, self.vals, self.splats, self.last_out,
+                            self.n_contrib, grad_out, grad_depth, self.splat_grads, self.counters)
+            elif self._slab_active:
                 fixed = None
                 if self.deterministic:
                     if self._fixed_acc is None or self._fixed_acc.numel() < 9 * self.cap_vis:
@@ -521,6 +528,8 @@ class _Rasterize(torch.autograd.Function):
             full[:, : shs.shape[1]] = shs
             seg.sh = full.view(-1, 48)
         task = RenderTask(dev)
+        task.slabs = False  # one pass: the backward of this interface may carry a depth gradient
+        task.deterministic = False
         out = task.forward(cam, [seg], want_depth=True, check=True)
         bg = settings.bg.to(dev).view(1, 1, 3)
         color = (out[..., :3] + out[..., 3:4] * bg).permute(2, 0, 1).contiguous()
@@ -550,7 +559,10 @@ class _Rasterize(torch.autograd.Function):
         seg.g_rot = torch.zeros(n, 4, device=dev)
         seg.g_opacity = torch.zeros(n, 1, device=dev)
         seg.g_mean2d = torch.zeros(n, 2, device=dev)
-        task.backward(grad.contiguous(), [seg])
+        gd = None
+        if g_depth is not None and bool((g_depth != 0).any()):
+            gd = g_depth[0].contiguous().float()
+        task.backward(grad.contiguous(), [seg], grad_depth=gd)
         g_means2D = torch.zeros(n, 3, device=dev)
         g_means2D[:, :2] = seg.g_mean2d
         g_sh = seg.g_sh.view(n, 16, 3)[:, : ctx.n_sh]

@@ -289,6 +289,14 @@ class PeerTransport:
             out[p.view] = [self.region.ptrs[self.rank] + self._slot_off(p.view, m) - e[0] * p.W * 16 for m in p.models]
         return out
 
+    def exchange_images(self, plans, local_images):
+        """Move arbitrary (H,W,4) images of the local sub-models to the owners of the row bands with point-to-point
+        messages of ``torch.distributed``: the off-step path (eval-time depth maps), which has no fused producer."""
+        if getattr(self, "_dist_transport", None) is None:
+            from .compositing import TorchDistTransport
+            self._dist_transport = TorchDistTransport(self.device, self.group)
+        return self._dist_transport.exchange_partials(plans, local_images)
+
     def local_grad_images(self, plans) -> dict:
         """Gradient images of this rank's renders, inside the exchange region (peer-writable)."""
         out = {}

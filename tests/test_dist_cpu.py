@@ -32,6 +32,9 @@ def _worker(rank, world, port, out_dir, slabs=False):
         for i in range(3):
             img, rows, _ = sess.render_view(i)
             imgs.append((img[:, rows[0]:rows[1]].clone(), rows))
+        d = sess.engine.render([sess.cams[1]], sess.relation[[1]], sess.sh_degree, want_depth=True)[0]
+        r0, r1 = d["rows"]
+        depth = (d["depth"][r0:r1].clone(), d["alpha"][r0:r1].clone(), d["rows"])
         losses = []
         for it in range(10):
             loss, _, _ = sess.step_e2e(it % 4)
@@ -40,7 +43,7 @@ def _worker(rank, world, port, out_dir, slabs=False):
             losses.append(float(t))
         img, rows, _ = sess.render_view(0)
         counts = {m: st.count for m, st in sess.stores.items()}
-        torch.save(dict(imgs=imgs, losses=losses, final=(img[:, rows[0]:rows[1]].clone(), rows), counts=counts,
+        torch.save(dict(imgs=imgs, losses=losses, depth=depth, final=(img[:, rows[0]:rows[1]].clone(), rows), counts=counts,
                         borrowed=int(sess.border._counts.sum())), os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
@@ -72,6 +75,17 @@ def test_two_ranks_match_single_rank(tmp_path, slabs):
         assert open_px.float().mean() > 0.3
         assert (diff[open_px] > 1e-5).float().mean() < 2e-3, float((diff[open_px] > 1e-5).float().mean())
         assert diff.max() < 2e-3
+    # depth composited over the two sub-models (sum_k T_<k D_k) == depth of the single render; alpha = 1 - T
+    sd = single.engine.render([single.cams[1]], single.relation[[1]], single.sh_degree, want_depth=True)[0]
+    got_d, got_a = torch.zeros_like(sd["depth"]), torch.zeros_like(sd["alpha"])
+    for r in res:
+        band_d, band_a, rows = r["depth"]
+        got_d[rows[0]:rows[1]], got_a[rows[0]:rows[1]] = band_d, band_a
+    open_px = sd["trans"] > 2e-3
+    dd = (got_d - sd["depth"]).abs()
+    assert float(sd["depth"].max()) > 0.5
+    assert (dd[open_px] > 1e-5 * (1 + sd["depth"][open_px])).float().mean() < 2e-3 and dd.max() < 1e-2
+    assert (got_a - sd["alpha"]).abs().max() < 2e-3
     ref_losses = [single.step_e2e(it % 4)[0] for it in range(10)]
     for a, b in zip(res[0]["losses"], ref_losses):
         assert abs(a - b) < 2e-4 * max(1.0, abs(b)), (res[0]["losses"], ref_losses)

@@ -283,3 +283,50 @@ def test_gradients_against_finite_differences():
             assert min(errs) < 0.06, (name, i, j, an, errs)
             checked += 1
     assert checked == 15
+
+
+def test_depth_gradient_matches_autograd():
+    """A loss on the depth output reaches means, scales, rotations and opacities like autograd through the oracle's
+    D = sum z_i alpha_i T_i (the reference's dL/ddepth path), alone and together with a colour loss."""
+    deg = 1
+    g, cams = small_scene(n=300, seed=13, sh_degree=deg)
+    cam = cams[1]
+    a = activated(g)
+    gen = torch.Generator().manual_seed(2)
+    for with_colour in (False, True):
+        leaves = {k: v.clone().requires_grad_(True) for k, v in a.items()}
+        C, T, D, _ = oracle.rasterize(cam, leaves["xyz"], leaves["sh"].view(-1, 16, 3), leaves["opacity"], leaves["scale"],
+                                      leaves["rot"], deg)
+        wD = torch.randn(D.shape, generator=gen)
+        wC = torch.randn(C.shape, generator=gen) if with_colour else torch.zeros(C.shape)
+        ((D * wD).sum() + (C * wC).sum()).backward()
+        out, task, seg, c = native_render(a, cam, deg, raw=False, want_depth=True)
+        torch.testing.assert_close(task.depth, D.detach(), atol=2e-5, rtol=1e-4)
+        n = seg.count
+        for name, w in (("g_xyz", 3), ("g_sh", 48), ("g_scale", 3), ("g_rot", 4), ("g_opacity", 1)):
+            setattr(seg, name, torch.zeros(n, w))
+        grad = torch.cat([wC.permute(1, 2, 0), torch.zeros(C.shape[1], C.shape[2], 1)], dim=-1).contiguous()
+        task.backward(grad, [seg], grad_depth=wD.contiguous())
+        for name, key in (("g_xyz", "xyz"), ("g_scale", "scale"), ("g_rot", "rot"), ("g_opacity", "opacity")):
+            ref = leaves[key].grad
+            got = getattr(seg, name)
+            scale = ref.abs().max().item() + 1e-12
+            assert (got - ref).abs().max().item() / scale < 2e-3, (name, with_colour)
+    # the autograd interface no longer drops the depth gradient
+    st = rasterize.GaussianRasterizationSettings(
+        image_height=cam.height, image_width=cam.width, tanfovx=cam.tan_fovx, tanfovy=cam.tan_fovy,
+        bg=torch.zeros(3), scale_modifier=1.0, viewmatrix=torch.tensor(cam.world_view_transform),
+        projmatrix=torch.tensor(cam.full_proj_transform), projmatrix_inv=torch.tensor(cam.view_world_transform),
+        range_low=torch.tensor([-1e9] * 3), range_up=torch.tensor([1e9] * 3), sh_degree=deg,
+        campos=torch.tensor(cam.camera_center))
+    xyz = a["xyz"].clone().requires_grad_(True)
+    _, depth, _, _ = rasterize.GaussianRasterizer(st)(xyz, torch.zeros(xyz.shape[0], 3), a["opacity"],
+                                                      shs=a["sh"].view(-1, 16, 3)[:, :4], scales=a["scale"], rotations=a["rot"])
+    (depth[0] * wD).sum().backward()
+    ref = leaves["xyz"].grad if not with_colour else None
+    leaves = {k: v.clone().requires_grad_(True) for k, v in a.items()}
+    _, _, D, _ = oracle.rasterize(cam, leaves["xyz"], leaves["sh"].view(-1, 16, 3), leaves["opacity"], leaves["scale"],
+                                  leaves["rot"], deg)
+    (D * wD).sum().backward()
+    ref = leaves["xyz"].grad
+    assert (xyz.grad - ref).abs().max().item() / (ref.abs().max().item() + 1e-12) < 2e-3
