@@ -29,10 +29,11 @@ static __device__ __align__(256) unsigned char rgs_noalloc_scratch[NA_BYTES];
 #define NA_MAX_DEVICES 64
 static unsigned char* g_scratch_ptr[NA_MAX_DEVICES];
 static std::mutex g_mutex;
-static char g_error[256] = "";
+// one message buffer per calling thread: the pointer handed out by rgs_cuda_noalloc_last_error stays valid and
+// unchanged while other threads report errors of their own
+static thread_local char g_error[256] = "";
 
 static int na_fail(int code, const char* fmt, long long a, long long b) {
-    std::lock_guard<std::mutex> lock(g_mutex);
     snprintf(g_error, sizeof(g_error), fmt, a, b);
     return code;
 }
@@ -94,10 +95,8 @@ int rgs_cuda_sort_ranges_noalloc(uint64_t* keys, uint32_t* vals, int64_t cap_pai
     rgs_tile_ranges_kernel<<<148 * 8, 256, 0, st>>>(kin, cnt, cap, reinterpret_cast<int2*>(ranges), (uint32_t)num_tiles,
                                                     in_tmp ? vin : nullptr, in_tmp ? vals : nullptr);
     cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) {
-        std::lock_guard<std::mutex> lock(g_mutex);
+    if (e != cudaSuccess)
         snprintf(g_error, sizeof(g_error), "rgs_cuda_sort_ranges_noalloc: launch failed: %s", cudaGetErrorString(e));
-    }
     return (int)e;
 }
 

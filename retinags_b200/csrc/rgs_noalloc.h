@@ -14,7 +14,10 @@
 //  * the scratch array (about 12.3 MB) is part of the library image: every GPU on which the library is
 //    loaded holds it until the process exits;
 //  * the first call on a device looks up the device address of the array (cudaGetSymbolAddress, with that
-//    device current). Make that first call before any stream capture on that device;
+//    device current). With the CUDA runtime's lazy module loading that first call may also be the moment at
+//    which the runtime loads the library's device image (and with it the scratch array) onto the device, which
+//    takes device memory once; every later call leaves the amount of free device memory unchanged. Make that
+//    first call at start-up, before any stream capture on that device;
 //  * all calls on a device share the one array and it keeps the previous call's contents. The sort
 //    overwrites every word it later reads, so nothing has to be cleared, but two calls that overlap on
 //    the GPU (different streams, no dependency) race on it: serialise them;
@@ -37,7 +40,8 @@ extern "C" {
 int rgs_cuda_sort_ranges_noalloc(uint64_t* keys, uint32_t* vals, int64_t cap_pairs, const int32_t* counters,
                                  int64_t num_tiles, int32_t* ranges, void* stream);
 
-// Text of the last error this entry point reported on the calling thread's process ("" when none).
+// Text of the last error this entry point reported to the calling thread ("" when none). The buffer belongs to
+// the calling thread: it is not rewritten by errors that other threads run into.
 const char* rgs_cuda_noalloc_last_error(void);
 
 #ifdef __cplusplus

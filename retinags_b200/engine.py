@@ -319,7 +319,10 @@ class StepEngine:
         the transport gave up, and tells whether that step's optimiser update was dropped. ``None`` while the copies
         are still in flight (the step is then looked at by a later call)."""
         if self.device.type != "cuda":
-            return self.poll()
+            info = self.poll()
+            info["dropped"] = bool(self._skip[CNT_OVERFLOW])
+            self.dropped_steps += int(info["dropped"])
+            return info
         ev = getattr(self, "_skip_event", None)
         if ev is None or not ev.query():
             return None

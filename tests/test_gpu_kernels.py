@@ -11,8 +11,6 @@ from retinags_b200.ops import native, rasterize
 from retinags_b200.ops.loss import CompositeLoss
 
 pytestmark = pytest.mark.gpu
-# kernels behind an opt-in switch whose latest version has not run on a GPU: their tests are opt-in as well
-EXPERIMENTAL = os.environ.get("RGS_TEST_EXPERIMENTAL", "0") == "1"
 
 
 def _scene(n=40000, w=320, h=208, deg=3, seed=4):
@@ -93,7 +91,7 @@ def test_raster_backward_matches_cpu():
     for name in ("g_xyz", "g_sh", "g_scale", "g_rot", "g_opacity", "g_mean2d", "stat_grad", "stat_denom", "stat_maxrad"):
         a, b = getattr(res["cuda"], name).cpu(), getattr(res["cpu"], name)
         # atomics reorder the sums and a stop-rule flip changes single pixels: compare in norm
-        assert (a - b).norm().item() <= 2e-2 * b.norm().item() + 1e-9, name
+        assert (a - b).norm().item() <= 5e-3 * b.norm().item() + 1e-9, name
 
 
 def test_radix_sort_matches_torch():
@@ -173,8 +171,6 @@ def test_adam_matches_cpu():
     assert float(stores["cuda"].grads.abs().sum()) == 0.0
 
 
-@pytest.mark.skipif(not EXPERIMENTAL, reason="the row-block Adam kernel (RGS_ADAM=rows) has not run on a GPU yet; its test "
-                    "only runs with RGS_TEST_EXPERIMENTAL=1")
 def test_adam_row_block_variant_matches_unit_variant():
     """Both work distributions of the fused Adam give the same bits: sparse marks, dense marks, a tail that is not a
     multiple of 32 rows."""
@@ -391,8 +387,6 @@ def test_peer_region_canaries_detect_an_out_of_bounds_store():
     region.close()
 
 
-@pytest.mark.skipif(not EXPERIMENTAL, reason="the two-slab forward is opt-in (RGS_SLABS=1); its buffer policy was rewritten "
-                    "after its last GPU run, so its GPU test only runs with RGS_TEST_EXPERIMENTAL=1 until it has run again")
 def test_two_slab_forward_matches_single_pass_and_emits_fewer_instances():
     """Near slab first, far slab only for unsaturated tiles: same image, contributor indices and gradients as the single
     pass, fewer tile instances in a dense opaque scene."""
@@ -425,3 +419,107 @@ def test_two_slab_forward_matches_single_pass_and_emits_fewer_instances():
     assert_mostly_close(a[2], b[2], atol=2e-4, rtol=1e-4, max_frac=1e-2, hard_atol=5e-2)
     assert b[3] < a[3], f"instances: single pass {a[3]}, two slabs {b[3]}"
     assert (a[4] - b[4]).norm().item() <= 1e-3 * a[4].norm().item(), "gradients differ"
+
+
+def test_cuda_render_and_gradients_match_the_pytorch_oracle():
+    """The CUDA path against the independent fp32 PyTorch restatement (``ops/oracle.py``), not against the CPU build of
+    the same header: forward image, transmittance and depth, and all five parameter gradients through autograd."""
+    from helpers import activated
+    from retinags_b200.ops import oracle
+    deg = 3
+    g, cams = small_scene(n=500, seed=21, width=96, height=64)
+    cam = cams[1]
+    box = ([-0.4, -1e9, -1e9], [1e9, 0.5, 1e9])
+    a = activated(g)
+    leaves = {k: v.clone().requires_grad_(True) for k, v in a.items()}
+    C, T, D, _ = oracle.rasterize(cam, leaves["xyz"], leaves["sh"].view(-1, 16, 3), leaves["opacity"], leaves["scale"],
+                                  leaves["rot"], deg, box[0], box[1])
+    gen = torch.Generator().manual_seed(0)
+    wC, wT, wD = torch.randn(C.shape, generator=gen), torch.randn(T.shape, generator=gen), torch.randn(D.shape, generator=gen)
+    ((C * wC).sum() + (T * wT).sum() + (D * wD).sum()).backward()
+    out, task, seg, c = native_render(a, cam, deg, box=box, raw=False, device="cuda", want_depth=True)
+    ref = torch.cat([C.detach().permute(1, 2, 0), T.detach()[..., None]], dim=-1)
+    assert (out.cpu() - ref).abs().max().item() <= 1e-4 * max(1.0, ref.abs().max().item())
+    assert (task.depth.cpu() - D.detach()).abs().max().item() <= 1e-4 * max(1.0, D.abs().max().item())
+    n = seg.count
+    for name, w in (("g_xyz", 3), ("g_sh", 48), ("g_scale", 3), ("g_rot", 4), ("g_opacity", 1)):
+        setattr(seg, name, torch.zeros(n, w, device="cuda"))
+    grad = torch.cat([wC.permute(1, 2, 0), wT[..., None]], dim=-1).contiguous().cuda()
+    task.backward(grad, [seg], grad_depth=wD.contiguous().cuda())
+    for name, key in (("g_xyz", "xyz"), ("g_sh", "sh"), ("g_scale", "scale"), ("g_rot", "rot"), ("g_opacity", "opacity")):
+        want = leaves[key].grad
+        got = getattr(seg, name).cpu()
+        assert (got - want).norm().item() <= 2e-3 * want.norm().item() + 1e-9, name
+
+
+def test_a_device_wait_that_runs_out_reports_and_leaves_the_context_usable():
+    """Failure detection on the device without a fault: a wait on an epoch that nobody will signal gives up after its
+    cycle budget, records which rank it waited for, the kernel returns normally and the host check raises. Afterwards
+    the same transport signals and waits as usual."""
+    from retinags_b200.parallel.peer import PeerTransport
+    dev = torch.device("cuda", 0)
+    tr = PeerTransport(dev)
+    tr._local_index = {0: 0}
+    tr._ensure(4096, 4096, 1, 1, 1)
+    tr.barrier()
+    torch.cuda.synchronize()
+    tr.check()  # healthy
+    native.call("p2p_wait", dev, tr.flags, 1, tr.epoch + 3, 2_000_000, tr.status, None, sig="piiippp")  # ~1 ms budget
+    torch.cuda.synchronize()
+    assert int(tr.status[0]) == 0x100
+    tr.record_status()
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="peer wait expired: no signal from rank 0"):
+        tr.check(block=False)
+    with pytest.raises(RuntimeError, match="peer wait expired"):
+        tr.check()
+    tr.status.zero_()
+    tr.barrier()
+    torch.cuda.synchronize()
+    tr.check()
+    assert float(torch.ones(4, device=dev).sum()) == 4.0
+    tr.close()
+
+
+def test_border_selection_kernel_matches_the_mask_selection_on_gpu():
+    """``rgs_border_mask_kernel`` (one pass, bit mask per Gaussian) against the boolean-mask selection, four boxes."""
+    from retinags_b200.parallel.border import select_border
+    g = synthetic.uniform_gaussians(50000, 9, sh_degree=1, log_scale_mean=-3.0)
+    st = GaussianStore(50000, "cuda", 1)
+    st.set_params({k: v.cuda() for k, v in g.items()})
+    lo = torch.tensor([[-9., -9, -9], [0, -9, -9], [-9, 0, -9], [0, 0, -9]]).cuda()
+    hi = torch.tensor([[0., 0, 9], [9, 0, 9], [0, 9, 9], [9, 9, 9]]).cuda()
+    for m in range(4):
+        a = select_border(st, m, lo, hi, 0.05, native_mask=False)
+        b = select_border(st, m, lo, hi, 0.05, native_mask=True)
+        assert sorted(a) == sorted(b) and len(a) > 0
+        for d in a:
+            assert torch.equal(a[d], b[d])
+
+
+def test_an_overflowing_step_is_dropped_by_the_optimiser_and_leaves_no_gradients():
+    """A render that runs out of instance capacity raises the overflow word; the fused Adam sees it, changes no
+    parameter, clears the step's gradients, and the next step (buffers grown by the poll) trains normally."""
+    from retinags_b200.bench_session import BenchSession
+    sess = BenchSession("cuda", 0, 1, 60000, 320, 208, batch=2, n_views=4, gt_gaussians=20000, seed=5, sh_degree=3,
+                        grid=(64, 64, 1), bvh_depth=1)
+    sess.step(0); sess.settle()
+    for task in sess.engine._tasks.values():  # shrink every instance buffer far below the need
+        task._grow_inst(task.min_inst)
+        task.cap_inst = 4096
+        task._pending_cap = 0
+    before = [st.params.clone() for st in sess.stores.values()]
+    sess.step(1)
+    torch.cuda.synchronize()
+    assert int(sess.engine._skip[native.CNT_OVERFLOW]) != 0
+    for st, b in zip(sess.stores.values(), before):
+        assert torch.equal(st.params, b)
+        assert float(st.grads.abs().sum()) == 0.0 and int(st.touched.sum()) == 0
+    info = None
+    while info is None:
+        info = sess.engine.poll_async()
+    assert info["dropped"] and info["overflow"]
+    sess.step(2)
+    torch.cuda.synchronize()
+    assert int(sess.engine._skip[native.CNT_OVERFLOW]) == 0
+    assert any(not torch.equal(st.params, b) for st, b in zip(sess.stores.values(), before))

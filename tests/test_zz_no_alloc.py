@@ -55,9 +55,16 @@ def test_noalloc_sort_matches_regular_entry_point():
         v1 = torch.zeros(cap, dtype=torch.int32, device=dev); v1[:n] = vals
         r1 = torch.full((tiles, 2), -1, dtype=torch.int32, device=dev)
         torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info(dev)
+        reserved_before = torch.cuda.memory_reserved(dev)
         rc = fn(k1.data_ptr(), v1.data_ptr(), cap, counters.data_ptr(), tiles, r1.data_ptr(), stream)
         assert rc == 0, err().decode()
         torch.cuda.synchronize()
+        if call > 0:
+            # the property in the name: once the first call has resolved the scratch address (and the runtime has
+            # loaded the library image), a call takes no device memory, neither from the driver nor from torch's pool
+            assert torch.cuda.mem_get_info(dev)[0] == free_before
+            assert torch.cuda.memory_reserved(dev) == reserved_before
         assert torch.equal(v1[:n], v0[:n])
         assert torch.equal(r1, r0)
         # and both agree with a plain stable sort
