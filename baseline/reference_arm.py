@@ -157,10 +157,77 @@ def prepare_tree():
     open(os.path.join(SHIMS, "simple_knn", "_C.py"), "w").write(SIMPLE_KNN_SHIM)
     os.makedirs(os.path.join(SHIMS, "diff_gaussian_rasterization"), exist_ok=True)
     open(os.path.join(SHIMS, "diff_gaussian_rasterization", "__init__.py"), "w").write(VANILLA_SHIM)
+    open(os.path.join(SHIMS, "sitecustomize.py"), "w").write(LPIPS_SHIM)
 
 
-def write_scene(root: str, args, n_views: int, device):
-    """Blender-layout dataset + ``<model>/point_cloud/iteration_1/point_cloud.ply`` with the own arm's Gaussians."""
+LPIPS_SHIM = '''"""Loaded at interpreter start of the reference's processes (PYTHONPATH): the reference's eval builds an LPIPS network
+per image and downloads its weights (lpipsPyTorch/modules/utils.py), which cannot work without a network. A stand-in
+module that reports 0 takes its place; PSNR, SSIM and L1 are the reference's own code."""
+import sys
+import types
+
+_m = types.ModuleType("lpipsPyTorch")
+
+
+def _lpips(x, y, net_type="alex", version="0.1"):
+    import torch
+    return torch.zeros((), device=x.device)
+
+
+class _LPIPS:
+    def __init__(self, *a, **k):
+        pass
+
+
+_m.lpips, _m.LPIPS = _lpips, _LPIPS
+sys.modules["lpipsPyTorch"] = _m
+'''
+
+
+def _render_targets(cams, g, device, renderer: str):
+    """Fill ``cam.image`` of every camera with a render of the Gaussians ``g`` (raw parameters). ``renderer`` =
+    "reference": the reference's own CUDA extension (nothing of this repository's native code is loaded by the
+    process); "own": this repository's rasteriser (only when the reference's extension is not installed)."""
+    import torch
+
+    if renderer == "reference":
+        from diff_gaussian_rasterization_half_gaussian import GaussianRasterizationSettings, GaussianRasterizer
+        xyz = g["xyz"].contiguous()
+        opac, scales = torch.sigmoid(g["opacity"]).contiguous(), torch.exp(g["scale"]).contiguous()
+        rots = torch.nn.functional.normalize(g["rot"]).contiguous()
+        shs = g["sh"].view(-1, 16, 3).contiguous()
+        big = 1.0e9
+        with torch.no_grad():
+            for cam in cams:
+                st = GaussianRasterizationSettings(
+                    image_height=cam.height, image_width=cam.width, tanfovx=cam.tan_fovx, tanfovy=cam.tan_fovy,
+                    bg=torch.zeros(3, device=device), scale_modifier=1.0,
+                    viewmatrix=torch.tensor(cam.world_view_transform, device=device),
+                    projmatrix=torch.tensor(cam.full_proj_transform, device=device),
+                    projmatrix_inv=torch.tensor(cam.view_world_transform, device=device),
+                    range_low=torch.tensor([-big] * 3, device=device), range_up=torch.tensor([big] * 3, device=device),
+                    sh_degree=3, campos=torch.tensor(cam.camera_center, device=device), prefiltered=False, debug=False)
+                color = GaussianRasterizer(st)(means3D=xyz, means2D=torch.zeros_like(xyz), opacities=opac, shs=shs,
+                                               scales=scales, rotations=rots)[0]
+                cam.image = color.clamp(0, 1).cpu()
+        return
+    from retinags_b200.ops.rasterize import RenderTask, Segment, make_camera
+    seg = Segment(g["xyz"], g["sh"], g["scale"], g["rot"], g["opacity"])
+    task = RenderTask(device)
+    for cam in cams:
+        out = task.forward(make_camera(cam, 3), [seg], check=True)
+        cam.image = out[..., :3].permute(2, 0, 1).contiguous().cpu()
+
+
+def scene_root(args, n_train: int, n_test: int) -> str:
+    base = os.environ.get("RGS_REF_WORKDIR", "/tmp/rgs_reference_arm")
+    return f"{base}_{args.gaussians}_{args.width}x{args.height}_{n_train}_{n_test}_{args.seed}"
+
+
+def write_scene(root: str, args, n_train: int, n_test: int, device, renderer: str = "reference"):
+    """Blender-layout dataset (``n_train`` + ``n_test`` hemisphere cameras with PNG targets rendered from the
+    independent ground-truth scene) + ``<model>/point_cloud/iteration_1/point_cloud.ply`` holding the seeded
+    Gaussians that both arms start from. Both arms read this one scene from disk."""
     import numpy as np
     import torch
 
@@ -168,27 +235,25 @@ def write_scene(root: str, args, n_views: int, device):
     from retinags_b200.bench_session import ClusterScene, chunks_of
     from retinags_b200.data import readers, synthetic
     from retinags_b200.models import ply_io
-    from retinags_b200.ops.rasterize import RenderTask, Segment, make_camera
 
     data_dir, model_dir = os.path.join(root, "data"), os.path.join(root, "model")
     done = os.path.join(root, "READY")
     if os.path.exists(done):
         return data_dir, model_dir
     os.makedirs(data_dir, exist_ok=True)
-    cams = synthetic.hemisphere_cameras(n_views, 8.0, args.width, args.height, 50.0, args.seed)
+    cams = synthetic.hemisphere_cameras(n_train, 8.0, args.width, args.height, 50.0, args.seed)
+    tests = synthetic.hemisphere_cameras(max(n_test, 1), 8.0, args.width, args.height, 50.0, args.seed + 17)
+    for i, cam in enumerate(tests):
+        cam.image_name = f"test_{i:04d}"
     gt = ClusterScene(args.seed + 1, device)
     parts = [gt.gaussians(m, k, 3) for k, m in chunks_of(args.gt_gaussians)]
     g = {name: torch.cat([p[name] for p in parts]) for name in parts[0]}
-    seg = Segment(g["xyz"], g["sh"], g["scale"], g["rot"], g["opacity"])
-    task = RenderTask(device)
-    for cam in cams:
-        out = task.forward(make_camera(cam, 3), [seg], check=True)
-        cam.image = out[..., :3].permute(2, 0, 1).contiguous().cpu()
+    _render_targets(cams + tests, g, device, renderer)
     pts = g["xyz"][:100000].cpu().numpy()
-    readers.write_blender_scene(data_dir, cams, cams[:2], pts, np.full_like(pts, 128.0))
-    del task, seg, g, parts
+    readers.write_blender_scene(data_dir, cams, tests, pts, np.full_like(pts, 128.0))
+    del g, parts
     torch.cuda.empty_cache()
-    # the Gaussians of the own arm, chunk by chunk, in vanilla-3DGS vertex layout
+    # the Gaussians both arms start from, chunk by chunk, in vanilla-3DGS vertex layout
     ply_dir = os.path.join(model_dir, "point_cloud", "iteration_1")
     os.makedirs(ply_dir, exist_ok=True)
     names = ply_io.gaussian_attribute_names(3)
@@ -203,12 +268,28 @@ def write_scene(root: str, args, n_views: int, device):
             rows = torch.cat([c["xyz"], torch.zeros(m, 3, device=device), sh[:, 0], sh[:, 1:].transpose(1, 2).reshape(m, 45),
                               c["opacity"], c["scale"], c["rot"]], dim=1)
             f.write(rows.cpu().numpy().astype("<f4").tobytes())
-    open(done, "w").write("ok")
+    open(done, "w").write(renderer)
     return data_dir, model_dir
 
 
+def ensure_scene(args, n_train: int, n_test: int):
+    """Write the on-disk scene in a child process (no CUDA context of the caller stays on GPU 0; the child loads the
+    reference's extension, never this repository's library, when the former is installed). Returns
+    (data_dir, model_dir, root) or raises RuntimeError with the child's last output."""
+    root = scene_root(args, n_train, n_test)
+    renderer = "reference" if available() is None else "own"
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE")}
+    env["PYTHONPATH"] = os.pathsep.join([REF, env.get("PYTHONPATH", "")])
+    wr = subprocess.run([sys.executable, os.path.abspath(__file__), "--write-scene", root, str(n_train), str(n_test),
+                         str(args.gaussians), str(args.width), str(args.height), str(args.gt_gaussians), str(args.seed),
+                         renderer], env=env, capture_output=True, text=True)
+    if wr.returncode != 0:
+        raise RuntimeError(("could not write the synthetic scene: " + wr.stderr[-400:]).replace("\n", " | "))
+    return os.path.join(root, "data"), os.path.join(root, "model"), root
+
+
 def read_iteration_stamps(tb_dir: str, world: int):
-    """Per rank: sorted (iteration, wall_time) of the ``iter_time`` scalars the reference logged."""
+    """Per rank: sorted (iteration, wall_time, iter_time value) of the ``iter_time`` scalars the reference logged."""
     from tensorboard.backend.event_processing.event_accumulator import EventAccumulator
     out = {}
     for r in range(world):
@@ -218,35 +299,13 @@ def read_iteration_stamps(tb_dir: str, world: int):
             acc = EventAccumulator(fn, size_guidance={"scalars": 0})
             acc.Reload()
             if "iter_time" in acc.Tags().get("scalars", []):
-                stamps += [(e.step, e.wall_time) for e in acc.Scalars("iter_time")]
+                stamps += [(e.step, e.wall_time, e.value) for e in acc.Scalars("iter_time")]
         out[r] = sorted(stamps)
     return out
 
 
-def main(args):
-    why = available()
-    if why:
-        print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
-        return
-    world = args.gpus
-    if int(os.environ.get("RANK", "0")) != 0:
-        return  # launched under torchrun: rank 0 drives the reference's own torchrun below
-    prepare_tree()
-    n_iter = args.warmup + args.steps + 1
-    n_views = n_iter * args.batch + 2 * args.batch
-    root = os.environ.get("RGS_REF_WORKDIR", "/tmp/rgs_reference_arm") + f"_{args.gaussians}_{args.width}x{args.height}_{n_views}"
-    data_dir, model_dir = os.path.join(root, "data"), os.path.join(root, "model")
-    # the scene is written by a child process so that no CUDA context of this driver stays on GPU 0
-    child_env = {k: v for k, v in os.environ.items() if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE")}
-    wr = subprocess.run([sys.executable, os.path.abspath(__file__), "--write-scene", root, str(n_views), str(args.gaussians),
-                         str(args.width), str(args.height), str(args.gt_gaussians), str(args.seed)], env=child_env,
-                        capture_output=True, text=True)
-    if wr.returncode != 0:
-        print(json.dumps({"impl": "reference", "unavailable": ("could not write the synthetic scene: " + wr.stderr[-300:]).replace("\n", " | ")}),
-              flush=True)
-        return
-    for d in glob.glob(os.path.join(model_dir, "rank_*")):
-        shutil.rmtree(d, ignore_errors=True)
+def reference_command(args, world: int, data_dir: str, model_dir: str, root: str, extra: list[str]):
+    """Command line and environment of the reference's own ``main.py`` under its own ``torch.distributed.run``."""
     depth = max(0, world.bit_length() - 1)
     max_load = 2 * args.batch
     if getattr(args, "bvh_depth", None) is not None and args.bvh_depth > depth:
@@ -263,61 +322,163 @@ def main(args):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
            "127.0.0.1", "--master-port", str(29800 + os.getpid() % 100), "main.py", "-s", data_dir, "-m", model_dir,
            "--bvh_depth", str(depth), "--MAX_BATCH_SIZE", str(args.batch), "--MAX_LOAD", str(max_load), "-r", "1",
-           "--ply_iteration", "1", "--ENABLE_TENSORBOARD", "--logdir", os.path.join(root, "tb"), "--epochs", "1",
-           "--iterations", str(n_views), "--EVAL_INTERVAL_EPOCH", "100000", "--SAVE_INTERVAL_EPOCH", "100000",
-           "--densify_from_iter", "100000000", "--log_level", "30", "--DATALOADER_FIX_SEED"]
+           "--ply_iteration", "1", "--ENABLE_TENSORBOARD", "--logdir", os.path.join(root, "tb"), "--eval",
+           "--densify_from_iter", "100000000", "--DATALOADER_FIX_SEED"] + extra
+    return cmd, env, depth
+
+
+def _base_line(args, world: int, depth: int) -> dict:
+    return {"n_gpus": world, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp32",
+            "data": "synthetic", "impl": "reference",
+            "config": {"model": "3DGS SH-3, seeded 64-cluster mixture in a 20-unit box", "gaussians": args.gaussians,
+                       "global_batch": args.batch, "resolution": [args.width, args.height], "bvh_depth": depth,
+                       "parallelism": f"spatial-mp{world}", "transport": "nccl send/recv (reference)"},
+            "gpu_launches": None}
+
+
+def _unavailable(why: str):
+    print(json.dumps({"impl": "reference", "unavailable": why[:900]}), flush=True)
+
+
+def _clean_run_dirs(model_dir: str, root: str):
+    for d in glob.glob(os.path.join(model_dir, "rank_*")):
+        shutil.rmtree(d, ignore_errors=True)
+    shutil.rmtree(os.path.join(root, "tb"), ignore_errors=True)
+
+
+def _eval_from_logs(model_dir: str, world: int, run_log: str) -> dict:
+    """PSNR / SSIM / L1 of the test split from the reference's own report line, and ms per frame from the time stamps
+    of its per-image log records (``trainer4tree_partition.py:730``): the frames after the first batch, over the time
+    between the first batch's last record and the last record, all ranks merged."""
+    import re
+    from datetime import datetime
+    out = {}
+    txt = open(run_log).read()
+    m = None
+    for m in re.finditer(r"Evaluating test: samples ([0-9.eE+-]+) L1 ([0-9.eE+-]+) PSNR ([0-9.eE+-]+) SSIM ([0-9.eE+-]+)", txt):
+        pass
+    if m:
+        out.update(samples=float(m.group(1)), l1=float(m.group(2)), psnr=float(m.group(3)), ssim=float(m.group(4)))
+    stamps = []
+    for fn in glob.glob(os.path.join(model_dir, "rank_*", "rank_*.txt")):
+        for line in open(fn, errors="replace"):
+            if "test, image " in line:
+                try:
+                    stamps.append(datetime.strptime(line[:23], "%Y-%m-%d %H:%M:%S,%f").timestamp())
+                except ValueError:
+                    pass
+    stamps.sort()
+    if len(stamps) > 3:
+        skip = min(len(stamps) - 2, 2)  # the first batch warms the loader and the allocator up
+        out["ms_per_frame"] = 1e3 * (stamps[-1] - stamps[skip - 1]) / (len(stamps) - skip)
+        out["frames_timed"] = len(stamps) - skip
+    return out
+
+
+def main(args):
+    why = available()
+    if why:
+        _unavailable(why)
+        return
+    world = args.gpus
+    if int(os.environ.get("RANK", "0")) != 0:
+        return  # launched under torchrun: rank 0 drives the reference's own torchrun below
+    prepare_tree()
+    mode = getattr(args, "mode", "train")
+    n_iter = args.warmup + args.steps + 1
+    if mode == "train":
+        n_train, n_test = n_iter * args.batch + 2 * args.batch, 2
+    else:
+        n_train, n_test = args.train_views, args.eval_frames
+    try:
+        data_dir, model_dir, root = ensure_scene(args, n_train, n_test)
+    except RuntimeError as exc:
+        _unavailable(str(exc))
+        return
+    _clean_run_dirs(model_dir, root)
     tb_dir = os.path.join(root, "tb")
-    shutil.rmtree(tb_dir, ignore_errors=True)
-    log = open(os.path.join(root, "reference_run.log"), "w")
+    run_log = os.path.join(root, "reference_run.log")
+    if mode == "train":
+        extra = ["--epochs", "1", "--iterations", str(n_train), "--EVAL_INTERVAL_EPOCH", "100000", "--SAVE_INTERVAL_EPOCH", "100000",
+                 "--log_level", "30"]
+    elif mode == "eval":
+        extra = ["--EVAL_ONLY", "--log_level", "20"]
+    else:  # train-psnr: E epochs over the training views, the reference evaluates after its last epoch by itself
+        extra = ["--epochs", str(args.epochs), "--EVAL_INTERVAL_EPOCH", "100000", "--SAVE_INTERVAL_EPOCH", "100000",
+                 "--log_level", "20"]
+    cmd, env, depth = reference_command(args, world, data_dir, model_dir, root, extra)
+    log = open(run_log, "w")
     proc = subprocess.Popen(cmd, cwd=SRC, env=env, stdout=log, stderr=subprocess.STDOUT)
     deadline = time.time() + float(os.environ.get("RGS_REF_TIMEOUT", "2400"))
     stamps, need = {}, args.warmup + args.steps + 1
     try:
         while time.time() < deadline:
             time.sleep(5.0)
-            try:
-                stamps = read_iteration_stamps(tb_dir, world)
-            except Exception:
-                stamps = {}
-            if stamps and all(len(v) >= need for v in stamps.values()):
-                break
+            if mode == "train":
+                try:
+                    stamps = read_iteration_stamps(tb_dir, world)
+                except Exception:
+                    stamps = {}
+                if stamps and all(len(v) >= need for v in stamps.values()):
+                    break
             if proc.poll() is not None:
-                stamps = read_iteration_stamps(tb_dir, world)
+                if mode == "train":
+                    stamps = read_iteration_stamps(tb_dir, world)
                 break
     finally:
-        if proc.poll() is None:  # enough iterations recorded: stop before the end-of-epoch save/eval
+        if proc.poll() is None:  # enough iterations recorded (or out of time): stop before the end-of-epoch save/eval
             proc.terminate()
             try:
                 proc.wait(timeout=60)
             except subprocess.TimeoutExpired:
                 proc.kill()
     log.close()
+    dbg = ""
+    for fn in sorted(glob.glob(os.path.join(SRC, "debugger", "debug_*.txt"))):
+        txt = open(fn).read()
+        if "Error" in txt or "error" in txt:
+            dbg = txt[-400:].replace("\n", " | ")
+    if mode != "train":
+        res = _eval_from_logs(model_dir, world, run_log)
+        if "psnr" not in res:
+            _unavailable(f"the reference's {mode} run reported no test evaluation: {dbg or open(run_log).read()[-300:]}".replace("\n", " | "))
+            return
+        out = _base_line(args, world, depth)
+        out.update({"metric": "render ms/frame and PSNR (reference eval loop)" if mode == "eval" else
+                    f"PSNR after {args.epochs} epochs over {n_train} views (reference trainer)",
+                    "value": res.get("ms_per_frame") if mode == "eval" else res["psnr"],
+                    "unit": "ms/frame" if mode == "eval" else "dB", "higher_is_better": mode != "eval", "mode": mode,
+                    "eval": res, "train_views": n_train, "eval_frames": n_test, "epochs": getattr(args, "epochs", None)})
+        out["config"]["timing"] = ("time stamps of the reference's per-image eval log records (PNG decode, render, compositing, "
+                                   "metrics), all ranks merged, first batch left out")
+        print(json.dumps(out), flush=True)
+        return
     if not stamps or not all(len(v) >= need for v in stamps.values()):
-        dbg = ""
-        for fn in sorted(glob.glob(os.path.join(SRC, "debugger", "debug_*.txt"))):
-            txt = open(fn).read()
-            if "Error" in txt or "error" in txt:
-                dbg = txt[-400:].replace("\n", " | ")
         got = min((len(v) for v in stamps.values()), default=0)
         partial = ""
         if got >= 3:
             per = max((v[got - 1][1] - v[1][1]) / (got - 2) for v in stamps.values())
             partial = f" (the {got - 2} iterations it completed after the first took {1e3 * per:.0f} ms each)"
-        print(json.dumps({"impl": "reference", "unavailable": f"the reference stopped after {got} of {need} iterations{partial}: {dbg}"[:900]}),
-              flush=True)
+        _unavailable(f"the reference stopped after {got} of {need} iterations{partial}: {dbg}")
         return
     W, K = args.warmup, args.steps
     per_rank = [v[W + K][1] - v[W][1] for v in stamps.values()]
     sec = max(per_rank)
-    out = {"metric": "train views/s (62.9M GS, 1600x1036)", "value": K * args.batch / sec, "unit": "views/s", "n_gpus": world,
-           "steps": K, "warmup": W, "ms_per_step": 1e3 * sec / K, "higher_is_better": True, "scaling": "strong",
-           "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "impl": "reference",
-           "config": {"model": "3DGS SH-3, seeded 64-cluster mixture in a 20-unit box", "gaussians": args.gaussians,
-                      "global_batch": args.batch, "resolution": [args.width, args.height], "bvh_depth": depth,
-                      "parallelism": f"spatial-mp{world}", "transport": "nccl send/recv (reference)",
-                      "timing": "wall-clock stamps of the reference's own per-iteration TensorBoard records, max over ranks"},
-           "e2e": {"value": K * args.batch / sec, "unit": "views/s", "note": "the reference loads PNG targets from disk through its DataLoader each step"},
-           "gpu_launches": None}
+    # where a box-to-box swing comes from: the median interval between consecutive records (robust against one slow
+    # iteration) and the reference's own CUDA-event iteration time (forward + backward on the device, no data loading,
+    # no optimiser step; trainer4tree_partition.py:641-643), both as the maximum over ranks
+    def _median(xs):
+        xs = sorted(xs)
+        return xs[len(xs) // 2] if xs else None
+    med = max(_median([v[i + 1][1] - v[i][1] for i in range(W, W + K)]) for v in stamps.values())
+    own_evt = max(sum(x[2] for x in v[W + 1:W + K + 1]) / K for v in stamps.values())
+    out = _base_line(args, world, depth)
+    out.update({"metric": "train views/s (62.9M GS, 1600x1036)", "value": K * args.batch / sec, "unit": "views/s",
+                "steps": K, "warmup": W, "ms_per_step": 1e3 * sec / K, "mode": "train",
+                "ms_per_step_median_interval": 1e3 * med, "reference_iter_time_ms_cuda_events": own_evt,
+                "e2e": {"value": K * args.batch / sec, "unit": "views/s",
+                        "note": "the reference loads PNG targets from disk through its DataLoader each step"}})
+    out["config"]["timing"] = "wall-clock stamps of the reference's own per-iteration TensorBoard records, max over ranks"
     print(json.dumps(out), flush=True)
 
 
@@ -326,9 +487,9 @@ if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "--write-scene":
         import argparse
         import torch
-        ns = argparse.Namespace(gaussians=int(sys.argv[4]), width=int(sys.argv[5]), height=int(sys.argv[6]),
-                                gt_gaussians=int(sys.argv[7]), seed=int(sys.argv[8]))
-        write_scene(sys.argv[2], ns, int(sys.argv[3]), torch.device("cuda", 0))
+        ns = argparse.Namespace(gaussians=int(sys.argv[5]), width=int(sys.argv[6]), height=int(sys.argv[7]),
+                                gt_gaussians=int(sys.argv[8]), seed=int(sys.argv[9]))
+        write_scene(sys.argv[2], ns, int(sys.argv[3]), int(sys.argv[4]), torch.device("cuda", 0), sys.argv[10])
         sys.exit(0)
     import bench
     a = bench.parse_args()

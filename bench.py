@@ -41,7 +41,9 @@ def parse_args():
                     help="2^depth sub-models (default: one per GPU); more sub-models than GPUs are spread round-robin")
     ap.add_argument("--slabs", type=int, default=None, metavar="N",
                     help="two-slab forward with the nearest N/256 of the splats in the first slab (same as RGS_SLABS=1 "
-                         "RGS_SLAB_FRACTION=N); experimental")
+                         "RGS_SLAB_FRACTION=N; default 32); 0 renders in one pass")
+    ap.add_argument("--occlusion", type=int, default=None, choices=[0, 1],
+                    help="occlusion culling between sub-models (finished-tile maps exchanged once per step)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--phases", action="store_true", help="also time the phases of a step (extra loop, after the timed one)")
     ap.add_argument("--task-times", default="", help="with --phases: write the per-(camera, sub-model) render times of every "
@@ -118,7 +120,9 @@ def run_own(args):
     from retinags_b200.bench_session import BenchSession
 
     if args.slabs is not None:
-        os.environ["RGS_SLABS"], os.environ["RGS_SLAB_FRACTION"] = "1", str(args.slabs)
+        os.environ["RGS_SLABS"], os.environ["RGS_SLAB_FRACTION"] = ("1", str(args.slabs)) if args.slabs > 0 else ("0", "32")
+    if args.occlusion is not None:
+        os.environ["RGS_OCCLUSION"] = str(args.occlusion)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -226,7 +230,8 @@ def run_own(args):
                        "visible_splats_per_step_rank0": sess.last_info.get("n_vis"),
                        "tile_instances_per_step_rank0": sess.last_info.get("n_inst"),
                        "rows_with_adam_moments_rank0": live_rows, "overflow_in_timed_region": overflow,
-                       "two_slab_forward": os.environ.get("RGS_SLABS", "0") == "1"},
+                       "two_slab_forward": os.environ.get("RGS_SLABS", "1") == "1",
+                       "occlusion_culling_between_submodels": bool(sess.engine.occlusion)},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "phases_ms_per_step_max_over_ranks": phases,
             "roofline_rank0_of_measured": roofline,
         }

@@ -823,17 +823,18 @@ __global__ void __launch_bounds__(1024) rgs_slab_sat_kernel(const uint8_t* __res
     }
 }
 
-// slot_cnt of every splat of the far slab = number of not-done tiles in its rectangle
+// slot_cnt of every splat of the slab = number of not-done tiles in its rectangle
 __global__ void __launch_bounds__(256) rgs_slab_filtered_count_kernel(const uint32_t* __restrict__ order,
                                                                       const uint2* __restrict__ slot_rect,
                                                                       const uint32_t* __restrict__ counters, uint32_t cap_vis,
-                                                                      uint32_t frac256, const uint32_t* __restrict__ sat,
+                                                                      uint32_t frac256, int slab, const uint32_t* __restrict__ sat,
                                                                       int tiles_x, uint32_t* __restrict__ slot_cnt) {
     const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);
     uint32_t s0, s1;
-    slab_segments(n, frac256, 1, s0, s1);
+    slab_segments(n, frac256, slab, s0, s1);
     const int pitch = tiles_x + 1;
-    for (uint32_t i = s0 * EM_SEG + blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const uint32_t end = s1 * EM_SEG < n ? s1 * EM_SEG : n;
+    for (uint32_t i = s0 * EM_SEG + blockIdx.x * blockDim.x + threadIdx.x; i < end; i += gridDim.x * blockDim.x) {
         const uint32_t slot = order[i];
         const uint2 r = slot_rect[slot];
         const int x0 = r.x & 0xffff, y0 = r.x >> 16, x1 = r.y & 0xffff, y1 = r.y >> 16;
@@ -1197,7 +1198,8 @@ int rgs_cuda_bin_instances(const RgsCamera* cam, const RgsSplat* splats, const u
 
 // Two-slab binning, one call per slab (see the comment above rgs_slab_count_kernel).
 //   slab 0: depth sort of all visible slots, then emission + tile sort of the near slab (frac256/256 of the splats)
-//           into the first region_cap elements of the instance buffers; count -> counters[RGS_CNT_INST].
+//           into the first region_cap elements of the instance buffers; count -> counters[RGS_CNT_INST]. With
+//           tile_done (+ sat) only tiles that are not marked get instances: tiles hidden behind nearer sub-models.
 //   slab 1: tile_done (one byte per tile, written by the blend of slab 0) -> summed-area table -> filtered counts,
 //           emission + tile sort of the far slab into the region starting at region_off; count -> counters[RGS_CNT_INST2];
 //           ranges hold absolute indices into inst_vals.
@@ -1226,10 +1228,12 @@ int rgs_cuda_bin_slab(const RgsCamera* cam, const uint32_t* slot_depth, const ui
     const uint2* rects = reinterpret_cast<const uint2*>(slot_rect);
     const uint32_t nseg_cap = (uint32_t)((cap_vis + EM_SEG - 1) / EM_SEG);
     const unsigned egrid = nseg_cap < 148u * 8u ? (nseg_cap ? nseg_cap : 1u) : 148u * 8u;
-    if (slab == 1) {
+    if (slab == 1 && (!tile_done || !sat)) return 15;
+    if (tile_done) {  // the far slab always filters; the near slab when tiles are known to be hidden by nearer sub-models
+        if (!sat) return 15;
         rgs_slab_sat_kernel<<<1, 1024, 0, st>>>(tile_done, cam->tiles_x, cam->tiles_y, sat);
-        rgs_slab_filtered_count_kernel<<<148 * 8, 256, 0, st>>>(order, rects, cnt, (uint32_t)cap_vis, (uint32_t)frac256, sat,
-                                                               cam->tiles_x, slot_cnt);
+        rgs_slab_filtered_count_kernel<<<148 * 8, 256, 0, st>>>(order, rects, cnt, (uint32_t)cap_vis, (uint32_t)frac256,
+                                                               (int)slab, sat, cam->tiles_x, slot_cnt);
     }
     rgs_slab_count_kernel<<<egrid, 256, 0, st>>>(order, slot_cnt, cnt, (uint32_t)cap_vis, (uint32_t)frac256, (int)slab, seg_sums);
     rgs_slab_scan_kernel<<<1, 1024, 0, st>>>(seg_sums, cnt, (uint32_t)cap_vis, (uint32_t)frac256, (int)slab, which,
@@ -1237,8 +1241,7 @@ int rgs_cuda_bin_slab(const RgsCamera* cam, const uint32_t* slot_depth, const ui
     uint32_t* rk = inst_keys + region_off;
     uint32_t* rv = inst_vals + region_off;
     rgs_slab_emit_kernel<<<egrid, 256, 0, st>>>(*cam, order, rects, slot_cnt, cnt, (uint32_t)cap_vis, (uint32_t)frac256,
-                                                (int)slab, seg_sums, rk, rv, (uint32_t)region_cap,
-                                                slab == 1 ? tile_done : nullptr);
+                                                (int)slab, seg_sums, rk, rv, (uint32_t)region_cap, tile_done);
     int tile_bits = 0;
     while ((1ll << tile_bits) < num_tiles) ++tile_bits;
     const int npass = tile_bits <= 8 ? 1 : 2;

@@ -453,6 +453,7 @@ int rgs_cpu_bin_slab(const RgsCamera* cam, const uint32_t* slot_depth, const uin
                      int64_t num_tiles, int32_t* ranges, uint32_t*, int64_t, int64_t slab, int64_t frac256,
                      const uint8_t* tile_done, uint32_t*, void*) {
     if (num_tiles > 65536 || cam->tight_rect >= 2 || slab < 0 || slab > 1) return 15;
+    if (slab == 1 && !tile_done) return 15;
     const int which = slab == 0 ? RGS_CNT_INST : RGS_CNT_INST2;
     std::memset(ranges, 0, num_tiles * 8);
     counters[which] = 0;
@@ -474,12 +475,12 @@ int rgs_cpu_bin_slab(const RgsCamera* cam, const uint32_t* slot_depth, const uin
         for (uint32_t y = lo >> 16; y < (hi >> 16); ++y)
             for (uint32_t x = lo & 0xffff; x < (hi & 0xffff); ++x) {
                 const uint32_t t = y * (uint32_t)tiles_x + x;
-                if (slab == 1 && tile_done[t]) continue;
+                if (tile_done && tile_done[t]) continue;
                 if (slab == 0 && slot_cnt[s] == 0) continue;
                 inst.emplace_back(t, s);
                 ++c;
             }
-        if (slab == 1) slot_cnt[s] = c;
+        if (tile_done) slot_cnt[s] = c;
     }
     counters[which] = (int32_t)std::min<size_t>(inst.size(), 0x7fffffff);
     if ((int64_t)inst.size() > region_cap) { counters[RGS_CNT_OVERFLOW] = 1; return 0; }
@@ -498,7 +499,7 @@ int rgs_cpu_bin_slab(const RgsCamera* cam, const uint32_t* slot_depth, const uin
 int rgs_cpu_blend_fwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const int32_t* ranges_b, const uint32_t* vals,
                            const RgsSplat* splats, float* out, float* depth, int32_t* n_contrib, int32_t* counters,
                            uint8_t* tile_done, int64_t, int64_t mode, int64_t n_dst, const int32_t* row0, const int32_t* row1,
-                           float* const* dst, void*) {
+                           float* const* dst, const uint8_t* occl, void*) {
     if (mode != 1 && mode != 2) return 15;
     const int W = cam->W, H = cam->H;
     const bool blank = counters[RGS_CNT_OVERFLOW] != 0;
@@ -531,7 +532,8 @@ int rgs_cpu_blend_fwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const 
                 n_contrib[pid] = mode == 1 ? (int32_t)((uint32_t)st.last | ((uint32_t)(st.done ? 1 : 0) << 31)) : st.last;
                 all_done = all_done && st.done;
             }
-        if (mode == 1) tile_done[tile] = all_done ? 1 : 0;
+        if (mode == 1) tile_done[tile] = (all_done || (occl && occl[tile])) ? 1 : 0;
+        else if (tile_done && all_done) tile_done[tile] = 1;
     }
     if (mode == 2)
         for (int64_t o = 0; o < n_dst; ++o)
@@ -540,9 +542,25 @@ int rgs_cpu_blend_fwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const 
     return 0;
 }
 
+// host twins of the tile-map helpers (rgs_p2p.cu)
+int rgs_cpu_tile_maps_or(const uint8_t* const* srcs, int64_t n, uint8_t* dst, int64_t nbytes, int64_t overwrite, void*) {
+    for (int64_t i = 0; i < nbytes; ++i) {
+        uint8_t v = overwrite ? 0 : dst[i];
+        for (int64_t k = 0; k < n; ++k) v |= srcs[k][i];
+        dst[i] = v ? 1 : 0;
+    }
+    return 0;
+}
+
+int rgs_cpu_tile_map_push(const uint8_t* src, uint8_t* const* dsts, int64_t n_dst, int64_t nbytes, void*) {
+    for (int64_t k = 0; k < n_dst; ++k) std::memcpy(dsts[k], src, (size_t)nbytes);
+    return 0;
+}
+
 int rgs_cpu_blend_bwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const int32_t* ranges_b, int64_t,
                            const uint32_t* vals, const RgsSplat* splats, const float* out, const int32_t* n_contrib,
-                           const float* grad_out, RgsSplatGrad* splat_grads, int32_t* counters, int64_t*, int64_t, void*) {
+                           const float* grad_out, RgsSplatGrad* splat_grads, int32_t* counters, int64_t*, int64_t,
+                           const float* grad_depth, void*) {
     const int W = cam->W, H = cam->H;
     if (counters[RGS_CNT_OVERFLOW]) return 0;
     for (int tile = 0; tile < cam->tiles_x * cam->tiles_y; ++tile) {
@@ -556,10 +574,12 @@ int rgs_cpu_blend_bwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const 
                 RgsPixelRay ray; rgs_pixel_ray(*cam, (float)x, (float)y, ray);
                 RgsPixelBwd st;
                 rgs_pixel_bwd_init(st, out[4 * pid + 3], grad_out + 4 * pid, grad_out[4 * pid + 3]);
+                RgsPixelBwdDepth dep = {0.f, 0.f, grad_depth ? grad_depth[pid] : 0.f};
                 for (int v = n_contrib[pid] - 1; v >= 0; --v) {  // position in the list "near range, then far range"
                     const uint32_t slot = vals[v < len_a ? a0 + v : b0 + (v - len_a)];
                     RgsSplatGrad g;
-                    if (!rgs_blend_bwd_step(*cam, ray, (float)x, (float)y, splats[slot], st, g)) continue;
+                    if (!rgs_blend_bwd_step(*cam, ray, (float)x, (float)y, splats[slot], st, g, grad_depth ? &dep : nullptr))
+                        continue;
                     float* d = reinterpret_cast<float*>(&splat_grads[slot]);
                     const float* src = reinterpret_cast<const float*>(&g);
                     for (int k = 0; k < 10; ++k) d[k] += src[k];

@@ -24,6 +24,7 @@
 // rank leaves the wait with the OR over all ranks and drops the optimiser update together.
 #define RGS_P2P_MAX_WORLD 32
 #define RGS_P2P_FLAG_WORDS 96
+#define RGS_MAX_PARTIALS_MAPS 64  // most sub-models in front of one (the compositing kernels handle as many partials)
 
 struct RgsPeerFlagPtrs { uint32_t* p[RGS_P2P_MAX_WORLD]; };
 
@@ -61,7 +62,49 @@ __global__ void rgs_p2p_wait_kernel(const uint32_t* __restrict__ my_flags, int w
     __threadfence_system();
 }
 
+// Per-tile "finished" maps (one byte per tile) that sub-models publish so that sub-models behind them skip hidden
+// tiles. rgs_tile_maps_or: dst |= OR of n source maps (local memory; remote maps were pushed here first).
+// rgs_tile_map_push: one local map is stored into the map slots of up to RGS_P2P_MAX_WORLD ranks (plain peer stores).
+struct RgsMapPtrs { const uint8_t* p[RGS_MAX_PARTIALS_MAPS]; };
+struct RgsMapDsts { uint8_t* p[RGS_P2P_MAX_WORLD]; };
+
+__global__ void rgs_tile_maps_or_kernel(const __grid_constant__ RgsMapPtrs srcs, int n, uint8_t* __restrict__ dst,
+                                        int nbytes, int overwrite) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < nbytes; i += gridDim.x * blockDim.x) {
+        uint8_t v = overwrite ? 0 : dst[i];
+        for (int k = 0; k < n; ++k) v |= srcs.p[k][i];
+        dst[i] = v ? 1 : 0;
+    }
+}
+
+__global__ void rgs_tile_map_push_kernel(const uint8_t* __restrict__ src, const __grid_constant__ RgsMapDsts dsts,
+                                         int nbytes) {
+    uint8_t* dst = dsts.p[blockIdx.y];
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < nbytes; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
 extern "C" {
+
+int rgs_cuda_tile_maps_or(const uint8_t* const* srcs, int64_t n, uint8_t* dst, int64_t nbytes, int64_t overwrite,
+                          void* stream) {
+    if (n < 0 || n > RGS_MAX_PARTIALS_MAPS || nbytes < 0 || nbytes > 0x7fffffffll) return 14;
+    if (nbytes == 0 || (n == 0 && !overwrite)) return 0;
+    RgsMapPtrs s;
+    for (int k = 0; k < n; ++k) s.p[k] = srcs[k];
+    const unsigned blocks = (unsigned)((nbytes + 255) / 256 > 64 ? 64 : (nbytes + 255) / 256);
+    rgs_tile_maps_or_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(s, (int)n, dst, (int)nbytes, (int)overwrite);
+    return (int)cudaGetLastError();
+}
+
+int rgs_cuda_tile_map_push(const uint8_t* src, uint8_t* const* dsts, int64_t n_dst, int64_t nbytes, void* stream) {
+    if (n_dst < 0 || n_dst > RGS_P2P_MAX_WORLD || nbytes < 0 || nbytes > 0x7fffffffll) return 14;
+    if (n_dst == 0 || nbytes == 0) return 0;
+    RgsMapDsts d;
+    for (int k = 0; k < n_dst; ++k) d.p[k] = dsts[k];
+    dim3 grid((unsigned)((nbytes + 255) / 256 > 16 ? 16 : (nbytes + 255) / 256), (unsigned)n_dst);
+    rgs_tile_map_push_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(src, d, (int)nbytes);
+    return (int)cudaGetLastError();
+}
 
 int rgs_cuda_ipc_alloc(int64_t bytes, void** out) {
     void* p = nullptr;

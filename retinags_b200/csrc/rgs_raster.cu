@@ -135,9 +135,10 @@ __device__ __forceinline__ int2 checked_range(int2 r, uint32_t* counters, int wh
 #define RGS_SLAB_FAR 2     // second launch: resumes from that state with the far slab's list
 struct RgsSlabArgs {
     const int2* ranges_b;   // per-tile ranges of the far slab (absolute indices into vals), null without slabs
-    uint8_t* tile_done;     // one byte per tile: every pixel of the tile is finished after the near slab
+    uint8_t* tile_done;     // one byte per tile: every pixel of the tile is finished (written by both slab launches)
     uint32_t base_b;        // first element of the far slab's region in vals
     int mode;
+    const uint8_t* occl;    // near launch, optional: tiles hidden behind nearer sub-models (they hold no instances)
 };
 
 __device__ __forceinline__ void blend_issue(BlendSmem& sm, int stage, const RgsSplat* __restrict__ splats,
@@ -252,9 +253,14 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
     }
     if (failed && tid == 0) atomicOr(&counters[RGS_CNT_STATUS], 1u);
     if (slab.mode == RGS_SLAB_NEAR) {
-        // a tile whose every pixel is finished needs no instance of the far slab
+        // a tile whose every pixel is finished needs no instance of the far slab; neither does a tile that nearer
+        // sub-models have finished already
         const int all_done = __syncthreads_and(st.done);
-        if (tid == 0) slab.tile_done[tile] = all_done ? 1 : 0;
+        if (tid == 0) slab.tile_done[tile] = (all_done || (slab.occl && slab.occl[tile])) ? 1 : 0;
+    } else if (slab.mode == RGS_SLAB_FAR && slab.tile_done) {
+        // final state of the tile: what sub-models behind this one may skip
+        const int all_done = __syncthreads_and(st.done);
+        if (tid == 0 && all_done) slab.tile_done[tile] = 1;
     }
     if (inside) {
         const int64_t pid = (int64_t)py * cam.W + px;
@@ -569,7 +575,7 @@ int rgs_cuda_blend_fwd(const RgsCamera* cam, const int32_t* ranges, const uint32
     push.n = 0;
     rgs_blend_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
         *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<float4*>(out), depth, n_contrib,
-        reinterpret_cast<uint32_t*>(counters), push, RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE});
+        reinterpret_cast<uint32_t*>(counters), push, RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE, nullptr});
     return (int)cudaGetLastError();
 }
 
@@ -585,16 +591,17 @@ int rgs_cuda_blend_fwd_push(const RgsCamera* cam, const int32_t* ranges, const u
     for (int o = 0; o < n_dst; ++o) { push.row0[o] = row0[o]; push.row1[o] = row1[o]; push.dst[o] = reinterpret_cast<float4*>(dst[o]); }
     rgs_blend_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
         *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<float4*>(out), depth, n_contrib,
-        reinterpret_cast<uint32_t*>(counters), push, RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE});
+        reinterpret_cast<uint32_t*>(counters), push, RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE, nullptr});
     return (int)cudaGetLastError();
 }
 
 // One launch of the two-slab forward. mode 1 (near slab): ranges_a is walked, tile_done is written, no push.
 // mode 2 (far slab): resumes from out / depth / n_contrib, walks ranges_b (indices from base_b on), pushes.
+// occl (near launch, optional): one byte per tile, tiles finished by nearer sub-models; they are marked done as well.
 int rgs_cuda_blend_fwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const int32_t* ranges_b, const uint32_t* vals,
                             const RgsSplat* splats, float* out, float* depth, int32_t* n_contrib, int32_t* counters,
                             uint8_t* tile_done, int64_t base_b, int64_t mode, int64_t n_dst, const int32_t* row0,
-                            const int32_t* row1, float* const* dst, void* stream) {
+                            const int32_t* row1, float* const* dst, const uint8_t* occl, void* stream) {
     if (n_dst < 0 || n_dst > RGS_MAX_PUSH || (mode != RGS_SLAB_NEAR && mode != RGS_SLAB_FAR)) return 15;
     dim3 grid(cam->tiles_x, cam->tiles_y);
     RgsPushPlan push;
@@ -603,7 +610,8 @@ int rgs_cuda_blend_fwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const
     rgs_blend_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
         *cam, reinterpret_cast<const int2*>(ranges_a), vals, splats, reinterpret_cast<float4*>(out), depth, n_contrib,
         reinterpret_cast<uint32_t*>(counters), push,
-        RgsSlabArgs{reinterpret_cast<const int2*>(ranges_b), tile_done, (uint32_t)base_b, (int)mode});
+        RgsSlabArgs{reinterpret_cast<const int2*>(ranges_b), tile_done, (uint32_t)base_b, (int)mode,
+                    mode == RGS_SLAB_NEAR ? occl : nullptr});
     return (int)cudaGetLastError();
 }
 
@@ -614,7 +622,7 @@ int rgs_cuda_blend_bwd(const RgsCamera* cam, const int32_t* ranges, const uint32
     rgs_blend_bwd_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(
         *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
         reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters), nullptr,
-        RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE});
+        RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE, nullptr});
     return (int)cudaGetLastError();
 }
 
@@ -627,7 +635,7 @@ int rgs_cuda_blend_bwd_depth(const RgsCamera* cam, const int32_t* ranges, const 
     rgs_blend_bwd_kernel<false, true><<<grid, 256, 0, (cudaStream_t)stream>>>(
         *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
         reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters), nullptr,
-        RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE}, grad_depth);
+        RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE, nullptr}, grad_depth);
     return (int)cudaGetLastError();
 }
 
@@ -636,9 +644,17 @@ int rgs_cuda_blend_bwd_depth(const RgsCamera* cam, const int32_t* ranges, const 
 int rgs_cuda_blend_bwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const int32_t* ranges_b, int64_t base_b,
                             const uint32_t* vals, const RgsSplat* splats, const float* out, const int32_t* n_contrib,
                             const float* grad_out, RgsSplatGrad* splat_grads, int32_t* counters, int64_t* fixed_acc,
-                            int64_t cap_vis, void* stream) {
+                            int64_t cap_vis, const float* grad_depth, void* stream) {
     dim3 grid(cam->tiles_x, cam->tiles_y);
-    const RgsSlabArgs slab{reinterpret_cast<const int2*>(ranges_b), nullptr, (uint32_t)base_b, RGS_SLAB_SINGLE};
+    const RgsSlabArgs slab{reinterpret_cast<const int2*>(ranges_b), nullptr, (uint32_t)base_b, RGS_SLAB_SINGLE, nullptr};
+    if (grad_depth) {  // gradient on the depth output as well (float accumulation only)
+        if (fixed_acc) return 15;
+        rgs_blend_bwd_kernel<false, true><<<grid, 256, 0, (cudaStream_t)stream>>>(
+            *cam, reinterpret_cast<const int2*>(ranges_a), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
+            reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters), nullptr, slab,
+            grad_depth);
+        return (int)cudaGetLastError();
+    }
     if (!fixed_acc) {
         rgs_blend_bwd_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(
             *cam, reinterpret_cast<const int2*>(ranges_a), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
@@ -666,7 +682,7 @@ int rgs_cuda_blend_bwd_fixed(const RgsCamera* cam, const int32_t* ranges, const 
     rgs_blend_bwd_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(
         *cam, reinterpret_cast<const int2*>(ranges), vals, splats, reinterpret_cast<const float4*>(out), n_contrib,
         reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters),
-        reinterpret_cast<unsigned long long*>(fixed_acc), RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE});
+        reinterpret_cast<unsigned long long*>(fixed_acc), RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE, nullptr});
     const int64_t want = (cap_vis * 9 + 255) / 256;
     const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > 148 * 32 ? 148 * 32 : want));
     rgs_fixed_fold_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<long long*>(fixed_acc), cap_vis,

@@ -11,6 +11,7 @@ blocking exchange phases reduced to two and no host synchronisation inside a ste
 from __future__ import annotations
 
 import contextlib
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -18,6 +19,7 @@ import torch
 from .data.cameras import Camera
 from .models.gaussians import GaussianStore
 from .ops.loss import CompositeLoss
+from .ops import native
 from .ops.native import CNT_OVERFLOW, CNT_WORDS
 from .ops.rasterize import RenderTask, Segment, make_camera
 from .parallel.compositing import LocalTransport, ViewPlan, band_rows
@@ -60,6 +62,9 @@ class StepEngine:
         if hasattr(self.transport, "attach_skip"):
             self.transport.attach_skip(self._skip)
         self.dropped_steps = 0
+        # occlusion culling between sub-models in the training forward (render_partials_occluded)
+        self.occlusion = os.environ.get("RGS_OCCLUSION", "0") == "1"
+        self._occl: dict = {}
         self._tasks: dict = {}
         self._grads: dict = {}
         self._closs: dict = {}
@@ -151,6 +156,69 @@ class StepEngine:
                                                         push=push)
         return local_out
 
+    def render_partials_occluded(self, cams: list[Camera], plans: list[ViewPlan], sh_degree: int) -> dict:
+        """Training forward with occlusion culling between sub-models (``self.occlusion``).
+
+        A sub-model cannot see by itself that nearer sub-models have already finished a tile (every pixel below the
+        transmittance threshold), so it bins and blends splats that cannot change the composite by more than that
+        threshold. Here every render publishes one byte per tile, "finished", and renders behind it skip those tiles:
+
+        1. every local (view, sub-model), front to back: projection + near slab, skipping the tiles that nearer local
+           sub-models finished in their near slabs;
+        2. the maps of all sub-models are exchanged (a few KB per map; peer stores + the flag barrier, or one
+           all-reduce with the torch.distributed transport);
+        3. every local (view, sub-model), front to back: far slab on the tiles that neither its own near slab nor any
+           nearer sub-model has finished -- remote ones as of their near slab, local ones as of their whole render.
+
+        Nothing depends on a chain over ranks: one exchange per step. The composite differs from the one without
+        culling by at most the transmittance threshold times a colour, like a single render that stops at that threshold."""
+        tasks, maps = {}, {}
+        for p, cam in zip(plans, cams):
+            chain = None
+            for m, r in zip(p.models, p.ranks):
+                if r != self.rank:
+                    continue
+                st = self.stores[m]
+                c = make_camera(cam, sh_degree, st.box_lo, st.box_hi, raw_params=True, tight_rect=self.tight_rect)
+                task = self._task(p.view, m)
+                with self._task_phase("fwd", cam, m):
+                    task.forward_near(c, self._segments(m, False), occl=chain)
+                tasks[(p.view, m)] = task
+                maps[(p.view, m)] = task.tile_done
+                chain = task.tile_done  # own finished tiles | what was hidden for it: all that is hidden for the next one
+        with self.timer.phase("exchange_maps"):
+            maps = self.transport.exchange_done_maps(plans, maps)
+        local_out: dict[int, dict[int, torch.Tensor]] = {}
+        for p, cam in zip(plans, cams):
+            local_out[p.view] = {}
+            for k, (m, r) in enumerate(zip(p.models, p.ranks)):
+                if r != self.rank:
+                    continue
+                task = tasks[(p.view, m)]
+                nearer = [maps[(p.view, j)] for j in p.models[:k]]
+                occl = None
+                if nearer:
+                    occl = self._occl_buf(p.view, m, nearer[0].numel())
+                    native.call("tile_maps_or", self.device, native.pointer_array(nearer), len(nearer), occl, occl.numel(), 1,
+                                sig="pipiip")
+                push = self.transport.push_plan(p, m) if hasattr(self.transport, "push_plan") else None
+                with self._task_phase("fwd", cam, m):
+                    local_out[p.view][m] = task.forward_far(occl, push=push)
+        return local_out
+
+    def _occl_buf(self, view: int, mid: int, n: int) -> torch.Tensor:
+        key = (view, mid)
+        b = self._occl.get(key)
+        if b is None or b.numel() != n:
+            b = torch.zeros(n, dtype=torch.uint8, device=self.device)
+            self._occl[key] = b
+        return b
+
+    def _use_occlusion(self, cams, plans) -> bool:
+        if not self.occlusion or len(self.model2rank) < 2:
+            return False
+        return all(RenderTask.can_split(make_camera(cam, 0, tight_rect=self.tight_rect)) for cam in cams)
+
     def render(self, cams: list[Camera], relations, sh_degree: int, background=None, want_depth: bool = False):
         """Eval-time render: returns per view the composited (3,H,W) image rows this rank owns
         (``image``, ``rows``) -- with world size 1 that is the whole image.
@@ -209,7 +277,10 @@ class StepEngine:
             with T("border_exchange"):
                 self.borrow.refresh(self.stores, need_grads=True)
         with T("render_forward"):
-            local_out = self.render_partials(cams, plans, sh_degree)
+            if self._use_occlusion(cams, plans):
+                local_out = self.render_partials_occluded(cams, plans, sh_degree)
+            else:
+                local_out = self.render_partials(cams, plans, sh_degree)
             self._collect_overflow(plans)
         with T("exchange_partials"):
             slots = self.transport.exchange_partials(plans, local_out)

@@ -205,7 +205,7 @@ class RenderTask:
         self.timer = None  # optional utils.profiler.PhaseTimer for per-kernel-group timing
         # Two-slab forward (CUDA, depth-first binning): bin and blend the nearest splats first, then emit instances of
         # the rest only for tiles that are not saturated yet. Bit-identical output, fewer instances in dense scenes.
-        self.slabs = os.environ.get("RGS_SLABS", "0") == "1"
+        self.slabs = os.environ.get("RGS_SLABS", "1") == "1"
         self.slab_frac256 = int(os.environ.get("RGS_SLAB_FRACTION", "32"))   # share of the splats in the near slab, /256
         self._pending_cap = 0             # capacity that poll() asked for; applied by the next forward
         self._need_a = self._need_b = 0   # largest instance counts of the near / far slab seen so far
@@ -213,6 +213,8 @@ class RenderTask:
         self._slab_active = False    # the last forward used two slabs (the backward walks two lists)
         self._base_b = 0
         self.ranges_b = self.tile_done = self.sat = None
+        self._own_order = self._own_rect = None  # set by forward_near: depth order / tile rectangles kept by the task
+        self._want_depth = False
         # debug mode: accumulate the blend backward through 64-bit fixed point so that two runs give identical bits
         self.deterministic = os.environ.get("RGS_DETERMINISTIC", "0") == "1"
         self._fixed_acc = None
@@ -288,6 +290,7 @@ class RenderTask:
             else:
                 bs = bin_scratch(self.device)
                 bs.ensure(self.cap_vis, self.cap_inst)
+                self._own_order = self._own_rect = None
                 # two-phase projection: conservative cull of everything, full projection of the survivors;
                 # the candidate list reuses a ping-pong buffer of the depth sort (free until then)
                 structs = (RgsSegment * len(segments))(*[s.struct(False) for s in segments])
@@ -340,39 +343,106 @@ class RenderTask:
         raise RuntimeError("the instance buffers still overflow after 12 attempts to grow them")
 
     _SIG_BIN_SLAB = "pppp" + "i" + "pppp" + "pppp" + "ii" + "p" + "i" + "p" + "p" + "iii" + "pp" + "p"
-    _SIG_FWD_SLAB = "pppppppppp" + "iii" + "ppp" + "p"
-    _SIG_BWD_SLAB = "ppp" + "i" + "pppppppp" + "i" + "p"
+    _SIG_FWD_SLAB = "pppppppppp" + "iii" + "ppp" + "p" + "p"
+    _SIG_BWD_SLAB = "ppp" + "i" + "pppppppp" + "i" + "p" + "p"
 
-    def _forward_slabs(self, cam: RgsCamera, bs: BinScratch, dst: torch.Tensor, want_depth: bool, push):
-        tiles = cam.tiles_x * cam.tiles_y
+    def _slab_regions(self):
         # The buffers are shared in proportion to the largest needs seen so far, so that both slabs keep the same head
         # room (_note_slab_counts keeps the total at 1.3x of their sum or more); before any count is known: 40 : 60.
         share = (self._need_a + 2048.0) / (self._need_a + self._need_b + 4096.0) if self._need_known else 0.4
         want_a = int(self.cap_inst * min(0.95, max(0.05, share)))
         cap_a = max(1024, min(want_a, self.cap_inst - 1024)) // 4 * 4
-        cap_b = self.cap_inst - cap_a
         self._base_b = cap_a
+        return cap_a, self.cap_inst - cap_a
+
+    def _bin_slab(self, cam, bs, slab, off, cap, ranges, filt):
+        tiles = cam.tiles_x * cam.tiles_y
+        # the depth order and the tile rectangles live in the shared scratch, or in buffers of the task when the two halves
+        # of the forward are separated by other tasks' work (forward_near / forward_far)
+        rect = bs.slot_rect if self._own_rect is None else self._own_rect
+        order = bs.vis[1] if self._own_order is None else self._own_order
+        native.call("bin_slab", self.device, cam, bs.slot_depth, rect, bs.slot_cnt, self.cap_vis, bs.vis[0], order,
+                    bs.vis[2], bs.vis[3], bs.inst_keys, self.vals, bs.inst_keys_tmp, bs.inst_vals_tmp, off, cap, self.counters,
+                    tiles, ranges, bs.words, self.cap_inst, slab, self.slab_frac256, filt, self.sat if filt is not None else None,
+                    sig=self._SIG_BIN_SLAB)
+
+    def _blend_slab(self, cam, dst, depth, mode, push, occl):
+        p = push if (mode == 2 and push is not None) else (0, None, None, None)
+        native.call("blend_fwd_slab", self.device, cam, self.ranges, self.ranges_b, self.vals, self.splats, dst, depth,
+                    self.n_contrib, self.counters, self.tile_done, self._base_b, mode, p[0], p[1], p[2], p[3], occl,
+                    sig=self._SIG_FWD_SLAB)
+
+    def _forward_slabs_near(self, cam: RgsCamera, bs: BinScratch, dst: torch.Tensor, want_depth: bool, occl=None):
+        """Near slab: bin (only tiles outside ``occl``) and blend; leaves ``tile_done`` = own finished tiles | occl."""
+        cap_a, _ = self._slab_regions()
         depth = self.depth if want_depth else None
-
-        def bin_slab(slab, off, cap, ranges):
-            native.call("bin_slab", self.device, cam, bs.slot_depth, bs.slot_rect, bs.slot_cnt, self.cap_vis, bs.vis[0], bs.vis[1],
-                        bs.vis[2], bs.vis[3], bs.inst_keys, self.vals, bs.inst_keys_tmp, bs.inst_vals_tmp, off, cap, self.counters,
-                        tiles, ranges, bs.words, self.cap_inst, slab, self.slab_frac256, self.tile_done if slab else None,
-                        self.sat if slab else None, sig=self._SIG_BIN_SLAB)
-
-        def blend(mode):
-            p = push if (mode == 2 and push is not None) else (0, None, None, None)
-            native.call("blend_fwd_slab", self.device, cam, self.ranges, self.ranges_b, self.vals, self.splats, dst, depth,
-                        self.n_contrib, self.counters, self.tile_done, cap_a, mode, p[0], p[1], p[2], p[3], sig=self._SIG_FWD_SLAB)
-
         with self._phase("fwd.binning"):
-            bin_slab(0, 0, cap_a, self.ranges)
+            self._bin_slab(cam, bs, 0, 0, cap_a, self.ranges, occl)
         with self._phase("fwd.blend"):
-            blend(1)
+            self._blend_slab(cam, dst, depth, 1, None, occl)
+
+    def _forward_slabs_far(self, cam: RgsCamera, bs: BinScratch, dst: torch.Tensor, want_depth: bool, push, occl=None):
+        """Far slab for the tiles that neither this sub-model (near slab) nor nearer sub-models (``occl``, optional:
+        what became known after the near slab) have finished; ``tile_done`` ends as the final state of the tiles."""
+        cap_a = self._base_b
+        depth = self.depth if want_depth else None
+        if occl is not None:
+            native.call("tile_maps_or", self.device, native.pointer_array([occl]), 1, self.tile_done, self.tile_done.numel(), 0,
+                        sig="pipiip")
         with self._phase("fwd.binning"):
-            bin_slab(1, cap_a, cap_b, self.ranges_b)
+            self._bin_slab(cam, bs, 1, cap_a, self.cap_inst - cap_a, self.ranges_b, self.tile_done)
         with self._phase("fwd.blend"):
-            blend(2)
+            self._blend_slab(cam, dst, depth, 2, push, None)
+
+    def _forward_slabs(self, cam: RgsCamera, bs: BinScratch, dst: torch.Tensor, want_depth: bool, push):
+        self._forward_slabs_near(cam, bs, dst, want_depth)
+        self._forward_slabs_far(cam, bs, dst, want_depth, push)
+
+    # -- forward in two halves: what the occlusion exchange between sub-models needs ---------------------------------
+    def forward_near(self, cam: RgsCamera, segments: list[Segment], want_depth: bool = False, occl: torch.Tensor | None = None):
+        """First half of an unchecked two-slab forward: projection and the near slab, skipping the tiles of ``occl``
+        (uint8 per tile: finished by nearer sub-models). Afterwards ``tile_done`` holds the tiles that are finished for
+        everything behind this sub-model's near slab. The depth order and the tile rectangles are kept in buffers of the
+        task, so that other tasks may run before :meth:`forward_far`."""
+        H, W = cam.H, cam.W
+        self.cam = cam
+        self.total_count = sum(s.count for s in segments)
+        self._ensure(self.total_count, H, W, want_depth)
+        if self._pending_cap > self.cap_inst:
+            self._grow_inst(self._pending_cap)
+        self._pending_cap = 0
+        self._want_depth = want_depth
+        self.counters.zero_()
+        bs = bin_scratch(self.device)
+        bs.ensure(self.cap_vis, self.cap_inst)
+        tiles = cam.tiles_x * cam.tiles_y
+        self._slab_active = self.binning == "depth_first" and cam.tight_rect < 2 and 8 <= tiles <= 65536
+        if not self._slab_active:
+            raise RuntimeError("forward_near needs the two-slab path (depth-first binning, 8..65536 tiles, tight_rect < 2)")
+        if self._own_order is None or self._own_order.numel() < self.cap_vis:
+            self._own_order = torch.empty(self.cap_vis, dtype=torch.int32, device=self.device)
+            self._own_rect = torch.empty(self.cap_vis, dtype=torch.int64, device=self.device)
+        structs = (RgsSegment * len(segments))(*[s.struct(False) for s in segments])
+        with self._phase("fwd.project"):
+            native.call("project_slots2", self.device, cam, structs, len(segments), bs.vis[3], self.cap_vis,
+                        self.splats, self.vis_ids, self.aux, self.cap_vis, bs.slot_depth, self._own_rect,
+                        bs.slot_cnt, self.counters, self.splat_grads)
+        self._forward_slabs_near(cam, bs, self.out, want_depth, occl)
+
+    def forward_far(self, occl: torch.Tensor | None = None, push=None) -> torch.Tensor:
+        """Second half: the far slab on the tiles that are still open (``occl``: tiles that nearer sub-models finished,
+        as far as known by now), with the fused push of the finished partial image."""
+        bs = bin_scratch(self.device)
+        bs.ensure(self.cap_vis, self.cap_inst)
+        self._forward_slabs_far(self.cam, bs, self.out, self._want_depth, push, occl)
+        self.last_out = self.out
+        self._record_counters()
+        return self.out
+
+    @staticmethod
+    def can_split(cam: RgsCamera) -> bool:
+        tiles = cam.tiles_x * cam.tiles_y
+        return cam.tight_rect < 2 and 8 <= tiles <= 65536
 
     def _note_slab_counts(self, n_a: int, n_b: int):
         """Remember the largest instance counts of both slabs and make the buffers hold 1.3x of each. The needs only grow
@@ -433,9 +503,10 @@ class RenderTask:
         assert grad_out.is_contiguous() and grad_out.shape == (cam.H, cam.W, 4)
         with self._phase("bwd.blend"):
             if grad_depth is not None:
-                if self._slab_active or self.deterministic:
-                    raise NotImplementedError("a depth gradient needs the single-pass, float-accumulating backward")
+                if self.deterministic:
+                    raise NotImplementedError("a depth gradient needs the float-accumulating backward")
                 assert grad_depth.is_contiguous() and grad_depth.shape == (cam.H, cam.W) and grad_depth.dtype == torch.float32
+            if grad_depth is not None and not self._slab_active:
                 native.call("blend_bwd_depth", self.device, cam, self.ranges, self.vals, self.splats, self.last_out,
                             self.n_contrib, grad_out, grad_depth, self.splat_grads, self.counters)
             elif self._slab_active:
@@ -446,7 +517,7 @@ class RenderTask:
                     fixed = self._fixed_acc
                 native.call("blend_bwd_slab", self.device, cam, self.ranges, self.ranges_b, self._base_b, self.vals, self.splats,
                             self.last_out, self.n_contrib, grad_out, self.splat_grads, self.counters, fixed, self.cap_vis,
-                            sig=self._SIG_BWD_SLAB)
+                            grad_depth, sig=self._SIG_BWD_SLAB)
             elif self.deterministic:
                 if self._fixed_acc is None or self._fixed_acc.numel() < 9 * self.cap_vis:
                     self._fixed_acc = torch.zeros(9 * self.cap_vis, dtype=torch.int64, device=self.device)
@@ -528,8 +599,7 @@ class _Rasterize(torch.autograd.Function):
             full[:, : shs.shape[1]] = shs
             seg.sh = full.view(-1, 48)
         task = RenderTask(dev)
-        task.slabs = False  # one pass: the backward of this interface may carry a depth gradient
-        task.deterministic = False
+        task.deterministic = False  # the backward of this interface may carry a depth gradient (float accumulation)
         out = task.forward(cam, [seg], want_depth=True, check=True)
         bg = settings.bg.to(dev).view(1, 1, 3)
         color = (out[..., :3] + out[..., 3:4] * bg).permute(2, 0, 1).contiguous()

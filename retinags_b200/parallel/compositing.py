@@ -83,6 +83,10 @@ class LocalTransport:
     def return_grads(self, plans, slots, local_grad):
         return None
 
+    def exchange_done_maps(self, plans, local_maps):
+        """{(view, model): uint8 map of finished tiles} of every visible sub-model; all are local here."""
+        return dict(local_maps)
+
     def barrier(self):
         return None
 
@@ -187,6 +191,29 @@ class TorchDistTransport:
                 elif b[1] > b[0]:
                     ops.append(dist.P2POp(dist.isend, slots[p.view][k][b[0]:b[1]], r, self.group))
         self._run(ops)
+
+    def exchange_done_maps(self, plans, local_maps):
+        """Every rank receives the finished-tile maps (uint8 per tile) of all visible sub-models: one all-reduce (MAX)
+        of a buffer in which each rank has filled in the maps of its own sub-models."""
+        out, bufs = dict(local_maps), []
+        for p in plans:
+            tiles = ((p.H + TILE - 1) // TILE) * ((p.W + TILE - 1) // TILE)
+            buf = torch.zeros(len(p.models), tiles, dtype=torch.uint8, device=self.device)
+            for k, (m, r) in enumerate(zip(p.models, p.ranks)):
+                if r == self.rank:
+                    buf[k].copy_(local_maps[(p.view, m)])
+            bufs.append(buf)
+        if bufs:
+            flat = torch.cat([b.reshape(-1) for b in bufs])
+            dist.all_reduce(flat, op=dist.ReduceOp.MAX, group=self.group)
+            off = 0
+            for p, b in zip(plans, bufs):
+                got = flat[off:off + b.numel()].view_as(b)
+                off += b.numel()
+                for k, (m, r) in enumerate(zip(p.models, p.ranks)):
+                    if r != self.rank:
+                        out[(p.view, m)] = got[k]
+        return out
 
     def reduce_skip(self, skip: torch.Tensor):
         """Every rank leaves with the maximum over ranks of the step's overflow word (queued on the stream)."""

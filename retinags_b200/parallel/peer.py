@@ -198,10 +198,12 @@ class PeerTransport:
             self.region.close()
         off_slots = self.FLAG_BYTES
         off_grads = off_slots + V * n_models * slot_bytes
-        total = off_grads + V * max_local * grad_bytes
+        off_maps = off_grads + V * max_local * grad_bytes
+        map_bytes = (grad_bytes // (16 * 256) + 512) // 256 * 256  # one byte per 16x16 tile, with room for ragged edges
+        total = off_maps + V * n_models * map_bytes
         self.region = PeerRegion(total, self.device, self.group)
         self.layout = dict(V=V, slot_bytes=slot_bytes, grad_bytes=grad_bytes, off_slots=off_slots, off_grads=off_grads,
-                           n_models=n_models, max_local=max_local)
+                           n_models=n_models, max_local=max_local, off_maps=off_maps, map_bytes=map_bytes)
         self.flags = self.region.view(0, (self.FLAG_BYTES // 4,), torch.int32)
         self._flag_ptrs = (ctypes.c_void_p * self.world)(*self.region.ptrs)
         self.epoch = 0
@@ -296,6 +298,28 @@ class PeerTransport:
             from .compositing import TorchDistTransport
             self._dist_transport = TorchDistTransport(self.device, self.group)
         return self._dist_transport.exchange_partials(plans, local_images)
+
+    def exchange_done_maps(self, plans, local_maps):
+        """Publish the finished-tile maps of this rank's sub-models into every peer's region (plain peer stores of a few
+        KB each), order with the flag barrier, and hand out the maps of all visible sub-models: remote ones as views of
+        this rank's region, local ones as given."""
+        L = self.layout
+        out = dict(local_maps)
+        for p in plans:
+            tiles = ((p.H + 15) // 16) * ((p.W + 15) // 16)
+            if tiles > L["map_bytes"]:
+                raise RuntimeError("a view has more tiles than the map slots of the exchange region hold")
+            for m, r in zip(p.models, p.ranks):
+                off = L["off_maps"] + (p.view * L["n_models"] + m) * L["map_bytes"]
+                if r == self.rank:
+                    dsts = [self.region.ptrs[o] + off for o in range(self.world) if o != self.rank]
+                    if dsts:
+                        native.call("tile_map_push", self.device, local_maps[(p.view, m)], (ctypes.c_void_p * len(dsts))(*dsts),
+                                    len(dsts), tiles, sig="ppiip")
+                else:
+                    out[(p.view, m)] = self.region.view(off, (tiles,), torch.uint8)
+        self._signal_wait()
+        return out
 
     def local_grad_images(self, plans) -> dict:
         """Gradient images of this rank's renders, inside the exchange region (peer-writable)."""

@@ -23,6 +23,7 @@ def _worker(rank, world, port, out_dir, slabs=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["RGS_SLABS"] = "1" if slabs else "0"
+    os.environ["RGS_OCCLUSION"] = "1" if slabs == "occlusion" else "0"  # maps travel through one all-reduce per step
     os.environ["RGS_SLAB_FRACTION"] = "96"
     torch.set_num_threads(2)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -50,11 +51,14 @@ def _worker(rank, world, port, out_dir, slabs=False):
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("slabs", [False, True])
-def test_two_ranks_match_single_rank(tmp_path, slabs):
-    """``slabs``: the ranks render with the two-slab forward (CPU twins), the single-rank reference without."""
+@pytest.mark.parametrize("slabs", [False, True, "occlusion"])
+def test_two_ranks_match_single_rank(tmp_path, slabs, monkeypatch):
+    """``slabs``: the ranks render with the two-slab forward (CPU twins), the single-rank reference without;
+    "occlusion": they also exchange their finished-tile maps and skip tiles hidden behind the other rank's sub-model."""
     sys.path.insert(0, ROOT)
-    port = 29500 + os.getpid() % 2000 + (1000 if slabs else 0)
+    monkeypatch.setenv("RGS_SLABS", "0")       # the single-rank reference of this process renders in one pass
+    monkeypatch.setenv("RGS_OCCLUSION", "0")
+    port = 29500 + os.getpid() % 2000 + (1000 if slabs else 0) + (500 if slabs == "occlusion" else 0)
     mp.spawn(_worker, args=(2, port, str(tmp_path), slabs), nprocs=2, join=True)
     res = [torch.load(os.path.join(tmp_path, f"rank{r}.pt"), weights_only=False) for r in range(2)]
     assert sum(sum(r["counts"].values()) for r in res) == N_GAUSS
