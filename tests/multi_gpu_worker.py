@@ -49,7 +49,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--transport", default="peer")
     ap.add_argument("--out", default="")
+    ap.add_argument("--occlusion", type=int, default=0)
     a = ap.parse_args()
+    os.environ["RGS_OCCLUSION"] = str(a.occlusion)  # finished-tile maps exchanged between the ranks (training forward)
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)

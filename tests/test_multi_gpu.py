@@ -11,14 +11,14 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
-@pytest.mark.parametrize("transport", ["peer", "nccl"])
+@pytest.mark.parametrize("transport", ["peer", "nccl", "peer+occlusion", "nccl+occlusion"])
 def test_multi_gpu_matches_single(tmp_path, transport):
     n = min(torch.cuda.device_count(), 4)
     n = 2 if n < 4 else 4
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
            "127.0.0.1", "--master-port", str(29600 + os.getpid() % 300), os.path.join(ROOT, "tests", "multi_gpu_worker.py"),
-           "--transport", transport, "--out", str(tmp_path)]
+           "--transport", transport.split("+")[0], "--out", str(tmp_path), "--occlusion", "1" if "+" in transport else "0"]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "MULTI_GPU_OK" in proc.stdout
