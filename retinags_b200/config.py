@@ -146,8 +146,18 @@ def add_trainer_flags(parser: ArgumentParser):
                         "in rank order, two-pass isend/irecv")
     p.add_argument("--BALANCE_BATCHES", action="store_true", default=False,
                    help="batch cameras whose estimated per-rank loads complement each other (same cameras per epoch)")
-    p.add_argument("--BORROW_REFRESH_INTERVAL", type=int, default=1,
-                   help="steps between recomputations of the border-Gaussian sets (1 = every step, as the reference)")
+    p.add_argument("--BORROW_REFRESH_INTERVAL", type=int, default=8,
+                   help="steps between recomputations of the border-Gaussian sets; the rows are re-sent every step, the "
+                        "sets are made 5 %% larger when they are kept (1 = recomputed every step, as the reference)")
+    p.add_argument("--PREFETCH_BATCHES", type=int, default=2,
+                   help="batches whose images are decoded ahead of the training step (0 = decode inside the step)")
+    p.add_argument("--PREFETCH_WORKERS", type=int, default=8, help="threads decoding images for the coming batches")
+    p.add_argument("--OCCLUSION_CULLING", type=int, default=-1, choices=[-1, 0, 1],
+                   help="skip tiles that nearer sub-models have finished (maps exchanged once per step); -1: the default "
+                        "of the build (RGS_OCCLUSION)")
+    p.add_argument("--MODEL_ASSIGNMENT", default="round_robin", choices=["round_robin", "cost"],
+                   help="sub-model -> rank map: i %% world as the reference, or balanced by the estimated render cost over "
+                        "the training cameras")
 
 
 def build_parser() -> tuple[ArgumentParser, ModelParams, OptimizationParams, PipelineParams]:

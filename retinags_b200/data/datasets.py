@@ -8,6 +8,8 @@ epochs only pay the host->device copy of the rows a rank owns.
 """
 from __future__ import annotations
 
+import threading
+
 import torch
 from torch.utils.data import Dataset
 
@@ -35,6 +37,7 @@ class CameraListDataset(Dataset):
         self.cache_bytes = cache_bytes
         self._cache: dict[int, torch.Tensor] = {}
         self._cached = 0
+        self._lock = threading.Lock()  # items may be fetched by the prefetch threads (data/prefetch.py)
 
     def __len__(self):
         return len(self.infos)
@@ -63,9 +66,10 @@ class CameraListDataset(Dataset):
             if self.pin:
                 img = img.pin_memory()
             nbytes = img.numel() * 4
-            if self._cached + nbytes <= self.cache_bytes:
-                self._cache[idx] = img
-                self._cached += nbytes
+            with self._lock:
+                if idx not in self._cache and self._cached + nbytes <= self.cache_bytes:
+                    self._cache[idx] = img
+                    self._cached += nbytes
         cam.image = img
         return cam
 

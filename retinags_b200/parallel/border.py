@@ -34,14 +34,14 @@ def select_border(store: GaussianStore, m: int, lo: torch.Tensor, hi: torch.Tens
     centre +- 3 exp(max log-scale) (1 + margin) leaves the box of m and overlaps the box of d. ``lo``/``hi``: (M,3).
 
     ``native_mask``: one pass of the mask kernel (``csrc/rgs_border.cu``, ``rgs_border.h``) instead of boolean-mask
-    gathers per destination; default: on for CPU stores, on CUDA only with ``RGS_BORDER_SELECT=native``."""
+    gathers per destination; the default for up to 63 sub-models (``RGS_BORDER_SELECT=torch`` selects the masks)."""
     M = int(lo.shape[0])
     out: dict[int, torch.Tensor] = {}
     if store.count == 0 or M < 2:
         return out
     v = store.views()
     if native_mask is None:
-        native_mask = (store.device.type == "cpu" or os.environ.get("RGS_BORDER_SELECT", "torch") == "native") and M <= 63
+        native_mask = os.environ.get("RGS_BORDER_SELECT", "native") == "native" and M <= 63
     if native_mask:
         boxes = torch.cat([lo, hi], dim=1).to(store.device, torch.float32).contiguous()
         masks = torch.empty(store.count, dtype=torch.int64, device=store.device)
@@ -79,6 +79,10 @@ class BorderExchange:
         self.M = len(self.model2rank)
         self.rank, self.world, self.device, self.group = rank, world, torch.device(device), group
         self.refresh_interval = max(1, refresh_interval)
+        # a selection that is kept for several steps is made with a slightly larger extent, so that a Gaussian that
+        # starts to reach a neighbour during the interval is lent already (a superset is harmless: the half-Gaussian
+        # clip decides per pixel what counts)
+        self.margin = 0.05 if self.refresh_interval > 1 else 0.0
         self.enabled = enabled
         self._step = 0
         self._index: dict[tuple[int, int], torch.Tensor] = {}   # (src local model, dst model) -> row ids
@@ -102,7 +106,7 @@ class BorderExchange:
         for m, st in stores.items():
             if st.count == 0:
                 continue
-            for d, idx in select_border(st, m, self.lo, self.hi).items():
+            for d, idx in select_border(st, m, self.lo, self.hi, self.margin).items():
                 self._index[(m, d)] = idx
                 counts[m, d] = idx.numel()
         if self.world > 1:

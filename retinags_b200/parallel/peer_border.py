@@ -59,6 +59,7 @@ class PeerBorderExchange:
         self.cap_b = self.cap_r = 0
         self._segs: dict[int, Segment] = {}
         self._need_grads = False
+        self._fresh = True
 
     def invalidate(self):
         self._counts = None
@@ -70,7 +71,11 @@ class PeerBorderExchange:
         return self.cap_b * ROW_FLOATS * 4
 
     def _ring_bytes(self) -> int:
-        return self.cap_r * GRAD_ROW_FLOATS * 4
+        # gradient rows, then one "this row carries a gradient" byte per row
+        return self.cap_r * GRAD_ROW_FLOATS * 4 + (self.cap_r + 255) // 256 * 256
+
+    def _ring_flags_off(self, model: int) -> int:
+        return self._ring_off(model) + self.cap_r * GRAD_ROW_FLOATS * 4
 
     def _block_off(self, model: int) -> int:
         return self.slot_of[model] * self._block_bytes()
@@ -116,7 +121,10 @@ class PeerBorderExchange:
             g = [torch.zeros(n, w, dtype=torch.float32, device=self.device) for w in WIDTHS]
             seg.g_xyz, seg.g_sh, seg.g_scale, seg.g_rot, seg.g_opacity = g
             seg.stat_grad = torch.zeros(n, dtype=torch.float32, device=self.device)
+            # first gradient of a step is stored, later ones are added; the marks are cleared when the rows are pushed back
+            seg.touched = torch.zeros(n, dtype=torch.uint8, device=self.device)
             self._segs[d] = seg
+        self._fresh = True  # the next refresh packs every lent row, later ones only rows that may have moved
 
     # -- per step -------------------------------------------------------------------------------------
     def refresh(self, stores: dict[int, GaussianStore], need_grads: bool):
@@ -138,11 +146,10 @@ class PeerBorderExchange:
                     continue
                 base = self.region.ptrs[self.model2rank[d]] + self._block_off(d)
                 dst = (ctypes.c_void_p * 5)(*self._column_ptrs(base))
-                native.call("border_pack", self.device, src, self._index[(s, d)], n, dst, self._in_off[(s, d)], sig="ppipip")
-        if need_grads:
-            for seg in self._segs.values():
-                for t in (seg.g_xyz, seg.g_sh, seg.g_scale, seg.g_rot, seg.g_opacity, seg.stat_grad):
-                    t.zero_()
+                # between two selections only rows with Adam moments can have moved: the others are skipped
+                native.call("border_pack", self.device, src, self._index[(s, d)], n, dst, self._in_off[(s, d)],
+                            None if self._fresh else st.active, sig="ppipipp")
+        self._fresh = False
         self.transport.barrier()  # rows have landed before anyone renders them
 
     def segment(self, d: int, with_grads: bool) -> Segment | None:
@@ -164,8 +171,11 @@ class PeerBorderExchange:
                 n = int(c[s, d])
                 if n == 0:
                     continue
-                rows = self.region.ptrs[self.model2rank[s]] + self._ring_off(s) + self._out_off[(s, d)] * GRAD_ROW_FLOATS * 4
-                native.call("border_grad_push", self.device, g, seg.stat_grad, self._in_off[(s, d)], n, rows, sig="ppiipp")
+                base = self.region.ptrs[self.model2rank[s]]
+                rows = base + self._ring_off(s) + self._out_off[(s, d)] * GRAD_ROW_FLOATS * 4
+                flags = base + self._ring_flags_off(s) + self._out_off[(s, d)]
+                native.call("border_grad_push", self.device, g, seg.stat_grad, seg.touched, self._in_off[(s, d)], n, rows, flags,
+                            sig="pppiippp")
         self.transport.barrier()  # gradient rows have landed at their owners
         for s in self.local:
             st = stores[s]
@@ -176,8 +186,9 @@ class PeerBorderExchange:
                 if n == 0:
                     continue
                 rows = self.region.ptrs[self.rank] + self._ring_off(s) + self._out_off[(s, d)] * GRAD_ROW_FLOATS * 4
-                native.call("border_grad_add", self.device, rows, self._index[(s, d)], n, g, st.grad_accum, st.touched,
-                            sig="ppipppp")
+                flags = self.region.ptrs[self.rank] + self._ring_flags_off(s) + self._out_off[(s, d)]
+                native.call("border_grad_add", self.device, rows, flags, self._index[(s, d)], n, g, st.grad_accum, st.touched,
+                            sig="pppipppp")
 
     def close(self):
         if self.region is not None:

@@ -35,6 +35,7 @@ import torch.distributed as dist
 from .data import readers
 from .data.cameras import Camera
 from .data.datasets import CameraListDataset, DatasetRepeater
+from .data.prefetch import BatchPrefetcher
 from .engine import StepEngine
 from .models import densify, ply_io
 from .models.gaussians import GaussianStore
@@ -112,6 +113,9 @@ class Trainer:
         self.test_rlt = self._relation(self.test_dataset, "testset_relation.pt")
         self._gen = torch.Generator(device=self.device)
         self._gen.manual_seed(1234 + self.rank)
+        self.steps_done = 0         # training steps (batches) run by this object
+        self.step_callback = None   # optional callable(step index), called before each training step (benchmarks)
+        self.eval_stamps: list = []  # (split, host time after the metrics of an image were read) of the last eval()
         self.watchdog = None
         if self.world > 1 and getattr(args, "WATCHDOG_TIMEOUT", 120.0) > 0:
             from .parallel.watchdog import Watchdog
@@ -329,6 +333,8 @@ class Trainer:
                 self.border = BorderExchange(lo, hi, self.model2rank, self.rank, self.world, self.device, self.group, interval)
         self.engine = StepEngine(self.stores, self.model2rank, self.device, tr, self.opt.lambda_dssim, self.background,
                                  borrow=self.border)
+        if getattr(a, "OCCLUSION_CULLING", -1) >= 0:
+            self.engine.occlusion = bool(a.OCCLUSION_CULLING)
         self.engine.debug = bool(getattr(self.pipe, "debug", False))
         self.engine.detect_anomaly = bool(getattr(self.args, "detect_anomaly", False))
         self.engine.dump_dir = self.model_path
@@ -399,10 +405,6 @@ class Trainer:
             self._cost, self._cost_key = cost.cpu().numpy(), key
         return self._cost
 
-    def _fetch(self, dataset, ids):
-        """Cameras of a batch; pixels are only needed by ranks that own rows (all of them with band ownership)."""
-        return [dataset[i] for i in ids]
-
     def train(self):
         o, a = self.opt, self.args
         n_train = len(self.train_dataset)
@@ -416,10 +418,13 @@ class Trainer:
             sh_deg = min(self.sh_degree, self.iteration // 1000)
             for st in self.stores.values():
                 st.active_sh_degree = sh_deg
-            for ids in groups:
+            feed = BatchPrefetcher(self.train_dataset, groups, depth=getattr(a, "PREFETCH_BATCHES", 2),
+                                   workers=getattr(a, "PREFETCH_WORKERS", 8))
+            for ids, cams in feed:  # the images of the next batches are decoded while this step runs
                 if self.watchdog is not None:
                     self.watchdog.check()  # a dead peer is noticed here, before the next kernels and collectives
-                cams = self._fetch(self.train_dataset, ids)
+                if self.step_callback is not None:
+                    self.step_callback(self.steps_done)
                 bs = len(cams)
                 t0 = time.perf_counter()
                 bg = None
@@ -451,6 +456,7 @@ class Trainer:
                     self.logger.warning("a render of the step before iteration %d ran out of instance capacity: its update "
                                         "was dropped on every rank, the buffers have been grown", self.iteration + bs)
                 self.iteration += bs
+                self.steps_done += 1
             last = epoch == epochs - 1
             if (epoch % a.SAVE_INTERVAL_EPOCH == 0 and epoch != 0) or last:
                 self.save(self.iteration)
@@ -500,6 +506,8 @@ class Trainer:
                 (self.mdp.white_background and is_point_in_batch(iteration, bs, o.densify_from_iter)):
             for st in self.stores.values():
                 densify.reset_opacity(st)
+            if self.border is not None:
+                self.border.invalidate()  # every opacity changed: the lent copies are stale
         if changed:
             for st in self.stores.values():
                 st.zero_grad()  # rows moved: gradients of this step are dropped, like the reference's rebuilt optimiser
@@ -550,6 +558,7 @@ class Trainer:
         if not hasattr(self, "_lpips"):
             from .utils.lpips import load_lpips
             self._lpips = load_lpips(getattr(a, "LPIPS_WEIGHTS", ""), self.device)
+        self.eval_stamps = []
         for name, ds, rlt, stride in splits:
             stat = torch.zeros(4, dtype=torch.float64, device=self.device)  # samples, l1, psnr, ssim
             lp_sum, lp_n = 0.0, 0
@@ -569,7 +578,11 @@ class Trainer:
                     npx = 3.0 * cam.height * cam.width
                     l1, ssim, mse = (sums / npx).tolist()
                     stat += torch.tensor([1.0, l1, psnr_from_mse(mse), ssim], dtype=torch.float64, device=self.device)
+                    self.eval_stamps.append((name, time.perf_counter()))  # the metrics were read back: the image is done
                     self.logger.info("%s, image %s, psnr %f, ssim %f, l1 %f", name, cam.image_name, psnr_from_mse(mse), ssim, l1)
+                    if self.tb and cam.uid < 1000 and cam.uid % 5 == 0:
+                        # every fifth view, render and ground truth (trainer4tree_partition.py:731-733 of the reference)
+                        self._tb_images(name, cam, out, gt)
                     if self._lpips is not None:
                         # the perceptual metric needs whole images: the row bands are summed into one on every rank
                         full = torch.zeros(3, cam.height, cam.width, device=self.device)
@@ -599,7 +612,24 @@ class Trainer:
                     self.tb.add_scalar(name + "/loss_viewpoint - l1_loss", l1 / n, self.iteration)
                     self.tb.add_scalar(name + "/loss_viewpoint - psnr", ps / n, self.iteration)
                     self.tb.add_scalar(name + "/loss_viewpoint - ssim", ss / n, self.iteration)
+                    self.tb.add_scalar(name + "/loss_viewpoint - lpips", lp, self.iteration)
+        if self.tb:
+            for m, st in self.stores.items():
+                self.tb.add_scalar(f"total_points_{m}", st.count, self.iteration)
         return results
+
+    def _tb_images(self, split: str, cam: Camera, out, gt: torch.Tensor):
+        """Whole render and ground truth of one view to TensorBoard (the row bands are summed over the ranks)."""
+        r0, r1 = out["rows"]
+        full = torch.zeros(3, cam.height, cam.width, device=self.device)
+        full[:, r0:r1] = out["image"][:, r0:r1]
+        gt_full = torch.zeros_like(full)
+        gt_full[:, r0:r1] = gt[:, r0:r1]
+        if self.world > 1:
+            dist.all_reduce(full, group=self.group)
+            dist.all_reduce(gt_full, group=self.group)
+        self.tb.add_images(f"{split}_view_{cam.image_name}/render", full.clamp(0, 1)[None].cpu(), global_step=self.iteration)
+        self.tb.add_images(f"{split}_view_{cam.image_name}/ground_truth", gt_full[None].cpu(), global_step=self.iteration)
 
     def _save_rows(self, out, cam: Camera, split: str):
         """Gather the row bands of a composited image on rank 0 and write it (plus the ground truth)."""
