@@ -44,6 +44,15 @@ def parse_args():
                          "RGS_SLAB_FRACTION=N; default 32); 0 renders in one pass")
     ap.add_argument("--occlusion", type=int, default=None, choices=[0, 1],
                     help="occlusion culling between sub-models (finished-tile maps exchanged once per step)")
+    ap.add_argument("--mode", default="train", choices=["train", "eval", "train-psnr", "trainer"],
+                    help="train: the headline (training views/s of the step engine on an in-memory scene). The other modes "
+                         "run the public trainer of either arm on one scene on disk (PNG targets, the initial model as a "
+                         "PLY file): eval = eval render of --eval-frames test views (ms/frame, PSNR/SSIM/L1); train-psnr = "
+                         "--epochs epochs over --train-views views, then that eval; trainer = views/s of Trainer.train(), "
+                         "image decoding included (own arm only)")
+    ap.add_argument("--train-views", type=int, default=40)
+    ap.add_argument("--eval-frames", type=int, default=20)
+    ap.add_argument("--epochs", type=int, default=8)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--phases", action="store_true", help="also time the phases of a step (extra loop, after the timed one)")
     ap.add_argument("--task-times", default="", help="with --phases: write the per-(camera, sub-model) render times of every "
@@ -184,6 +193,23 @@ def run_own(args):
         wall = float(tw.item())
         e2e = {"value": args.steps * args.batch / wall, "unit": "views/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "last_loss": loss}
+    # ---- eval render: composited frames through the engine's render path (the one Trainer.eval() uses) ------------
+    frames = min(args.eval_frames, len(sess.cams))
+    for i in range(min(2, frames)):
+        sess.render_view(i)
+    sess.barrier()
+    torch.cuda.synchronize()
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    r0.record()
+    for i in range(frames):
+        sess.render_view(i)
+    r1.record()
+    torch.cuda.synchronize()
+    tr = torch.tensor([r0.elapsed_time(r1)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(tr, op=dist.ReduceOp.MAX)
+    render = {"ms_per_frame": float(tr) / max(frames, 1), "frames": frames,
+              "what": "eval render incl. compositing across sub-models, device-timed, max over ranks"}
     phases = None
     if args.phases:
         sess.engine.timer.enabled = True
@@ -232,9 +258,118 @@ def run_own(args):
                        "rows_with_adam_moments_rank0": live_rows, "overflow_in_timed_region": overflow,
                        "two_slab_forward": os.environ.get("RGS_SLABS", "1") == "1",
                        "occlusion_culling_between_submodels": bool(sess.engine.occlusion)},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "phases_ms_per_step_max_over_ranks": phases,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "render": render,
+            "phases_ms_per_step_max_over_ranks": phases,
             "roofline_rank0_of_measured": roofline,
         }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_own_trainer(args):
+    """The own arm through its public trainer (``main.py``'s ``Trainer``) on the scene that the reference arm reads."""
+    import torch
+    import torch.distributed as dist
+
+    from baseline import reference_arm
+    from retinags_b200.config import build_parser
+    from retinags_b200.trainer import Trainer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    mode = args.mode
+    if mode == "trainer":
+        n_train, n_test = (args.warmup + args.steps + 3) * args.batch, 2
+    else:
+        n_train, n_test = args.train_views, args.eval_frames
+    err = ""
+    if rank == 0:
+        try:
+            reference_arm.ensure_scene(args, n_train, n_test)
+        except RuntimeError as exc:
+            err = str(exc)
+    if world > 1:
+        box = [err]
+        dist.broadcast_object_list(box, src=0)
+        err = box[0]
+    if err:
+        raise SystemExit(err)
+    root = reference_arm.scene_root(args, n_train, n_test)
+    data_dir = os.path.join(root, "data")
+    model_dir = os.path.join(root, f"own_model_{mode}_{world}")
+    if rank == 0:  # the initial model, shared with the reference arm, under this run's own model directory
+        import shutil
+        shutil.rmtree(model_dir, ignore_errors=True)
+        os.makedirs(os.path.join(model_dir, "point_cloud", "iteration_1"))
+        os.symlink(os.path.join(root, "model", "point_cloud", "iteration_1", "point_cloud.ply"),
+                   os.path.join(model_dir, "point_cloud", "iteration_1", "point_cloud.ply"))
+    if world > 1:
+        dist.barrier()
+    depth = max(0, world.bit_length() - 1) if args.bvh_depth is None else args.bvh_depth
+    max_load = args.batch * max(2, (2 ** depth + world - 1) // world)
+    argv = ["-s", data_dir, "-m", model_dir, "--bvh_depth", str(depth), "--MAX_BATCH_SIZE", str(args.batch), "--MAX_LOAD",
+            str(max_load), "-r", "1", "--ply_iteration", "1", "--eval", "--densify_from_iter", "100000000",
+            "--DATALOADER_FIX_SEED", "--quiet", "--EVAL_INTERVAL_EPOCH", "100000", "--SAVE_INTERVAL_EPOCH", "100000",
+            "--epochs", str(args.epochs if mode == "train-psnr" else 1), "--transport", {"nccl": "dist"}.get(args.transport, args.transport),
+            "--BORROW_REFRESH_INTERVAL", str(args.borrow_refresh)]
+    if mode == "eval":
+        argv.append("--EVAL_ONLY")
+    parser, lp, op, pp = build_parser()
+    a = parser.parse_args(argv)
+    if args.occlusion is not None:
+        os.environ["RGS_OCCLUSION"] = str(args.occlusion)
+    tr = Trainer(a, lp.extract(a), op.extract(a), pp.extract(a))
+    out = {"impl": "own", "n_gpus": world, "mode": mode, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+           "dtype": "fp32", "data": "synthetic", "train_views": n_train, "eval_frames": n_test,
+           "config": {"model": "3DGS SH-3, seeded 64-cluster mixture in a 20-unit box", "gaussians": args.gaussians,
+                      "global_batch": args.batch, "resolution": [args.width, args.height], "bvh_depth": depth,
+                      "parallelism": f"spatial-mp{world}", "transport": type(tr.engine.transport).__name__}}
+    from retinags_b200.ops import native
+    if mode == "trainer":
+        marks = {}
+
+        def hook(step):  # device-synchronised stamps around exactly K steps, after W warm-up steps
+            if step in (args.warmup, args.warmup + args.steps):
+                torch.cuda.synchronize()
+                if world > 1:
+                    dist.barrier()
+                    torch.cuda.synchronize()
+                marks[step] = (time.perf_counter(), native.launch_count())
+        tr.step_callback = hook
+        tr.opt.epochs = 1
+        tr.train()
+        (t0, l0), (t1, l1) = marks[args.warmup], marks[args.warmup + args.steps]
+        sec = torch.tensor([t1 - t0], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(sec, op=dist.ReduceOp.MAX)
+        sec = float(sec)
+        out.update({"metric": "train views/s through Trainer.train() (scene on disk, image decoding included)",
+                    "value": args.steps * args.batch / sec, "unit": "views/s", "steps": args.steps, "warmup": args.warmup,
+                    "ms_per_step": 1e3 * sec / args.steps, "gpu_launches": l1 - l0})
+    else:
+        if mode == "train-psnr":
+            tr.train()     # evaluates after its last epoch, like the reference; evaluated again below for the stamps
+        res = tr.eval()
+        stamps = [t for name, t in tr.eval_stamps if name == "test"]
+        ms_frame = None
+        if len(stamps) > 3:
+            skip = min(len(stamps) - 2, 2)
+            ms_frame = 1e3 * (stamps[-1] - stamps[skip - 1]) / (len(stamps) - skip)
+        ev = dict(res["test"])
+        ev["ms_per_frame"] = ms_frame
+        out.update({"metric": "render ms/frame and PSNR (own eval loop)" if mode == "eval" else
+                    f"PSNR after {args.epochs} epochs over {n_train} views (own trainer)",
+                    "value": ms_frame if mode == "eval" else ev["psnr"], "unit": "ms/frame" if mode == "eval" else "dB",
+                    "higher_is_better": mode != "eval", "eval": ev, "epochs": args.epochs,
+                    "gpu_launches": native.launch_count()})
+    if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -249,5 +384,7 @@ if __name__ == "__main__":
     a = parse_args()
     if a.impl == "reference":
         run_reference(a)
+    elif a.mode != "train":
+        run_own_trainer(a)
     else:
         run_own(a)

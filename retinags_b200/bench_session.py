@@ -37,8 +37,12 @@ class ClusterScene:
         self.centers = (torch.rand(n_clusters, 3, device=device, generator=g) - 0.5) * box * 0.8
         self.centers[:, 2] = self.centers[:, 2].abs() * 0.5
         self.axes = 0.3 + 1.7 * torch.rand(n_clusters, 3, device=device, generator=g)
-        q, _ = torch.linalg.qr(torch.randn(n_clusters, 3, 3, device=device, generator=g))
-        self.rot = q
+        # random rotations from normalised quaternions (element-wise arithmetic only: no solver library is involved)
+        q = torch.nn.functional.normalize(torch.randn(n_clusters, 4, device=device, generator=g), dim=1)
+        w, x, y, z = q.unbind(1)
+        self.rot = torch.stack([1 - 2 * (y * y + z * z), 2 * (x * y - w * z), 2 * (x * z + w * y),
+                                2 * (x * y + w * z), 1 - 2 * (x * x + z * z), 2 * (y * z - w * x),
+                                2 * (x * z - w * y), 2 * (y * z + w * x), 1 - 2 * (x * x + y * y)], dim=1).view(n_clusters, 3, 3)
 
     def means(self, n: int, chunk: int) -> torch.Tensor:
         g = torch.Generator(device=self.device)

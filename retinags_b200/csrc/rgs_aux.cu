@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(256) rgs_mark_visible_kernel(const float* __re
 
 static inline unsigned aux_grid(int64_t n, int threads) {
     const int64_t want = (n + threads - 1) / threads;
-    return (unsigned)(want < 1 ? 1 : (want > 148 * 32 ? 148 * 32 : want));
+    return (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 32 ? RGS_SMS * 32 : want));
 }
 
 extern "C" {

@@ -1023,7 +1023,7 @@ static void bs_pass(const uint32_t* kin, const uint32_t* vin, uint32_t* kout, ui
                     uint32_t cap, int shift, uint32_t* hist, uint32_t* totals, uint32_t nchunks_cap, int iota, cudaStream_t st) {
     const uint32_t chunk = BS_THREADS * ITEMS;
     const uint32_t nch = (cap + chunk - 1) / chunk;
-    const unsigned grid = nch < 1u ? 1u : (nch < 148u * 8u ? nch : 148u * 8u);
+    const unsigned grid = nch < 1u ? 1u : (nch < (unsigned)(RGS_SMS * 8) ? nch : (unsigned)(RGS_SMS * 8));
     // which == CNT_INST is the tile sort: its upper digit repeats inside a warp, everything else is close to random
     const int aggregate = ((which == RGS_CNT_INST || which == RGS_CNT_INST2) && shift >= 8) ? 1 : 0;
     rgs_bs_hist_kernel<ITEMS><<<grid, BS_THREADS, 0, st>>>(kin, cnt, which, cap, shift, hist, nchunks_cap, aggregate);
@@ -1092,7 +1092,7 @@ int rgs_cuda_project_slots2(const RgsCamera* cam, const RgsSegment* segs, int64_
         base += segs[k].count;
     }
     const int64_t want = (cap_cand + PC_THREADS - 1) / PC_THREADS;
-    const unsigned grid = (unsigned)(want < 1 ? 1 : (want > 148 * 8 ? 148 * 8 : want));
+    const unsigned grid = (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 8 ? RGS_SMS * 8 : want));
     rgs_project_cand_kernel<<<grid, PC_THREADS, 0, st>>>(*cam, s4, cand, (uint32_t)cap_cand, splats, vis_ids, aux, (uint32_t)cap_vis,
                                                   slot_depth, reinterpret_cast<uint2*>(slot_rect), slot_cnt, cnt, splat_grads);
     return (int)cudaGetLastError();
@@ -1100,7 +1100,7 @@ int rgs_cuda_project_slots2(const RgsCamera* cam, const RgsSegment* segs, int64_
 
 // The counter table of the segmented counting holds (warps x tiles) words; warps per SM x tiles x 4 bytes never
 // exceeds the shared memory of an SM, which bounds the table for any image size.
-#define SC_TABLE_WORDS ((int64_t)148 * 227 * 256)
+#define SC_TABLE_WORDS (RGS_SMS * 227 * 256)
 
 // 1: group by tile with the segmented counting (RGS_TILE_GROUPING=count), 0: with the radix sort (default).
 // Measured at 62.9 M Gaussians, 1600x1036 (85 M instances per view): 17 ms per view against 3.6 ms for pair
@@ -1144,7 +1144,7 @@ int rgs_cuda_bin_instances(const RgsCamera* cam, const RgsSplat* splats, const u
             &order);
     // 2. emission in depth order
     const uint32_t nseg_cap = (uint32_t)((cap_vis + EM_SEG - 1) / EM_SEG);
-    const unsigned egrid = nseg_cap < 148u * 8u ? (nseg_cap ? nseg_cap : 1u) : 148u * 8u;
+    const unsigned egrid = nseg_cap < (unsigned)(RGS_SMS * 8) ? (nseg_cap ? nseg_cap : 1u) : (unsigned)(RGS_SMS * 8);
     rgs_emit_count_kernel<<<egrid, 256, 0, st>>>(order, slot_cnt, cnt, (uint32_t)cap_vis, seg_sums);
     rgs_emit_scan_kernel<<<1, 1024, 0, st>>>(seg_sums, cnt, (uint32_t)cap_vis, (uint32_t)cap_inst);
     if (sc_enabled() && num_tiles <= SC_MAX_TILES) {
@@ -1154,7 +1154,7 @@ int rgs_cuda_bin_instances(const RgsCamera* cam, const RgsSplat* splats, const u
         const size_t smem = (size_t)num_tiles * 4;
         int per_sm = (int)((227 * 1024) / (smem + 1024));
         per_sm = per_sm > 8 ? 8 : (per_sm < 1 ? 1 : per_sm);
-        const unsigned W = 148u * (unsigned)per_sm;
+        const unsigned W = (unsigned)RGS_SMS * (unsigned)per_sm;
         if ((int64_t)W * num_tiles > SC_TABLE_WORDS) return 13;
         static bool attr_set = false;
         if (!attr_set) {
@@ -1191,7 +1191,7 @@ int rgs_cuda_bin_instances(const RgsCamera* cam, const RgsSplat* splats, const u
         return (int)cudaGetLastError();
     }
     RGS_CUDA_CHECK(cudaMemsetAsync(ranges, 0, (size_t)num_tiles * 8, st));
-    rgs_bs_tile_ranges_kernel<<<148 * 8, 256, 0, st>>>(tk, cnt, (uint32_t)cap_inst, reinterpret_cast<int2*>(ranges),
+    rgs_bs_tile_ranges_kernel<<<(unsigned)(RGS_SMS * 8), 256, 0, st>>>(tk, cnt, (uint32_t)cap_inst, reinterpret_cast<int2*>(ranges),
                                                        (uint32_t)num_tiles, in_tmp ? tv : nullptr, in_tmp ? inst_vals : nullptr);
     return (int)cudaGetLastError();
 }
@@ -1227,12 +1227,12 @@ int rgs_cuda_bin_slab(const RgsCamera* cam, const uint32_t* slot_depth, const ui
     const int which = slab == 0 ? RGS_CNT_INST : RGS_CNT_INST2;
     const uint2* rects = reinterpret_cast<const uint2*>(slot_rect);
     const uint32_t nseg_cap = (uint32_t)((cap_vis + EM_SEG - 1) / EM_SEG);
-    const unsigned egrid = nseg_cap < 148u * 8u ? (nseg_cap ? nseg_cap : 1u) : 148u * 8u;
+    const unsigned egrid = nseg_cap < (unsigned)(RGS_SMS * 8) ? (nseg_cap ? nseg_cap : 1u) : (unsigned)(RGS_SMS * 8);
     if (slab == 1 && (!tile_done || !sat)) return 15;
     if (tile_done) {  // the far slab always filters; the near slab when tiles are known to be hidden by nearer sub-models
         if (!sat) return 15;
         rgs_slab_sat_kernel<<<1, 1024, 0, st>>>(tile_done, cam->tiles_x, cam->tiles_y, sat);
-        rgs_slab_filtered_count_kernel<<<148 * 8, 256, 0, st>>>(order, rects, cnt, (uint32_t)cap_vis, (uint32_t)frac256,
+        rgs_slab_filtered_count_kernel<<<(unsigned)(RGS_SMS * 8), 256, 0, st>>>(order, rects, cnt, (uint32_t)cap_vis, (uint32_t)frac256,
                                                                (int)slab, sat, cam->tiles_x, slot_cnt);
     }
     rgs_slab_count_kernel<<<egrid, 256, 0, st>>>(order, slot_cnt, cnt, (uint32_t)cap_vis, (uint32_t)frac256, (int)slab, seg_sums);

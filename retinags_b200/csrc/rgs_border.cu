@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(256) rgs_border_mask_kernel(const float* __res
 
 static inline unsigned border_grid(int64_t n) {
     const int64_t want = (n * 15 + 255) / 256;
-    return (unsigned)(want < 1 ? 1 : (want > 148 * 16 ? 148 * 16 : want));
+    return (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 16 ? RGS_SMS * 16 : want));
 }
 
 extern "C" {
@@ -162,7 +162,7 @@ int rgs_cuda_border_mask(const float* xyz, const float* scale, int64_t n, const 
     if (M < 1 || M > RGS_MAX_BORDER_MODELS || self < 0 || self >= M) return 17;
     if (n <= 0) return 0;
     const int64_t want = (n + 255) / 256;
-    const unsigned blocks = (unsigned)(want > 148 * 32 ? 148 * 32 : want);
+    const unsigned blocks = (unsigned)(want > RGS_SMS * 32 ? RGS_SMS * 32 : want);
     rgs_border_mask_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(xyz, scale, n, boxes, (int)M, (int)self, (float)margin, masks);
     return (int)cudaGetLastError();
 }
@@ -176,7 +176,7 @@ int rgs_cuda_border_grad_push(const float* const* g, float* stat, uint8_t* touch
     rgs_border_grad_push_kernel<<<border_grid(n), 256, 0, (cudaStream_t)stream>>>(s, stat, touched, row0, n, rows, flags);
     if (touched) {
         const int64_t want = (n + 255) / 256;
-        rgs_border_clear_marks_kernel<<<(unsigned)(want > 148 * 8 ? 148 * 8 : want), 256, 0, (cudaStream_t)stream>>>(
+        rgs_border_clear_marks_kernel<<<(unsigned)(want > RGS_SMS * 8 ? RGS_SMS * 8 : want), 256, 0, (cudaStream_t)stream>>>(
             touched, stat, row0, n);
     }
     return (int)cudaGetLastError();
@@ -189,7 +189,7 @@ int rgs_cuda_border_grad_add(const float* rows, const uint8_t* flags, const int6
     rgs_border_grad_add_kernel<<<border_grid(n), 256, 0, (cudaStream_t)stream>>>(rows, flags, idx, n, d, stat, touched);
     if (touched) {
         const int64_t want = (n + 255) / 256;
-        rgs_border_mark_touched_kernel<<<(unsigned)(want > 148 * 8 ? 148 * 8 : want), 256, 0, (cudaStream_t)stream>>>(
+        rgs_border_mark_touched_kernel<<<(unsigned)(want > RGS_SMS * 8 ? RGS_SMS * 8 : want), 256, 0, (cudaStream_t)stream>>>(
             flags, idx, n, touched);
     }
     return (int)cudaGetLastError();

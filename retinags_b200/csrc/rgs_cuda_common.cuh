@@ -54,6 +54,20 @@ __device__ __forceinline__ uint32_t rgs_ld_acquire_sys(const uint32_t* p) {
     return v;
 }
 
+// Number of SMs of the current device, queried once per device: launch grids are sized as a multiple of it.
+static inline int64_t rgs_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+#define RGS_SMS rgs_sm_count()
+
 #define RGS_CUDA_CHECK(expr)                          \
     do {                                              \
         cudaError_t _e = (expr);                      \

@@ -387,7 +387,7 @@ int rgs_cuda_composite_fwd(const float* const* partials, int64_t K, const float*
     for (int k = 0; k < K; ++k) pp.p[k] = partials[k];
     const int64_t n = (row1 - row0) * W;
     const int64_t want = (n + 255) / 256;
-    const unsigned blocks = (unsigned)(want > 148 * 32 ? 148 * 32 : want);
+    const unsigned blocks = (unsigned)(want > RGS_SMS * 32 ? RGS_SMS * 32 : want);
     rgs_composite_fwd_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(pp, (int)K, bg[0], bg[1], bg[2], H, W, row0, row1,
                                                                       image, trans);
     return (int)cudaGetLastError();
@@ -402,7 +402,7 @@ int rgs_cuda_composite_bwd(const float* const* partials, float* const* grads, in
     for (int k = 0; k < K; ++k) { pp.p[k] = partials[k]; gp.p[k] = grads[k]; }
     const int64_t n = (row1 - row0) * W;
     const int64_t want = (n + 255) / 256;
-    const unsigned blocks = (unsigned)(want > 148 * 32 ? 148 * 32 : want);
+    const unsigned blocks = (unsigned)(want > RGS_SMS * 32 ? RGS_SMS * 32 : want);
     rgs_composite_bwd_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(pp, gp, (int)K, bg[0], bg[1], bg[2], H, W, row0,
                                                                       row1, g_image);
     return (int)cudaGetLastError();

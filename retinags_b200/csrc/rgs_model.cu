@@ -260,7 +260,7 @@ int rgs_cuda_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t
     const float bc2s = (float)(1.0 / sqrt(1.0 - pow(beta2, (double)step)));
     const int64_t tv = (count * 59 + 3) / 4 + 5;
     const int64_t want = (tv + 255) / 256;
-    const unsigned blocks = (unsigned)(want > 148 * 64 ? 148 * 64 : want);
+    const unsigned blocks = (unsigned)(want > RGS_SMS * 64 ? RGS_SMS * 64 : want);
     rgs_adam_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, count, cap, t, (float)beta1, (float)beta2,
                                                              (float)eps, bc1, bc2s, (int)zero_grad,
                                                              reinterpret_cast<const uint32_t*>(skip), touched, active);
@@ -278,7 +278,7 @@ int rgs_cuda_adam_rows(float* p, float* g, float* m, float* v, int64_t count, in
     const float bc1 = (float)(1.0 / (1.0 - pow(beta1, (double)step)));
     const float bc2s = (float)(1.0 / sqrt(1.0 - pow(beta2, (double)step)));
     const int64_t want = ((count + 31) / 32 + 7) / 8;  // 8 warps per block, one 32-row block per warp and pass
-    const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > 148 * 64 ? 148 * 64 : want));
+    const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 64 ? RGS_SMS * 64 : want));
     rgs_adam_rows_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, count, cap, t, (float)beta1, (float)beta2,
                                                                   (float)eps, bc1, bc2s, (int)zero_grad,
                                                                   reinterpret_cast<const uint32_t*>(skip), touched, active);

@@ -79,7 +79,7 @@ int rgs_cuda_sort_ranges_noalloc(uint64_t* keys, uint32_t* vals, int64_t cap_pai
     while ((1ll << tile_bits) < num_tiles) ++tile_bits;
     const int npass = (32 + tile_bits + 7) / 8;
     const uint32_t need_chunks = (cap + SORT_CHUNK - 1) / SORT_CHUNK;
-    const unsigned grid = need_chunks < 1u ? 1u : (need_chunks < 148u * 8u ? need_chunks : 148u * 8u);
+    const unsigned grid = need_chunks < 1u ? 1u : (need_chunks < (unsigned)(RGS_SMS * 8) ? need_chunks : (unsigned)(RGS_SMS * 8));
     const uint32_t* cnt = reinterpret_cast<const uint32_t*>(counters);
     uint64_t* kin = keys; uint32_t* vin = vals; uint64_t* kout = keys_tmp; uint32_t* vout = vals_tmp;
     for (int p = 0; p < npass; ++p) {
@@ -92,7 +92,7 @@ int rgs_cuda_sort_ranges_noalloc(uint64_t* keys, uint32_t* vals, int64_t cap_pai
     }
     RGS_CUDA_CHECK(cudaMemsetAsync(ranges, 0, (size_t)num_tiles * 8, st));
     const bool in_tmp = (vin != vals);
-    rgs_tile_ranges_kernel<<<148 * 8, 256, 0, st>>>(kin, cnt, cap, reinterpret_cast<int2*>(ranges), (uint32_t)num_tiles,
+    rgs_tile_ranges_kernel<<<(unsigned)(RGS_SMS * 8), 256, 0, st>>>(kin, cnt, cap, reinterpret_cast<int2*>(ranges), (uint32_t)num_tiles,
                                                     in_tmp ? vin : nullptr, in_tmp ? vals : nullptr);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess)

@@ -666,7 +666,7 @@ int rgs_cuda_blend_bwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const
         reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters),
         reinterpret_cast<unsigned long long*>(fixed_acc), slab);
     const int64_t want = (cap_vis * 9 + 255) / 256;
-    const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > 148 * 32 ? 148 * 32 : want));
+    const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 32 ? RGS_SMS * 32 : want));
     rgs_fixed_fold_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<long long*>(fixed_acc), cap_vis,
                                                                    reinterpret_cast<const uint32_t*>(counters), splat_grads);
     return (int)cudaGetLastError();
@@ -684,7 +684,7 @@ int rgs_cuda_blend_bwd_fixed(const RgsCamera* cam, const int32_t* ranges, const 
         reinterpret_cast<const float4*>(grad_out), splat_grads, reinterpret_cast<uint32_t*>(counters),
         reinterpret_cast<unsigned long long*>(fixed_acc), RgsSlabArgs{nullptr, nullptr, 0u, RGS_SLAB_SINGLE, nullptr});
     const int64_t want = (cap_vis * 9 + 255) / 256;
-    const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > 148 * 32 ? 148 * 32 : want));
+    const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 32 ? RGS_SMS * 32 : want));
     rgs_fixed_fold_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<long long*>(fixed_acc), cap_vis,
                                                                    reinterpret_cast<const uint32_t*>(counters), splat_grads);
     return (int)cudaGetLastError();
@@ -699,7 +699,7 @@ int rgs_cuda_geom_bwd(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg
     s.n = (int)nseg;
     for (int k = 0; k < (int)nseg; ++k) s.s[k] = segs[k];
     const int64_t want = (cap_vis + 127) / 128;
-    const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > 148 * 16 ? 148 * 16 : want));
+    const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 16 ? RGS_SMS * 16 : want));
     rgs_geom_bwd_kernel<<<blocks, 128, 0, (cudaStream_t)stream>>>(*cam, s, reinterpret_cast<const uint32_t*>(counters),
                                                                  vis_ids, aux, splat_grads);
     return (int)cudaGetLastError();
@@ -707,7 +707,7 @@ int rgs_cuda_geom_bwd(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg
 
 int rgs_cuda_scatter_radii(const int32_t* counters, const int32_t* vis_ids, const uint32_t* aux, int64_t id_base,
                            int64_t count, int32_t* radii, void* stream) {
-    rgs_scatter_radii_kernel<<<148 * 4, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const uint32_t*>(counters),
+    rgs_scatter_radii_kernel<<<(unsigned)(RGS_SMS * 4), 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<const uint32_t*>(counters),
                                                                          vis_ids, aux, id_base, count, radii);
     return (int)cudaGetLastError();
 }

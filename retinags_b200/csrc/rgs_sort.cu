@@ -209,7 +209,7 @@ int rgs_cuda_sort_ranges(uint64_t* keys, uint32_t* vals, uint64_t* keys_tmp, uin
     while ((1ll << tile_bits) < num_tiles) ++tile_bits;
     const int end_bit = 32 + tile_bits;
     const int npass = (end_bit + 7) / 8;
-    const unsigned grid = nchunks_cap < 148u * 8u ? nchunks_cap : 148u * 8u;
+    const unsigned grid = nchunks_cap < (unsigned)(RGS_SMS * 8) ? nchunks_cap : (unsigned)(RGS_SMS * 8);
     const uint32_t* cnt = reinterpret_cast<const uint32_t*>(counters);
     uint64_t* kin = keys; uint32_t* vin = vals; uint64_t* kout = keys_tmp; uint32_t* vout = vals_tmp;
     for (int p = 0; p < npass; ++p) {
@@ -222,7 +222,7 @@ int rgs_cuda_sort_ranges(uint64_t* keys, uint32_t* vals, uint64_t* keys_tmp, uin
     }
     RGS_CUDA_CHECK(cudaMemsetAsync(ranges, 0, (size_t)num_tiles * 8, st));
     const bool in_tmp = (vin != vals);
-    rgs_tile_ranges_kernel<<<148 * 8, 256, 0, st>>>(kin, cnt, cap, reinterpret_cast<int2*>(ranges), (uint32_t)num_tiles,
+    rgs_tile_ranges_kernel<<<(unsigned)(RGS_SMS * 8), 256, 0, st>>>(kin, cnt, cap, reinterpret_cast<int2*>(ranges), (uint32_t)num_tiles,
                                                     in_tmp ? vin : nullptr, in_tmp ? vals : nullptr);
     return (int)cudaGetLastError();
 }

@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(256) rgs_records_unpack_kernel(const float* __
 
 static inline unsigned surgery_grid(int64_t work, int per_block) {
     const int64_t want = (work + per_block - 1) / per_block;
-    return (unsigned)(want < 1 ? 1 : (want > 148 * 16 ? 148 * 16 : want));
+    return (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 16 ? RGS_SMS * 16 : want));
 }
 
 extern "C" {
