@@ -53,6 +53,8 @@ def parse_args():
     ap.add_argument("--train-views", type=int, default=40)
     ap.add_argument("--eval-frames", type=int, default=20)
     ap.add_argument("--epochs", type=int, default=8)
+    ap.add_argument("--no-spatial-sort", action="store_true", help="keep the Gaussians in generation order (default: rows "
+                    "are sorted along a Morton curve, the trainer's default as well)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--phases", action="store_true", help="also time the phases of a step (extra loop, after the timed one)")
     ap.add_argument("--task-times", default="", help="with --phases: write the per-(camera, sub-model) render times of every "
@@ -146,7 +148,8 @@ def run_own(args):
     sess = BenchSession(device=device, rank=rank, world=world, n_gaussians=args.gaussians, width=args.width,
                         height=args.height, batch=args.batch, n_views=(args.steps + args.warmup) * args.batch,
                         gt_gaussians=args.gt_gaussians, transport=args.transport, seed=args.seed,
-                        borrow_refresh=args.borrow_refresh, bvh_depth=args.bvh_depth)
+                        borrow_refresh=args.borrow_refresh, bvh_depth=args.bvh_depth,
+                        spatial_sort=not args.no_spatial_sort)
     # ---- device-timed region ------------------------------------------------------------------
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -257,7 +260,8 @@ def run_own(args):
                        "tile_instances_per_step_rank0": sess.last_info.get("n_inst"),
                        "rows_with_adam_moments_rank0": live_rows, "overflow_in_timed_region": overflow,
                        "two_slab_forward": os.environ.get("RGS_SLABS", "1") == "1",
-                       "occlusion_culling_between_submodels": bool(sess.engine.occlusion)},
+                       "occlusion_culling_between_submodels": bool(sess.engine.occlusion),
+                       "rows_in_morton_order": not args.no_spatial_sort},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "render": render,
             "phases_ms_per_step_max_over_ranks": phases,
             "roofline_rank0_of_measured": roofline,

@@ -86,7 +86,7 @@ class BenchSession:
     def __init__(self, device, rank: int, world: int, n_gaussians: int, width: int, height: int, batch: int,
                  n_views: int, gt_gaussians: int, transport: str = "auto", seed: int = 0, sh_degree: int = 3,
                  grid=(2048, 2048, 1), bvh_depth: int | None = None, scene_kind: str = "cluster",
-                 borrow: bool = True, borrow_refresh: int = 1, group=None):
+                 borrow: bool = True, borrow_refresh: int = 1, group=None, spatial_sort: bool = True):
         self.device = torch.device(device)
         self.rank, self.world, self.batch = rank, world, batch
         self.sh_degree = sh_degree
@@ -121,6 +121,9 @@ class BenchSession:
                 if sel.numel():
                     self.stores[m].append_new({name: v[sel] for name, v in g.items()})
             del g, ids
+        if spatial_sort:  # rows along a space-filling curve: the visible rows of a view lie close together in memory
+            for st in self.stores.values():
+                st.spatial_sort()
         torch.cuda.empty_cache() if self.device.type == "cuda" else None
         # ---- cameras, relation, ground truth -----------------------------------------------------
         if scene_kind == "cluster":

@@ -155,6 +155,9 @@ def add_trainer_flags(parser: ArgumentParser):
     p.add_argument("--OCCLUSION_CULLING", type=int, default=-1, choices=[-1, 0, 1],
                    help="skip tiles that nearer sub-models have finished (maps exchanged once per step); -1: the default "
                         "of the build (RGS_OCCLUSION)")
+    p.add_argument("--SPATIAL_SORT", type=int, default=1, choices=[0, 1],
+                   help="keep the rows of every sub-model in Morton order of their positions (re-sorted after load, "
+                        "densification and repartition)")
     p.add_argument("--MODEL_ASSIGNMENT", default="round_robin", choices=["round_robin", "cost"],
                    help="sub-model -> rank map: i %% world as the reference, or balanced by the estimated render cost over "
                         "the training cameras")

@@ -254,6 +254,35 @@ class GaussianStore:
             s[:n] = s[idx]
         self.count = n
 
+    def spatial_sort(self, bits: int = 16) -> torch.Tensor | None:
+        """Reorder the rows along a Morton (Z-order) curve through their positions, in all buffers and statistics.
+
+        A camera sees a compact region of space, and the render kernels fetch the rows of the visible Gaussians (236
+        bytes each, from five column groups): with rows in the order of a space-filling curve those fetches fall into
+        a few contiguous stretches of each group instead of being spread evenly over gigabytes. The reference keeps
+        the order of the input file (``scene/gaussian_nn_module.py:134-174``). Call between steps only (it drops the
+        gradients of the step like any other surgery); returns the permutation that was applied."""
+        n = self.count
+        if n < 2:
+            return None
+        xyz = self.views()["xyz"]
+        lo, hi = xyz.min(0).values, xyz.max(0).values
+        q = ((xyz - lo) / (hi - lo).clamp_min(1e-12) * ((1 << bits) - 1)).round().clamp_(0, (1 << bits) - 1).to(torch.int64)
+
+        def spread(v):  # bit k of a 21-bit value -> bit 3k
+            v = (v | (v << 32)) & 0x1F00000000FFFF
+            v = (v | (v << 16)) & 0x1F0000FF0000FF
+            v = (v | (v << 8)) & 0x100F00F00F00F00F
+            v = (v | (v << 4)) & 0x10C30C30C30C30C3
+            v = (v | (v << 2)) & 0x1249249249249249
+            return v
+
+        key = spread(q[:, 0]) | (spread(q[:, 1]) << 1) | (spread(q[:, 2]) << 2)
+        perm = torch.argsort(key, stable=True)
+        del key, q
+        self.keep(perm)
+        return perm
+
     def adopt(self, params: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, cap: int, count: int,
               with_moments: int = 0):
         """Take over freshly written buffers of ``cap`` rows (the output of the compaction kernels): gradients and

@@ -215,6 +215,7 @@ class Trainer:
                 sel = (ids == m).nonzero(as_tuple=True)[0]
                 self.stores[m] = self._create_from_points(p[sel], c[sel], lo[m], hi[m], m)
         active = min(self.sh_degree, self.iteration // 1000) if self.load_iteration > 0 else 0
+        self._spatial_sort()
         for st in self.stores.values():
             st.active_sh_degree = active
         self.logger.info("sub-models %s on rank %d: %s", self.local_ids, self.rank, {m: s.count for m, s in self.stores.items()})
@@ -278,6 +279,11 @@ class Trainer:
                     sel = (ids == m).nonzero(as_tuple=True)[0]
                     if sel.numel():
                         self.stores[m].append_new({k: v[sel].to(self.device) for k, v in g.items()})
+
+    def _spatial_sort(self):
+        if getattr(self.args, "SPATIAL_SORT", 1):
+            for st in self.stores.values():
+                st.spatial_sort()
 
     def _create_from_points(self, pts: torch.Tensor, rgb: torch.Tensor, lo, hi, mid: int) -> GaussianStore:
         """3DGS initialisation per sub-model (``scene/gaussian_nn_module.py:403-427``): SH DC from the point
@@ -509,6 +515,7 @@ class Trainer:
             if self.border is not None:
                 self.border.invalidate()  # every opacity changed: the lent copies are stale
         if changed:
+            self._spatial_sort()  # children were appended at the end: restore the memory locality of the rows
             for st in self.stores.values():
                 st.zero_grad()  # rows moved: gradients of this step are dropped, like the reference's rebuilt optimiser
             if self.border is not None:
@@ -668,6 +675,7 @@ class Trainer:
         from .parallel.migrate import migrate
         self.stores = migrate(old, self.tree, lo, hi, self.model2rank, self.rank, self.world, self.device, self.sh_degree,
                               self.group)
+        self._spatial_sort()
         for st in self.stores.values():
             st.active_sh_degree = min(self.sh_degree, self.iteration // 1000)
         self._close_engine()  # the old exchange regions are unmapped before new ones are created
