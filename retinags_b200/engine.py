@@ -63,7 +63,7 @@ class StepEngine:
             self.transport.attach_skip(self._skip)
         self.dropped_steps = 0
         # occlusion culling between sub-models in the training forward (render_partials_occluded)
-        self.occlusion = os.environ.get("RGS_OCCLUSION", "0") == "1"
+        self.occlusion = os.environ.get("RGS_OCCLUSION", "1") == "1"
         self._occl: dict = {}
         self._tasks: dict = {}
         self._grads: dict = {}

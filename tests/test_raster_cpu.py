@@ -223,6 +223,7 @@ def test_training_steps_are_identical_with_two_slabs(monkeypatch):
     def run(slabs):
         monkeypatch.setenv("RGS_SLABS", "1" if slabs else "0")
         monkeypatch.setenv("RGS_SLAB_FRACTION", "64")
+        monkeypatch.setenv("RGS_OCCLUSION", "0")  # culling between the two sub-models is not bit-neutral: tested elsewhere
         sess = BenchSession("cpu", 0, 1, 30000, 160, 112, batch=2, n_views=4, gt_gaussians=3000, seed=3, sh_degree=2,
                             grid=(32, 32, 1), bvh_depth=1, scene_kind="uniform")
         for st in sess.stores.values():
