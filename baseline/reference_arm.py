@@ -360,7 +360,9 @@ def _eval_from_logs(model_dir: str, world: int, run_log: str) -> dict:
     if m:
         out.update(samples=float(m.group(1)), l1=float(m.group(2)), psnr=float(m.group(3)), ssim=float(m.group(4)))
     stamps = []
-    for fn in glob.glob(os.path.join(model_dir, "rank_*", "rank_*.txt")):
+    # the per-rank log file sits beside the TensorBoard records when --logdir is given, else in the model folder
+    for fn in glob.glob(os.path.join(model_dir, "rank_*", "rank_*.txt")) + \
+            glob.glob(os.path.join(os.path.dirname(model_dir), "tb", "rank_*", "rank_*.txt")):
         for line in open(fn, errors="replace"):
             if "test, image " in line:
                 try:

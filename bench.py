@@ -44,17 +44,24 @@ def parse_args():
                          "RGS_SLAB_FRACTION=N; default 32); 0 renders in one pass")
     ap.add_argument("--occlusion", type=int, default=None, choices=[0, 1],
                     help="occlusion culling between sub-models (finished-tile maps exchanged once per step)")
-    ap.add_argument("--mode", default="train", choices=["train", "eval", "train-psnr", "trainer"],
+    ap.add_argument("--mode", default="train", choices=["train", "eval", "train-psnr", "trainer", "push", "city"],
                     help="train: the headline (training views/s of the step engine on an in-memory scene). The other modes "
                          "run the public trainer of either arm on one scene on disk (PNG targets, the initial model as a "
                          "PLY file): eval = eval render of --eval-frames test views (ms/frame, PSNR/SSIM/L1); train-psnr = "
                          "--epochs epochs over --train-views views, then that eval; trainer = views/s of Trainer.train(), "
-                         "image decoding included (own arm only)")
+                         "image decoding included (own arm only); push = the blend kernel with and without its fused "
+                         "stores into the peers' compositing slots, against the NVLink roofline (own arm, >= 2 GPUs); "
+                         "city = train steps on --scene, then one densification and one repartition with migration "
+                         "(time, Gaussians moved, peak memory per rank)")
+    ap.add_argument("--scene", default="cluster", choices=["cluster", "aerial"],
+                    help="synthetic scene: the 64-cluster mixture of the headline, or the aerial city scene (ground plane "
+                         "2000 x 2000 units + building-like vertical clusters, downward-tilted grid cameras)")
     ap.add_argument("--train-views", type=int, default=40)
     ap.add_argument("--eval-frames", type=int, default=20)
     ap.add_argument("--epochs", type=int, default=8)
     ap.add_argument("--no-spatial-sort", action="store_true", help="keep the Gaussians in generation order (default: rows "
                     "are sorted along a Morton curve, the trainer's default as well)")
+    ap.add_argument("--densify-threshold", type=float, default=2e-4, help="--mode city: screen-gradient threshold")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--phases", action="store_true", help="also time the phases of a step (extra loop, after the timed one)")
     ap.add_argument("--task-times", default="", help="with --phases: write the per-(camera, sub-model) render times of every "
@@ -149,7 +156,7 @@ def run_own(args):
                         height=args.height, batch=args.batch, n_views=(args.steps + args.warmup) * args.batch,
                         gt_gaussians=args.gt_gaussians, transport=args.transport, seed=args.seed,
                         borrow_refresh=args.borrow_refresh, bvh_depth=args.bvh_depth,
-                        spatial_sort=not args.no_spatial_sort)
+                        spatial_sort=not args.no_spatial_sort, scene_kind=args.scene)
     # ---- device-timed region ------------------------------------------------------------------
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -196,6 +203,41 @@ def run_own(args):
         wall = float(tw.item())
         e2e = {"value": args.steps * args.batch / wall, "unit": "views/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "last_loss": loss}
+    city = None
+    if args.mode == "city":
+        import resource
+
+        def timed(fn):
+            sess.barrier(); torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            res = fn()
+            torch.cuda.synchronize(); sess.barrier()
+            dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=device)
+            if world > 1:
+                dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+            return res, float(dt)
+
+        before = sum(st.count for st in sess.stores.values())
+        info, t_dens = timed(lambda: sess.densify(args.densify_threshold))
+        grown = sum(st.count for st in sess.stores.values())
+        rep, t_rep = timed(sess.repartition)
+        for i in range(2):  # the new partition trains
+            sess.step(args.warmup + i)
+        after_overflow = sess.settle()
+        cnt = torch.tensor([before, grown, rep["moved"], rep["after"]], dtype=torch.float64, device=device)
+        mem = torch.tensor([torch.cuda.max_memory_allocated(device) / 2 ** 30,
+                            resource.getrusage(resource.RUSAGE_SELF).ru_maxrss / 2 ** 20], dtype=torch.float64, device=device)
+        mems = [torch.zeros_like(mem) for _ in range(world)]
+        if world > 1:
+            dist.all_reduce(cnt)
+            dist.all_gather(mems, mem)
+        else:
+            mems = [mem]
+        city = {"gaussians_before": int(cnt[0]), "after_densify": int(cnt[1]), "moved_by_repartition": int(cnt[2]),
+                "after_repartition": int(cnt[3]), "densify_s": round(t_dens, 3), "repartition_s": round(t_rep, 3),
+                "peak_device_gib_per_rank": [round(float(m[0]), 2) for m in mems],
+                "peak_host_rss_gib_per_rank": [round(float(m[1]), 2) for m in mems],
+                "trains_after_repartition": not after_overflow}
     # ---- eval render: composited frames through the engine's render path (the one Trainer.eval() uses) ------------
     frames = min(args.eval_frames, len(sess.cams))
     for i in range(min(2, frames)):
@@ -250,7 +292,9 @@ def run_own(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
             "impl": "own",
-            "config": {"model": "3DGS SH-3, seeded 64-cluster mixture in a 20-unit box", "gaussians": args.gaussians,
+            "config": {"model": "3DGS SH-3, seeded 64-cluster mixture in a 20-unit box" if args.scene == "cluster" else
+                       "3DGS SH-3, seeded aerial city scene (2000 x 2000 ground plane + building clusters)",
+                       "gaussians": args.gaussians,
                        "global_batch": args.batch, "resolution": [args.width, args.height],
                        "submodels": sess.n_models, "bvh_depth": sess.bvh_depth,
                        "parallelism": f"spatial-mp{world}", "transport": sess.transport_name,
@@ -262,7 +306,7 @@ def run_own(args):
                        "two_slab_forward": os.environ.get("RGS_SLABS", "1") == "1",
                        "occlusion_culling_between_submodels": bool(sess.engine.occlusion),
                        "rows_in_morton_order": not args.no_spatial_sort},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "render": render,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "render": render, "city": city,
             "phases_ms_per_step_max_over_ranks": phases,
             "roofline_rank0_of_measured": roofline,
         }
@@ -379,6 +423,94 @@ def run_own_trainer(args):
         dist.destroy_process_group()
 
 
+def run_push(args):
+    """Isolates the fused push of the blend epilogue: every rank renders its sub-model for one view and then repeats
+    the blend kernel alone, first without destinations, then storing every row into the slot of the rank that owns it
+    (peer-mapped memory), all ranks at the same time. Roofline of the fused kernel: the slower of the blend itself and
+    the bytes that must leave this GPU over NVLink at the measured peer-copy bandwidth (770 GB/s per direction)."""
+    import torch
+    import torch.distributed as dist
+
+    from retinags_b200.bench_session import BenchSession
+    from retinags_b200.ops import native
+    from retinags_b200.ops.rasterize import make_camera
+
+    world, rank, local_rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise SystemExit("--mode push needs >= 2 ranks (torch.distributed.run --nproc-per-node N)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=device)
+    os.environ["RGS_SLABS"] = "0"  # one blend launch per render: the same launch is repeated with and without the push
+    sess = BenchSession(device=device, rank=rank, world=world, n_gaussians=args.gaussians, width=args.width, height=args.height,
+                        batch=1, n_views=2, gt_gaussians=min(args.gt_gaussians, 1_000_000), transport="peer", seed=args.seed,
+                        borrow_refresh=args.borrow_refresh, bvh_depth=args.bvh_depth)
+    eng, tr = sess.engine, sess.engine.transport
+    cams, rel = sess._batch(0)
+    plans = eng.plan(cams, rel)
+    eng._prepare_transport(plans)
+    if eng.borrow is not None:
+        eng.borrow.refresh(eng.stores, need_grads=False)
+    p, cam = plans[0], cams[0]
+    mine = [m for m, r in zip(p.models, p.ranks) if r == rank]
+    reps = max(20, args.steps)
+    rows = []
+    for m in mine[:1]:
+        st = eng.stores[m]
+        c = make_camera(cam, sess.sh_degree, st.box_lo, st.box_hi, raw_params=True, tight_rect=eng.tight_rect)
+        task = eng._task(p.view, m)
+        task.slabs = False
+        task.forward(c, eng._segments(m, False), check=True)
+        push = tr.push_plan(p, m)
+        remote_bytes = sum((e[1] - e[0]) * p.W * 16 for o, e in enumerate(tr._plan_ext(p)) if o != rank and e[1] > e[0])
+
+        def loop(with_push):
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                if with_push:
+                    native.call("blend_fwd_push", device, c, task.ranges, task.vals, task.splats, task.out, None, task.n_contrib,
+                                task.counters, push[0], push[1], push[2], push[3])
+                else:
+                    native.call("blend_fwd", device, c, task.ranges, task.vals, task.splats, task.out, None, task.n_contrib,
+                                task.counters)
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / reps
+
+        for _ in range(3):
+            loop(True)
+        t0, t1 = loop(False), loop(True)
+        rows.append((t0, t1, remote_bytes))
+    tr._signal_wait()
+    torch.cuda.synchronize()
+    tr.check()
+    t0, t1, nbytes = rows[0] if rows else (0.0, 0.0, 0)
+    stat = torch.tensor([t0, t1, float(nbytes)], dtype=torch.float64, device=device)
+    allst = [torch.zeros_like(stat) for _ in range(world)]
+    dist.all_gather(allst, stat)
+    if rank == 0:
+        per = [[float(x) for x in s_.tolist()] for s_ in allst]
+        link = 770e9
+        frac = [max(a, nb / link * 1e3) / b if b > 0 else None for a, b, nb in per]
+        out = {"impl": "own", "mode": "push", "n_gpus": world, "metric": "blend kernel with the fused push vs its roofline",
+               "unit": "fraction of roofline (min over ranks)", "value": min(f for f in frac if f is not None),
+               "higher_is_better": True, "repeats": reps, "resolution": [args.width, args.height],
+               "blend_ms_without_push": [round(a, 4) for a, _, _ in per], "blend_ms_with_push": [round(b, 4) for _, b, _ in per],
+               "remote_bytes_per_launch": [int(nb) for _, _, nb in per],
+               "link_ms_at_770GBs": [round(nb / link * 1e3, 4) for _, _, nb in per],
+               "fraction_of_roofline": [round(f, 3) if f is not None else None for f in frac],
+               "roofline": "max(blend without push, remote bytes / 770 GB/s measured peer copy) / blend with push",
+               "config": {"gaussians": args.gaussians, "submodels": sess.n_models}}
+        print(json.dumps(out), flush=True)
+    dist.barrier()
+    tr.close()
+    dist.destroy_process_group()
+
+
 def run_reference(args):
     from baseline import reference_arm
     reference_arm.main(args)
@@ -388,7 +520,9 @@ if __name__ == "__main__":
     a = parse_args()
     if a.impl == "reference":
         run_reference(a)
-    elif a.mode != "train":
+    elif a.mode == "push":
+        run_push(a)
+    elif a.mode not in ("train", "city"):
         run_own_trainer(a)
     else:
         run_own(a)

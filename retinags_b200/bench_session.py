@@ -82,6 +82,42 @@ class UniformScene:
         return synthetic.random_gaussians(n, self.means(n, chunk), self.seed * 104729 + chunk, self.device, sh_degree)
 
 
+class AerialScene:
+    """City-scale aerial scene in chunks: half of the Gaussians on a ground plane of ``box`` x ``box`` units (heights
+    exponentially distributed), half in seeded building-like vertical boxes; log-scales around exp(-1) unit."""
+
+    box = 2000.0
+    kind = "aerial"
+
+    def __init__(self, seed: int, device, n_buildings: int = 4096):
+        self.seed, self.device = seed, device
+        g = torch.Generator(device=device)
+        g.manual_seed(seed + 211)
+        self.bc = (torch.rand(n_buildings, 2, device=device, generator=g) - 0.5) * self.box
+        self.bh = 10.0 + 60.0 * torch.rand(n_buildings, device=device, generator=g)
+        self.bw = 5.0 + 20.0 * torch.rand(n_buildings, 2, device=device, generator=g)
+
+    def means(self, n: int, chunk: int) -> torch.Tensor:
+        g = torch.Generator(device=self.device)
+        g.manual_seed(self.seed * 7919 + 13 * chunk + 1)
+        dev = self.device
+        n_ground = n // 2
+        pts = torch.empty(n, 3, device=dev)
+        pts[:n_ground, :2] = (torch.rand(n_ground, 2, device=dev, generator=g) - 0.5) * self.box
+        pts[:n_ground, 2] = -3.0 * torch.log(torch.rand(n_ground, device=dev, generator=g).clamp_min(1e-6))
+        nb = n - n_ground
+        which = torch.randint(0, self.bc.shape[0], (nb,), device=dev, generator=g)
+        pts[n_ground:, :2] = self.bc[which] + (torch.rand(nb, 2, device=dev, generator=g) - 0.5) * self.bw[which]
+        pts[n_ground:, 2] = torch.rand(nb, device=dev, generator=g) * self.bh[which]
+        half = self.box / 2
+        pts[:, :2].clamp_(-half, half)
+        return pts
+
+    def gaussians(self, n: int, chunk: int, sh_degree: int = 3) -> dict:
+        return synthetic.random_gaussians(n, self.means(n, chunk), self.seed * 104729 + chunk, self.device, sh_degree,
+                                          log_scale_mean=-1.0)
+
+
 class BenchSession:
     def __init__(self, device, rank: int, world: int, n_gaussians: int, width: int, height: int, batch: int,
                  n_views: int, gt_gaussians: int, transport: str = "auto", seed: int = 0, sh_degree: int = 3,
@@ -92,7 +128,7 @@ class BenchSession:
         self.sh_degree = sh_degree
         self.bvh_depth = int(round(math.log2(world))) if bvh_depth is None else bvh_depth
         assert 2 ** self.bvh_depth >= world, "need at least one sub-model per rank"
-        make_scene = ClusterScene if scene_kind == "cluster" else UniformScene
+        make_scene = {"cluster": ClusterScene, "aerial": AerialScene}.get(scene_kind, UniformScene)
         self._make_scene = make_scene
         scene = make_scene(seed, self.device)
         # ---- partition from the load histogram of all positions -------------------------------
@@ -128,6 +164,8 @@ class BenchSession:
         # ---- cameras, relation, ground truth -----------------------------------------------------
         if scene_kind == "cluster":
             self.cams = synthetic.hemisphere_cameras(max(n_views, 1), 8.0, width, height, 50.0, seed)
+        elif scene_kind == "aerial":
+            self.cams = synthetic.aerial_cameras(max(n_views, 1), scene.box, width, height, 60.0, seed)
         else:
             self.cams = synthetic.ring_cameras(max(n_views, 1), 3.0, width, height, 60.0)
         self.relation = self.tree.relation(self.cams, 0.01, 1000.0)
@@ -163,7 +201,9 @@ class BenchSession:
                 self.border = BorderExchange(lo, hi, self.model2rank, rank, world, self.device, group, borrow_refresh)
         self.borrow_refresh = borrow_refresh
         self.engine = StepEngine(self.stores, self.model2rank, self.device, tr, borrow=self.border)
-        extent = 1.1 * 8.0
+        extent = 1.1 * 8.0 if scene_kind != "aerial" else 1.1 * 0.5 * scene.box
+        self.extent = extent
+        self.group = group
         self.lrs = (1.6e-4 * extent, 2.5e-3, 2.5e-3 / 20.0, 5e-3, 1e-3, 5e-2)
         self.last_info: dict = {}
         self._launch_base = 0
@@ -214,6 +254,60 @@ class BenchSession:
             if b[1] > b[0]:
                 h2d += 3 * (min(p.H, b[1] + 5) - max(0, b[0] - 5)) * p.W * 4
         return loss, h2d, int(sums.numel() * 8)
+
+    # -- model surgery at scale (what the trainer does every densification interval / repartition epoch) ------------
+    def densify(self, grad_threshold: float = 2e-4) -> dict:
+        """Clone / split / prune every local sub-model from the statistics gathered by the steps so far."""
+        from .models import densify as dz
+        info = {}
+        for m, st in self.stores.items():
+            info[m] = dz.densify_and_prune(st, grad_threshold, 0.005, self.extent, None, 0.01, None, False, False, False,
+                                           None, seed=1234 + m)
+            st.zero_grad()
+        if self.border is not None:
+            self.border.invalidate()
+        return info
+
+    def repartition(self) -> dict:
+        """Rebuild the kd-tree from the current load and move every Gaussian (parameters + Adam moments) to the sub-model
+        whose new box holds it; returns counts and the engine is rebuilt on the new stores."""
+        from .parallel.migrate import migrate
+        grid = self.tree.grid
+        hist = torch.zeros(grid.grid_size, dtype=torch.float32, device=self.device)
+        for st in self.stores.values():
+            if st.count:
+                hist += load_histogram(st.xyz, grid)
+        if self.world > 1:
+            dist.all_reduce(hist, group=self.group)
+        grid.load = hist.double().cpu().numpy()
+        new_tree = BvhTree.build(grid, self.bvh_depth, (0, 1), previous=self.tree, rng=np.random.default_rng(7))
+        lo, hi = new_tree.leaf_boxes_world(open_border=True)
+        moved = sum(int((new_tree.label(st.xyz) != m).sum()) for m, st in self.stores.items() if st.count)
+        before = sum(st.count for st in self.stores.values())
+        if self.border is not None and hasattr(self.border, "close"):
+            self.border.close()
+        if hasattr(self.engine.transport, "close"):
+            self.engine.transport.close()
+        self.stores = migrate(self.stores, new_tree, lo, hi, self.model2rank, self.rank, self.world, self.device,
+                              self.sh_degree, self.group)
+        self.tree = new_tree
+        for st in self.stores.values():
+            st.active_sh_degree = self.sh_degree
+            st.spatial_sort()
+        self.relation = self.tree.relation(self.cams, 0.01, 1000.0)
+        tr = self.engine.transport.__class__(self.device, self.group) if self.world > 1 else LocalTransport(self.device)
+        self.border = None
+        if self.n_models > 1 and self.engine.borrow is not None:
+            if hasattr(tr, "push_plan"):
+                from .parallel.peer_border import PeerBorderExchange
+                self.border = PeerBorderExchange(lo, hi, self.model2rank, self.rank, self.world, self.device, tr, self.group,
+                                                 self.borrow_refresh)
+            else:
+                from .parallel.border import BorderExchange
+                self.border = BorderExchange(lo, hi, self.model2rank, self.rank, self.world, self.device, self.group,
+                                             self.borrow_refresh)
+        self.engine = StepEngine(self.stores, self.model2rank, self.device, tr, borrow=self.border)
+        return dict(moved=moved, before=before, after=sum(st.count for st in self.stores.values()))
 
     def settle(self) -> bool:
         """Synchronise and let every render task look at its counters (grows buffers after an overflow)."""

@@ -65,6 +65,9 @@ class StepEngine:
         # occlusion culling between sub-models in the training forward (render_partials_occluded)
         self.occlusion = os.environ.get("RGS_OCCLUSION", "1") == "1"
         self._occl: dict = {}
+        self._copy_stream = None
+        self._gt_event = None
+        self._gt_ready: dict = {}
         self._tasks: dict = {}
         self._grads: dict = {}
         self._closs: dict = {}
@@ -100,6 +103,24 @@ class StepEngine:
             self._closs[view] = cl
         return cl
 
+    def _prefetch_gt(self, plans, cams):
+        """Start the host -> device copies of this step's ground-truth rows on a copy stream of their own, so that they
+        run under the rendering kernels; ``_gt_rows`` then only makes the compute stream wait for them."""
+        if self.device.type != "cuda":
+            return
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(self.device)
+        cur = torch.cuda.current_stream(self.device)
+        self._copy_stream.wait_stream(cur)  # the previous step's loss kernels have read the buffers
+        with torch.cuda.stream(self._copy_stream):
+            for p, cam in zip(plans, cams):
+                b = p.bands[self.rank]
+                if b[1] > b[0]:
+                    self._gt_rows(p.view, cam, (max(0, b[0] - 5), min(p.H, b[1] + 5)))
+                    self._gt_ready[p.view] = (cam.uid, b)
+        self._gt_event = torch.cuda.Event()
+        self._gt_event.record(self._copy_stream)
+
     def _gt_rows(self, view: int, cam: Camera, rows: tuple[int, int]) -> torch.Tensor:
         """Device (3,H,W) buffer with the ground truth uploaded on ``rows`` only (pinned host -> device)."""
         H, W = cam.height, cam.width
@@ -107,6 +128,12 @@ class StepEngine:
         if buf is None or buf.shape != (3, H, W):
             buf = torch.zeros(3, H, W, dtype=torch.float32, device=self.device)
             self._gt[view] = buf
+        if self._gt_event is not None and self._gt_ready.get(view) is not None and \
+                torch.cuda.current_stream(self.device) != self._copy_stream:
+            # uploaded ahead by _prefetch_gt: wait for the copy stream instead of copying again
+            self._gt_ready.pop(view)
+            torch.cuda.current_stream(self.device).wait_event(self._gt_event)
+            return buf
         if cam.image is not None and rows[1] > rows[0]:
             src = cam.image
             if src.device == buf.device:
@@ -231,8 +258,23 @@ class StepEngine:
         self._prepare_transport(plans)
         if self.borrow is not None:
             self.borrow.refresh(self.stores, need_grads=False)
-        local_out = self.render_partials(cams, plans, sh_degree, want_depth=want_depth, check=True)
-        slots = self.transport.exchange_partials(plans, local_out)
+        if self._use_occlusion(cams, plans) and not want_depth:
+            # the culled forward runs unchecked: all ranks look at the step's overflow word together (it travels with the
+            # exchange) and repeat the render with grown buffers when any render ran out of instance capacity
+            for attempt in range(8):
+                local_out = self.render_partials_occluded(cams, plans, sh_degree)
+                self._collect_overflow(plans)
+                slots = self.transport.exchange_partials(plans, local_out)
+                overflow = bool(int(self._skip[CNT_OVERFLOW].item()))
+                self.poll()
+                if not overflow:
+                    break
+                self.transport.barrier()
+            else:
+                raise RuntimeError("the instance buffers still overflow after 8 attempts to grow them")
+        else:
+            local_out = self.render_partials(cams, plans, sh_degree, want_depth=want_depth, check=True)
+            slots = self.transport.exchange_partials(plans, local_out)
         out = []
         for p in plans:
             cl = self._loss(p.view, p.H, p.W)
@@ -273,6 +315,7 @@ class StepEngine:
         T = self.timer.phase
         plans = self.plan(cams, relations)
         self._prepare_transport(plans)
+        self._prefetch_gt(plans, cams)
         if self.borrow is not None:
             with T("border_exchange"):
                 self.borrow.refresh(self.stores, need_grads=True)

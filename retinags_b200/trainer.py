@@ -579,14 +579,20 @@ class Trainer:
                     r0, r1 = out["rows"]
                     gt = self.engine._gt_rows(out["plan"].view, cam, (max(0, r0 - 5), min(cam.height, r1 + 5)))
                     # SSIM needs the composited neighbours: composite the halo rows as well
-                    sums = cl.stats(gt, r0, r1).clone() if r1 > r0 else torch.zeros(3, dtype=torch.float64, device=self.device)
+                    sums = torch.zeros(6, dtype=torch.float64, device=self.device)
+                    if r1 > r0:
+                        sums[:3] = cl.stats(gt, r0, r1)
+                        # squared error per colour channel: the reference's PSNR is the mean over the channels of the
+                        # per-channel PSNR (utils/image_utils.py:17-19), not the PSNR of the pooled error
+                        sums[3:] = ((out["image"][:, r0:r1] - gt[:, r0:r1]).double() ** 2).sum(dim=(1, 2))
                     if self.world > 1:
                         dist.all_reduce(sums, group=self.group)
                     npx = 3.0 * cam.height * cam.width
-                    l1, ssim, mse = (sums / npx).tolist()
-                    stat += torch.tensor([1.0, l1, psnr_from_mse(mse), ssim], dtype=torch.float64, device=self.device)
+                    l1, ssim, _ = (sums[:3] / npx).tolist()
+                    psnr = sum(psnr_from_mse(v) for v in (sums[3:] / (npx / 3.0)).tolist()) / 3.0
+                    stat += torch.tensor([1.0, l1, psnr, ssim], dtype=torch.float64, device=self.device)
                     self.eval_stamps.append((name, time.perf_counter()))  # the metrics were read back: the image is done
-                    self.logger.info("%s, image %s, psnr %f, ssim %f, l1 %f", name, cam.image_name, psnr_from_mse(mse), ssim, l1)
+                    self.logger.info("%s, image %s, psnr %f, ssim %f, l1 %f", name, cam.image_name, psnr, ssim, l1)
                     if self.tb and cam.uid < 1000 and cam.uid % 5 == 0:
                         # every fifth view, render and ground truth (trainer4tree_partition.py:731-733 of the reference)
                         self._tb_images(name, cam, out, gt)
