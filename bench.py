@@ -288,7 +288,9 @@ def run_own(args):
     if rank == 0:
         value = args.steps * args.batch / (ms / 1e3)
         out = {
-            "metric": "train views/s (62.9M GS, 1600x1036)", "value": value, "unit": "views/s", "n_gpus": world,
+            "metric": "train views/s (62.9M GS, 1600x1036)" if (args.gaussians, args.width, args.height, args.scene) ==
+            (62_900_000, 1600, 1036, "cluster") else f"train views/s ({args.gaussians / 1e6:.1f}M GS, {args.width}x{args.height})",
+            "value": value, "unit": "views/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
             "impl": "own",
