@@ -163,7 +163,9 @@ __global__ void __launch_bounds__(PC_THREADS, 6) rgs_project_cand_kernel(
     const __grid_constant__ RgsCamera cam, const __grid_constant__ RgsSegs4 segs, const uint32_t* __restrict__ cand,
     uint32_t cap_cand, RgsSplat* __restrict__ splats, int32_t* __restrict__ vis_ids, uint32_t* __restrict__ aux,
     const uint32_t cap_vis, uint32_t* __restrict__ slot_depth, uint2* __restrict__ slot_rect, uint32_t* __restrict__ slot_cnt,
-    uint32_t* __restrict__ counters, RgsSplatGrad* __restrict__ splat_grads) {
+    uint32_t* __restrict__ counters, RgsSplatGrad* __restrict__ splat_grads, const int lazy) {
+    // lazy: geometry only; the SH rows are neither fetched nor evaluated (rgs_colour_slab_kernel does that later for the
+    // splats that have tile instances)
     __shared__ __align__(128) float s_sh[PC_THREADS * PC_ROW];
     __shared__ unsigned long long bar;
     __shared__ uint32_t warp_vis[PC_THREADS / 32];
@@ -188,24 +190,26 @@ __global__ void __launch_bounds__(PC_THREADS, 6) rgs_project_cand_kernel(
         uint32_t gid = 0;
         float p[3] = {0.f, 0.f, 0.f}, s[3] = {0.f, 0.f, 0.f}, q[4] = {1.f, 0.f, 0.f, 0.f}, o = 0.f;
         rgs_fence_proxy_async();  // the rows read in the previous round may be overwritten now
-        if (threadIdx.x == 0) rgs_mbar_expect_tx(&bar, valid * 192u);
+        if (threadIdx.x == 0 && !lazy) rgs_mbar_expect_tx(&bar, valid * 192u);
         if (c < n) {
             gid = cand[c];
             int64_t i = gid;
             int sidx = 0;
             while (sidx < segs.n - 1 && i >= segs.s[sidx].count) { i -= segs.s[sidx].count; ++sidx; }
             const RgsSegment& seg = segs.s[sidx];
-            rgs_bulk_g2s(&s_sh[threadIdx.x * PC_ROW], seg.sh + 48 * i, 192u, &bar);
+            if (!lazy) rgs_bulk_g2s(&s_sh[threadIdx.x * PC_ROW], seg.sh + 48 * i, 192u, &bar);
             p[0] = seg.xyz[3 * i]; p[1] = seg.xyz[3 * i + 1]; p[2] = seg.xyz[3 * i + 2];
             s[0] = seg.scale[3 * i]; s[1] = seg.scale[3 * i + 1]; s[2] = seg.scale[3 * i + 2];
             const float4 q4 = reinterpret_cast<const float4*>(seg.rot)[i];
             q[0] = q4.x; q[1] = q4.y; q[2] = q4.z; q[3] = q4.w;
             o = seg.opacity[i];
         }
-        if (!rgs_mbar_wait(&bar, round & 1u, RGS_BIN_WAIT_LIMIT)) failed = true;
-        failed = __syncthreads_or(failed) != 0;
-        if (failed) break;  // a wait ran out: give up on the remaining candidates, the host reads the status word
-        if (c < n) ok = rgs_project(cam, p, s, q, o, &s_sh[threadIdx.x * PC_ROW], sp, rc, radius, clamped);
+        if (!lazy) {
+            if (!rgs_mbar_wait(&bar, round & 1u, RGS_BIN_WAIT_LIMIT)) failed = true;
+            failed = __syncthreads_or(failed) != 0;
+            if (failed) break;  // a wait ran out: give up on the remaining candidates, the host reads the status word
+        }
+        if (c < n) ok = rgs_project(cam, p, s, q, o, lazy ? nullptr : &s_sh[threadIdx.x * PC_ROW], sp, rc, radius, clamped);
         const uint32_t vmask = __ballot_sync(0xffffffffu, ok);
         if (lane == 0) warp_vis[wid] = __popc(vmask);
         __syncthreads();
@@ -648,6 +652,38 @@ __device__ __forceinline__ void slab_segments(uint32_t n, uint32_t frac256, int 
     s1 = slab == 0 ? split : nseg;
 }
 
+// Colours of the splats of one slab that have tile instances (slot_cnt != 0 after the filter): the SH rows (192 bytes
+// per Gaussian, by far the largest part of what the projection reads) are fetched for those alone. In a dense scene
+// most visible splats lie behind finished tiles and never get here.
+__global__ void __launch_bounds__(128) rgs_colour_slab_kernel(const __grid_constant__ RgsCamera cam,
+                                                              const __grid_constant__ RgsSegs4 segs,
+                                                              const uint32_t* __restrict__ order,
+                                                              const uint32_t* __restrict__ slot_cnt,
+                                                              const uint32_t* __restrict__ counters, uint32_t cap_vis,
+                                                              uint32_t frac256, int slab, RgsSplat* __restrict__ splats,
+                                                              const int32_t* __restrict__ vis_ids, uint32_t* __restrict__ aux) {
+    const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);
+    uint32_t s0, s1;
+    slab_segments(n, frac256, slab, s0, s1);
+    const uint32_t end = s1 * EM_SEG < n ? s1 * EM_SEG : n;
+    for (uint32_t i = s0 * EM_SEG + blockIdx.x * blockDim.x + threadIdx.x; i < end; i += gridDim.x * blockDim.x) {
+        const uint32_t slot = order[i];
+        if (slot_cnt[slot] == 0) continue;
+        int64_t id = vis_ids[slot];
+        int sidx = 0;
+        while (sidx < segs.n - 1 && id >= segs.s[sidx].count) { id -= segs.s[sidx].count; ++sidx; }
+        const RgsSegment& seg = segs.s[sidx];
+        if (id < 0 || id >= seg.count) continue;
+        const float p[3] = {seg.xyz[3 * id], seg.xyz[3 * id + 1], seg.xyz[3 * id + 2]};
+        float r, g, b;
+        unsigned clamped;
+        rgs_splat_colour(cam, p, seg.sh + 48 * id, r, g, b, clamped);
+        float* rec = reinterpret_cast<float*>(splats + slot);
+        rec[6] = r; rec[7] = g; rec[8] = b;
+        aux[slot] = (aux[slot] & ~7u) | clamped;
+    }
+}
+
 __global__ void __launch_bounds__(256) rgs_slab_count_kernel(const uint32_t* __restrict__ order,
                                                              const uint32_t* __restrict__ slot_cnt,
                                                              const uint32_t* __restrict__ counters, uint32_t cap_vis,
@@ -1069,10 +1105,10 @@ int rgs_cuda_project_slots(const RgsCamera* cam, const RgsSegment* seg, int64_t 
 
 // Two-phase variant of rgs_cuda_project_slots over up to 4 segments: cull all, then project the survivors.
 // `cand` holds cap_cand uint32 candidate ids (scratch owned by the caller).
-int rgs_cuda_project_slots2(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg, uint32_t* cand, int64_t cap_cand,
-                            RgsSplat* splats, int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint32_t* slot_depth,
-                            uint32_t* slot_rect, uint32_t* slot_cnt, int32_t* counters, RgsSplatGrad* splat_grads,
-                            void* stream) {
+static int project_slots2_impl(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg, uint32_t* cand, int64_t cap_cand,
+                               RgsSplat* splats, int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint32_t* slot_depth,
+                               uint32_t* slot_rect, uint32_t* slot_cnt, int32_t* counters, RgsSplatGrad* splat_grads,
+                               int lazy, void* stream) {
     if (nseg < 1 || nseg > 4) return 11;
     for (int k = 0; k < (int)nseg; ++k)  // SH rows are fetched as 16-byte aligned bulk copies
         if (segs[k].count > 0 && ((uintptr_t)segs[k].sh & 15u)) return 14;
@@ -1094,7 +1130,44 @@ int rgs_cuda_project_slots2(const RgsCamera* cam, const RgsSegment* segs, int64_
     const int64_t want = (cap_cand + PC_THREADS - 1) / PC_THREADS;
     const unsigned grid = (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 8 ? RGS_SMS * 8 : want));
     rgs_project_cand_kernel<<<grid, PC_THREADS, 0, st>>>(*cam, s4, cand, (uint32_t)cap_cand, splats, vis_ids, aux, (uint32_t)cap_vis,
-                                                  slot_depth, reinterpret_cast<uint2*>(slot_rect), slot_cnt, cnt, splat_grads);
+                                                  slot_depth, reinterpret_cast<uint2*>(slot_rect), slot_cnt, cnt, splat_grads,
+                                                  lazy);
+    return (int)cudaGetLastError();
+}
+
+int rgs_cuda_project_slots2(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg, uint32_t* cand, int64_t cap_cand,
+                            RgsSplat* splats, int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint32_t* slot_depth,
+                            uint32_t* slot_rect, uint32_t* slot_cnt, int32_t* counters, RgsSplatGrad* splat_grads,
+                            void* stream) {
+    return project_slots2_impl(cam, segs, nseg, cand, cap_cand, splats, vis_ids, aux, cap_vis, slot_depth, slot_rect, slot_cnt,
+                               counters, splat_grads, 0, stream);
+}
+
+// Geometry only (colours stay zero): rgs_cuda_colour_slab fills them in for the splats that get tile instances.
+int rgs_cuda_project_slots2_geom(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg, uint32_t* cand, int64_t cap_cand,
+                                 RgsSplat* splats, int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint32_t* slot_depth,
+                                 uint32_t* slot_rect, uint32_t* slot_cnt, int32_t* counters, RgsSplatGrad* splat_grads,
+                                 void* stream) {
+    return project_slots2_impl(cam, segs, nseg, cand, cap_cand, splats, vis_ids, aux, cap_vis, slot_depth, slot_rect, slot_cnt,
+                               counters, splat_grads, 1, stream);
+}
+
+// Colours of the splats of slab `slab` (the split of rgs_cuda_bin_slab) whose slot_cnt is not zero; call between the
+// slab's binning and its blend. `order`: the depth order left by the binning of slab 0.
+int rgs_cuda_colour_slab(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg, const uint32_t* order,
+                         const uint32_t* slot_cnt, const int32_t* counters, int64_t cap_vis, int64_t frac256, int64_t slab,
+                         RgsSplat* splats, const int32_t* vis_ids, uint32_t* aux, void* stream) {
+    if (nseg < 1 || nseg > 4 || slab < 0 || slab > 1) return 11;
+    for (int k = 0; k < (int)nseg; ++k)
+        if (segs[k].count > 0 && ((uintptr_t)segs[k].sh & 15u)) return 14;
+    RgsSegs4 s4;
+    s4.n = (int)nseg;
+    for (int k = 0; k < (int)nseg; ++k) s4.s[k] = segs[k];
+    const int64_t want = (cap_vis + 127) / 128;
+    const unsigned grid = (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 16 ? RGS_SMS * 16 : want));
+    rgs_colour_slab_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(*cam, s4, order, slot_cnt,
+                                                                  reinterpret_cast<const uint32_t*>(counters), (uint32_t)cap_vis,
+                                                                  (uint32_t)frac256, (int)slab, splats, vis_ids, aux);
     return (int)cudaGetLastError();
 }
 

@@ -62,7 +62,7 @@ int rgs_cpu_project_slots(const RgsCamera* cam, const RgsSegment* seg, int64_t i
     for (int64_t i = 0; i < seg->count; ++i) {
         RgsSplat sp; RgsRect rc; int radius; unsigned clamped;
         if (!rgs_project(*cam, seg->xyz + 3 * i, seg->scale + 3 * i, seg->rot + 4 * i, seg->opacity[i],
-                         seg->sh + 48 * i, sp, rc, radius, clamped))
+                         seg->sh ? seg->sh + 48 * i : nullptr, sp, rc, radius, clamped))
             continue;
         if (n_vis >= cap_vis) { counters[RGS_CNT_OVERFLOW] = 1; continue; }
         int64_t slot = n_vis++;
@@ -81,6 +81,49 @@ int rgs_cpu_project_slots(const RgsCamera* cam, const RgsSegment* seg, int64_t i
         if (splat_grads) std::memset(&splat_grads[slot], 0, sizeof(RgsSplatGrad));
     }
     counters[RGS_CNT_VIS] = (int32_t)n_vis;
+    return 0;
+}
+
+// Geometry-only variant of rgs_cpu_project_slots2: the colours are filled in later by rgs_cpu_colour_slab for the
+// splats that have tile instances.
+int rgs_cpu_project_slots2_geom(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg, uint32_t*, int64_t,
+                                RgsSplat* splats, int32_t* vis_ids, uint32_t* aux, int64_t cap_vis, uint32_t* slot_depth,
+                                uint32_t* slot_rect, uint32_t* slot_cnt, int32_t* counters, RgsSplatGrad* splat_grads,
+                                void* stream) {
+    int64_t base = 0;
+    for (int64_t k = 0; k < nseg; ++k) {
+        RgsSegment geo = segs[k];
+        geo.sh = nullptr;
+        rgs_cpu_project_slots(cam, &geo, base, splats, vis_ids, aux, cap_vis, slot_depth, slot_rect, slot_cnt, counters,
+                              splat_grads, stream);
+        base += segs[k].count;
+    }
+    return 0;
+}
+
+// Colours of the splats of one slab (depth-ordered positions, see rgs_cpu_bin_slab) whose instance count is not zero.
+int rgs_cpu_colour_slab(const RgsCamera* cam, const RgsSegment* segs, int64_t nseg, const uint32_t* order,
+                        const uint32_t* slot_cnt, const int32_t* counters, int64_t cap_vis, int64_t frac256, int64_t slab,
+                        RgsSplat* splats, const int32_t* vis_ids, uint32_t* aux, void*) {
+    if (counters[RGS_CNT_OVERFLOW]) return 0;
+    const int64_t n = std::min<int64_t>(counters[RGS_CNT_VIS], cap_vis);
+    const int64_t seg = 1024, nsegs = (n + seg - 1) / seg;
+    const int64_t split = std::min<int64_t>(nsegs, ((n * frac256) >> 8) / seg);
+    const int64_t i0 = (slab == 0 ? 0 : split) * seg, i1 = std::min<int64_t>(n, (slab == 0 ? split : nsegs) * seg);
+    for (int64_t i = i0; i < i1; ++i) {
+        const uint32_t s = order[i];
+        if (slot_cnt[s] == 0) continue;
+        int64_t id = vis_ids[s];
+        const RgsSegment* sg = nullptr;
+        for (int64_t k = 0; k < nseg; ++k) {
+            if (id < segs[k].count) { sg = &segs[k]; break; }
+            id -= segs[k].count;
+        }
+        if (!sg) continue;
+        unsigned clamped = 0;
+        rgs_splat_colour(*cam, sg->xyz + 3 * id, sg->sh + 48 * id, splats[s].r, splats[s].g, splats[s].b, clamped);
+        aux[s] = (aux[s] & ~7u) | clamped;
+    }
     return 0;
 }
 

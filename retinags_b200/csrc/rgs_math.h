@@ -244,8 +244,29 @@ RGS_HD void rgs_sh_load(const float* sh, int nc, float* out) {
 #endif
 }
 
+// View-dependent colour of one Gaussian from its SH coefficients (16 RGB triples, coefficient-major): the colour part
+// of the projection, also run on its own for the splats that turn out to have tile instances (rgs_colour_slab_kernel).
+// `clamped` receives 3 bits (colour channel was clamped at 0).
+RGS_HD void rgs_splat_colour(const RgsCamera& cam, const float* p, const float* sh, float& r, float& g, float& b,
+                             unsigned& clamped) {
+    float dx = p[0] - cam.campos[0], dy = p[1] - cam.campos[1], dz = p[2] - cam.campos[2];
+    float inv = 1.0f / sqrtf(dx * dx + dy * dy + dz * dz);
+    float B[16];
+    rgs_sh_basis(cam.sh_degree, dx * inv, dy * inv, dz * inv, B);
+    int nc = (cam.sh_degree + 1) * (cam.sh_degree + 1);
+    float c0 = 0.5f, c1 = 0.5f, c2 = 0.5f;
+    float shv[48];
+    rgs_sh_load(sh, nc, shv);
+    RGS_UNROLL
+    for (int k = 0; k < 16; ++k)
+        if (k < nc) { c0 += B[k] * shv[3 * k]; c1 += B[k] * shv[3 * k + 1]; c2 += B[k] * shv[3 * k + 2]; }
+    clamped = (c0 < 0.0f ? 1u : 0u) | (c1 < 0.0f ? 2u : 0u) | (c2 < 0.0f ? 4u : 0u);
+    r = fmaxf(c0, 0.0f); g = fmaxf(c1, 0.0f); b = fmaxf(c2, 0.0f);
+}
+
 // Forward projection of one Gaussian. Returns false when it is culled (near plane, singular
-// covariance, empty tile rectangle). `sh` points at 16 RGB triples (coefficient-major).
+// covariance, empty tile rectangle). `sh` points at 16 RGB triples (coefficient-major); with a null `sh` the colour
+// is left at zero for a later rgs_splat_colour (the geometry decides whether the splat is ever blended).
 // `clamped` receives 3 bits (colour channel was clamped at 0), `radius` the 3-sigma pixel radius.
 RGS_HD bool rgs_project(const RgsCamera& cam, const float* p, const float* s_in, const float* q_in, float o_in,
                         const float* sh, RgsSplat& out, RgsRect& rect, int& radius, unsigned& clamped) {
@@ -288,23 +309,11 @@ RGS_HD bool rgs_project(const RgsCamera& cam, const float* p, const float* s_in,
         rect.y0 = rgs_imax(rect.y0, ty0); rect.y1 = rgs_imin(rect.y1, ty1);
         if (rect.x1 <= rect.x0 || rect.y1 <= rect.y0) return false;
     }
-    // colour
-    float dx = p[0] - cam.campos[0], dy = p[1] - cam.campos[1], dz = p[2] - cam.campos[2];
-    float inv = 1.0f / sqrtf(dx * dx + dy * dy + dz * dz);
-    float B[16];
-    rgs_sh_basis(cam.sh_degree, dx * inv, dy * inv, dz * inv, B);
-    int nc = (cam.sh_degree + 1) * (cam.sh_degree + 1);
-    float c0 = 0.5f, c1 = 0.5f, c2 = 0.5f;
-    float shv[48];
-    rgs_sh_load(sh, nc, shv);
-    RGS_UNROLL
-    for (int k = 0; k < 16; ++k)
-        if (k < nc) { c0 += B[k] * shv[3 * k]; c1 += B[k] * shv[3 * k + 1]; c2 += B[k] * shv[3 * k + 2]; }
-    clamped = (c0 < 0.0f ? 1u : 0u) | (c1 < 0.0f ? 2u : 0u) | (c2 < 0.0f ? 4u : 0u);
+    out.r = 0.0f; out.g = 0.0f; out.b = 0.0f;
+    if (sh) rgs_splat_colour(cam, p, sh, out.r, out.g, out.b, clamped);
     out.px = px; out.py = py;
     out.ca = e.c * det_inv; out.cb = -e.b * det_inv; out.cc = e.a * det_inv;
     out.opacity = o;
-    out.r = fmaxf(c0, 0.0f); out.g = fmaxf(c1, 0.0f); out.b = fmaxf(c2, 0.0f);
     out.w = hw; out.depth = t[2];
     // alpha = o exp(power) < 1/255  <=>  power < -ln(255 o); slightly lowered so that the cheap test never rejects a
     // pair the exact test would keep

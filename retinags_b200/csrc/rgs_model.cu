@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(256) rgs_adam_kernel(float* __restrict__ p, fl
     }
 }
 
-// Row-block variant: a warp looks at the marks of 32 consecutive rows first (one byte pair per lane, one ballot) and
+// Row-block variant: a warp looks at the marks of a stretch of consecutive rows first (see the kernel) and
 // then works only on the rows that are live, two rows per pass (15 units of a row on 15 lanes of a half-warp:
 // 12 float4 of SH, the rotation, position, scale + opacity). A block of rows without a live row costs a few
 // instructions instead of fifteen unit tests per row, which is what bounds rgs_adam_kernel when few rows are live
@@ -210,38 +210,71 @@ __global__ void __launch_bounds__(256) rgs_adam_rows_kernel(float* __restrict__ 
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    const int64_t nblk = (count + 31) / 32;
-    for (int64_t blk = warp; blk < nblk; blk += nwarps) {
-        const int64_t r = blk * 32 + lane;
-        bool t = false, live = false;
-        if (r < count) {
-            t = touched ? touched[r] != 0 : true;
-            live = t || !touched || !active || active[r] != 0;  // without marks every row counts as live
-            if (t && touched && active) active[r] = 1;          // read again by no lane of this launch
-        }
-        uint32_t mask = __ballot_sync(0xffffffffu, live);
-        const uint32_t tmask = __ballot_sync(0xffffffffu, t);
-        const int half = lane >> 4, u = lane & 15;
-        while (mask) {
-            const int j0 = __ffs(mask) - 1;
-            mask &= mask - 1;
-            int j1 = -1;
-            if (mask) { j1 = __ffs(mask) - 1; mask &= mask - 1; }
-            const int jr = half ? j1 : j0;
-            if (jr < 0 || u >= 15) continue;
-            const int64_t row = blk * 32 + jr;
-            const bool tr = (tmask >> jr) & 1u;
-            if (u < 12) {
-                adam_quad<1>(p, g, m, v, o1 + row * 48 + u * 4, u * 4, tr, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad);
-            } else if (u == 12) {
-                adam_quad<3>(p, g, m, v, o3 + row * 4, 0, tr, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad);
-            } else if (u == 13) {
-                for (int c = 0; c < 3; ++c)
-                    adam_scalar(p, g, m, v, row * 3 + c, tr, lrs.lr[RGS_LR_XYZ], beta1, beta2, eps, bc1, bc2s, zero_grad);
+    // A warp looks at the marks of 512 consecutive rows per iteration: every lane fetches the 16 mark bytes of its 16
+    // rows with one 128-bit load per array, so that a stretch without a live row costs two wide loads per lane instead of
+    // sixteen dependent byte loads (with few live rows the kernel is bound by the latency of exactly these loads).
+    const int64_t nsuper = (count + 511) / 512;
+    const int half = lane >> 4, u = lane & 15;
+    for (int64_t sb = warp; sb < nsuper; sb += nwarps) {
+        const int64_t r0 = sb * 512 + (int64_t)lane * 16;
+        uint32_t tbits = 0, lbits = 0;  // bit k: row r0 + k was touched this step / has to be updated
+        if (r0 < count) {
+            uint32_t tw[4] = {0, 0, 0, 0}, aw[4] = {0, 0, 0, 0};
+            const bool wide = r0 + 16 <= cap;
+            if (wide) {
+                if (touched) { const uint4 q = *reinterpret_cast<const uint4*>(touched + r0); tw[0] = q.x; tw[1] = q.y; tw[2] = q.z; tw[3] = q.w; }
+                if (active) { const uint4 q = *reinterpret_cast<const uint4*>(active + r0); aw[0] = q.x; aw[1] = q.y; aw[2] = q.z; aw[3] = q.w; }
             } else {
-                for (int c = 0; c < 3; ++c)
-                    adam_scalar(p, g, m, v, o2 + row * 3 + c, tr, lrs.lr[RGS_LR_SCALE], beta1, beta2, eps, bc1, bc2s, zero_grad);
-                adam_scalar(p, g, m, v, o4 + row, tr, lrs.lr[RGS_LR_OPACITY], beta1, beta2, eps, bc1, bc2s, zero_grad);
+                for (int k = 0; k < 16 && r0 + k < cap; ++k) {
+                    if (touched) tw[k >> 2] |= (uint32_t)touched[r0 + k] << (8 * (k & 3));
+                    if (active) aw[k >> 2] |= (uint32_t)active[r0 + k] << (8 * (k & 3));
+                }
+            }
+            bool mark = false;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                if (r0 + k >= count) break;
+                const bool t = touched ? ((tw[k >> 2] >> (8 * (k & 3))) & 0xffu) != 0 : true;
+                const bool a = ((aw[k >> 2] >> (8 * (k & 3))) & 0xffu) != 0;
+                if (t) tbits |= 1u << k;
+                if (t || !touched || !active || a) lbits |= 1u << k;   // without marks every row counts as live
+                if (t && touched && active && !a) { aw[k >> 2] |= 1u << (8 * (k & 3)); mark = true; }
+            }
+            if (mark) {  // rows that received their first gradient carry moments from now on
+                if (wide) *reinterpret_cast<uint4*>(active + r0) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+                else for (int k = 0; k < 16 && r0 + k < cap; ++k) active[r0 + k] = (uint8_t)((aw[k >> 2] >> (8 * (k & 3))) & 0xffu);
+            }
+        }
+        uint32_t lanes = __ballot_sync(0xffffffffu, lbits != 0);
+        while (lanes) {
+            const int src = __ffs(lanes) - 1;
+            lanes &= lanes - 1;
+            uint32_t lb = __shfl_sync(0xffffffffu, lbits, src);
+            const uint32_t tb = __shfl_sync(0xffffffffu, tbits, src);
+            const int64_t base_row = sb * 512 + (int64_t)src * 16;
+            // two live rows per pass: the 15 units of a row on 15 lanes of a half-warp
+            // (12 float4 of SH, the rotation, position, scale + opacity)
+            while (lb) {
+                const int j0 = __ffs(lb) - 1;
+                lb &= lb - 1;
+                int j1 = -1;
+                if (lb) { j1 = __ffs(lb) - 1; lb &= lb - 1; }
+                const int jr = half ? j1 : j0;
+                if (jr < 0 || u >= 15) continue;
+                const int64_t row = base_row + jr;
+                const bool tr = (tb >> jr) & 1u;
+                if (u < 12) {
+                    adam_quad<1>(p, g, m, v, o1 + row * 48 + u * 4, u * 4, tr, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad);
+                } else if (u == 12) {
+                    adam_quad<3>(p, g, m, v, o3 + row * 4, 0, tr, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad);
+                } else if (u == 13) {
+                    for (int c = 0; c < 3; ++c)
+                        adam_scalar(p, g, m, v, row * 3 + c, tr, lrs.lr[RGS_LR_XYZ], beta1, beta2, eps, bc1, bc2s, zero_grad);
+                } else {
+                    for (int c = 0; c < 3; ++c)
+                        adam_scalar(p, g, m, v, o2 + row * 3 + c, tr, lrs.lr[RGS_LR_SCALE], beta1, beta2, eps, bc1, bc2s, zero_grad);
+                    adam_scalar(p, g, m, v, o4 + row, tr, lrs.lr[RGS_LR_OPACITY], beta1, beta2, eps, bc1, bc2s, zero_grad);
+                }
             }
         }
     }
@@ -277,7 +310,7 @@ int rgs_cuda_adam_rows(float* p, float* g, float* m, float* v, int64_t count, in
     for (int k = 0; k < 6; ++k) t.lr[k] = (float)lrs[k];
     const float bc1 = (float)(1.0 / (1.0 - pow(beta1, (double)step)));
     const float bc2s = (float)(1.0 / sqrt(1.0 - pow(beta2, (double)step)));
-    const int64_t want = ((count + 31) / 32 + 7) / 8;  // 8 warps per block, one 32-row block per warp and pass
+    const int64_t want = ((count + 511) / 512 + 7) / 8;  // 8 warps per block, 512 rows per warp and iteration
     const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 64 ? RGS_SMS * 64 : want));
     rgs_adam_rows_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, count, cap, t, (float)beta1, (float)beta2,
                                                                   (float)eps, bc1, bc2s, (int)zero_grad,

@@ -215,6 +215,7 @@ class RenderTask:
         self.ranges_b = self.tile_done = self.sat = None
         self._own_order = self._own_rect = None  # set by forward_near: depth order / tile rectangles kept by the task
         self._want_depth = False
+        self._seg_structs = None  # ctypes array of the segments of the current forward (kept alive for the colour passes)
         # debug mode: accumulate the blend backward through 64-bit fixed point so that two runs give identical bits
         self.deterministic = os.environ.get("RGS_DETERMINISTIC", "0") == "1"
         self._fixed_acc = None
@@ -294,12 +295,15 @@ class RenderTask:
                 # two-phase projection: conservative cull of everything, full projection of the survivors;
                 # the candidate list reuses a ping-pong buffer of the depth sort (free until then)
                 structs = (RgsSegment * len(segments))(*[s.struct(False) for s in segments])
-                with self._phase("fwd.project"):
-                    native.call("project_slots2", self.device, cam, structs, len(segments), bs.vis[3], self.cap_vis,
-                                self.splats, self.vis_ids, self.aux, self.cap_vis, bs.slot_depth, bs.slot_rect,
-                                bs.slot_cnt, self.counters, self.splat_grads)
                 tiles = cam.tiles_x * cam.tiles_y
                 self._slab_active = self.slabs and cam.tight_rect < 2 and 8 <= tiles <= 65536
+                self._seg_structs = (structs, len(segments), segments)
+                with self._phase("fwd.project"):
+                    # with two slabs the SH colours are evaluated later, only for splats that get tile instances
+                    native.call("project_slots2_geom" if self._slab_active else "project_slots2", self.device, cam, structs,
+                                len(segments), bs.vis[3], self.cap_vis, self.splats, self.vis_ids, self.aux, self.cap_vis,
+                                bs.slot_depth, bs.slot_rect, bs.slot_cnt, self.counters, self.splat_grads,
+                                sig=native.SIGNATURES["project_slots2"])
                 if self._slab_active:
                     self._forward_slabs(cam, bs, dst, want_depth, push)
                     self.last_out = dst
@@ -366,6 +370,14 @@ class RenderTask:
                     tiles, ranges, bs.words, self.cap_inst, slab, self.slab_frac256, filt, self.sat if filt is not None else None,
                     sig=self._SIG_BIN_SLAB)
 
+    def _colour_slab(self, cam, bs, slab):
+        """SH colours of the slab's splats that have tile instances (the projection left them at zero)."""
+        order = bs.vis[1] if self._own_order is None else self._own_order
+        structs, nseg, _ = self._seg_structs
+        with self._phase("fwd.project"):
+            native.call("colour_slab", self.device, cam, structs, nseg, order, bs.slot_cnt, self.counters, self.cap_vis,
+                        self.slab_frac256, slab, self.splats, self.vis_ids, self.aux, sig="ppipppiiipppp")
+
     def _blend_slab(self, cam, dst, depth, mode, push, occl):
         p = push if (mode == 2 and push is not None) else (0, None, None, None)
         native.call("blend_fwd_slab", self.device, cam, self.ranges, self.ranges_b, self.vals, self.splats, dst, depth,
@@ -378,6 +390,7 @@ class RenderTask:
         depth = self.depth if want_depth else None
         with self._phase("fwd.binning"):
             self._bin_slab(cam, bs, 0, 0, cap_a, self.ranges, occl)
+        self._colour_slab(cam, bs, 0)
         with self._phase("fwd.blend"):
             self._blend_slab(cam, dst, depth, 1, None, occl)
 
@@ -391,6 +404,7 @@ class RenderTask:
                         sig="pipiip")
         with self._phase("fwd.binning"):
             self._bin_slab(cam, bs, 1, cap_a, self.cap_inst - cap_a, self.ranges_b, self.tile_done)
+        self._colour_slab(cam, bs, 1)
         with self._phase("fwd.blend"):
             self._blend_slab(cam, dst, depth, 2, push, None)
 
@@ -423,10 +437,11 @@ class RenderTask:
             self._own_order = torch.empty(self.cap_vis, dtype=torch.int32, device=self.device)
             self._own_rect = torch.empty(self.cap_vis, dtype=torch.int64, device=self.device)
         structs = (RgsSegment * len(segments))(*[s.struct(False) for s in segments])
+        self._seg_structs = (structs, len(segments), segments)  # the tensors must outlive the far half's colour pass
         with self._phase("fwd.project"):
-            native.call("project_slots2", self.device, cam, structs, len(segments), bs.vis[3], self.cap_vis,
+            native.call("project_slots2_geom", self.device, cam, structs, len(segments), bs.vis[3], self.cap_vis,
                         self.splats, self.vis_ids, self.aux, self.cap_vis, bs.slot_depth, self._own_rect,
-                        bs.slot_cnt, self.counters, self.splat_grads)
+                        bs.slot_cnt, self.counters, self.splat_grads, sig=native.SIGNATURES["project_slots2"])
         self._forward_slabs_near(cam, bs, self.out, want_depth, occl)
 
     def forward_far(self, occl: torch.Tensor | None = None, push=None) -> torch.Tensor:
