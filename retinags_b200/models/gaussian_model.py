@@ -29,7 +29,7 @@ from ..utils.general import expon_lr, inverse_sigmoid
 from . import densify, ply_io
 from .gaussians import NAMES, GaussianStore
 
-SH_C0 = 0.28209479177387814
+from ..utils.sh import C0 as SH_C0  # noqa: E402
 
 
 class GaussianModel:

@@ -187,27 +187,10 @@ def composite(partials_C, partials_T, bg):
     return acc + bg * t[None], t
 
 
+# the loss of the oracle is the PyTorch loss of utils/loss.py (one implementation: depthwise conv2d SSIM + L1)
+from ..utils.loss import ssim, training_loss  # noqa: E402,F401
+
+
 def gaussian_window(dtype=torch.float32):
-    g = torch.tensor([math.exp(-((i - 5) ** 2) / (2 * 1.5 ** 2)) for i in range(11)], dtype=dtype)
-    return g / g.sum()
-
-
-def ssim(img1: torch.Tensor, img2: torch.Tensor) -> torch.Tensor:
-    """Mean SSIM of two (3,H,W) images (11x11 window, sigma 1.5, zero padding)."""
-    import torch.nn.functional as F
-    g = gaussian_window(img1.dtype)
-    win = (g[:, None] * g[None, :]).expand(3, 1, 11, 11).contiguous()
-    a, b = img1[None], img2[None]
-    mu1 = F.conv2d(a, win, padding=5, groups=3)
-    mu2 = F.conv2d(b, win, padding=5, groups=3)
-    s1 = F.conv2d(a * a, win, padding=5, groups=3) - mu1 * mu1
-    s2 = F.conv2d(b * b, win, padding=5, groups=3) - mu2 * mu2
-    s12 = F.conv2d(a * b, win, padding=5, groups=3) - mu1 * mu2
-    C1, C2 = 0.01 ** 2, 0.03 ** 2
-    m = ((2 * mu1 * mu2 + C1) * (2 * s12 + C2)) / ((mu1 * mu1 + mu2 * mu2 + C1) * (s1 + s2 + C2))
-    return m.mean()
-
-
-def training_loss(image, gt, lambda_dssim: float = 0.2):
-    l1 = (image - gt).abs().mean()
-    return (1 - lambda_dssim) * l1 + lambda_dssim * (1 - ssim(image, gt))
+    from ..utils.loss import gaussian_window as _gw
+    return _gw(11, 1.5, dtype)

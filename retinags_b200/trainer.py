@@ -47,11 +47,7 @@ from .parallel.partition import BvhTree, Grid3D, assign_models, load_histogram
 from .utils.general import expon_lr, inverse_sigmoid, is_interval_in_batch, is_point_in_batch
 from .utils.image import psnr_from_mse, save_png
 
-SH_C0 = 0.28209479177387814
-
-
-def rgb_to_sh(rgb):
-    return (rgb - 0.5) / SH_C0
+from .utils.sh import RGB2SH as rgb_to_sh  # noqa: E402
 
 
 class CkptCleaner:
