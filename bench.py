@@ -59,6 +59,12 @@ def parse_args():
     ap.add_argument("--train-views", type=int, default=40)
     ap.add_argument("--eval-frames", type=int, default=20)
     ap.add_argument("--epochs", type=int, default=8)
+    ap.add_argument("--pool-views", type=int, default=0,
+                    help="form the batches from a seeded shuffle of this many training cameras (160 in the named config) "
+                         "instead of consecutive cameras of a short list")
+    ap.add_argument("--balance-batches", action="store_true",
+                    help="with --pool-views: pair cameras whose estimated per-rank loads complement each other (the "
+                         "trainer's --BALANCE_BATCHES)")
     ap.add_argument("--no-spatial-sort", action="store_true", help="keep the Gaussians in generation order (default: rows "
                     "are sorted along a Morton curve, the trainer's default as well)")
     ap.add_argument("--densify-threshold", type=float, default=2e-4, help="--mode city: screen-gradient threshold")
@@ -156,7 +162,8 @@ def run_own(args):
                         height=args.height, batch=args.batch, n_views=(args.steps + args.warmup) * args.batch,
                         gt_gaussians=args.gt_gaussians, transport=args.transport, seed=args.seed,
                         borrow_refresh=args.borrow_refresh, bvh_depth=args.bvh_depth,
-                        spatial_sort=not args.no_spatial_sort, scene_kind=args.scene)
+                        spatial_sort=not args.no_spatial_sort, scene_kind=args.scene, pool_views=args.pool_views,
+                        balance_batches=args.balance_batches)
     # ---- device-timed region ------------------------------------------------------------------
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -307,7 +314,9 @@ def run_own(args):
                        "rows_with_adam_moments_rank0": live_rows, "overflow_in_timed_region": overflow,
                        "two_slab_forward": os.environ.get("RGS_SLABS", "1") == "1",
                        "occlusion_culling_between_submodels": bool(sess.engine.occlusion),
-                       "rows_in_morton_order": not args.no_spatial_sort},
+                       "rows_in_morton_order": not args.no_spatial_sort,
+                       "batches": ("balanced pairs" if args.balance_batches else "shuffled") + f" from {args.pool_views} cameras"
+                       if args.pool_views else "consecutive cameras"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "render": render, "city": city,
             "phases_ms_per_step_max_over_ranks": phases,
             "roofline_rank0_of_measured": roofline,

@@ -122,7 +122,8 @@ class BenchSession:
     def __init__(self, device, rank: int, world: int, n_gaussians: int, width: int, height: int, batch: int,
                  n_views: int, gt_gaussians: int, transport: str = "auto", seed: int = 0, sh_degree: int = 3,
                  grid=(2048, 2048, 1), bvh_depth: int | None = None, scene_kind: str = "cluster",
-                 borrow: bool = True, borrow_refresh: int = 1, group=None, spatial_sort: bool = True):
+                 borrow: bool = True, borrow_refresh: int = 1, group=None, spatial_sort: bool = True,
+                 pool_views: int = 0, balance_batches: bool = False):
         self.device = torch.device(device)
         self.rank, self.world, self.batch = rank, world, batch
         self.sh_degree = sh_degree
@@ -169,6 +170,9 @@ class BenchSession:
         else:
             self.cams = synthetic.ring_cameras(max(n_views, 1), 3.0, width, height, 60.0)
         self.relation = self.tree.relation(self.cams, 0.01, 1000.0)
+        self.batches = None
+        if pool_views > len(self.cams) and scene_kind == "cluster":
+            self._batches_from_pool(pool_views, n_views, width, height, seed, balance_batches, group)
         self._render_ground_truth(seed, gt_gaussians, sh_degree)
         # ---- engine ---------------------------------------------------------------------------
         self.transport_name = "local"
@@ -208,6 +212,34 @@ class BenchSession:
         self.last_info: dict = {}
         self._launch_base = 0
 
+    def _batches_from_pool(self, pool_views: int, n_views: int, width: int, height: int, seed: int, balance: bool, group):
+        """Batches as the trainer forms them: a seeded shuffle of a pool of training cameras packed into batches, either
+        in sequence (the reference's balancer, ``utils/workload_utils.py:20-59``) or, with ``balance``, pairing cameras
+        whose estimated per-rank loads complement each other (``WorkloadBalancer.groups_balanced``, the trainer's
+        ``--BALANCE_BATCHES``). Only the cameras of the first ``n_views / batch`` batches are kept (and get targets)."""
+        from .parallel.balancer import WorkloadBalancer, estimate_costs
+        pool = synthetic.hemisphere_cameras(pool_views, 8.0, width, height, 50.0, seed)
+        rel = self.tree.relation(pool, 0.01, 1000.0)
+        g = torch.Generator()
+        g.manual_seed(seed)
+        order = torch.randperm(pool_views, generator=g).tolist()
+        bal = WorkloadBalancer(self.world, self.model2rank)
+        max_task = self.batch * max(2, -(-self.n_models // self.world))
+        if balance and self.world > 1:
+            cost = torch.from_numpy(estimate_costs(self.stores, pool, self.n_models)).to(self.device)
+            dist.all_reduce(cost, group=group)
+            groups = bal.groups_balanced(rel, order, cost.cpu().numpy(), max_task, self.batch)
+        else:
+            groups = bal.groups(rel, order, max_task, self.batch)
+        groups = [g_ for g_ in groups if len(g_) == self.batch][:max(1, n_views // self.batch)]
+        used = [i for g_ in groups for i in g_]
+        remap = {i: k for k, i in enumerate(used)}
+        self.cams = [pool[i] for i in used]
+        for k, cam in enumerate(self.cams):
+            cam.uid = k
+        self.relation = rel[used]
+        self.batches = [tuple(remap[i] for i in g_) for g_ in groups]
+
     # -- ground truth -----------------------------------------------------------------------------
     def _render_ground_truth(self, seed: int, gt_gaussians: int, sh_degree: int):
         """Targets come from an independent seeded scene; each view is rendered once and parked in pinned
@@ -231,7 +263,10 @@ class BenchSession:
 
     # -- steps ------------------------------------------------------------------------------------
     def _batch(self, i: int):
-        idx = [(i * self.batch + j) % len(self.cams) for j in range(self.batch)]
+        if self.batches:
+            idx = list(self.batches[i % len(self.batches)])
+        else:
+            idx = [(i * self.batch + j) % len(self.cams) for j in range(self.batch)]
         return [self.cams[k] for k in idx], self.relation[idx]
 
     def step(self, i: int):

@@ -662,25 +662,56 @@ __global__ void __launch_bounds__(128) rgs_colour_slab_kernel(const __grid_const
                                                               const uint32_t* __restrict__ counters, uint32_t cap_vis,
                                                               uint32_t frac256, int slab, RgsSplat* __restrict__ splats,
                                                               const int32_t* __restrict__ vis_ids, uint32_t* __restrict__ aux) {
+    // A warp looks at 32 depth-ordered positions at a time. The SH rows of the splats among them that have instances are
+    // fetched by the whole warp, one row after the other: lanes 0..11 load the twelve 128-bit words of a row (one
+    // coalesced 192-byte request per row, all rows of the batch in flight together) into the owner lane's padded row in
+    // shared memory; every owner then evaluates its colour from there with the arithmetic of the projection.
+    __shared__ __align__(16) float s_sh[4][32][PC_ROW];
     const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);
     uint32_t s0, s1;
     slab_segments(n, frac256, slab, s0, s1);
-    const uint32_t end = s1 * EM_SEG < n ? s1 * EM_SEG : n;
-    for (uint32_t i = s0 * EM_SEG + blockIdx.x * blockDim.x + threadIdx.x; i < end; i += gridDim.x * blockDim.x) {
-        const uint32_t slot = order[i];
-        if (slot_cnt[slot] == 0) continue;
-        int64_t id = vis_ids[slot];
-        int sidx = 0;
-        while (sidx < segs.n - 1 && id >= segs.s[sidx].count) { id -= segs.s[sidx].count; ++sidx; }
-        const RgsSegment& seg = segs.s[sidx];
-        if (id < 0 || id >= seg.count) continue;
-        const float p[3] = {seg.xyz[3 * id], seg.xyz[3 * id + 1], seg.xyz[3 * id + 2]};
-        float r, g, b;
-        unsigned clamped;
-        rgs_splat_colour(cam, p, seg.sh + 48 * id, r, g, b, clamped);
-        float* rec = reinterpret_cast<float*>(splats + slot);
-        rec[6] = r; rec[7] = g; rec[8] = b;
-        aux[slot] = (aux[slot] & ~7u) | clamped;
+    const uint32_t begin = s0 * EM_SEG, end = s1 * EM_SEG < n ? s1 * EM_SEG : n;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+    for (uint32_t i0 = begin + warp * 32; i0 < end; i0 += nwarps * 32) {
+        const uint32_t i = i0 + lane;
+        bool act = false;
+        uint32_t slot = 0;
+        const float* sh_row = nullptr;
+        float p[3] = {0.f, 0.f, 0.f};
+        if (i < end) {
+            slot = order[i];
+            if (slot_cnt[slot] != 0) {
+                int64_t id = vis_ids[slot];
+                int sidx = 0;
+                while (sidx < segs.n - 1 && id >= segs.s[sidx].count) { id -= segs.s[sidx].count; ++sidx; }
+                const RgsSegment& seg = segs.s[sidx];
+                if (id >= 0 && id < seg.count) {
+                    act = true;
+                    sh_row = seg.sh + 48 * id;
+                    p[0] = seg.xyz[3 * id]; p[1] = seg.xyz[3 * id + 1]; p[2] = seg.xyz[3 * id + 2];
+                }
+            }
+        }
+        uint32_t m = __ballot_sync(0xffffffffu, act);
+        if (m == 0) continue;
+        const unsigned long long mine = (unsigned long long)(uintptr_t)sh_row;
+        while (m) {
+            const int a = __ffs(m) - 1;
+            m &= m - 1;
+            const float4* src = reinterpret_cast<const float4*>((uintptr_t)__shfl_sync(0xffffffffu, mine, a));
+            if (lane < 12) reinterpret_cast<float4*>(&s_sh[wid][a][0])[lane] = src[lane];
+        }
+        __syncwarp();
+        if (act) {
+            float r, g, b;
+            unsigned clamped;
+            rgs_splat_colour(cam, p, &s_sh[wid][lane][0], r, g, b, clamped);
+            float* rec = reinterpret_cast<float*>(splats + slot);
+            rec[6] = r; rec[7] = g; rec[8] = b;
+            aux[slot] = (aux[slot] & ~7u) | clamped;
+        }
+        __syncwarp();
     }
 }
 
@@ -761,7 +792,7 @@ __global__ void __launch_bounds__(256) rgs_slab_emit_kernel(const __grid_constan
                                                             uint32_t frac256, int slab, const uint32_t* __restrict__ seg_excl,
                                                             uint32_t* __restrict__ tile_keys, uint32_t* __restrict__ vals,
                                                             uint32_t region_cap, const uint8_t* __restrict__ tile_done) {
-    __shared__ uint32_t warp_tot[8];
+    __shared__ uint32_t warp_tot[8], warp_nz[8];
     __shared__ uint32_t s_slot[EM_SEG], s_base[EM_SEG];
     __shared__ uint2 s_rect[EM_SEG];
     const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);  // 0 after an overflow: nothing is written
@@ -791,16 +822,30 @@ __global__ void __launch_bounds__(256) rgs_slab_emit_kernel(const __grid_constan
         uint32_t wbase = 0;
         for (int w = 0; w < wid; ++w) wbase += warp_tot[w];
         uint32_t base = seg_excl[s] + wbase + incl - mine;
+        // Only splats that emit something are parked, compacted (their output ranges are fixed by `base`, so the order
+        // in which warps take them does not matter): behind finished tiles most splats of the far slab emit nothing, and
+        // walking them one by one was the serial part of this kernel.
+        uint32_t nz = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) nz += cnt[k] ? 1u : 0u;
+        uint32_t nz_incl = nz;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t t = __shfl_up_sync(0xffffffffu, nz_incl, d);
+            if (lane >= d) nz_incl += t;
+        }
+        if (lane == 31) warp_nz[wid] = nz_incl;
+        __syncthreads();
+        uint32_t nz_base = 0, nz_total = 0;
+        for (int w = 0; w < 8; ++w) { if (w < wid) nz_base += warp_nz[w]; nz_total += warp_nz[w]; }
+        uint32_t pos = nz_base + nz_incl - nz;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const int e = threadIdx.x * 4 + k;
-            s_slot[e] = slot[k]; s_base[e] = base;
-            s_rect[e] = cnt[k] ? rect[k] : make_uint2(0, 0);
+            if (cnt[k]) { s_slot[pos] = slot[k]; s_base[pos] = base; s_rect[pos] = rect[k]; ++pos; }
             base += cnt[k];
         }
         __syncthreads();
-        for (int j = 0; j < EM_SEG / 8; ++j) {
-            const int e = wid * (EM_SEG / 8) + j;
+        for (uint32_t e = wid; e < nz_total; e += 8) {
             const uint2 r = s_rect[e];
             const uint32_t c = rect_count(r);
             if (c == 0) continue;

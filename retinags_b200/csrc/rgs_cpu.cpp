@@ -379,7 +379,7 @@ int rgs_cpu_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t 
 // the row-block variant of the CUDA library is a different work distribution of the same update
 int rgs_cpu_adam_rows(float* p, float* g, float* m, float* v, int64_t count, int64_t cap, const double* lrs, double beta1,
                       double beta2, double eps, int64_t step, int64_t zero_grad, const int32_t* skip, const uint8_t* touched,
-                      uint8_t* active, void*) {
+                      uint8_t* active, uint32_t*, uint32_t*, void*) {
     return rgs_cpu_adam(p, g, m, v, count, cap, lrs, beta1, beta2, eps, step, zero_grad, skip, touched, active, nullptr);
 }
 

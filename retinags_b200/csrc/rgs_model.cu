@@ -196,25 +196,22 @@ __device__ __forceinline__ void adam_quad(float* __restrict__ p, float* __restri
     if (zero_grad && touched_row) *reinterpret_cast<float4*>(g + base) = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
-__global__ void __launch_bounds__(256) rgs_adam_rows_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
-                                                            float* __restrict__ v, int64_t count, int64_t cap,
-                                                            const __grid_constant__ RgsLrTable lrs, float beta1, float beta2,
-                                                            float eps, float bc1, float bc2s, int zero_grad,
-                                                            const uint32_t* __restrict__ skip,
-                                                            const uint8_t* __restrict__ touched, uint8_t* __restrict__ active) {
-    if (skip && skip[RGS_CNT_OVERFLOW]) {
-        if (zero_grad) adam_drop_gradients(g, count, cap, touched);
-        return;
-    }
-    const int64_t o1 = cap * 3, o2 = o1 + cap * 48, o3 = o2 + cap * 3, o4 = o3 + cap * 4;
+// Row-block Adam in two launches. (1) rgs_adam_live_kernel scans the marks -- a warp looks at 512 consecutive rows per
+// iteration, every lane fetching the 16 mark bytes of its rows with one 128-bit load per array -- carries the `active`
+// marks forward and appends the live rows (touched this step, or holding moments) to a list, one atomic per warp.
+// (2) rgs_adam_rows_kernel updates the listed rows, one half-warp per row (the 15 units of a row on 15 lanes: 12 float4
+// of SH, the rotation, position, scale + opacity). Dead rows cost two wide loads per 16 rows, and the live rows are
+// spread evenly over the machine wherever they lie: after the rows were sorted along a space-filling curve the live
+// ones (the visible, blended Gaussians) sit in dense runs, which a kernel that walked fixed row blocks serialised.
+__global__ void __launch_bounds__(256) rgs_adam_live_kernel(int64_t count, int64_t cap, const uint8_t* __restrict__ touched,
+                                                            uint8_t* __restrict__ active, uint32_t* __restrict__ live_list,
+                                                            uint32_t* __restrict__ live_count,
+                                                            const uint32_t* __restrict__ skip) {
+    if (skip && skip[RGS_CNT_OVERFLOW]) return;
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    // A warp looks at the marks of 512 consecutive rows per iteration: every lane fetches the 16 mark bytes of its 16
-    // rows with one 128-bit load per array, so that a stretch without a live row costs two wide loads per lane instead of
-    // sixteen dependent byte loads (with few live rows the kernel is bound by the latency of exactly these loads).
     const int64_t nsuper = (count + 511) / 512;
-    const int half = lane >> 4, u = lane & 15;
     for (int64_t sb = warp; sb < nsuper; sb += nwarps) {
         const int64_t r0 = sb * 512 + (int64_t)lane * 16;
         uint32_t tbits = 0, lbits = 0;  // bit k: row r0 + k was touched this step / has to be updated
@@ -245,37 +242,62 @@ __global__ void __launch_bounds__(256) rgs_adam_rows_kernel(float* __restrict__ 
                 else for (int k = 0; k < 16 && r0 + k < cap; ++k) active[r0 + k] = (uint8_t)((aw[k >> 2] >> (8 * (k & 3))) & 0xffu);
             }
         }
-        uint32_t lanes = __ballot_sync(0xffffffffu, lbits != 0);
-        while (lanes) {
-            const int src = __ffs(lanes) - 1;
-            lanes &= lanes - 1;
-            uint32_t lb = __shfl_sync(0xffffffffu, lbits, src);
-            const uint32_t tb = __shfl_sync(0xffffffffu, tbits, src);
-            const int64_t base_row = sb * 512 + (int64_t)src * 16;
-            // two live rows per pass: the 15 units of a row on 15 lanes of a half-warp
-            // (12 float4 of SH, the rotation, position, scale + opacity)
-            while (lb) {
-                const int j0 = __ffs(lb) - 1;
-                lb &= lb - 1;
-                int j1 = -1;
-                if (lb) { j1 = __ffs(lb) - 1; lb &= lb - 1; }
-                const int jr = half ? j1 : j0;
-                if (jr < 0 || u >= 15) continue;
-                const int64_t row = base_row + jr;
-                const bool tr = (tb >> jr) & 1u;
-                if (u < 12) {
-                    adam_quad<1>(p, g, m, v, o1 + row * 48 + u * 4, u * 4, tr, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad);
-                } else if (u == 12) {
-                    adam_quad<3>(p, g, m, v, o3 + row * 4, 0, tr, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad);
-                } else if (u == 13) {
-                    for (int c = 0; c < 3; ++c)
-                        adam_scalar(p, g, m, v, row * 3 + c, tr, lrs.lr[RGS_LR_XYZ], beta1, beta2, eps, bc1, bc2s, zero_grad);
-                } else {
-                    for (int c = 0; c < 3; ++c)
-                        adam_scalar(p, g, m, v, o2 + row * 3 + c, tr, lrs.lr[RGS_LR_SCALE], beta1, beta2, eps, bc1, bc2s, zero_grad);
-                    adam_scalar(p, g, m, v, o4 + row, tr, lrs.lr[RGS_LR_OPACITY], beta1, beta2, eps, bc1, bc2s, zero_grad);
-                }
-            }
+        // warp-wide exclusive scan of the live counts, one reservation per warp
+        const uint32_t mine = __popc(lbits);
+        uint32_t incl = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += y;
+        }
+        const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+        if (total == 0) continue;
+        uint32_t base = 0;
+        if (lane == 31) base = atomicAdd(live_count, total);
+        base = __shfl_sync(0xffffffffu, base, 31);
+        uint32_t pos = base + incl - mine;
+        uint32_t lb = lbits;
+        while (lb) {
+            const int k = __ffs(lb) - 1;
+            lb &= lb - 1;
+            live_list[pos++] = (uint32_t)(r0 + k) | (((tbits >> k) & 1u) << 31);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) rgs_adam_rows_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ m,
+                                                            float* __restrict__ v, int64_t count, int64_t cap,
+                                                            const __grid_constant__ RgsLrTable lrs, float beta1, float beta2,
+                                                            float eps, float bc1, float bc2s, int zero_grad,
+                                                            const uint32_t* __restrict__ skip,
+                                                            const uint8_t* __restrict__ touched,
+                                                            const uint32_t* __restrict__ live_list,
+                                                            const uint32_t* __restrict__ live_count) {
+    if (skip && skip[RGS_CNT_OVERFLOW]) {
+        if (zero_grad) adam_drop_gradients(g, count, cap, touched);
+        return;
+    }
+    const int64_t o1 = cap * 3, o2 = o1 + cap * 48, o3 = o2 + cap * 3, o4 = o3 + cap * 4;
+    const uint32_t n = *live_count;
+    const int u = threadIdx.x & 15;
+    const uint32_t hw = (uint32_t)(((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 4);
+    const uint32_t nhw = (uint32_t)(((int64_t)gridDim.x * blockDim.x) >> 4);
+    if (u >= 15) return;
+    for (uint32_t i = hw; i < n; i += nhw) {
+        const uint32_t e = live_list[i];
+        const int64_t row = (int64_t)(e & 0x7fffffffu);
+        const bool tr = (e >> 31) != 0;
+        if (u < 12) {
+            adam_quad<1>(p, g, m, v, o1 + row * 48 + u * 4, u * 4, tr, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad);
+        } else if (u == 12) {
+            adam_quad<3>(p, g, m, v, o3 + row * 4, 0, tr, lrs, beta1, beta2, eps, bc1, bc2s, zero_grad);
+        } else if (u == 13) {
+            for (int c = 0; c < 3; ++c)
+                adam_scalar(p, g, m, v, row * 3 + c, tr, lrs.lr[RGS_LR_XYZ], beta1, beta2, eps, bc1, bc2s, zero_grad);
+        } else {
+            for (int c = 0; c < 3; ++c)
+                adam_scalar(p, g, m, v, o2 + row * 3 + c, tr, lrs.lr[RGS_LR_SCALE], beta1, beta2, eps, bc1, bc2s, zero_grad);
+            adam_scalar(p, g, m, v, o4 + row, tr, lrs.lr[RGS_LR_OPACITY], beta1, beta2, eps, bc1, bc2s, zero_grad);
         }
     }
 }
@@ -300,21 +322,28 @@ int rgs_cuda_adam(float* p, float* g, float* m, float* v, int64_t count, int64_t
     return (int)cudaGetLastError();
 }
 
-// Same contract as rgs_cuda_adam, row-block kernel (see rgs_adam_rows_kernel).
+// Same contract as rgs_cuda_adam, row-block kernels (see above). live_list: `cap` words of scratch, live_count: one word;
+// both owned by the caller, contents irrelevant on entry. Rows are limited to 2^31 per store.
 int rgs_cuda_adam_rows(float* p, float* g, float* m, float* v, int64_t count, int64_t cap, const double* lrs, double beta1,
                        double beta2, double eps, int64_t step, int64_t zero_grad, const int32_t* skip, const uint8_t* touched,
-                       uint8_t* active, void* stream) {
+                       uint8_t* active, uint32_t* live_list, uint32_t* live_count, void* stream) {
     if (count <= 0) return 0;
-    if (cap % 4 != 0) return 13;
+    if (cap % 4 != 0 || cap > 0x7fffffffll || !live_list || !live_count) return 13;
+    cudaStream_t st = (cudaStream_t)stream;
     RgsLrTable t;
     for (int k = 0; k < 6; ++k) t.lr[k] = (float)lrs[k];
     const float bc1 = (float)(1.0 / (1.0 - pow(beta1, (double)step)));
     const float bc2s = (float)(1.0 / sqrt(1.0 - pow(beta2, (double)step)));
-    const int64_t want = ((count + 511) / 512 + 7) / 8;  // 8 warps per block, 512 rows per warp and iteration
-    const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 64 ? RGS_SMS * 64 : want));
-    rgs_adam_rows_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, count, cap, t, (float)beta1, (float)beta2,
-                                                                  (float)eps, bc1, bc2s, (int)zero_grad,
-                                                                  reinterpret_cast<const uint32_t*>(skip), touched, active);
+    RGS_CUDA_CHECK(cudaMemsetAsync(live_count, 0, 4, st));
+    int64_t want = ((count + 511) / 512 + 7) / 8;  // 8 warps per block, 512 rows per warp and iteration
+    unsigned blocks = (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 64 ? RGS_SMS * 64 : want));
+    rgs_adam_live_kernel<<<blocks, 256, 0, st>>>(count, cap, touched, active, live_list, live_count,
+                                                 reinterpret_cast<const uint32_t*>(skip));
+    want = (count + 15) / 16;  // 16 rows per block and pass; the kernel strides over the list
+    blocks = (unsigned)(want < 1 ? 1 : (want > RGS_SMS * 32 ? RGS_SMS * 32 : want));
+    rgs_adam_rows_kernel<<<blocks, 256, 0, st>>>(p, g, m, v, count, cap, t, (float)beta1, (float)beta2, (float)eps, bc1, bc2s,
+                                                 (int)zero_grad, reinterpret_cast<const uint32_t*>(skip), touched, live_list,
+                                                 live_count);
     return (int)cudaGetLastError();
 }
 

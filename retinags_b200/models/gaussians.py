@@ -120,6 +120,7 @@ class GaussianStore:
         # (csrc/rgs_model.cu: rgs_adam_rows_kernel, much cheaper when few rows are live); "auto": "rows" on CUDA devices
         # on which a one-off comparison of the two kernels agreed bit for bit, "units" otherwise
         self.adam_variant = os.environ.get("RGS_ADAM", "auto")
+        self._live_list = self._live_count = None
         self.touched = None  # uint8 per row: a gradient was written this step (rows with 0 hold zero gradients)
         self.active = None   # uint8 per row: the Adam moments may be non-zero (rows with 0 hold zero moments)
         self._alloc(_round_cap(capacity))
@@ -327,9 +328,16 @@ class GaussianStore:
         variant = self.adam_variant
         if variant == "auto":
             variant = "rows" if (self.device.type == "cuda" and adam_rows_agrees(self.device)) else "units"
-        native.call("adam_rows" if variant == "rows" else "adam", self.device, self.params, self.grads, self.exp_avg, self.exp_avg_sq, self.count, self.cap, arr,
-                    float(beta1), float(beta2), float(eps), self.step, 1 if zero_grad else 0, skip,
-                    self.touched if zero_grad else None, self.active if zero_grad else None)
+        common = (self.device, self.params, self.grads, self.exp_avg, self.exp_avg_sq, self.count, self.cap, arr, float(beta1),
+                  float(beta2), float(eps), self.step, 1 if zero_grad else 0, skip, self.touched if zero_grad else None,
+                  self.active if zero_grad else None)
+        if variant == "rows":
+            if self._live_list is None or self._live_list.numel() < self.cap:  # scratch of the row-block kernels
+                self._live_list = torch.empty(self.cap, dtype=torch.int32, device=self.device)
+                self._live_count = torch.zeros(1, dtype=torch.int32, device=self.device)
+            native.call("adam_rows", *common, self._live_list, self._live_count)
+        else:
+            native.call("adam", *common)
         if zero_grad:
             self.touched.zero_()
         else:

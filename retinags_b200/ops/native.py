@@ -36,7 +36,7 @@ SIGNATURES = {
     "geom_bwd": "ppipppppip",
     "scatter_radii": "pppiipp",
     "adam": "ppppiipfffiipppp",
-    "adam_rows": "ppppiipfffiipppp",
+    "adam_rows": "ppppiipfffiipppppp",
     "composite_fwd": "pipiiiippp",
     "composite_bwd": "ppipiiiipp",
     "ssim_fwd": "ppiiiiiippp",
@@ -155,7 +155,7 @@ def stream_ptr(device: torch.device):
 
 
 # kernels launched by one call of an entry point (the radix sort's count depends on the tile count)
-_KERNELS = {"project_slots": 1, "project_slots2": 2, "project_slots2_geom": 2, "colour_slab": 1, "tile_maps_or": 1, "tile_map_push": 1, "project_emit": 1, "blend_fwd": 1, "blend_bwd": 1, "geom_bwd": 1, "scatter_radii": 1, "adam": 1,
+_KERNELS = {"project_slots": 1, "project_slots2": 2, "project_slots2_geom": 2, "colour_slab": 1, "tile_maps_or": 1, "tile_map_push": 1, "project_emit": 1, "blend_fwd": 1, "blend_bwd": 1, "geom_bwd": 1, "scatter_radii": 1, "adam": 1, "adam_rows": 2,
             "composite_fwd": 1, "composite_bwd": 1, "ssim_fwd": 1, "ssim_bwd": 1, "densify_classify": 2, "bin_slab": 14, "blend_fwd_slab": 1, "blend_bwd_slab": 1}
 _LAUNCHES = [0]
 
