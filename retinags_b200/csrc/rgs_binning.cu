@@ -663,9 +663,10 @@ __global__ void __launch_bounds__(128) rgs_colour_slab_kernel(const __grid_const
                                                               uint32_t frac256, int slab, RgsSplat* __restrict__ splats,
                                                               const int32_t* __restrict__ vis_ids, uint32_t* __restrict__ aux) {
     // A warp looks at 32 depth-ordered positions at a time. The SH rows of the splats among them that have instances are
-    // fetched by the whole warp, one row after the other: lanes 0..11 load the twelve 128-bit words of a row (one
-    // coalesced 192-byte request per row, all rows of the batch in flight together) into the owner lane's padded row in
-    // shared memory; every owner then evaluates its colour from there with the arithmetic of the projection.
+    // fetched by the whole warp, one row after the other: lanes 0..11 copy the twelve 128-bit words of a row (one
+    // coalesced 192-byte request per row; asynchronous copies, so all rows of the batch are in flight together) into
+    // the owner lane's padded row in shared memory; every owner then evaluates its colour from there with the
+    // arithmetic of the projection.
     __shared__ __align__(16) float s_sh[4][32][PC_ROW];
     const uint32_t n = bs_count(counters, RGS_CNT_VIS, cap_vis);
     uint32_t s0, s1;
@@ -700,8 +701,9 @@ __global__ void __launch_bounds__(128) rgs_colour_slab_kernel(const __grid_const
             const int a = __ffs(m) - 1;
             m &= m - 1;
             const float4* src = reinterpret_cast<const float4*>((uintptr_t)__shfl_sync(0xffffffffu, mine, a));
-            if (lane < 12) reinterpret_cast<float4*>(&s_sh[wid][a][0])[lane] = src[lane];
+            if (lane < 12) rgs_cp_async16(&s_sh[wid][a][4 * lane], src + lane);
         }
+        rgs_cp_async_wait_all();
         __syncwarp();
         if (act) {
             float r, g, b;

@@ -45,6 +45,13 @@ __device__ __forceinline__ void rgs_bulk_g2s(void* smem_dst, const void* gsrc, u
                  : "memory");
 }
 
+// 16-byte asynchronous copy global -> shared (no register in between, so many can be in flight per thread) and the
+// wait for all copies this thread has issued.
+__device__ __forceinline__ void rgs_cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(rgs_smem_addr(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void rgs_cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 __device__ __forceinline__ void rgs_st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
