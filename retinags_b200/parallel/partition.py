@@ -275,6 +275,24 @@ def frustum_overlaps_boxes(cam, lo: np.ndarray, hi: np.ndarray, z_near: float, z
     return ~separated.any(axis=1)
 
 
-def assign_models(num_models: int, world: int) -> list[int]:
-    """Sub-model i lives on rank i % world (``scene_utils.py:185-189``)."""
-    return [i % world for i in range(num_models)]
+def assign_models(num_models: int, world: int, costs=None) -> list[int]:
+    """Sub-model -> rank map. Without costs sub-model i lives on rank i % world (``scene_utils.py:185-189``). With
+    one cost per sub-model (and more sub-models than ranks) the costliest sub-model goes first to the rank that
+    carries least so far; every rank holds at least one sub-model, and ties fall to the lower rank, so that all
+    ranks compute the same map from the same costs."""
+    if costs is None or num_models <= world:
+        return [i % world for i in range(num_models)]
+    costs = [float(c) for c in costs]
+    if len(costs) != num_models:
+        raise ValueError("one cost per sub-model")
+    order = sorted(range(num_models), key=lambda m: (-costs[m], m))
+    load, held, out = [0.0] * world, [0] * world, [0] * num_models
+    for pos, m in enumerate(order):
+        left = num_models - pos
+        empty = [r for r in range(world) if held[r] == 0]
+        pool = empty if len(empty) >= left else range(world)
+        r = min(pool, key=lambda q: (load[q], q))
+        out[m] = r
+        load[r] += costs[m]
+        held[r] += 1
+    return out

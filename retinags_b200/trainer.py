@@ -166,12 +166,25 @@ class Trainer:
     def _stores_from_tree(self):
         lo, hi = self.tree.leaf_boxes_world(open_border=True)
         self.n_models = len(self.tree.leaves)
-        self.model2rank = assign_models(self.n_models, self.world)
+        self.model2rank = assign_models(self.n_models, self.world, self._assignment_costs())
         self.local_ids = [m for m in range(self.n_models) if self.model2rank[m] == self.rank]
         if not self.local_ids:
             raise RuntimeError("empty rank")
         self.boxes = (lo, hi)
         return lo, hi
+
+    def _assignment_costs(self):
+        """Per sub-model cost for ``--MODEL_ASSIGNMENT cost``: how many training cameras see its box (the median
+        split already gives every leaf the same number of points). None keeps the reference's i % world."""
+        if getattr(self.args, "MODEL_ASSIGNMENT", "round_robin") != "cost" or self.n_models <= self.world:
+            return None
+        costs = None
+        if self.rank == 0:
+            ds = self.train_dataset
+            cams = [ds.empty_item(i) for i in range(len(ds))]
+            rel = self.tree.relation(cams, self.args.Z_NEAR, self.args.Z_FAR)
+            costs = [float(c) + 1.0 for c in (rel >= 0).sum(0)]
+        return self._bcast(costs)
 
     def _init_partition_and_models(self):
         a = self.args

