@@ -435,6 +435,207 @@ __global__ void __launch_bounds__(BS_THREADS) rgs_bs_scatter_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------
+// single-sweep variant of the same sort: one kernel counts the digits of every pass before the first pass, and the
+// scatter of a pass finds where its chunk starts inside every digit's run by looking back at the chunks before it
+// (decoupled look-back), instead of a histogram and a scan launch per pass.
+//   look-back word of (chunk, digit): count << 2 | state; EMPTY: not there yet, AGG: count of this chunk alone,
+//   INCL: count of this chunk and all chunks before it.
+// Chunks are handed out by a ticket counter, so every chunk a block waits for belongs to a block that is already
+// running and publishes its AGG words without waiting for anybody. The wait is bounded all the same: when it runs
+// out, bit 2 of the status word is set, the chunk publishes what it has (so that later chunks do not wait as well),
+// and the blocks stop taking tickets; the host raises on the status word and the slower three-kernel sort remains
+// available (RGS_SORT=3k).
+// ---------------------------------------------------------------------------------------------
+#define BS_LB_EMPTY 0u
+#define BS_LB_AGG 1u
+#define BS_LB_INCL 2u
+#define BS_LB_SPINS (1u << 20)
+#define BS_STATUS_LOOKBACK 4u
+#define BS_SWEEP_MAX_PASSES 4
+#define BS_SWEEP_SMALL_WORDS (BS_SWEEP_MAX_PASSES * 256 + 8)  // digit totals of every pass + one ticket per pass
+
+__device__ __forceinline__ uint32_t bs_ld_relaxed(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void bs_st_relaxed(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Digit counts of all passes in one read of the keys (the counts of a digit do not depend on the order of the
+// keys, so they hold for every later pass), and the look-back words of the first pass are cleared on the way.
+// agg_mask: bit p set when the digits of pass p repeat inside a warp (one shared update per distinct digit).
+template <int BS_ITEMS>
+__global__ void __launch_bounds__(BS_THREADS) rgs_bs_digits_kernel(const uint32_t* __restrict__ keys,
+                                                                  const uint32_t* __restrict__ counters, int which,
+                                                                  uint32_t cap, int npass, int agg_mask,
+                                                                  uint32_t* __restrict__ totals, uint32_t* __restrict__ lb) {
+    constexpr uint32_t BS_CHUNK = BS_THREADS * BS_ITEMS, BS_WARP_SPAN = 32 * BS_ITEMS;
+    __shared__ uint32_t sh[BS_SWEEP_MAX_PASSES][256];
+    const uint32_t n = bs_count(counters, which, cap);
+    const uint32_t nchunks = (n + BS_CHUNK - 1) / BS_CHUNK;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    for (int k = threadIdx.x; k < BS_SWEEP_MAX_PASSES * 256; k += BS_THREADS) (&sh[0][0])[k] = 0;
+    __syncthreads();
+    for (uint32_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        lb[(size_t)c * 256 + threadIdx.x] = 0u;
+        const uint32_t base = c * BS_CHUNK + wid * BS_WARP_SPAN;
+#pragma unroll 4
+        for (int r = 0; r < BS_ITEMS; ++r) {
+            const uint32_t idx = base + r * 32 + lane;
+            const bool valid = idx < n;
+            const uint32_t key = valid ? keys[idx] : 0u;
+            for (int p = 0; p < npass; ++p) {
+                const uint32_t digit = valid ? ((key >> (8 * p)) & 0xffu) : 0xffffffffu;
+                if ((agg_mask >> p) & 1) {
+                    const uint32_t m = __match_any_sync(0xffffffffu, digit);
+                    if (valid && lane == (__ffs(m) - 1)) atomicAdd(&sh[p][digit], (uint32_t)__popc(m));
+                } else if (valid) {
+                    atomicAdd(&sh[p][digit], 1u);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int p = 0; p < npass; ++p) {
+        const uint32_t v = sh[p][threadIdx.x];
+        if (v) atomicAdd(&totals[p * 256 + threadIdx.x], v);
+    }
+}
+
+template <int BS_ITEMS>
+__global__ void __launch_bounds__(BS_THREADS) rgs_bs_sweep_kernel(
+    const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ keys_out,
+    uint32_t* __restrict__ vals_out, uint32_t* __restrict__ counters, int which, uint32_t cap, int shift,
+    const uint32_t* __restrict__ totals, uint32_t* __restrict__ lb, uint32_t* __restrict__ lb_next,
+    uint32_t* __restrict__ ticket, int iota_vals) {
+    constexpr uint32_t BS_CHUNK = BS_THREADS * BS_ITEMS, BS_WARP_SPAN = 32 * BS_ITEMS;
+    __shared__ uint32_t sh[BS_WARPS][256];
+    __shared__ uint32_t digit_base[256];
+    __shared__ uint32_t local_start[256];
+    __shared__ uint32_t global_start[256];
+    __shared__ uint32_t warp_tot[8];
+    __shared__ uint32_t chunk_s, fail_s;
+    __shared__ uint32_t stage_k[BS_CHUNK], stage_v[BS_CHUNK];
+    const uint32_t n = bs_count(counters, which, cap);
+    const uint32_t nchunks = (n + BS_CHUNK - 1) / BS_CHUNK;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    {
+        const uint32_t t = totals[threadIdx.x];
+        uint32_t incl = t;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            uint32_t u = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += u;
+        }
+        if (lane == 31) warp_tot[wid] = incl;
+        if (threadIdx.x == 0) fail_s = 0u;
+        __syncthreads();
+        uint32_t wbase = 0;
+        for (int w = 0; w < wid; ++w) wbase += warp_tot[w];
+        digit_base[threadIdx.x] = wbase + incl - t;
+    }
+    __syncthreads();
+    for (;;) {
+        if (threadIdx.x == 0) chunk_s = atomicAdd(ticket, 1u);
+        for (int k = threadIdx.x; k < BS_WARPS * 256; k += BS_THREADS) (&sh[0][0])[k] = 0;
+        __syncthreads();
+        const uint32_t c = chunk_s;
+        if (c >= nchunks || fail_s) break;  // the same for every thread: both words were written before the barrier
+        const uint32_t base = c * BS_CHUNK + wid * BS_WARP_SPAN;
+        uint32_t key[BS_ITEMS], val[BS_ITEMS], rank[BS_ITEMS];
+#pragma unroll
+        for (int r = 0; r < BS_ITEMS; ++r) {
+            const uint32_t idx = base + r * 32 + lane;
+            const bool valid = idx < n;
+            key[r] = valid ? keys_in[idx] : 0xffffffffu;
+            val[r] = valid ? (iota_vals ? idx : vals_in[idx]) : 0u;
+        }
+#pragma unroll
+        for (int r = 0; r < BS_ITEMS; ++r) {
+            const uint32_t idx = base + r * 32 + lane;
+            const bool valid = idx < n;
+            const uint32_t digit = valid ? ((key[r] >> shift) & 0xffu) : 0xffffffffu;
+            const uint32_t m = __match_any_sync(0xffffffffu, digit);
+            const int leader = __ffs(m) - 1;
+            uint32_t pre = 0;
+            if (valid && lane == leader) { pre = sh[wid][digit]; sh[wid][digit] = pre + __popc(m); }
+            pre = __shfl_sync(0xffffffffu, pre, leader);
+            rank[r] = pre + __popc(m & lt_mask);
+            __syncwarp();
+        }
+        __syncthreads();
+        {
+            const int d = threadIdx.x;
+            uint32_t run = 0;
+#pragma unroll
+            for (int w = 0; w < BS_WARPS; ++w) { uint32_t t = sh[w][d]; sh[w][d] = run; run += t; }
+            // tell the later chunks at once how many elements of digit d this chunk holds
+            uint32_t* mine = lb + (size_t)c * 256 + d;
+            if (c > 0) bs_st_relaxed(mine, (run << 2) | BS_LB_AGG);
+            uint32_t incl = run;
+#pragma unroll
+            for (int dd = 1; dd < 32; dd <<= 1) {
+                uint32_t u = __shfl_up_sync(0xffffffffu, incl, dd);
+                if (lane >= dd) incl += u;
+            }
+            if (lane == 31) warp_tot[wid] = incl;
+            __syncthreads();
+            uint32_t wbase = 0;
+            for (int w = 0; w < wid; ++w) wbase += warp_tot[w];
+            local_start[d] = wbase + incl - run;
+            // elements of digit d in the chunks before this one
+            uint32_t excl = 0;
+            bool failed = false;
+            for (uint32_t j = c; j > 0 && !failed;) {
+                --j;
+                const uint32_t* theirs = lb + (size_t)j * 256 + d;
+                uint32_t w = bs_ld_relaxed(theirs), spins = 0;
+                while ((w & 3u) == BS_LB_EMPTY) {
+                    if (++spins > BS_LB_SPINS ||
+                        ((spins & 1023u) == 0u && (bs_ld_relaxed(counters + RGS_CNT_STATUS) & BS_STATUS_LOOKBACK))) {
+                        failed = true;
+                        break;
+                    }
+                    w = bs_ld_relaxed(theirs);
+                }
+                if (failed) break;
+                excl += w >> 2;
+                if ((w & 3u) == BS_LB_INCL) break;
+            }
+            bs_st_relaxed(mine, ((excl + run) << 2) | BS_LB_INCL);
+            lb_next[(size_t)c * 256 + d] = 0u;  // the words the next pass starts from
+            if (failed) {
+                atomicOr(counters + RGS_CNT_STATUS, BS_STATUS_LOOKBACK);
+                fail_s = 1u;
+            }
+            global_start[d] = digit_base[d] + excl;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < BS_ITEMS; ++r) {
+            const uint32_t idx = base + r * 32 + lane;
+            if (idx < n) {
+                const uint32_t digit = (key[r] >> shift) & 0xffu;
+                const uint32_t pos = local_start[digit] + sh[wid][digit] + rank[r];
+                stage_k[pos] = key[r]; stage_v[pos] = val[r];
+            }
+        }
+        __syncthreads();
+        const uint32_t chunk_n = min(BS_CHUNK, n - c * BS_CHUNK);
+        for (uint32_t i = threadIdx.x; i < chunk_n; i += BS_THREADS) {
+            const uint32_t k = stage_k[i];
+            const uint32_t digit = (k >> shift) & 0xffu;
+            const uint32_t dst = global_start[digit] + (i - local_start[digit]);
+            if (dst < cap) { keys_out[dst] = k; vals_out[dst] = stage_v[i]; }
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // instance emission in depth order: per-segment counts -> scan of segment sums -> emit
 // ---------------------------------------------------------------------------------------------
 #define EM_SEG 1024  // splats per segment (256 threads x 4)
@@ -1090,6 +1291,16 @@ static inline uint32_t chunks_of(int64_t n) {
     return (uint32_t)(c > 0 ? c : 1);
 }
 
+// scratch words in front of the area of the single-sweep sort (which holds a second look-back table, the digit
+// totals of every pass and the tickets)
+// The counter table of the segmented counting holds (warps x tiles) words; warps per SM x tiles x 4 bytes never
+// exceeds the shared memory of an SM, which bounds the table for any image size.
+#define SC_TABLE_WORDS (RGS_SMS * 227 * 256)
+static inline int64_t scratch_base_words(int64_t cap_vis, int64_t cap_inst) {
+    const int64_t cap = cap_vis > cap_inst ? cap_vis : cap_inst;
+    return 256 * (int64_t)chunks_of(cap) + 256 + (cap_vis + EM_SEG - 1) / EM_SEG + 16 + SC_TABLE_WORDS + SC_MAX_TILES;
+}
+
 // items per thread of the sort kernels: 16 (4096-pair chunks) or 8 (2048-pair chunks, half the registers);
 // RGS_SORT_ITEMS selects the variant.
 static int sort_items() {
@@ -1115,14 +1326,63 @@ static void bs_pass(const uint32_t* kin, const uint32_t* vin, uint32_t* kout, ui
                                                               nchunks_cap, iota);
 }
 
-static void bs_sort(const uint32_t* keys_first, uint32_t* ka, uint32_t* va, uint32_t* kb, uint32_t* vb, const uint32_t* cnt,
-                    int which, uint32_t cap, int npass, uint32_t* hist, uint32_t* totals, int iota_first, cudaStream_t st,
-                    uint32_t** k_out, uint32_t** v_out) {
-    const uint32_t nchunks_cap = chunks_of(cap);
+// 1: single-sweep sort (digit counts up front, decoupled look-back in the scatter; default), 0: histogram, scan and
+// scatter launches per pass (RGS_SORT=3k).
+static int g_sort_sweep = -1;
+static int sort_sweep() {
+    if (g_sort_sweep < 0) {
+        const char* e = getenv("RGS_SORT");
+        g_sort_sweep = (e && !strcmp(e, "3k")) ? 0 : 1;
+    }
+    return g_sort_sweep;
+}
+
+template <int ITEMS>
+static void bs_sweep_passes(const uint32_t* keys_first, uint32_t* ka, uint32_t* va, uint32_t* kb, uint32_t* vb, uint32_t* cnt,
+                            int which, uint32_t cap, int npass, uint32_t* lb_a, uint32_t* lb_b, uint32_t* small,
+                            int iota_first, cudaStream_t st, uint32_t** k_out, uint32_t** v_out) {
+    const uint32_t chunk = BS_THREADS * ITEMS;
+    const uint32_t nch = (cap + chunk - 1) / chunk;
+    const unsigned grid = nch < 1u ? 1u : (nch < (unsigned)(RGS_SMS * 8) ? nch : (unsigned)(RGS_SMS * 8));
+    uint32_t* totals = small;
+    uint32_t* tickets = small + BS_SWEEP_MAX_PASSES * 256;
+    cudaMemsetAsync(small, 0, BS_SWEEP_SMALL_WORDS * sizeof(uint32_t), st);
+    // digits that repeat inside a warp: the upper digit of the tile keys, the exponent byte of the depth keys
+    const bool tile_sort = which == RGS_CNT_INST || which == RGS_CNT_INST2;
+    const int agg_mask = tile_sort ? 0xe : 0x8;
+    rgs_bs_digits_kernel<ITEMS><<<grid, BS_THREADS, 0, st>>>(keys_first, cnt, which, cap, npass, agg_mask, totals, lb_a);
     const uint32_t* kin = keys_first;
     uint32_t* vin = va;
     uint32_t *kout = kb, *vout = vb;
+    for (int p = 0; p < npass; ++p) {
+        const int iota = (p == 0 && iota_first) ? 1 : 0;
+        rgs_bs_sweep_kernel<ITEMS><<<grid, BS_THREADS, 0, st>>>(kin, vin, kout, vout, cnt, which, cap, 8 * p, totals + 256 * p,
+                                                                (p & 1) ? lb_b : lb_a, (p & 1) ? lb_a : lb_b, tickets + p, iota);
+        kin = kout; vin = vout;
+        if (kout == kb) { kout = ka; vout = va; } else { kout = kb; vout = vb; }
+    }
+    *k_out = const_cast<uint32_t*>(kin);
+    *v_out = vin;
+}
+
+// sweep: the area of the single-sweep sort inside the scratch (second look-back table + digit totals + tickets), or
+// null to force the three-kernel passes.
+static void bs_sort(const uint32_t* keys_first, uint32_t* ka, uint32_t* va, uint32_t* kb, uint32_t* vb, uint32_t* cnt,
+                    int which, uint32_t cap, int npass, uint32_t* hist, uint32_t* totals, int iota_first, cudaStream_t st,
+                    uint32_t** k_out, uint32_t** v_out, uint32_t* sweep = nullptr) {
+    const uint32_t nchunks_cap = chunks_of(cap);
     const int items = sort_items();
+    if (sweep && sort_sweep() && npass <= BS_SWEEP_MAX_PASSES && cap < (1u << 30)) {
+        // hist is the first look-back table (256 words per chunk, as many as the histogram of the other variant)
+        uint32_t* lb_b = sweep;
+        uint32_t* small = sweep + 256 * (size_t)nchunks_cap;
+        if (items == 16) bs_sweep_passes<16>(keys_first, ka, va, kb, vb, cnt, which, cap, npass, hist, lb_b, small, iota_first, st, k_out, v_out);
+        else bs_sweep_passes<8>(keys_first, ka, va, kb, vb, cnt, which, cap, npass, hist, lb_b, small, iota_first, st, k_out, v_out);
+        return;
+    }
+    const uint32_t* kin = keys_first;
+    uint32_t* vin = va;
+    uint32_t *kout = kb, *vout = vb;
     for (int p = 0; p < npass; ++p) {
         const int iota = (p == 0 && iota_first) ? 1 : 0;
         if (items == 16) bs_pass<16>(kin, vin, kout, vout, cnt, which, cap, 8 * p, hist, totals, nchunks_cap, iota, st);
@@ -1218,10 +1478,6 @@ int rgs_cuda_colour_slab(const RgsCamera* cam, const RgsSegment* segs, int64_t n
     return (int)cudaGetLastError();
 }
 
-// The counter table of the segmented counting holds (warps x tiles) words; warps per SM x tiles x 4 bytes never
-// exceeds the shared memory of an SM, which bounds the table for any image size.
-#define SC_TABLE_WORDS (RGS_SMS * 227 * 256)
-
 // 1: group by tile with the segmented counting (RGS_TILE_GROUPING=count), 0: with the radix sort (default).
 // Measured at 62.9 M Gaussians, 1600x1036 (85 M instances per view): 17 ms per view against 3.6 ms for pair
 // emission + 2 radix passes + range detection. One warp per piece walks its splats strictly in order, so only
@@ -1239,7 +1495,14 @@ static int sc_enabled() {
 // words of uint32 scratch for capacities (cap_vis, cap_inst)
 int64_t rgs_cuda_bin_scratch_words(int64_t cap_vis, int64_t cap_inst) {
     const int64_t cap = cap_vis > cap_inst ? cap_vis : cap_inst;
-    return 256 * (int64_t)chunks_of(cap) + 256 + (cap_vis + EM_SEG - 1) / EM_SEG + 16 + SC_TABLE_WORDS + SC_MAX_TILES;
+    return scratch_base_words(cap_vis, cap_inst) + 256 * (int64_t)chunks_of(cap) + BS_SWEEP_SMALL_WORDS;
+}
+
+// 1 selects the single-sweep radix sort, 0 the three-kernel passes; returns the setting that was in force.
+int rgs_cuda_sort_sweep(int on) {
+    const int old = sort_sweep();
+    g_sort_sweep = on ? 1 : 0;
+    return old;
 }
 
 // Depth-order the visible slots, emit instances in that order, group them by tile.
@@ -1258,10 +1521,11 @@ int rgs_cuda_bin_instances(const RgsCamera* cam, const RgsSplat* splats, const u
     uint32_t* hist = scratch;
     uint32_t* totals = scratch + 256 * (size_t)chunks_of(cap);
     uint32_t* seg_sums = totals + 256;
+    uint32_t* sweep = scratch + scratch_base_words(cap_vis, cap_inst);
     // 1. depth sort of the slots (values start as 0..n-1 == the slots themselves)
     uint32_t *dk, *order;
     bs_sort(slot_depth, vis_ka, vis_va, vis_kb, vis_vb, cnt, RGS_CNT_VIS, (uint32_t)cap_vis, 4, hist, totals, 1, st, &dk,
-            &order);
+            &order, sweep);
     // 2. emission in depth order
     const uint32_t nseg_cap = (uint32_t)((cap_vis + EM_SEG - 1) / EM_SEG);
     const unsigned egrid = nseg_cap < (unsigned)(RGS_SMS * 8) ? (nseg_cap ? nseg_cap : 1u) : (unsigned)(RGS_SMS * 8);
@@ -1303,7 +1567,7 @@ int rgs_cuda_bin_instances(const RgsCamera* cam, const RgsSplat* splats, const u
     const int npass = tile_bits <= 8 ? 1 : (tile_bits + 7) / 8;
     uint32_t *tk, *tv;
     bs_sort(inst_keys, inst_keys, inst_vals, inst_keys_tmp, inst_vals_tmp, cnt, RGS_CNT_INST, (uint32_t)cap_inst, npass, hist,
-            totals, 0, st, &tk, &tv);
+            totals, 0, st, &tk, &tv, sweep);
     const bool in_tmp = (tv != inst_vals);
     if (!in_tmp) {  // nothing to copy back: find the ranges without reading every key
         rgs_bs_tile_ranges_search_kernel<<<(unsigned)((num_tiles + 127) / 128), 128, 0, st>>>(
@@ -1323,7 +1587,7 @@ int rgs_cuda_bin_instances(const RgsCamera* cam, const RgsSplat* splats, const u
 //   slab 1: tile_done (one byte per tile, written by the blend of slab 0) -> summed-area table -> filtered counts,
 //           emission + tile sort of the far slab into the region starting at region_off; count -> counters[RGS_CNT_INST2];
 //           ranges hold absolute indices into inst_vals.
-// sat: (tiles_x + 1) * (tiles_y + 1) words. Only tile grids of at most 65536 tiles and tight_rect < 2.
+// sat: (tiles_x + 1) * (tiles_y + 1) words. Only tile grids of at most 2^24 tiles and tight_rect < 2.
 int rgs_cuda_bin_slab(const RgsCamera* cam, const uint32_t* slot_depth, const uint32_t* slot_rect, uint32_t* slot_cnt,
                       int64_t cap_vis, uint32_t* vis_ka, uint32_t* vis_va, uint32_t* vis_kb, uint32_t* vis_vb,
                       uint32_t* inst_keys, uint32_t* inst_vals, uint32_t* inst_keys_tmp, uint32_t* inst_vals_tmp,
@@ -1331,17 +1595,19 @@ int rgs_cuda_bin_slab(const RgsCamera* cam, const uint32_t* slot_depth, const ui
                       uint32_t* scratch, int64_t scratch_cap_inst, int64_t slab, int64_t frac256, const uint8_t* tile_done,
                       uint32_t* sat, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
-    if (num_tiles > 65536 || cam->tight_rect >= 2 || slab < 0 || slab > 1) return 15;
+    if (num_tiles > (1 << 24) || cam->tight_rect >= 2 || slab < 0 || slab > 1) return 15;
     if (region_off + region_cap > 0xfffffe00ll || frac256 < 0 || frac256 > 256) return 10;
     uint32_t* cnt = reinterpret_cast<uint32_t*>(counters);
     const int64_t cap = cap_vis > scratch_cap_inst ? cap_vis : scratch_cap_inst;
     uint32_t* hist = scratch;
     uint32_t* totals = scratch + 256 * (size_t)chunks_of(cap);
     uint32_t* seg_sums = totals + 256;
+    uint32_t* sweep = scratch + scratch_base_words(cap_vis, scratch_cap_inst);
     uint32_t* order = vis_va;  // where four ping-pong passes leave the sorted values
     if (slab == 0) {
         uint32_t *dk, *ord;
-        bs_sort(slot_depth, vis_ka, vis_va, vis_kb, vis_vb, cnt, RGS_CNT_VIS, (uint32_t)cap_vis, 4, hist, totals, 1, st, &dk, &ord);
+        bs_sort(slot_depth, vis_ka, vis_va, vis_kb, vis_vb, cnt, RGS_CNT_VIS, (uint32_t)cap_vis, 4, hist, totals, 1, st, &dk, &ord,
+                sweep);
         if (ord != order) return 16;
     }
     const int which = slab == 0 ? RGS_CNT_INST : RGS_CNT_INST2;
@@ -1364,10 +1630,10 @@ int rgs_cuda_bin_slab(const RgsCamera* cam, const uint32_t* slot_depth, const ui
                                                 (int)slab, seg_sums, rk, rv, (uint32_t)region_cap, tile_done);
     int tile_bits = 0;
     while ((1ll << tile_bits) < num_tiles) ++tile_bits;
-    const int npass = tile_bits <= 8 ? 1 : 2;
+    const int npass = tile_bits <= 8 ? 1 : (tile_bits + 7) / 8;
     uint32_t *tk, *tv;
     bs_sort(rk, rk, rv, inst_keys_tmp + region_off, inst_vals_tmp + region_off, cnt, which, (uint32_t)region_cap, npass, hist,
-            totals, 0, st, &tk, &tv);
+            totals, 0, st, &tk, &tv, sweep);
     if (tv != rv) {  // a single pass leaves the result in the second buffer
         RGS_CUDA_CHECK(cudaMemcpyAsync(rv, tv, (size_t)region_cap * 4, cudaMemcpyDeviceToDevice, st));
     }

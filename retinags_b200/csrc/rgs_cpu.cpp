@@ -495,7 +495,7 @@ int rgs_cpu_bin_slab(const RgsCamera* cam, const uint32_t* slot_depth, const uin
                      uint32_t* inst_vals, uint32_t*, uint32_t*, int64_t region_off, int64_t region_cap, int32_t* counters,
                      int64_t num_tiles, int32_t* ranges, uint32_t*, int64_t, int64_t slab, int64_t frac256,
                      const uint8_t* tile_done, uint32_t*, void*) {
-    if (num_tiles > 65536 || cam->tight_rect >= 2 || slab < 0 || slab > 1) return 15;
+    if (num_tiles > (1 << 24) || cam->tight_rect >= 2 || slab < 0 || slab > 1) return 15;
     if (slab == 1 && !tile_done) return 15;
     const int which = slab == 0 ? RGS_CNT_INST : RGS_CNT_INST2;
     std::memset(ranges, 0, num_tiles * 8);

@@ -156,8 +156,30 @@ def stream_ptr(device: torch.device):
 
 # kernels launched by one call of an entry point (the radix sort's count depends on the tile count)
 _KERNELS = {"project_slots": 1, "project_slots2": 2, "project_slots2_geom": 2, "colour_slab": 1, "tile_maps_or": 1, "tile_map_push": 1, "project_emit": 1, "blend_fwd": 1, "blend_bwd": 1, "geom_bwd": 1, "scatter_radii": 1, "adam": 1, "adam_rows": 2,
-            "composite_fwd": 1, "composite_bwd": 1, "ssim_fwd": 1, "ssim_bwd": 1, "densify_classify": 2, "bin_slab": 14, "blend_fwd_slab": 1, "blend_bwd_slab": 1}
+            "composite_fwd": 1, "composite_bwd": 1, "ssim_fwd": 1, "ssim_bwd": 1, "densify_classify": 2, "blend_fwd_slab": 1, "blend_bwd_slab": 1}
 _LAUNCHES = [0]
+_SORT_SWEEP = [os.environ.get("RGS_SORT", "") != "3k"]
+
+
+def _sort_launches(passes: int) -> int:
+    """Kernels of one radix sort of the binning: digit counts + one scatter per pass, or three kernels per pass."""
+    return 1 + passes if _SORT_SWEEP[0] else 3 * passes
+
+
+def cuda_switch(name: str, on: bool) -> bool:
+    """Flip a run-time switch of the CUDA library and return the setting that was in force.
+
+    ``loss_cluster``: the fused composite + SSIM forward runs as 2 x 2 thread-block clusters that share the rims of
+    their windows through distributed shared memory (off, the default: every block composites its whole window).
+    ``sort_sweep``: the radix sort of the binning counts the digits of all passes up front and scatters with a
+    decoupled look-back (off: histogram, scan and scatter launches per pass).
+    """
+    fn = getattr(lib("cuda"), f"rgs_cuda_{name}")
+    fn.argtypes = [ctypes.c_int]
+    fn.restype = ctypes.c_int
+    if name == "sort_sweep":
+        _SORT_SWEEP[0] = bool(on)
+    return bool(fn(1 if on else 0))
 
 
 def launch_count() -> int:
@@ -173,8 +195,14 @@ def _count_launches(name: str, args) -> int:
     if name == "bin_instances":
         tiles = max(int(args[17]), 1)
         if tiles <= 14336 and os.environ.get("RGS_TILE_GROUPING", "") == "count":
-            return 3 * 4 + 2 + 4  # depth sort, instance count + scan, segmented counting (count, 2 scans, emit)
-        return 3 * 4 + 3 + 3 * max(1, (max(tiles - 1, 0).bit_length() + 7) // 8) + 1
+            return _sort_launches(4) + 2 + 4  # depth sort, instance count + scan, segmented counting (count, 2 scans, emit)
+        return _sort_launches(4) + 3 + _sort_launches(max(1, (max(tiles - 1, 0).bit_length() + 7) // 8)) + 1
+    if name == "bin_slab":
+        tiles, slab, filtered = max(int(args[16]), 1), int(args[20]), args[22] is not None
+        n = _sort_launches(4) if slab == 0 else 0  # depth order of the visible splats, shared by both slabs
+        n += 2 if filtered else 0  # summed-area table of the open tiles + filtered instance counts
+        n += 3  # instance counts per segment, their scan, emission
+        return n + _sort_launches(max(1, (max(tiles - 1, 0).bit_length() + 7) // 8)) + 1  # tile sort + tile ranges
     return _KERNELS.get(name, 1)
 
 

@@ -25,6 +25,7 @@ from . import native
 from .native import CNT_INST, CNT_INST2, CNT_OVERFLOW, CNT_STATUS, CNT_VIS, CNT_WORDS, RgsCamera, RgsSegment
 
 TILE = 16
+MAX_SLAB_TILES = 1 << 24  # tile keys of the two-slab path are sorted in up to three 8-bit passes
 INF = float("inf")
 
 
@@ -296,7 +297,7 @@ class RenderTask:
                 # the candidate list reuses a ping-pong buffer of the depth sort (free until then)
                 structs = (RgsSegment * len(segments))(*[s.struct(False) for s in segments])
                 tiles = cam.tiles_x * cam.tiles_y
-                self._slab_active = self.slabs and cam.tight_rect < 2 and 8 <= tiles <= 65536
+                self._slab_active = self.slabs and cam.tight_rect < 2 and 8 <= tiles <= MAX_SLAB_TILES
                 self._seg_structs = (structs, len(segments), segments)
                 with self._phase("fwd.project"):
                     # with two slabs the SH colours are evaluated later, only for splats that get tile instances
@@ -430,9 +431,9 @@ class RenderTask:
         bs = bin_scratch(self.device)
         bs.ensure(self.cap_vis, self.cap_inst)
         tiles = cam.tiles_x * cam.tiles_y
-        self._slab_active = self.binning == "depth_first" and cam.tight_rect < 2 and 8 <= tiles <= 65536
+        self._slab_active = self.binning == "depth_first" and cam.tight_rect < 2 and 8 <= tiles <= MAX_SLAB_TILES
         if not self._slab_active:
-            raise RuntimeError("forward_near needs the two-slab path (depth-first binning, 8..65536 tiles, tight_rect < 2)")
+            raise RuntimeError("forward_near needs the two-slab path (depth-first binning, 8..2^24 tiles, tight_rect < 2)")
         if self._own_order is None or self._own_order.numel() < self.cap_vis:
             self._own_order = torch.empty(self.cap_vis, dtype=torch.int32, device=self.device)
             self._own_rect = torch.empty(self.cap_vis, dtype=torch.int64, device=self.device)
@@ -457,7 +458,7 @@ class RenderTask:
     @staticmethod
     def can_split(cam: RgsCamera) -> bool:
         tiles = cam.tiles_x * cam.tiles_y
-        return cam.tight_rect < 2 and 8 <= tiles <= 65536
+        return cam.tight_rect < 2 and 8 <= tiles <= MAX_SLAB_TILES
 
     def _note_slab_counts(self, n_a: int, n_b: int):
         """Remember the largest instance counts of both slabs and make the buffers hold 1.3x of each. The needs only grow

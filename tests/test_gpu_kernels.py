@@ -310,6 +310,18 @@ def test_fused_composite_loss_matches_separate_kernels():
                 s = cl.loss(gt.to(dev), 0.2, rows[0], rows[1]).clone()
                 cl.backward(pp, gg, bg, rows[0], rows[1])
             out[(dev, fused)] = (s.cpu(), [x.cpu() for x in gg], cl.image[:, rows[0]:rows[1]].cpu())
+        # the same fused kernels as 2 x 2 thread-block clusters: the same arithmetic per pixel, hence the same bits
+        was = native.cuda_switch("loss_cluster", True)
+        try:
+            cl = CompositeLoss("cuda", H, W)
+            gg = [torch.zeros(H, W, 4, device="cuda") for _ in range(K)]
+            s = cl.fused_loss_backward([p.cuda() for p in parts], gg, gt.cuda(), bg, 0.2, rows[0], rows[1]).clone()
+        finally:
+            native.cuda_switch("loss_cluster", was)
+        plain = out[("cuda", True)]
+        torch.testing.assert_close(s.cpu(), plain[0], rtol=1e-12, atol=0)  # double sums, other order of the atomics
+        assert torch.equal(cl.image[:, rows[0]:rows[1]].cpu(), plain[2])
+        assert all(torch.equal(x.cpu(), y) for x, y in zip(gg, plain[1]))
         ref = out[("cuda", False)]
         for key in (("cuda", True), ("cpu", True)):
             got = out[key]
@@ -524,3 +536,55 @@ def test_an_overflowing_step_is_dropped_by_the_optimiser_and_leaves_no_gradients
     torch.cuda.synchronize()
     assert int(sess.engine._skip[native.CNT_OVERFLOW]) == 0
     assert any(not torch.equal(st.params, b) for st, b in zip(sess.stores.values(), before))
+
+
+def test_single_sweep_sort_orders_like_the_three_kernel_sort():
+    """Binning with the look-back scatter against the histogram / scan / scatter passes. Two renders number their slots
+    in the order of the projection's atomics, so the sorted lists are checked for what the blend relies on (tile by
+    tile, depth ascending, equal depths by slot) and the images are compared, not the slot numbers. 400 k splats give
+    the depth sort about a hundred chunks and the tile sort several hundred, more than one per SM."""
+    g, cams = _scene(n=400000)
+    was = native.cuda_switch("sort_sweep", True)
+    try:
+        for cam in cams[:2]:
+            for slabs in (True, False):
+                got = {}
+                for sweep in (True, False):
+                    native.cuda_switch("sort_sweep", sweep)
+                    seg = rasterize.Segment(*(g[k].cuda().contiguous() for k in ("xyz", "sh", "scale", "rot", "opacity")))
+                    task = rasterize.RenderTask("cuda")
+                    task.slabs = slabs
+                    img = task.forward(rasterize.make_camera(cam, 3), [seg], check=True).clone()
+                    got[sweep] = (img, task.n_vis, task.n_inst, task.ranges.clone())
+                    if not slabs:
+                        vals = task.vals[:task.n_inst].long()
+                        depth = rasterize.bin_scratch(torch.device("cuda")).slot_depth.view(torch.int32)[vals]
+                        starts = task.ranges[:, 0][task.ranges[:, 1] > task.ranges[:, 0]].long()
+                        inside = torch.ones(task.n_inst - 1, dtype=torch.bool, device="cuda")
+                        inside[starts[starts > 0] - 1] = False  # pairs that straddle two tiles
+                        assert not ((depth[1:] < depth[:-1]) & inside).any(), "depth order broken inside a tile"
+                        assert not ((depth[1:] == depth[:-1]) & (vals[1:] < vals[:-1]) & inside).any(), "not stable"
+                        assert int((task.ranges[:, 1] - task.ranges[:, 0]).sum()) == task.n_inst
+                assert got[True][1:3] == got[False][1:3]
+                assert torch.equal(got[True][3], got[False][3])
+                assert_mostly_close(got[True][0], got[False][0], atol=1e-5, rtol=1e-4, max_frac=1e-3)
+    finally:
+        native.cuda_switch("sort_sweep", was)
+
+
+def test_two_slab_forward_with_more_than_65536_tiles():
+    """A 4400 x 4000 image has 68 750 tiles: the tile keys of the slabs need a third 8-bit pass (and the single-sweep
+    sort ends in the other buffer); the image equals the single-pass render."""
+    g = synthetic.uniform_gaussians(60000, 6, sh_degree=1, log_scale_mean=-3.2)
+    cam = synthetic.ring_cameras(3, 3.0, 4400, 4000)[1]
+    assert (4400 + 15) // 16 * ((4000 + 15) // 16) > 65536
+    out = {}
+    for slabs in (False, True):
+        seg = rasterize.Segment(*(g[k].cuda().contiguous() for k in ("xyz", "sh", "scale", "rot", "opacity")))
+        task = rasterize.RenderTask("cuda")
+        task.slabs = slabs
+        out[slabs] = task.forward(rasterize.make_camera(cam, 1), [seg], check=True).clone()
+        assert task._slab_active == slabs
+        del task
+    assert float(out[False][..., :3].sum()) > 0
+    assert_mostly_close(out[False], out[True], atol=1e-5, rtol=1e-4, max_frac=1e-2)
