@@ -578,9 +578,11 @@ class Trainer:
         for name, ds, rlt, stride in splits:
             stat = torch.zeros(4, dtype=torch.float64, device=self.device)  # samples, l1, psnr, ssim
             lp_sum, lp_n = 0.0, 0
-            for b0 in range(0, len(ds), max(a.MAX_BATCH_SIZE, 1)):
-                idx = list(range(b0, min(len(ds), b0 + a.MAX_BATCH_SIZE)))
-                cams = [ds[i] for i in idx]
+            step = max(a.MAX_BATCH_SIZE, 1)
+            feed = BatchPrefetcher(ds, [range(b0, min(len(ds), b0 + step)) for b0 in range(0, len(ds), step)],
+                                   depth=getattr(a, "PREFETCH_BATCHES", 2), workers=getattr(a, "PREFETCH_WORKERS", 8))
+            for idx, cams in feed:  # the targets of the next batches are decoded while this one is rendered
+                idx = list(idx)
                 rel = rlt[[(i * stride) % max(len(rlt), 1) for i in idx]]
                 outs = self.engine.render(cams, rel, sh_deg, self.background)
                 for cam, out in zip(cams, outs):
