@@ -49,12 +49,19 @@ def select_border(store: GaussianStore, m: int, lo: torch.Tensor, hi: torch.Tens
                     sig="ppipiifpp")
         cand = masks.nonzero(as_tuple=True)[0]
         if cand.numel():
-            cm = masks[cand]
+            # all destinations at once (three host round trips instead of two per destination): row d of `bits` marks
+            # the candidates lent to d, and a boolean gather of the row-expanded candidates lists them destination by
+            # destination, ascending inside each
+            shifts = torch.arange(M, device=store.device, dtype=torch.int64).unsqueeze(1)
+            bits = ((masks[cand].unsqueeze(0) >> shifts) & 1).bool()
+            bits[m] = False
+            counts = bits.sum(dim=1).tolist()
+            flat = cand.unsqueeze(0).expand(M, -1)[bits]
+            off = 0
             for d in range(M):
-                if d != m:
-                    idx = cand[((cm >> d) & 1).bool()]
-                    if idx.numel():
-                        out[d] = idx.contiguous()
+                if counts[d]:
+                    out[d] = flat[off:off + counts[d]].contiguous()
+                    off += counts[d]
         return out
     ext = 3.0 * torch.exp(v["scale"]).max(dim=1, keepdim=True).values * (1.0 + margin)
     blo, bhi = v["xyz"] - ext, v["xyz"] + ext
