@@ -262,7 +262,7 @@ def run_own(args):
         dist.all_reduce(tr, op=dist.ReduceOp.MAX)
     render = {"ms_per_frame": float(tr) / max(frames, 1), "frames": frames,
               "what": "eval render incl. compositing across sub-models, device-timed, max over ranks"}
-    phases = None
+    phases, host_phases = None, None
     if args.phases:
         sess.engine.timer.enabled = True
         sess.engine.timer.reset()
@@ -278,6 +278,7 @@ def run_own(args):
                            "relation": [[int(x) for x in row] for row in sess.relation.tolist()]}, f)
             for k in [k for k in tot if k.startswith("task.")]:  # the names differ from rank to rank: keep them out
                 del sess.engine.timer.totals[k]                   # of the reduction over ranks
+        host_phases = {k: round(v / args.steps, 3) for k, v in sess.engine.timer.host_totals.items() if not k.startswith("task.")}
         phases = sess.engine.timer.table(args.steps)
         if args.trace:
             sess.engine.timer.export_chrome_trace(f"{args.trace}.rank{rank}.json", rank)
@@ -319,6 +320,7 @@ def run_own(args):
                        if args.pool_views else "consecutive cameras"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "render": render, "city": city,
             "phases_ms_per_step_max_over_ranks": phases,
+            "phases_host_ms_per_step_rank0": host_phases if phases else None,
             "roofline_rank0_of_measured": roofline,
         }
         print(json.dumps(out), flush=True)

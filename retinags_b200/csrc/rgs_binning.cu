@@ -98,43 +98,71 @@ __global__ void __launch_bounds__(256) rgs_project_slots_kernel(
 // the exact projection: behind the near plane, or its screen rectangle (centre +- an upper bound of the
 // 3-sigma radius) misses the image. The radius bound uses ||J W||_2 <= ||J||_F with the clamped Jacobian of
 // rgs_ewa and the largest scale; it is never smaller than the exact radius, so no visible splat is lost.
+__device__ __forceinline__ bool rgs_cull_keep(const RgsCamera& cam, float p0, float p1, float p2, float s0, float s1, float s2) {
+    const float p[3] = {p0, p1, p2};
+    float t[3];
+    rgs_view_point(cam.view, p, t);
+    if (!(t[2] > RGS_NEAR_Z)) return false;
+    // exp is monotonic: the largest activated scale is the activation of the largest raw scale (one exp, same value)
+    float smax = fmaxf(s0, fmaxf(s1, s2));
+    if (cam.raw_params) smax = expf(smax);
+    smax *= cam.scale_modifier;
+    const float tz = t[2], itz = 1.0f / tz;
+    const float limx = 1.3f * cam.tan_fovx, limy = 1.3f * cam.tan_fovy;
+    const float ax = fminf(limx, fabsf(t[0] * itz)), ay = fminf(limy, fabsf(t[1] * itz));
+    const float fx = cam.focal_x * itz, fy = cam.focal_y * itz;
+    const float jf2 = fx * fx * (1.0f + ax * ax) + fy * fy * (1.0f + ay * ay);
+    // +0.3 low-pass, +0.32 because rgs_project floors the eigenvalue discriminant at 0.1 (sqrt(0.1) < 0.32)
+    const float rad = ceilf(3.0f * sqrtf(smax * smax * jf2 + 0.62f)) * 1.0001f + 1.0f;
+    const float* m = cam.proj;
+    const float hx = m[0] * p[0] + m[4] * p[1] + m[8] * p[2] + m[12];
+    const float hy = m[1] * p[0] + m[5] * p[1] + m[9] * p[2] + m[13];
+    const float hw = m[3] * p[0] + m[7] * p[1] + m[11] * p[2] + m[15];
+    const float pw = 1.0f / (hw + 0.0000001f);
+    const float px = rgs_ndc2pix(hx * pw, cam.W), py = rgs_ndc2pix(hy * pw, cam.H);
+    // same rectangle rule as rgs_project, with the enlarged radius; NaNs fall through as "keep"
+    return !(px + rad + RGS_TILE - 1 < 0.0f || px - rad >= (float)(cam.tiles_x * RGS_TILE) ||
+             py + rad + RGS_TILE - 1 < 0.0f || py - rad >= (float)(cam.tiles_y * RGS_TILE));
+}
+
+// Every thread tests four consecutive Gaussians, read as three 128-bit loads per column group (VEC: both arrays
+// start on a 16-byte boundary; otherwise scalar loads), and the block appends its survivors in row order.
+#define CULL_ROWS 1024  // rows per block: 256 threads x 4
+template <bool VEC>
 __global__ void __launch_bounds__(256) rgs_cull_kernel(const __grid_constant__ RgsCamera cam, const float* __restrict__ xyz,
                                                        const float* __restrict__ scale, int64_t count, int64_t id_base,
                                                        uint32_t* __restrict__ cand, uint32_t cap_cand,
                                                        uint32_t* __restrict__ counters) {
-    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    bool keep = false;
-    if (i < count) {
-        const float p[3] = {xyz[3 * i], xyz[3 * i + 1], xyz[3 * i + 2]};
-        float t[3];
-        rgs_view_point(cam.view, p, t);
-        if (t[2] > RGS_NEAR_Z) {
-            float s0 = scale[3 * i], s1 = scale[3 * i + 1], s2 = scale[3 * i + 2];
-            if (cam.raw_params) { s0 = expf(s0); s1 = expf(s1); s2 = expf(s2); }
-            const float smax = fmaxf(s0, fmaxf(s1, s2)) * cam.scale_modifier;
-            const float tz = t[2], itz = 1.0f / tz;
-            const float limx = 1.3f * cam.tan_fovx, limy = 1.3f * cam.tan_fovy;
-            const float ax = fminf(limx, fabsf(t[0] * itz)), ay = fminf(limy, fabsf(t[1] * itz));
-            const float fx = cam.focal_x * itz, fy = cam.focal_y * itz;
-            const float jf2 = fx * fx * (1.0f + ax * ax) + fy * fy * (1.0f + ay * ay);
-            // +0.3 low-pass, +0.32 because rgs_project floors the eigenvalue discriminant at 0.1 (sqrt(0.1) < 0.32)
-            const float rad = ceilf(3.0f * sqrtf(smax * smax * jf2 + 0.62f)) * 1.0001f + 1.0f;
-            const float* m = cam.proj;
-            const float hx = m[0] * p[0] + m[4] * p[1] + m[8] * p[2] + m[12];
-            const float hy = m[1] * p[0] + m[5] * p[1] + m[9] * p[2] + m[13];
-            const float hw = m[3] * p[0] + m[7] * p[1] + m[11] * p[2] + m[15];
-            const float pw = 1.0f / (hw + 0.0000001f);
-            const float px = rgs_ndc2pix(hx * pw, cam.W), py = rgs_ndc2pix(hy * pw, cam.H);
-            // same rectangle rule as rgs_project, with the enlarged radius; NaNs fall through as "keep"
-            keep = !(px + rad + RGS_TILE - 1 < 0.0f || px - rad >= (float)(cam.tiles_x * RGS_TILE) ||
-                     py + rad + RGS_TILE - 1 < 0.0f || py - rad >= (float)(cam.tiles_y * RGS_TILE));
+    const int64_t i0 = (int64_t)blockIdx.x * CULL_ROWS + 4 * (int64_t)threadIdx.x;
+    uint32_t keep = 0;  // bit k: row i0 + k survives
+    if (i0 + 3 < count && VEC) {
+        const float4* xp = reinterpret_cast<const float4*>(xyz + 3 * i0);
+        const float4* sp = reinterpret_cast<const float4*>(scale + 3 * i0);
+        const float4 a = xp[0], b = xp[1], c = xp[2], d = sp[0], e = sp[1], f = sp[2];
+        keep = (rgs_cull_keep(cam, a.x, a.y, a.z, d.x, d.y, d.z) ? 1u : 0u) |
+               (rgs_cull_keep(cam, a.w, b.x, b.y, d.w, e.x, e.y) ? 2u : 0u) |
+               (rgs_cull_keep(cam, b.z, b.w, c.x, e.z, e.w, f.x) ? 4u : 0u) |
+               (rgs_cull_keep(cam, c.y, c.z, c.w, f.y, f.z, f.w) ? 8u : 0u);
+    } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t i = i0 + k;
+            if (i < count && rgs_cull_keep(cam, xyz[3 * i], xyz[3 * i + 1], xyz[3 * i + 2], scale[3 * i], scale[3 * i + 1],
+                                           scale[3 * i + 2]))
+                keep |= 1u << k;
         }
     }
     __shared__ uint32_t warp_n[8];
     __shared__ uint32_t base_s;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const uint32_t mask = __ballot_sync(0xffffffffu, keep);
-    if (lane == 0) warp_n[wid] = __popc(mask);
+    const uint32_t mine = __popc(keep);
+    uint32_t incl = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += t;
+    }
+    if (lane == 31) warp_n[wid] = incl;
     __syncthreads();
     if (threadIdx.x == 0) {
         uint32_t tot = 0;
@@ -147,7 +175,12 @@ __global__ void __launch_bounds__(256) rgs_cull_kernel(const __grid_constant__ R
         base_s = b;
     }
     __syncthreads();
-    if (keep && base_s != 0xffffffffu) cand[base_s + warp_n[wid] + __popc(mask & ((1u << lane) - 1u))] = (uint32_t)(id_base + i);
+    if (keep && base_s != 0xffffffffu) {
+        uint32_t o = base_s + warp_n[wid] + incl - mine;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (keep & (1u << k)) cand[o++] = (uint32_t)(id_base + i0 + k);
+    }
 }
 
 struct RgsSegs4 { RgsSegment s[4]; int n; };
@@ -1428,9 +1461,13 @@ static int project_slots2_impl(const RgsCamera* cam, const RgsSegment* segs, int
     for (int k = 0; k < (int)nseg; ++k) {
         s4.s[k] = segs[k];
         if (segs[k].count > 0) {
-            const unsigned blocks = (unsigned)((segs[k].count + 255) / 256);
-            rgs_cull_kernel<<<blocks, 256, 0, st>>>(*cam, segs[k].xyz, segs[k].scale, segs[k].count, base, cand,
-                                                    (uint32_t)cap_cand, cnt);
+            const unsigned blocks = (unsigned)((segs[k].count + CULL_ROWS - 1) / CULL_ROWS);
+            if ((((uintptr_t)segs[k].xyz | (uintptr_t)segs[k].scale) & 15u) == 0)
+                rgs_cull_kernel<true><<<blocks, 256, 0, st>>>(*cam, segs[k].xyz, segs[k].scale, segs[k].count, base, cand,
+                                                              (uint32_t)cap_cand, cnt);
+            else
+                rgs_cull_kernel<false><<<blocks, 256, 0, st>>>(*cam, segs[k].xyz, segs[k].scale, segs[k].count, base, cand,
+                                                               (uint32_t)cap_cand, cnt);
         }
         base += segs[k].count;
     }

@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(256) rgs_composite_bwd_kernel(const __grid_con
         float s = bg0 * g0 + bg1 * g1 + bg2 * g2;
         for (int k = K - 1; k >= 0; --k) {
             const float4 q = reinterpret_cast<const float4*>(parts.p[k])[pid];
-            const float tp = tpre[k];
+            const float tp = rgs_composite_grad_weight(tpre[k]);
             reinterpret_cast<float4*>(grads.p[k])[pid] = make_float4(tp * g0, tp * g1, tp * g2, tp * s);
             s = q.x * g0 + q.y * g1 + q.z * g2 + q.w * s;
         }
@@ -402,7 +402,7 @@ __global__ void __launch_bounds__(256) rgs_ssim_composite_bwd_kernel(
         float s = bg0 * g0 + bg1 * g1 + bg2 * g2;
         for (int k = K - 1; k >= 0; --k) {
             const float4 v = reinterpret_cast<const float4*>(parts.p[k])[pid];
-            const float tp = tpre[k];
+            const float tp = rgs_composite_grad_weight(tpre[k]);
             reinterpret_cast<float4*>(grads.p[k])[pid] = make_float4(tp * g0, tp * g1, tp * g2, tp * s);
             s = v.x * g0 + v.y * g1 + v.z * g2 + v.w * s;
         }

@@ -51,6 +51,12 @@ RGS_HD void rgs_composite_pixel_fwd(const float* const* partials, int K, int64_t
 
 // Backward: dL/dC_k = T_<k g ;  dL/dT_k = T_<k * (S_k . g) with S_k the colour behind partial k
 // (S_{K-1} = bg, S_{k-1} = C_k + T_k S_k).
+// A partial behind less than RGS_COMPOSITE_T_STOP of transmittance receives exactly zero instead of a gradient scaled
+// by that factor: the rule by which a single render stops at a saturated pixel, applied across sub-models. The
+// blend backward skips pixels (and whole tiles) whose gradient is zero, and their Gaussians get no Adam moments.
+#define RGS_COMPOSITE_T_STOP 0.0001f
+RGS_HD float rgs_composite_grad_weight(float t_before) { return t_before < RGS_COMPOSITE_T_STOP ? 0.f : t_before; }
+
 RGS_HD void rgs_composite_pixel_bwd(const float* const* partials, float* const* grads, int K, int64_t pid,
                                     const float* bg, const float* g) {
     float tpre[RGS_MAX_PARTIALS];
@@ -60,7 +66,7 @@ RGS_HD void rgs_composite_pixel_bwd(const float* const* partials, float* const* 
     for (int k = K - 1; k >= 0; --k) {
         const float* q = partials[k] + 4 * pid;
         float* o = grads[k] + 4 * pid;
-        float tp = tpre[k];
+        float tp = rgs_composite_grad_weight(tpre[k]);
         o[0] = tp * g[0]; o[1] = tp * g[1]; o[2] = tp * g[2];
         o[3] = tp * s;
         s = q[0] * g[0] + q[1] * g[1] + q[2] * g[2] + q[3] * s;

@@ -313,7 +313,12 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
     const int len_a = range.y - range.x, len_b = range_b.y - range_b.x;
     const uint32_t n_vis = counters[RGS_CNT_VIS];
     const int64_t pid = (int64_t)py * cam.W + px;
-    const int last = inside ? n_contrib[pid] : 0;
+    // a pixel whose incoming gradient is exactly zero (outside the loss rows, or behind saturated nearer sub-models)
+    // adds nothing to any splat: it replays nothing, and a tile of such pixels ends here
+    const float4 g_pix = inside ? grad_out[pid] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float gd_pix = (DEPTH && inside) ? grad_depth[pid] : 0.f;
+    const bool g_live = g_pix.x != 0.f || g_pix.y != 0.f || g_pix.z != 0.f || g_pix.w != 0.f || gd_pix != 0.f;
+    const int last = (inside && g_live) ? n_contrib[pid] : 0;
     // only the first max(last) instances of the tile contributed to any pixel
     __shared__ int sm_max_last;
     if (tid == 0) { sm_max_last = 0; rgs_mbar_init(&sm.bar[0], 1); rgs_mbar_init(&sm.bar[1], 1); rgs_fence_mbar_init(); }
@@ -334,11 +339,10 @@ __global__ void __launch_bounds__(256) rgs_blend_bwd_kernel(
     RgsPixelBwd st;
     {
         float4 o = inside ? out[pid] : make_float4(0.f, 0.f, 0.f, 1.f);
-        float4 g = inside ? grad_out[pid] : make_float4(0.f, 0.f, 0.f, 0.f);
-        float gC[3] = {g.x, g.y, g.z};
-        rgs_pixel_bwd_init(st, o.w, gC, g.w);
+        float gC[3] = {g_pix.x, g_pix.y, g_pix.z};
+        rgs_pixel_bwd_init(st, o.w, gC, g_pix.w);
     }
-    RgsPixelBwdDepth dep = {0.f, 0.f, (DEPTH && inside) ? grad_depth[pid] : 0.f};
+    RgsPixelBwdDepth dep = {0.f, 0.f, gd_pix};
     auto issue = [&](int b) {
         const int stage = b & 1;
         const int cnt = min(BLEND_BATCH, total - b * BLEND_BATCH);

@@ -317,6 +317,8 @@ class StepEngine:
         self._prepare_transport(plans)
         self._prefetch_gt(plans, cams)
         if self.borrow is not None:
+            if hasattr(self.borrow, "timer"):
+                self.borrow.timer = self.timer
             with T("border_exchange"):
                 self.borrow.refresh(self.stores, need_grads=True)
         with T("render_forward"):

@@ -18,6 +18,7 @@ Reference: ``result_aggregator.py:55-147`` (selection by boolean masks every ite
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 
 import torch
@@ -60,6 +61,10 @@ class PeerBorderExchange:
         self._segs: dict[int, Segment] = {}
         self._need_grads = False
         self._fresh = True
+        self.timer = None  # a PhaseTimer of the engine: the parts of refresh / return_grads get their own entries
+
+    def _phase(self, name: str):
+        return self.timer.phase(name) if self.timer is not None and self.timer.enabled else contextlib.nullcontext()
 
     def invalidate(self):
         self._counts = None
@@ -131,11 +136,19 @@ class PeerBorderExchange:
         if self.M == 1:
             return
         if self._counts is None or self._step % self.refresh_interval == 0:
-            self.transport.barrier()  # nobody still reads the old layout
-            self._select(stores)
+            with self._phase("border.select"):
+                self.transport.barrier()  # nobody still reads the old layout
+                self._select(stores)
         self._step += 1
         self._need_grads = need_grads
         c = self._counts
+        with self._phase("border.pack"):
+            self._pack(stores, c)
+        self._fresh = False
+        with self._phase("border.barrier"):
+            self.transport.barrier()  # rows have landed before anyone renders them
+
+    def _pack(self, stores, c):
         for s in self.local:
             st = stores[s]
             p = st.views()
@@ -149,8 +162,6 @@ class PeerBorderExchange:
                 # between two selections only rows with Adam moments can have moved: the others are skipped
                 native.call("border_pack", self.device, src, self._index[(s, d)], n, dst, self._in_off[(s, d)],
                             None if self._fresh else st.active, sig="ppipipp")
-        self._fresh = False
-        self.transport.barrier()  # rows have landed before anyone renders them
 
     def segment(self, d: int, with_grads: bool) -> Segment | None:
         if self.M == 1:
@@ -161,6 +172,14 @@ class PeerBorderExchange:
         if self.M == 1 or not self._need_grads:
             return
         c = self._counts
+        with self._phase("border.push"):
+            self._push_grads(c)
+        with self._phase("border.barrier"):
+            self.transport.barrier()  # gradient rows have landed at their owners
+        with self._phase("border.add"):
+            self._add_grads(stores, c)
+
+    def _push_grads(self, c):
         for d in self.local:
             seg = self._segs.get(d)
             if seg is None:
@@ -176,7 +195,8 @@ class PeerBorderExchange:
                 flags = base + self._ring_flags_off(s) + self._out_off[(s, d)]
                 native.call("border_grad_push", self.device, g, seg.stat_grad, seg.touched, self._in_off[(s, d)], n, rows, flags,
                             sig="pppiippp")
-        self.transport.barrier()  # gradient rows have landed at their owners
+
+    def _add_grads(self, stores, c):
         for s in self.local:
             st = stores[s]
             gv = st.views("grads")

@@ -25,6 +25,7 @@ class PhaseTimer:
         self.nvtx = nvtx and self.cuda
         self._pending: list[tuple[str, object, object]] = []
         self.totals: dict[str, float] = defaultdict(float)
+        self.host_totals: dict[str, float] = defaultdict(float)  # wall clock of the host inside the phase (ms)
         self.counts: dict[str, int] = defaultdict(int)
         self.trace = False              # keep every phase instance for export_chrome_trace
         self.events: list[tuple[str, float, float]] = []  # (name, start ms, duration ms) relative to the first phase
@@ -37,6 +38,7 @@ class PhaseTimer:
             return
         if self.nvtx:
             torch.cuda.nvtx.range_push(name)
+        h0 = time.perf_counter()
         if self.cuda:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(torch.cuda.current_stream(self.device))
@@ -49,6 +51,7 @@ class PhaseTimer:
         try:
             yield
         finally:
+            self.host_totals[name] += (time.perf_counter() - h0) * 1e3
             if self.cuda:
                 b.record(torch.cuda.current_stream(self.device))
                 self._pending.append((name, a, b))
@@ -77,6 +80,7 @@ class PhaseTimer:
     def reset(self):
         self._pending.clear()
         self.totals.clear()
+        self.host_totals.clear()
         self.counts.clear()
         self.events.clear()
         self._origin = None

@@ -72,12 +72,19 @@ def test_raster_small_capacity_regrows():
     assert_mostly_close(out.cpu(), ref, atol=3e-5, rtol=1e-4)
 
 
-def test_raster_backward_matches_cpu():
+@pytest.mark.parametrize("holes", [False, True])
+def test_raster_backward_matches_cpu(holes):
+    """``holes``: the incoming gradient is exactly zero on most of the image (pixels, 8x4 strips and whole tiles), which
+    the CUDA blend backward skips and the CPU loops walk through."""
     deg = 3
     g, cams = _scene(n=20000, w=160, h=112)
     cam = cams[1]
     gen = torch.Generator().manual_seed(0)
     grad = torch.randn(cam.height, cam.width, 4, generator=gen)
+    if holes:
+        grad[:64] = 0.0
+        grad[64:, ::3] = 0.0
+        grad[80:100, 48:120] = 0.0
     res = {}
     for dev in ("cpu", "cuda"):
         out, task, seg, c = native_render(g, cam, deg, device=dev)

@@ -84,3 +84,37 @@ def test_fused_training_path_equals_separate_steps():
         for x, y in zip(ga, gb):
             assert torch.equal(x, y)
         assert float(sum(x.abs().sum() for x in gb)) > 0
+
+
+def test_partials_behind_saturated_ones_get_exactly_zero_gradient():
+    """Where the partials in front leave less than 1e-4 of transmittance, the partials behind receive zero instead of
+    a gradient scaled by that factor (both backward paths); everywhere else the gradients are those of autograd."""
+    H, W, K = 40, 48, 3
+    parts = _partials(K, H, W, seed=3)
+    parts[0][:20, :, 3] = 5e-5      # the front partial saturates the upper half
+    parts[1][30:, 10:20, 3] = 0.0   # the second one a patch of the lower half (exactly opaque)
+    gt = torch.rand(3, H, W, generator=torch.Generator().manual_seed(7))
+    bg = (0.2, 0.1, 0.3)
+    leaves = [p.clone().requires_grad_(True) for p in parts]
+    img, _ = oracle.composite([p[..., :3].permute(2, 0, 1) for p in leaves], [p[..., 3] for p in leaves], bg)
+    oracle.training_loss(img, gt, 0.2).backward()
+    for fused in (False, True):
+        cl = CompositeLoss("cpu", H, W)
+        grads = [torch.full_like(p, 7.0) for p in parts]
+        if fused:
+            cl.fused_loss_backward(parts, grads, gt, bg, 0.2)
+        else:
+            cl.composite(parts, bg)
+            cl.loss(gt, 0.2)
+            cl.backward(parts, grads, bg)
+        assert float(grads[1][:20].abs().max()) == 0.0 and float(grads[2][:20].abs().max()) == 0.0
+        assert float(grads[2][30:, 10:20].abs().max()) == 0.0
+        assert float(grads[0].abs().max()) > 0 and float(grads[1][20:].abs().max()) > 0
+        keep = torch.ones(H, W, dtype=torch.bool)
+        keep[:20] = False
+        for k in range(K):
+            ref = leaves[k].grad
+            m = keep.clone() if k > 0 else torch.ones(H, W, dtype=torch.bool)
+            if k == 2:
+                m[30:, 10:20] = False
+            assert (grads[k] - ref)[m].abs().max().item() < 2e-3 * ref.abs().max().item() + 1e-9
