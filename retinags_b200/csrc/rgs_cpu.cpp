@@ -216,7 +216,7 @@ int rgs_cpu_blend_fwd(const RgsCamera* cam, const int32_t* ranges, const uint32_
                     rgs_blend_fwd_step(*cam, ray, (float)x, (float)y, splats[vals[i]], st);
                 int64_t pid = (int64_t)y * W + x;
                 out[4 * pid + 0] = st.C[0]; out[4 * pid + 1] = st.C[1]; out[4 * pid + 2] = st.C[2];
-                out[4 * pid + 3] = st.T;
+                out[4 * pid + 3] = rgs_mark_finished(st.T, st.done);
                 if (depth) depth[pid] = st.D;
                 n_contrib[pid] = st.last;
             }
@@ -406,13 +406,13 @@ int rgs_cpu_composite_fwd(const float* const* partials, int64_t K, const float* 
 
 // g_image: (3,H,W) dL/dimage; grads: K pointers to (H,W,4) buffers receiving dL/dC_k, dL/dT_k.
 int rgs_cpu_composite_bwd(const float* const* partials, float* const* grads, int64_t K, const float* bg,
-                          int64_t H, int64_t W, int64_t row0, int64_t row1, const float* g_image, void*) {
+                          int64_t H, int64_t W, int64_t row0, int64_t row1, const float* g_image, int64_t marked, void*) {
 #pragma omp parallel for
     for (int64_t y = row0; y < row1; ++y)
         for (int64_t x = 0; x < W; ++x) {
             int64_t pid = y * W + x;
             float g[3] = {g_image[pid], g_image[H * W + pid], g_image[2 * H * W + pid]};
-            rgs_composite_pixel_bwd(partials, grads, (int)K, pid, bg, g);
+            rgs_composite_pixel_bwd(partials, grads, (int)K, pid, bg, g, marked ? 1 : 0);
         }
     return 0;
 }
@@ -570,7 +570,8 @@ int rgs_cpu_blend_fwd_slab(const RgsCamera* cam, const int32_t* ranges_a, const 
                     st.contributor = (mode == 2 ? len_a : 0) + (i - r0);
                     rgs_blend_fwd_step(*cam, ray, (float)x, (float)y, splats[vals[i]], st);
                 }
-                out[4 * pid] = st.C[0]; out[4 * pid + 1] = st.C[1]; out[4 * pid + 2] = st.C[2]; out[4 * pid + 3] = st.T;
+                out[4 * pid] = st.C[0]; out[4 * pid + 1] = st.C[1]; out[4 * pid + 2] = st.C[2];
+                out[4 * pid + 3] = mode == 1 ? st.T : rgs_mark_finished(st.T, st.done);  // the near slab's value is resumed
                 if (depth) depth[pid] = st.D;
                 n_contrib[pid] = mode == 1 ? (int32_t)((uint32_t)st.last | ((uint32_t)(st.done ? 1 : 0) << 31)) : st.last;
                 all_done = all_done && st.done;
@@ -653,11 +654,11 @@ int rgs_cpu_composite_ssim_fwd(const float* const* partials, int64_t K, const fl
 int rgs_cpu_ssim_composite_bwd(const float* const* partials, float* const* grads, int64_t K, const float* bg,
                                const float* img, const float* gt, const float* dmaps, int64_t H, int64_t W, int64_t row0,
                                int64_t row1, int64_t vrow0, int64_t vrow1, double w_l1, double w_ssim, float* g_image,
-                               void*) {
+                               int64_t marked, void*) {
     if (row1 <= row0) return 0;
     int rc = rgs_cpu_ssim_bwd(img, gt, dmaps, H, W, row0, row1, vrow0, vrow1, w_l1, w_ssim, g_image, nullptr);
     if (rc) return rc;
-    return rgs_cpu_composite_bwd(partials, grads, K, bg, H, W, row0, row1, g_image, nullptr);
+    return rgs_cpu_composite_bwd(partials, grads, K, bg, H, W, row0, row1, g_image, marked, nullptr);
 }
 
 // CPU twin of rgs_border_mask_kernel

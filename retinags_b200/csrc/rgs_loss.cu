@@ -39,14 +39,20 @@ __global__ void __launch_bounds__(256) rgs_composite_bwd_kernel(const __grid_con
                                                                 const __grid_constant__ RgsGradPtrs grads, int K,
                                                                 float bg0, float bg1, float bg2, int64_t H, int64_t W,
                                                                 int64_t row0, int64_t row1,
-                                                                const float* __restrict__ g_image) {
+                                                                const float* __restrict__ g_image, int marked) {
     const int64_t n = (row1 - row0) * W;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t pid = row0 * W + i;
         const float g0 = g_image[pid], g1 = g_image[H * W + pid], g2 = g_image[2 * H * W + pid];
         float tpre[RGS_MAX_PARTIALS];
         float t = 1.f;
-        for (int k = 0; k < K; ++k) { tpre[k] = t; t *= parts.p[k][4 * pid + 3]; }
+        int blocked = 0;
+        for (int k = 0; k < K; ++k) {
+            const float tk = parts.p[k][4 * pid + 3];
+            tpre[k] = blocked ? 0.f : t;
+            blocked |= marked & rgs_is_finished(tk);
+            t *= tk;
+        }
         float s = bg0 * g0 + bg1 * g1 + bg2 * g2;
         for (int k = K - 1; k >= 0; --k) {
             const float4 q = reinterpret_cast<const float4*>(parts.p[k])[pid];
@@ -334,7 +340,7 @@ __global__ void __launch_bounds__(256) rgs_composite_ssim_fwd_kernel(
 __global__ void __launch_bounds__(256) rgs_ssim_composite_bwd_kernel(
     const __grid_constant__ RgsPartialPtrs parts, const __grid_constant__ RgsGradPtrs grads, int K, float bg0, float bg1,
     float bg2, const float* __restrict__ img, const float* __restrict__ gt, const float* __restrict__ dmaps, int H, int W,
-    int row0, int row1, int vrow0, int vrow1, float w_l1, float w_ssim, float* __restrict__ g_image) {
+    int row0, int row1, int vrow0, int vrow1, float w_l1, float w_ssim, float* __restrict__ g_image, int marked) {
     __shared__ float in[3][SH_][SH_ + 1];
     __shared__ float hb[3][SH_][ST];
     float gw[11];
@@ -398,7 +404,13 @@ __global__ void __launch_bounds__(256) rgs_ssim_composite_bwd_kernel(
         const float g0 = g[i][0], g1 = g[i][1], g2 = g[i][2];
         float tpre[RGS_MAX_PARTIALS];
         float t = 1.f;
-        for (int k = 0; k < K; ++k) { tpre[k] = t; t *= parts.p[k][4 * pid + 3]; }
+        int blocked = 0;
+        for (int k = 0; k < K; ++k) {
+            const float tk = parts.p[k][4 * pid + 3];
+            tpre[k] = blocked ? 0.f : t;
+            blocked |= marked & rgs_is_finished(tk);
+            t *= tk;
+        }
         float s = bg0 * g0 + bg1 * g1 + bg2 * g2;
         for (int k = K - 1; k >= 0; --k) {
             const float4 v = reinterpret_cast<const float4*>(parts.p[k])[pid];
@@ -426,7 +438,7 @@ int rgs_cuda_composite_fwd(const float* const* partials, int64_t K, const float*
 }
 
 int rgs_cuda_composite_bwd(const float* const* partials, float* const* grads, int64_t K, const float* bg, int64_t H,
-                           int64_t W, int64_t row0, int64_t row1, const float* g_image, void* stream) {
+                           int64_t W, int64_t row0, int64_t row1, const float* g_image, int64_t marked, void* stream) {
     if (K < 0 || K > RGS_MAX_PARTIALS) return 12;
     if (row1 <= row0) return 0;
     RgsPartialPtrs pp;
@@ -436,7 +448,7 @@ int rgs_cuda_composite_bwd(const float* const* partials, float* const* grads, in
     const int64_t want = (n + 255) / 256;
     const unsigned blocks = (unsigned)(want > RGS_SMS * 32 ? RGS_SMS * 32 : want);
     rgs_composite_bwd_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(pp, gp, (int)K, bg[0], bg[1], bg[2], H, W, row0,
-                                                                      row1, g_image);
+                                                                      row1, g_image, marked ? 1 : 0);
     return (int)cudaGetLastError();
 }
 
@@ -534,7 +546,7 @@ int rgs_cuda_composite_ssim_fwd(const float* const* partials, int64_t K, const f
 int rgs_cuda_ssim_composite_bwd(const float* const* partials, float* const* grads, int64_t K, const float* bg,
                                 const float* img, const float* gt, const float* dmaps, int64_t H, int64_t W, int64_t row0,
                                 int64_t row1, int64_t vrow0, int64_t vrow1, double w_l1, double w_ssim, float* g_image,
-                                void* stream) {
+                                int64_t marked, void* stream) {
     if (K < 0 || K > RGS_MAX_PARTIALS) return 12;
     if (row1 <= row0) return 0;
     RgsPartialPtrs pp;
@@ -543,7 +555,7 @@ int rgs_cuda_ssim_composite_bwd(const float* const* partials, float* const* grad
     dim3 grid((unsigned)((W + ST - 1) / ST), (unsigned)((row1 - row0 + ST - 1) / ST), 1);
     rgs_ssim_composite_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(pp, gp, (int)K, bg[0], bg[1], bg[2], img, gt, dmaps,
                                                                          (int)H, (int)W, (int)row0, (int)row1, (int)vrow0,
-                                                                         (int)vrow1, (float)w_l1, (float)w_ssim, g_image);
+                                                                         (int)vrow1, (float)w_l1, (float)w_ssim, g_image, marked ? 1 : 0);
     return (int)cudaGetLastError();
 }
 

@@ -51,17 +51,26 @@ RGS_HD void rgs_composite_pixel_fwd(const float* const* partials, int K, int64_t
 
 // Backward: dL/dC_k = T_<k g ;  dL/dT_k = T_<k * (S_k . g) with S_k the colour behind partial k
 // (S_{K-1} = bg, S_{k-1} = C_k + T_k S_k).
-// A partial behind less than RGS_COMPOSITE_T_STOP of transmittance receives exactly zero instead of a gradient scaled
-// by that factor: the rule by which a single render stops at a saturated pixel, applied across sub-models. The
-// blend backward skips pixels (and whole tiles) whose gradient is zero, and their Gaussians get no Adam moments.
+// A partial behind less than RGS_COMPOSITE_T_STOP of transmittance, or (with `marked`) behind a pixel that a nearer
+// partial finished, receives exactly zero instead of a gradient scaled by that small factor: the rule by which a single
+// render stops at a saturated pixel, applied across sub-models. The blend backward skips pixels (and whole tiles)
+// whose gradient is zero, and their Gaussians get no Adam moments.
 #define RGS_COMPOSITE_T_STOP 0.0001f
 RGS_HD float rgs_composite_grad_weight(float t_before) { return t_before < RGS_COMPOSITE_T_STOP ? 0.f : t_before; }
 
+// marked: the partials come from the blend kernels, whose transmittance carries the finished mark of
+// rgs_mark_finished; partials behind a finished pixel then receive zero as well.
 RGS_HD void rgs_composite_pixel_bwd(const float* const* partials, float* const* grads, int K, int64_t pid,
-                                    const float* bg, const float* g) {
+                                    const float* bg, const float* g, int marked = 0) {
     float tpre[RGS_MAX_PARTIALS];
     float t = 1.f;
-    for (int k = 0; k < K; ++k) { tpre[k] = t; t *= partials[k][4 * pid + 3]; }
+    int blocked = 0;
+    for (int k = 0; k < K; ++k) {
+        const float tk = partials[k][4 * pid + 3];
+        tpre[k] = blocked ? 0.f : t;
+        blocked |= marked & rgs_is_finished(tk);
+        t *= tk;
+    }
     float s = bg[0] * g[0] + bg[1] * g[1] + bg[2] * g[2];
     for (int k = K - 1; k >= 0; --k) {
         const float* q = partials[k] + 4 * pid;

@@ -13,6 +13,7 @@
 #pragma once
 #include <math.h>
 #include <stdint.h>
+#include <string.h>
 
 #if defined(__CUDACC__)
 #define RGS_HD __host__ __device__ __forceinline__
@@ -31,6 +32,30 @@
 #define RGS_ALPHA_MIN (1.0f / 255.0f)
 #define RGS_ALPHA_MAX 0.99f
 #define RGS_T_STOP 0.0001f
+
+// The transmittance a finished render hands to the compositor carries "this pixel stopped at the RGS_T_STOP rule" in
+// its lowest mantissa bit (a change of at most one unit in the last place). The compositing backward may use it to
+// give nothing to the partials behind such a pixel, as a single render gives nothing to the splats behind it.
+RGS_HD float rgs_mark_finished(float T, int finished) {
+#ifdef __CUDA_ARCH__
+    return __uint_as_float((__float_as_uint(T) & ~1u) | (finished ? 1u : 0u));
+#else
+    uint32_t u;
+    memcpy(&u, &T, 4);
+    u = (u & ~1u) | (finished ? 1u : 0u);
+    memcpy(&T, &u, 4);
+    return T;
+#endif
+}
+RGS_HD int rgs_is_finished(float T) {
+#ifdef __CUDA_ARCH__
+    return (int)(__float_as_uint(T) & 1u);
+#else
+    uint32_t u;
+    memcpy(&u, &T, 4);
+    return (int)(u & 1u);
+#endif
+}
 #define RGS_SH_COEFFS 16
 
 // Camera + sub-model description handed by value to every kernel of one render task.

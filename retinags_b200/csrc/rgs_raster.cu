@@ -264,7 +264,9 @@ __global__ void __launch_bounds__(256) rgs_blend_fwd_kernel(
     }
     if (inside) {
         const int64_t pid = (int64_t)py * cam.W + px;
-        const float4 val = make_float4(st.C[0], st.C[1], st.C[2], st.T);
+        // what the near slab leaves is resumed by the far slab; a final value carries the finished mark for the compositor
+        const float4 val = make_float4(st.C[0], st.C[1], st.C[2],
+                                       slab.mode == RGS_SLAB_NEAR ? st.T : rgs_mark_finished(st.T, st.done));
         out[pid] = val;
         if (depth) depth[pid] = st.D;
         // between the two launches the finished flag travels in the top bit

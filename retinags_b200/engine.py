@@ -101,6 +101,9 @@ class StepEngine:
         if cl is None or (cl.H, cl.W) != (H, W):
             cl = CompositeLoss(self.device, H, W)
             self._closs[view] = cl
+        # with occlusion culling the backward also stops behind pixels that nearer sub-models finished (the partials of
+        # the render tasks carry the mark); without it every partial gets its exact, if tiny, gradient as in the reference
+        cl.marked = bool(self.occlusion) and len(self.model2rank) > 1
         return cl
 
     def _prefetch_gt(self, plans, cams):

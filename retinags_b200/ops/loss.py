@@ -39,6 +39,10 @@ class CompositeLoss:
         self.g_image = torch.zeros(3, H, W, dtype=torch.float32, device=dev)
         self.sums = torch.zeros(3, dtype=torch.float64, device=dev)
         self.status = torch.zeros(native.CNT_WORDS, dtype=torch.int32, device=dev)
+        # the partials come from the blend kernels, whose transmittance carries a "pixel finished" mark in its lowest
+        # mantissa bit: the backward then gives exactly zero to the partials behind a finished pixel (set by the engine;
+        # off for partials of any other origin, whose low bits mean nothing)
+        self.marked = False
         self.tensor_cores = USE_TENSOR_CORES and self.device.type == "cuda" and self._tc_supported()
 
     def _tc_supported(self) -> bool:
@@ -113,7 +117,7 @@ class CompositeLoss:
         npx = 3.0 * H * W
         native.call("ssim_composite_bwd", self.device, pp, gp, len(partials), bgc, self.image, gt, self.dmaps, H, W, row0, row1,
                     c0, c1, weight * (1.0 - lambda_dssim) / npx, weight * lambda_dssim / npx, self.g_image,
-                    sig="ppippppiiiiiiffpp")
+                    1 if self.marked else 0, sig="ppippppiiiiiiffpip")
         return self.sums
 
     def stats(self, gt: torch.Tensor, row0: int = 0, row1: int | None = None):
@@ -138,4 +142,4 @@ class CompositeLoss:
         pp = native.pointer_array(partials)
         gp = native.pointer_array(grads)
         native.call("composite_bwd", self.device, pp, gp, len(partials), self._bg(bg), self.H, self.W, row0, row1,
-                    self.g_image)
+                    self.g_image, 1 if self.marked else 0)

@@ -38,7 +38,7 @@ SIGNATURES = {
     "adam": "ppppiipfffiipppp",
     "adam_rows": "ppppiipfffiipppppp",
     "composite_fwd": "pipiiiippp",
-    "composite_bwd": "ppipiiiipp",
+    "composite_bwd": "ppipiiiipip",
     "ssim_fwd": "ppiiiiiippp",
     "ssim_bwd": "pppiiiiiiffpp",
     "densify_classify": "piipppppppp",

@@ -118,3 +118,29 @@ def test_partials_behind_saturated_ones_get_exactly_zero_gradient():
             if k == 2:
                 m[30:, 10:20] = False
             assert (grads[k] - ref)[m].abs().max().item() < 2e-3 * ref.abs().max().item() + 1e-9
+
+
+def test_finished_mark_in_the_transmittance_blocks_the_partials_behind():
+    """``CompositeLoss.marked``: the lowest mantissa bit of a partial's transmittance says "this pixel is finished"
+    (``rgs_mark_finished`` in the blend kernels); the partials behind it get zero. Unmarked use ignores the bit."""
+    H, W, K = 24, 32, 3
+    parts = _partials(K, H, W, seed=4)
+    for p in parts:  # clear the low bits of random data, then mark the upper half of the middle partial as finished
+        bits = p[..., 3].contiguous().view(torch.int32) & ~1
+        p[..., 3] = bits.view(torch.float32)
+    bits = parts[1][..., 3].contiguous().view(torch.int32)
+    bits[:12] |= 1
+    parts[1][..., 3] = bits.view(torch.float32)
+    gt = torch.rand(3, H, W, generator=torch.Generator().manual_seed(8))
+    bg = (0.3, 0.3, 0.1)
+    out = {}
+    for marked in (False, True):
+        cl = CompositeLoss("cpu", H, W)
+        cl.marked = marked
+        grads = [torch.zeros_like(p) for p in parts]
+        cl.fused_loss_backward(parts, grads, gt, bg, 0.2)
+        out[marked] = grads
+    assert float(out[True][2][:12].abs().max()) == 0.0 and float(out[False][2][:12].abs().max()) > 0.0
+    for k in range(K):
+        rows = slice(12, None) if k == 2 else slice(None)
+        assert torch.equal(out[True][k][rows], out[False][k][rows])
