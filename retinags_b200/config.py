@@ -150,7 +150,8 @@ def add_trainer_flags(parser: ArgumentParser):
                    help="steps between recomputations of the border-Gaussian sets; the rows are re-sent every step, the "
                         "sets are made 5 %% larger when they are kept (1 = recomputed every step, as the reference)")
     p.add_argument("--PREFETCH_BATCHES", type=int, default=2,
-                   help="batches whose images are decoded ahead of the training step (0 = decode inside the step)")
+                   help="batches decoded ahead of the step per decoding thread (the reference's prefetch_factor); 0 decodes "
+                        "in the training thread")
     p.add_argument("--PREFETCH_WORKERS", type=int, default=8, help="threads decoding images for the coming batches")
     p.add_argument("--OCCLUSION_CULLING", type=int, default=-1, choices=[-1, 0, 1],
                    help="skip tiles that nearer sub-models have finished (maps exchanged once per step); -1: the default "

@@ -395,6 +395,13 @@ class Trainer:
     # ------------------------------------------------------------------------------------------------
     # training
     # ------------------------------------------------------------------------------------------------
+    def _prefetch_depth(self) -> int:
+        """Batches decoded ahead of the step: ``--PREFETCH_BATCHES`` per decoding thread, the reference's
+        ``prefetch_factor`` x ``num_workers`` (2 x 8 batches in flight), so that every thread has an image to work on
+        even when a batch is a single view. 0 decodes in the training thread."""
+        a = self.args
+        return max(0, int(getattr(a, "PREFETCH_BATCHES", 2))) * max(1, int(getattr(a, "PREFETCH_WORKERS", 8)))
+
     def _epoch_groups(self, epoch: int):
         seed = 0 if self.args.DATALOADER_FIX_SEED else epoch
         g = torch.Generator()
@@ -433,7 +440,7 @@ class Trainer:
             sh_deg = min(self.sh_degree, self.iteration // 1000)
             for st in self.stores.values():
                 st.active_sh_degree = sh_deg
-            feed = BatchPrefetcher(self.train_dataset, groups, depth=getattr(a, "PREFETCH_BATCHES", 2),
+            feed = BatchPrefetcher(self.train_dataset, groups, depth=self._prefetch_depth(),
                                    workers=getattr(a, "PREFETCH_WORKERS", 8))
             for ids, cams in feed:  # the images of the next batches are decoded while this step runs
                 if self.watchdog is not None:
@@ -580,7 +587,7 @@ class Trainer:
             lp_sum, lp_n = 0.0, 0
             step = max(a.MAX_BATCH_SIZE, 1)
             feed = BatchPrefetcher(ds, [range(b0, min(len(ds), b0 + step)) for b0 in range(0, len(ds), step)],
-                                   depth=getattr(a, "PREFETCH_BATCHES", 2), workers=getattr(a, "PREFETCH_WORKERS", 8))
+                                   depth=self._prefetch_depth(), workers=getattr(a, "PREFETCH_WORKERS", 8))
             for idx, cams in feed:  # the targets of the next batches are decoded while this one is rendered
                 idx = list(idx)
                 rel = rlt[[(i * stride) % max(len(rlt), 1) for i in idx]]
