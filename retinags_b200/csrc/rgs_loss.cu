@@ -35,18 +35,37 @@ __global__ void __launch_bounds__(256) rgs_composite_fwd_kernel(const __grid_con
     }
 }
 
-__global__ void __launch_bounds__(256) rgs_composite_bwd_kernel(const __grid_constant__ RgsPartialPtrs parts,
-                                                                const __grid_constant__ RgsGradPtrs grads, int K,
-                                                                float bg0, float bg1, float bg2, int64_t H, int64_t W,
-                                                                int64_t row0, int64_t row1,
-                                                                const float* __restrict__ g_image, int marked) {
-    const int64_t n = (row1 - row0) * W;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t pid = row0 * W + i;
-        const float g0 = g_image[pid], g1 = g_image[H * W + pid], g2 = g_image[2 * H * W + pid];
-        float tpre[RGS_MAX_PARTIALS];
-        float t = 1.f;
-        int blocked = 0;
+// d(loss)/d(partial_k) of one pixel for all K partials. KMAX = 8: fully unrolled, the prefix transmittances and the
+// partials stay in registers (the usual case: at most 8 sub-models overlap a pixel's row band); KMAX = RGS_MAX_PARTIALS:
+// plain loops over a local array for anything larger.
+template <int KMAX>
+__device__ __forceinline__ void composite_pixel_grads(const RgsPartialPtrs& parts, const RgsGradPtrs& grads, int K, size_t pid,
+                                                      float g0, float g1, float g2, float bg0, float bg1, float bg2,
+                                                      int marked) {
+    float tpre[KMAX];
+    float t = 1.f;
+    int blocked = 0;
+    if (KMAX <= 8) {
+        float4 q[KMAX];
+#pragma unroll
+        for (int k = 0; k < KMAX; ++k) {
+            if (k < K) {
+                q[k] = reinterpret_cast<const float4*>(parts.p[k])[pid];
+                tpre[k] = blocked ? 0.f : t;
+                blocked |= marked & rgs_is_finished(q[k].w);
+                t *= q[k].w;
+            }
+        }
+        float s = bg0 * g0 + bg1 * g1 + bg2 * g2;
+#pragma unroll
+        for (int k = KMAX - 1; k >= 0; --k) {
+            if (k < K) {
+                const float tp = rgs_composite_grad_weight(tpre[k]);
+                reinterpret_cast<float4*>(grads.p[k])[pid] = make_float4(tp * g0, tp * g1, tp * g2, tp * s);
+                s = q[k].x * g0 + q[k].y * g1 + q[k].z * g2 + q[k].w * s;
+            }
+        }
+    } else {
         for (int k = 0; k < K; ++k) {
             const float tk = parts.p[k][4 * pid + 3];
             tpre[k] = blocked ? 0.f : t;
@@ -60,6 +79,20 @@ __global__ void __launch_bounds__(256) rgs_composite_bwd_kernel(const __grid_con
             reinterpret_cast<float4*>(grads.p[k])[pid] = make_float4(tp * g0, tp * g1, tp * g2, tp * s);
             s = q.x * g0 + q.y * g1 + q.z * g2 + q.w * s;
         }
+    }
+}
+
+template <int KMAX>
+__global__ void __launch_bounds__(256) rgs_composite_bwd_kernel(const __grid_constant__ RgsPartialPtrs parts,
+                                                                const __grid_constant__ RgsGradPtrs grads, int K,
+                                                                float bg0, float bg1, float bg2, int64_t H, int64_t W,
+                                                                int64_t row0, int64_t row1,
+                                                                const float* __restrict__ g_image, int marked) {
+    const int64_t n = (row1 - row0) * W;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t pid = row0 * W + i;
+        const float g0 = g_image[pid], g1 = g_image[H * W + pid], g2 = g_image[2 * H * W + pid];
+        composite_pixel_grads<KMAX>(parts, grads, K, (size_t)pid, g0, g1, g2, bg0, bg1, bg2, marked);
     }
 }
 
@@ -337,6 +370,7 @@ __global__ void __launch_bounds__(256) rgs_composite_ssim_fwd_kernel(
     }
 }
 
+template <int KMAX>
 __global__ void __launch_bounds__(256) rgs_ssim_composite_bwd_kernel(
     const __grid_constant__ RgsPartialPtrs parts, const __grid_constant__ RgsGradPtrs grads, int K, float bg0, float bg1,
     float bg2, const float* __restrict__ img, const float* __restrict__ gt, const float* __restrict__ dmaps, int H, int W,
@@ -401,23 +435,7 @@ __global__ void __launch_bounds__(256) rgs_ssim_composite_bwd_kernel(
         const int y = y0 + r, x = x0 + q;
         if (!(y < row1 && y < H && x < W)) continue;
         const size_t pid = (size_t)y * W + x;
-        const float g0 = g[i][0], g1 = g[i][1], g2 = g[i][2];
-        float tpre[RGS_MAX_PARTIALS];
-        float t = 1.f;
-        int blocked = 0;
-        for (int k = 0; k < K; ++k) {
-            const float tk = parts.p[k][4 * pid + 3];
-            tpre[k] = blocked ? 0.f : t;
-            blocked |= marked & rgs_is_finished(tk);
-            t *= tk;
-        }
-        float s = bg0 * g0 + bg1 * g1 + bg2 * g2;
-        for (int k = K - 1; k >= 0; --k) {
-            const float4 v = reinterpret_cast<const float4*>(parts.p[k])[pid];
-            const float tp = rgs_composite_grad_weight(tpre[k]);
-            reinterpret_cast<float4*>(grads.p[k])[pid] = make_float4(tp * g0, tp * g1, tp * g2, tp * s);
-            s = v.x * g0 + v.y * g1 + v.z * g2 + v.w * s;
-        }
+        composite_pixel_grads<KMAX>(parts, grads, K, pid, g[i][0], g[i][1], g[i][2], bg0, bg1, bg2, marked);
     }
 }
 
@@ -447,8 +465,12 @@ int rgs_cuda_composite_bwd(const float* const* partials, float* const* grads, in
     const int64_t n = (row1 - row0) * W;
     const int64_t want = (n + 255) / 256;
     const unsigned blocks = (unsigned)(want > RGS_SMS * 32 ? RGS_SMS * 32 : want);
-    rgs_composite_bwd_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(pp, gp, (int)K, bg[0], bg[1], bg[2], H, W, row0,
-                                                                      row1, g_image, marked ? 1 : 0);
+    if (K <= 8)
+        rgs_composite_bwd_kernel<8><<<blocks, 256, 0, (cudaStream_t)stream>>>(pp, gp, (int)K, bg[0], bg[1], bg[2], H, W, row0,
+                                                                             row1, g_image, marked ? 1 : 0);
+    else
+        rgs_composite_bwd_kernel<RGS_MAX_PARTIALS><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+            pp, gp, (int)K, bg[0], bg[1], bg[2], H, W, row0, row1, g_image, marked ? 1 : 0);
     return (int)cudaGetLastError();
 }
 
@@ -553,9 +575,14 @@ int rgs_cuda_ssim_composite_bwd(const float* const* partials, float* const* grad
     RgsGradPtrs gp;
     for (int k = 0; k < K; ++k) { pp.p[k] = partials[k]; gp.p[k] = grads[k]; }
     dim3 grid((unsigned)((W + ST - 1) / ST), (unsigned)((row1 - row0 + ST - 1) / ST), 1);
-    rgs_ssim_composite_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(pp, gp, (int)K, bg[0], bg[1], bg[2], img, gt, dmaps,
-                                                                         (int)H, (int)W, (int)row0, (int)row1, (int)vrow0,
-                                                                         (int)vrow1, (float)w_l1, (float)w_ssim, g_image, marked ? 1 : 0);
+    if (K <= 8)
+        rgs_ssim_composite_bwd_kernel<8><<<grid, 256, 0, (cudaStream_t)stream>>>(
+            pp, gp, (int)K, bg[0], bg[1], bg[2], img, gt, dmaps, (int)H, (int)W, (int)row0, (int)row1, (int)vrow0, (int)vrow1,
+            (float)w_l1, (float)w_ssim, g_image, marked ? 1 : 0);
+    else
+        rgs_ssim_composite_bwd_kernel<RGS_MAX_PARTIALS><<<grid, 256, 0, (cudaStream_t)stream>>>(
+            pp, gp, (int)K, bg[0], bg[1], bg[2], img, gt, dmaps, (int)H, (int)W, (int)row0, (int)row1, (int)vrow0, (int)vrow1,
+            (float)w_l1, (float)w_ssim, g_image, marked ? 1 : 0);
     return (int)cudaGetLastError();
 }
 
