@@ -41,7 +41,7 @@ def parse_args():
                     help="2^depth sub-models (default: one per GPU); more sub-models than GPUs are spread round-robin")
     ap.add_argument("--slabs", type=int, default=None, metavar="N",
                     help="two-slab forward with the nearest N/256 of the splats in the first slab (same as RGS_SLABS=1 "
-                         "RGS_SLAB_FRACTION=N; default 32); 0 renders in one pass")
+                         "RGS_SLAB_FRACTION=N; default 6); 0 renders in one pass")
     ap.add_argument("--occlusion", type=int, default=None, choices=[0, 1],
                     help="occlusion culling between sub-models (finished-tile maps exchanged once per step)")
     ap.add_argument("--mode", default="train", choices=["train", "eval", "train-psnr", "trainer", "push", "city"],
@@ -144,7 +144,7 @@ def run_own(args):
     from retinags_b200.bench_session import BenchSession
 
     if args.slabs is not None:
-        os.environ["RGS_SLABS"], os.environ["RGS_SLAB_FRACTION"] = ("1", str(args.slabs)) if args.slabs > 0 else ("0", "32")
+        os.environ["RGS_SLABS"], os.environ["RGS_SLAB_FRACTION"] = ("1", str(args.slabs)) if args.slabs > 0 else ("0", "6")
     if args.occlusion is not None:
         os.environ["RGS_OCCLUSION"] = str(args.occlusion)
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -207,7 +207,10 @@ class RenderTask:
         # Two-slab forward (CUDA, depth-first binning): bin and blend the nearest splats first, then emit instances of
         # the rest only for tiles that are not saturated yet. Bit-identical output, fewer instances in dense scenes.
         self.slabs = os.environ.get("RGS_SLABS", "1") == "1"
-        self.slab_frac256 = int(os.environ.get("RGS_SLAB_FRACTION", "32"))   # share of the splats in the near slab, /256
+        # share of the depth-ordered splats in the near slab, /256. Small is right: the near slab only has to finish the
+        # tiles that saturate early, and every splat it holds is binned without the finished-tile filter (measured at
+        # 62.9 M Gaussians, one GPU: 12.2 ms per step with 32/256, 10.6 with 6/256, 10.5 with 4/256; 2/256 overflowed)
+        self.slab_frac256 = int(os.environ.get("RGS_SLAB_FRACTION", "6"))
         self._pending_cap = 0             # capacity that poll() asked for; applied by the next forward
         self._need_a = self._need_b = 0   # largest instance counts of the near / far slab seen so far
         self._need_known = False
