@@ -504,6 +504,8 @@ class RenderTask:
             what = []
             if info["status"] & 3:
                 what.append("a bounded wait on a bulk copy ran out")
+            if info["status"] & 4:
+                what.append("a look-back wait of the single-sweep radix sort ran out (RGS_SORT=3k selects the other sort)")
             if info["status"] & 16:
                 what.append("an index read from the binning buffers was out of bounds (clamped)")
             raise RuntimeError(f"rasteriser status {info['status']}: " + "; ".join(what or ["unknown"]))
