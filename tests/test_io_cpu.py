@@ -235,3 +235,33 @@ def test_scannetpp_and_mill19_layouts(tmp_path):
     assert sc.kind == "Mill19" and len(sc.test_cameras) == 2 and len(sc.train_cameras) == 6
     assert sc.test_cameras[1].image_path.endswith(os.path.join("test", "img_004.png"))
     assert sc.train_cameras[0].image_path.endswith(os.path.join("train", "img_001.png"))
+
+
+def test_prefetcher_keeps_the_order_of_the_batches_and_raises_where_a_decode_failed(tmp_path):
+    """``BatchPrefetcher`` (decode threads ahead of the step) against ``GroupedItems`` (the reference's dataset of
+    batches): same cameras in the same order for any depth; an image that cannot be decoded raises at its batch."""
+    from retinags_b200.data.datasets import GroupedItems
+    from retinags_b200.data.prefetch import BatchPrefetcher
+    cams = synthetic.ring_cameras(7, 3.0, 32, 24)
+    for c in cams:
+        c.image = torch.rand(3, 24, 32)
+    readers.write_blender_scene(str(tmp_path), cams[:6], cams[6:], np.zeros((10, 3), np.float32))
+    sc = readers.read_scene(str(tmp_path), eval_split=True)
+    ds = CameraListDataset(sc.train_cameras, resolution=1, cache_bytes=0)  # nothing cached: every fetch decodes
+    groups = [(0, 3), (5,), (2, 1), (4, 0)]
+    want = GroupedItems(ds, groups)
+    for depth in (0, 1, 16):
+        got = list(BatchPrefetcher(ds, groups, depth=depth, workers=3))
+        assert [ids for ids, _ in got] == groups
+        for i, (ids, batch) in enumerate(got):
+            ref_ids, ref_batch = want[i]
+            assert tuple(ref_ids) == ids and [c.image_name for c in batch] == [c.image_name for c in ref_batch]
+            assert all(torch.equal(a.image, b.image) for a, b in zip(batch, ref_batch))
+    os.remove(sc.train_cameras[5].image_path)
+    feed = iter(BatchPrefetcher(ds, groups, depth=4, workers=2))
+    assert next(feed)[0] == (0, 3)
+    try:
+        next(feed)
+        raise AssertionError("the missing image of batch 1 went unnoticed")
+    except (FileNotFoundError, OSError):
+        pass
