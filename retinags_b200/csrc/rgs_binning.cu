@@ -1634,6 +1634,7 @@ int rgs_cuda_bin_slab(const RgsCamera* cam, const uint32_t* slot_depth, const ui
     cudaStream_t st = (cudaStream_t)stream;
     if (num_tiles > (1 << 24) || cam->tight_rect >= 2 || slab < 0 || slab > 1) return 15;
     if (region_off + region_cap > 0xfffffe00ll || frac256 < 0 || frac256 > 256) return 10;
+    if (region_off < 0 || region_cap <= 0 || region_off + region_cap > scratch_cap_inst) return 10;  // outside the buffers
     uint32_t* cnt = reinterpret_cast<uint32_t*>(counters);
     const int64_t cap = cap_vis > scratch_cap_inst ? cap_vis : scratch_cap_inst;
     uint32_t* hist = scratch;

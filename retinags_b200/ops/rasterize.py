@@ -254,7 +254,7 @@ class RenderTask:
             self.depth = torch.empty(H, W, dtype=torch.float32, device=dev)
 
     def _grow_inst(self, cap: int):
-        cap = int(min(max(cap, self.min_inst), 0xFFFFFF00))
+        cap = int(min(max(cap, self.min_inst, 64), 0xFFFFFF00))
         self.cap_inst = cap
         self.vals = torch.empty(cap, dtype=torch.int32, device=self.device)
         if self.binning == "keyed":
@@ -359,7 +359,9 @@ class RenderTask:
         # room (_note_slab_counts keeps the total at 1.3x of their sum or more); before any count is known: 40 : 60.
         share = (self._need_a + 2048.0) / (self._need_a + self._need_b + 4096.0) if self._need_known else 0.4
         want_a = int(self.cap_inst * min(0.95, max(0.05, share)))
-        cap_a = max(1024, min(want_a, self.cap_inst - 1024)) // 4 * 4
+        floor = min(1024, self.cap_inst // 4)  # both regions stay inside the buffer however small it is
+        cap_a = max(4, max(floor, min(want_a, self.cap_inst - floor)) // 4 * 4)
+        assert 0 < cap_a < self.cap_inst
         self._base_b = cap_a
         return cap_a, self.cap_inst - cap_a
 

@@ -2,7 +2,8 @@
 import pytest
 import torch
 
-from helpers import activated, native_render, oracle_render, small_scene
+from helpers import activated, assert_mostly_close, native_render, oracle_render, small_scene
+from retinags_b200.data import synthetic
 from retinags_b200.ops import oracle, rasterize
 
 
@@ -331,3 +332,20 @@ def test_depth_gradient_matches_autograd():
     (D * wD).sum().backward()
     ref = leaves["xyz"].grad
     assert (xyz.grad - ref).abs().max().item() / (ref.abs().max().item() + 1e-12) < 2e-3
+
+
+def test_tiny_instance_capacity_regrows_with_two_slabs():
+    """An instance buffer far smaller than one slab needs (256 entries): both slab regions stay inside it, the render
+    reports the overflow, grows and ends with the image of a comfortably sized task."""
+    g = synthetic.uniform_gaussians(20000, 4, sh_degree=3, log_scale_mean=-3.6)
+    cam = synthetic.ring_cameras(3, 3.0, 320, 208)[0]
+    ref, _, _, _ = native_render(g, cam, 3)
+    for frac in (6, 32, 200):
+        seg = rasterize.Segment(*(g[k].contiguous() for k in ("xyz", "sh", "scale", "rot", "opacity")))
+        task = rasterize.RenderTask("cpu", inst_per_gaussian=0.01, min_inst=256)
+        task.slabs, task.slab_frac256 = True, frac
+        out = task.forward(rasterize.make_camera(cam, 3), [seg], check=True)
+        assert task._slab_active and task.cap_inst > 256
+        cap_a, cap_b = task._slab_regions()
+        assert 0 < cap_a < task.cap_inst and cap_a + cap_b == task.cap_inst
+        assert_mostly_close(out, ref, atol=1e-5, rtol=1e-4)
